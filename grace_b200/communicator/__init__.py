@@ -1,0 +1,9 @@
+"""Communicators.  ``Allreduce``/``Allgather``/``Broadcast``/``AllToAll`` call
+``torch.distributed`` (NCCL or gloo) and have the reference's semantics; they
+are the baseline.  ``FusedExchange`` (``fused.py``) is the sm_100a path."""
+from .allreduce import Allreduce
+from .allgather import Allgather
+from .broadcast import Broadcast
+from .all_to_all import AllToAll
+
+__all__ = ["Allreduce", "Allgather", "Broadcast", "AllToAll"]

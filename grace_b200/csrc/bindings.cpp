@@ -1,0 +1,134 @@
+// Python bindings (pybind11, no torch headers): kernels take raw device
+// pointers that the Python side obtains from tensor.data_ptr(), so this file
+// compiles in a few seconds and the extension has no ABI tie to libtorch.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "exchange.h"
+#include "runtime.h"
+
+namespace py = pybind11;
+using namespace grace;
+
+namespace {
+
+template <class T> T* ptr(uintptr_t p) { return reinterpret_cast<T*>(p); }
+
+void check(cudaError_t err, const char* what) {
+  if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+PeerTable make_peers(int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
+                     const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
+                     unsigned long long slot_off) {
+  if (world < 1 || world > kMaxWorldH || (int)heaps.size() != world || rank < 0 || rank >= world)
+    throw std::invalid_argument("bad rank/world/heap table");
+  PeerTable t{};
+  t.rank = rank; t.world = world; t.seq = seq; t.timeout_ns = timeout_ns;
+  for (int i = 0; i < world; ++i) t.heap[i] = reinterpret_cast<char*>(heaps[i]);
+  t.ready_off = ready_off; t.ack_off = ack_off; t.slot_off = slot_off;
+  return t;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "grace_b200 native kernels and runtime (sm_100a)";
+
+  // ---- symmetric heap ----
+  m.def("heap_alloc", [](size_t bytes) {
+    void* p = nullptr;
+    check(symm_alloc(&p, bytes), "heap_alloc");
+    return reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("heap_free", [](uintptr_t p) { check(symm_free(ptr<void>(p)), "heap_free"); });
+  m.def("heap_export", [](uintptr_t p) {
+    char handle[kIpcHandleBytes];
+    check(symm_export(ptr<void>(p), handle), "heap_export");
+    return py::bytes(handle, kIpcHandleBytes);
+  });
+  m.def("heap_import", [](const std::string& handle) {
+    if (handle.size() != kIpcHandleBytes) throw std::invalid_argument("bad ipc handle size");
+    void* p = nullptr;
+    check(symm_import(handle.data(), &p), "heap_import");
+    return reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("heap_release", [](uintptr_t p) { check(symm_release(ptr<void>(p)), "heap_release"); });
+  m.def("enable_peer_access", [](int peer_device) { check(symm_enable_peer(peer_device), "enable_peer_access"); });
+  m.def("memset_async", [](uintptr_t p, int value, size_t bytes, uintptr_t stream) {
+    check(cudaMemsetAsync(ptr<void>(p), value, bytes, reinterpret_cast<cudaStream_t>(stream)), "memset_async");
+  });
+
+  // ---- sizes / occupancy ----
+  m.def("sparse_slot_bytes", &sparse_slot_bytes);
+  m.def("sparse_max_grid", &sparse_max_grid);
+  m.def("quant_slot_bytes", &quant_slot_bytes);
+  m.def("quant_max_grid", &quant_max_grid);
+  m.def("sgd_table_chunk", &sgd_table_chunk);
+  m.attr("SEGMENT_BYTES") = sizeof(Segment);
+  m.attr("SPARSE_STATE_BYTES") = sizeof(SparseState);
+  m.attr("QUANT_STATS_BYTES") = sizeof(QuantSegStats);
+  m.attr("SGD_TENSOR_BYTES") = sizeof(SgdTensor);
+  m.attr("MAX_WORLD") = (int)kMaxWorldH;
+
+  // ---- fused sparse exchange ----
+  m.def("sparse_exchange",
+        [](uintptr_t g, uintptr_t acc, uintptr_t u, uintptr_t out, uintptr_t segs, int nseg, long long total, int mode,
+           int levels, float beta, float gamma, float momentum, float threshold, float scale, uintptr_t hist,
+           uintptr_t state, uintptr_t barrier, uintptr_t status, unsigned cap, int phases, int rank, int world,
+           unsigned long long seq, unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps,
+           unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
+           uintptr_t stream) {
+          SparseArgs a{};
+          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.u = ptr<float>(u); a.out = ptr<float>(out);
+          a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.mode = mode; a.levels = levels;
+          a.beta = beta; a.gamma = gamma; a.momentum = momentum; a.threshold = threshold; a.scale = scale;
+          a.hist = ptr<unsigned>(hist); a.state = ptr<SparseState>(state); a.barrier = ptr<unsigned>(barrier);
+          a.status = ptr<unsigned>(status); a.cap = cap; a.phases = phases;
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
+          if (total % 128 != 0 || cap % 16 != 0) throw std::invalid_argument("total %128 / cap %16");
+          check(launch_sparse_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "sparse_exchange");
+        });
+
+  // ---- fused quantised exchange ----
+  m.def("quant_exchange",
+        [](uintptr_t g, uintptr_t acc, uintptr_t mom, uintptr_t out, uintptr_t segs, int nseg, long long total,
+           int codec, int quantum, int deterministic, int first_step, float beta, float gamma, float mom_beta, float lr,
+           float scale, unsigned long long seed, unsigned step, uintptr_t stats, uintptr_t barrier, uintptr_t status,
+           int phases, int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
+           const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
+           unsigned long long slot_off, int grid, uintptr_t stream) {
+          QuantArgs a{};
+          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
+          a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.codec = codec; a.quantum = quantum;
+          a.deterministic = deterministic; a.first_step = first_step; a.beta = beta; a.gamma = gamma;
+          a.mom_beta = mom_beta; a.lr = lr; a.scale = scale; a.seed = seed; a.step = step;
+          a.stats = ptr<QuantSegStats>(stats); a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status);
+          a.phases = phases;
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
+          if (total % 128 != 0) throw std::invalid_argument("total must be a multiple of 128");
+          check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
+        });
+
+  // ---- fused SGD ----
+  m.def("fused_sgd", [](uintptr_t p, uintptr_t g, uintptr_t buf, long long numel, float lr, float momentum,
+                        float dampening, float weight_decay, int nesterov, int first_step, int zero_grad,
+                        float grad_scale, uintptr_t stream) {
+    check(launch_fused_sgd(ptr<float>(p), ptr<float>(g), ptr<float>(buf), numel, lr, momentum, dampening, weight_decay,
+                           nesterov, first_step, zero_grad, grad_scale, reinterpret_cast<cudaStream_t>(stream)),
+          "fused_sgd");
+  });
+  m.def("multi_sgd", [](uintptr_t table, uintptr_t blocks, int nblocks, float lr, float momentum, float dampening,
+                        float weight_decay, int nesterov, int first_step, int zero_grad, float grad_scale,
+                        uintptr_t stream) {
+    check(launch_multi_sgd(ptr<const SgdTensor>(table), ptr<const int>(blocks), nblocks, lr, momentum, dampening,
+                           weight_decay, nesterov, first_step, zero_grad, grad_scale,
+                           reinterpret_cast<cudaStream_t>(stream)),
+          "multi_sgd");
+  });
+}

@@ -1,0 +1,145 @@
+// Host/device shared argument blocks and launcher declarations for the fused
+// gradient-exchange kernels.  No torch headers here: the .cu files compile in
+// seconds and are linked into the extension by bindings.cpp.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace grace {
+
+constexpr int kMaxWorldH = 16;
+
+// One named gradient inside a flat buffer.  `offset` (in elements) must be a
+// multiple of 128 so that 16-byte vector accesses and 128-element code groups
+// never straddle two tensors.
+struct Segment {
+  long long offset;
+  int numel;
+  int k;  // number of elements to keep (TopK / DGC); unused otherwise
+};
+
+// Where the other ranks are.  heap[r] is rank r's symmetric heap mapped into
+// this process (heap[rank] is the local one).  All offsets are identical on
+// every rank.  `ready`/`ack` are arrays of kMaxWorldH uint64 flags:
+//   ready[p] on rank r = last sequence number whose send slot rank p published,
+//   ack[p]   on rank r = last sequence number rank p finished reading from r.
+// Send slots are double buffered by sequence parity; slot_off already selects
+// the parity of `seq`.
+struct PeerTable {
+  int rank;
+  int world;
+  unsigned long long seq;
+  unsigned long long timeout_ns;
+  char* heap[kMaxWorldH];
+  unsigned long long ready_off;
+  unsigned long long ack_off;
+  unsigned long long slot_off;
+};
+
+enum Phase : int {
+  kPhaseCompress = 1,  // compensate + encode into the local send slot
+  kPhasePublish = 2,   // release the slot to the peers
+  kPhaseExchange = 4,  // wait for peers, pull, decode, aggregate, acknowledge
+  kPhaseAll = 7,
+};
+
+// ---------------------------------------------------------------- sparse ----
+enum SparseMode : int { kSparseTopK = 0, kSparseThreshold = 1 };
+
+struct SparseState {       // per segment, device scratch
+  unsigned prefix;         // selected key prefix after each radix level
+  unsigned need;           // how many elements to take from the pivot bin
+  unsigned tie_taken;      // claimed so far among keys equal to the pivot
+  unsigned max_bits;       // ordered-int encoding of max(acc) (threshold mode)
+};
+
+struct SparseArgs {
+  const float* g;     // gradients, flat
+  float* acc;         // accumulator / residual state (nullable: no memory)
+  float* u;           // DGC momentum state (nullable)
+  float* out;         // dense aggregated output; may alias g (nullable)
+  const Segment* segs;
+  int nseg;
+  long long total;    // padded flat length, multiple of 128
+  int mode;
+  int levels;         // 3 = exact k-th magnitude, 2 = top 24 key bits
+  float beta, gamma, momentum, threshold;
+  float scale;        // factor applied while aggregating (1/W when averaging)
+  unsigned* hist;     // nseg * 4096, zero on entry, left zero on exit
+  SparseState* state; // nseg
+  unsigned* barrier;  // one word, zeroed by the launcher
+  unsigned* status;   // 4 words
+  unsigned cap;       // slot capacity in entries (multiple of 16)
+  int phases;
+  PeerTable peers;
+};
+
+size_t sparse_slot_bytes(unsigned cap);
+size_t sparse_smem_bytes();
+int sparse_max_grid(int device, int sm_limit);
+cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t stream);
+
+// ----------------------------------------------------------------- quant ----
+enum Codec : int {
+  kCodecQSGD = 0,      // int8 codes + fp32 norm per 128 elements
+  kCodecTernGrad = 1,  // 2 bits per element + scale per segment
+  kCodecNatural = 2,   // 8-bit sign/exponent code
+  kCodecU8bit = 3,     // 8-bit table code + scale per segment
+  kCodecSign = 4,      // 1 bit, majority vote (signSGD / signum)
+  kCodecEFSign = 5,    // 1 bit + mean |x| per segment, scaled sum / lr
+  kCodecOneBit = 6,    // 1 bit + two means per segment
+  kCodecFP16 = 7,      // half cast, sum
+};
+
+struct QuantSegStats {   // per segment, device scratch (double for stable sums)
+  double sum, sumsq, sum_neg, sum_pos;
+  unsigned long long cnt_neg;
+  unsigned maxabs_bits;
+  unsigned pad;
+};
+
+struct QuantArgs {
+  const float* g;
+  float* acc;          // residual state (nullable)
+  float* mom;          // signum momentum state (nullable)
+  float* out;          // may alias g
+  const Segment* segs;
+  int nseg;
+  long long total;     // padded flat length, multiple of 128
+  int codec;
+  int quantum;         // QSGD levels
+  int deterministic;   // natural: round at 0.5 instead of drawing
+  int first_step;      // signum: momentum not yet initialised
+  float beta, gamma;   // acc = beta*residual + gamma*g
+  float mom_beta;      // signum
+  float lr;            // EF-signSGD aggregate divisor
+  float scale;         // 1/W when averaging
+  unsigned long long seed;
+  unsigned step;
+  QuantSegStats* stats;  // nseg, zero on entry, left zero on exit
+  unsigned* barrier;
+  unsigned* status;
+  int phases;
+  PeerTable peers;
+};
+
+size_t quant_slot_bytes(int codec, long long total, int nseg);
+int quant_max_grid(int device, int sm_limit);
+cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
+
+// ------------------------------------------------------------------- sgd ----
+struct SgdTensor {
+  float* p;
+  const float* g;
+  float* buf;
+  int numel;
+};
+cudaError_t launch_fused_sgd(float* p, float* g, float* buf, long long numel, float lr, float momentum, float dampening,
+                             float weight_decay, int nesterov, int first_step, int zero_grad, float grad_scale,
+                             cudaStream_t stream);
+int sgd_table_chunk();
+cudaError_t launch_multi_sgd(const SgdTensor* table, const int* blocks_xy, int nblocks, float lr, float momentum,
+                             float dampening, float weight_decay, int nesterov, int first_step, int zero_grad,
+                             float grad_scale, cudaStream_t stream);
+
+}  // namespace grace

@@ -1,0 +1,420 @@
+// Fused sparse gradient exchange for TopK / DGC / Threshold on sm_100a.
+//
+// One persistent cooperative kernel does, for a flat buffer holding any number
+// of named gradients (segments):
+//   A   acc = beta*residual + gamma*g   (DGC: u = m*u + g, v += u, acc = v),
+//       store acc as the new residual, zero the output, histogram the top 12
+//       magnitude bits per segment;
+//   P1..P3 / A2, A3   radix select of the k-th largest magnitude per segment,
+//       entirely on device (12 + 12 + 7 key bits);
+//   B   compaction of (value, flat index) into this rank's send slot through a
+//       shared-memory staging buffer, zeroing the residual (and DGC u, v) at
+//       the selected positions, which is the whole error-feedback update;
+//   publish   st.release.sys of the sequence number into every peer's flag pad;
+//   X   for every rank: bounded wait for its flag, stream its list with
+//       ld.global.cg over NVLink and red.global.add.f32 into the dense output
+//       scaled by 1/W; then acknowledge so the slot can be reused.
+//
+// What it replaces in the reference: ATen topk / nonzero / scatter_, the
+// rdxtopk extension with its three blocking copies per digit
+// (radixtopk_cuda/rdxtopk_cuda.cu:459-529), the W dense decompressions of
+// communicator/allgather.py:40-45, memory/residual.py:18-20 and
+// memory/dgc.py:21-39.
+#include "common.cuh"
+#include "exchange.h"
+#include "segments.cuh"
+
+namespace grace {
+
+namespace {
+
+constexpr int kBlock = 512;
+constexpr int kBins = 4096;
+constexpr int kStageCap = 8192;           // staged (value, index) pairs per CTA
+constexpr int kIterElems = kBlock * 4;    // elements per CTA iteration
+constexpr unsigned kSlotHeaderBytes = 128;
+
+__device__ __forceinline__ unsigned ordered_bits(float f) {
+  // monotone map float -> unsigned (for atomicMax on signed floats)
+  unsigned b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_bits(unsigned b) {
+  return __uint_as_float((b & 0x80000000u) ? (b & 0x7fffffffu) : ~b);
+}
+
+struct Smem {
+  union {
+    unsigned hist[kBins];
+    struct {
+      float val[kStageCap];
+      int idx[kStageCap];
+    } stage;
+  };
+  unsigned stage_count;
+  unsigned flush_base;
+  unsigned scan[kBlock / 32 + 1];
+  unsigned pick[4];
+};
+
+__device__ __forceinline__ void flush_hist(Smem& sm, unsigned* __restrict__ ghist) {
+  __syncthreads();
+  for (int b = threadIdx.x; b < kBins; b += kBlock) {
+    const unsigned c = sm.hist[b];
+    if (c) {
+      atomicAdd(ghist + b, c);
+      sm.hist[b] = 0;
+    }
+  }
+  __syncthreads();
+}
+
+// Suffix-scan one segment's histogram and pick the bin holding the `need`-th
+// largest key.  All threads of the CTA take part; the histogram is left zero.
+__device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseState* __restrict__ st, unsigned need,
+                              int bits) {
+  constexpr int kPer = kBins / kBlock;  // 8 bins per thread
+  const int t = threadIdx.x;
+  unsigned c[kPer];
+  unsigned local = 0;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    c[j] = ghist[t * kPer + j];
+    ghist[t * kPer + j] = 0;
+    local += c[j];
+  }
+  // inclusive scan of `local` over threads in *descending* thread order
+  const int lane = t & 31, warp = t >> 5;
+  unsigned incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned n = __shfl_down_sync(0xffffffffu, incl, o);
+    if (lane + o < 32) incl += n;
+  }
+  if (lane == 0) sm.scan[warp] = incl;  // warp total
+  __syncthreads();
+  unsigned above_warps = 0;
+  for (int w = warp + 1; w < kBlock / 32; ++w) above_warps += sm.scan[w];
+  const unsigned above = above_warps + incl - local;  // keys in bins owned by higher threads
+  if (above < need && need <= above + local) {
+    unsigned cum = above;
+#pragma unroll
+    for (int j = kPer - 1; j >= 0; --j) {
+      if (cum < need && need <= cum + c[j]) {
+        st->prefix = (st->prefix << bits) | (unsigned)(t * kPer + j);
+        st->need = need - cum;
+        st->tie_taken = 0;
+      }
+      cum += c[j];
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kBlock) sparse_exchange_kernel(const SparseArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+  const Status status{a.status};
+  GridBarrier bar{a.barrier, 0u, a.peers.timeout_ns, status};
+  const int tid = threadIdx.x;
+  const int rank = a.peers.rank, world = a.peers.world;
+  char* const my_heap = a.peers.heap[rank];
+  unsigned* const my_hdr = reinterpret_cast<unsigned*>(my_heap + a.peers.slot_off);
+  float* const my_vals = reinterpret_cast<float*>(my_heap + a.peers.slot_off + kSlotHeaderBytes);
+  int* const my_idx = reinterpret_cast<int*>(my_vals + a.cap);
+
+  // contiguous share of the flat buffer for this CTA
+  long long chunk = (a.total + gridDim.x - 1) / gridDim.x;
+  chunk = (chunk + kIterElems - 1) / kIterElems * kIterElems;
+  const long long lo = (long long)blockIdx.x * chunk;
+  const long long hi = lo + chunk < a.total ? lo + chunk : a.total;
+  const float* __restrict__ src = a.acc ? a.acc : a.g;
+  const bool topk = a.mode == kSparseTopK;
+
+  if (a.phases & kPhaseCompress) {
+    // Before overwriting the slot of parity (seq & 1): every peer must have
+    // finished reading what sequence seq-2 put there.
+    if (blockIdx.x == 0 && tid < world && tid != rank && a.peers.seq > 2) {
+      const uint64_t* ack = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ack_off) + tid;
+      wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
+    }
+    if (blockIdx.x == 0 && tid == 0) { my_hdr[0] = 0; my_hdr[1] = 0; }
+    for (int b = tid; b < kBins; b += kBlock) sm.hist[b] = 0;
+    __syncthreads();
+
+    // ---- phase A: compensate, store accumulator, zero output, histogram ----
+    if (lo < hi) {
+      for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+        float tmax = -INFINITY;
+        for (long long i = b0 + 4ll * tid; i < e0; i += kIterElems) {
+          const int valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+          float gv[4], rv[4] = {0.f, 0.f, 0.f, 0.f}, av[4];
+          load4(a.g, i, valid, gv);
+          if (a.u) {
+            float uv[4];
+            load4(a.u, i, valid, uv);
+            load4(a.acc, i, valid, rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { uv[j] = a.momentum * uv[j] + gv[j]; av[j] = rv[j] + uv[j]; }
+            store4(a.u, i, valid, uv);
+          } else {
+            if (a.acc && a.beta != 0.f) load4(a.acc, i, valid, rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[j] + a.gamma * gv[j];
+          }
+          if (a.acc) store4(a.acc, i, valid, av);
+          if (a.out) { const float z[4] = {0.f, 0.f, 0.f, 0.f}; store4(a.out, i, valid, z); }
+          if (topk) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (j < valid) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) if (j < valid) tmax = fmaxf(tmax, av[j]);
+          }
+        }
+        if (topk) {
+          flush_hist(sm, a.hist + (size_t)s * kBins);
+        } else {
+          tmax = warp_max(tmax);
+          if ((tid & 31) == 0 && tmax > -INFINITY) atomicMax(&a.state[s].max_bits, ordered_bits(tmax));
+        }
+      });
+    }
+    // zero the padding gaps of the output (between segments) is unnecessary:
+    // nothing ever writes there.
+    bool ok = bar.sync();
+
+    if (topk) {
+      // ---- radix select: levels of 12, 12 and 7 key bits ----
+      const int nlevels = a.levels;
+      for (int level = 0; level < nlevels; ++level) {
+        const int bits = level == 2 ? 7 : 12;
+        if (ok) {
+          for (int s = blockIdx.x; s < a.nseg; s += gridDim.x) {
+            const unsigned need = level == 0 ? (unsigned)a.segs[s].k : a.state[s].need;
+            pivot_segment(sm, a.hist + (size_t)s * kBins, &a.state[s], need, bits);
+          }
+        }
+        ok = bar.sync();
+        if (level + 1 < nlevels) {
+          // histogram of the next digit among keys that match the prefix
+          const int shift_prefix = level == 0 ? 19 : 7;
+          const int shift_digit = level == 0 ? 7 : 0;
+          const unsigned digit_mask = level == 0 ? 0xfffu : 0x7fu;
+          if (ok && lo < hi) {
+            for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+              const unsigned prefix = a.state[s].prefix;
+              for (long long i = b0 + 4ll * tid; i < e0; i += kIterElems) {
+                const int valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+                float av[4];
+                load4(src, i, valid, av);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned key = __float_as_uint(av[j]) & 0x7fffffffu;
+                  if (j < valid && (key >> shift_prefix) == prefix)
+                    atomicAdd(&sm.hist[(key >> shift_digit) & digit_mask], 1u);
+                }
+              }
+              flush_hist(sm, a.hist + (size_t)s * kBins);
+            });
+          }
+          ok = bar.sync();
+        }
+      }
+    }
+
+    // ---- phase B: compaction into the send slot + error-feedback update ----
+    __syncthreads();
+    if (tid == 0) sm.stage_count = 0;
+    __syncthreads();
+    const int key_shift = topk ? (a.levels == 3 ? 0 : (a.levels == 2 ? 7 : 19)) : 0;
+    auto flush_stage = [&]() {
+      // called by all threads; copies the staged pairs to the slot (coalesced)
+      const unsigned n = sm.stage_count;
+      if (tid == 0) sm.flush_base = n ? atomicAdd(&my_hdr[0], n) : 0u;
+      __syncthreads();
+      const unsigned base = sm.flush_base;
+      for (unsigned e = tid; e < n; e += kBlock) {
+        const unsigned pos = base + e;
+        if (pos < a.cap) {
+          my_vals[pos] = sm.stage.val[e];
+          my_idx[pos] = sm.stage.idx[e];
+        } else {
+          // no room: give the value back to the residual so nothing is lost
+          if (a.acc) a.acc[sm.stage.idx[e]] = sm.stage.val[e];
+          atomicAdd(&a.status[3], 1u);
+        }
+      }
+      __syncthreads();
+      if (tid == 0) sm.stage_count = 0;
+      __syncthreads();
+    };
+    unsigned since_flush = 0;
+    if (ok && lo < hi) {
+      for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+        const unsigned pivot = a.state[s].prefix;
+        const unsigned need = a.state[s].need;
+        float thr = a.threshold;
+        if (!topk) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));
+        const long long span = e0 - b0;
+        const long long iters = (span + kIterElems - 1) / kIterElems;
+        for (long long it = 0; it < iters; ++it) {
+          // at most 3 * 2048 pairs are staged between flushes (capacity 8192)
+          if (since_flush == 3) { __syncthreads(); flush_stage(); since_flush = 0; }
+          ++since_flush;
+          const long long i = b0 + it * kIterElems + 4ll * tid;
+          int valid = 0;
+          if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+          float av[4] = {0.f, 0.f, 0.f, 0.f};
+          if (valid) load4(src, i, valid, av);
+          unsigned mask = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j >= valid) continue;
+            bool sel;
+            if (topk) {
+              const unsigned kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
+              sel = kp > pivot;
+              if (kp == pivot) sel = atomicAdd(&a.state[s].tie_taken, 1u) < need;
+            } else {
+              sel = fabsf(av[j]) >= thr;
+            }
+            if (sel) mask |= 1u << j;
+          }
+          const unsigned cnt = __popc(mask);
+          // warp-aggregated reservation in the staging buffer
+          unsigned incl = cnt;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const unsigned n = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((tid & 31) >= o) incl += n;
+          }
+          const unsigned wtotal = __shfl_sync(0xffffffffu, incl, 31);
+          unsigned wbase = 0;
+          if ((tid & 31) == 31 && wtotal) wbase = atomicAdd(&sm.stage_count, wtotal);
+          wbase = __shfl_sync(0xffffffffu, wbase, 31);
+          unsigned pos = wbase + incl - cnt;
+          if (mask) {
+            float zv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              zv[j] = av[j];
+              if (mask & (1u << j)) {
+                sm.stage.val[pos] = av[j];
+                sm.stage.idx[pos] = (int)(i + j);
+                ++pos;
+                zv[j] = 0.f;
+              }
+            }
+            if (a.acc) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) if (mask & (1u << j)) a.acc[i + j] = 0.f;
+            }
+            if (a.u) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) if (mask & (1u << j)) a.u[i + j] = 0.f;
+            }
+          }
+        }
+      });
+    }
+    __syncthreads();
+    flush_stage();
+    ok = bar.sync();
+    if (blockIdx.x == 0 && tid == 0) {
+      // clamp the published count to the capacity
+      const unsigned n = my_hdr[0];
+      if (n > a.cap) { my_hdr[1] = n - a.cap; my_hdr[0] = a.cap; }
+      __threadfence_system();
+    }
+  }
+
+  if (a.phases & kPhasePublish) {
+    // All CTAs' slot writes are ordered before this point by the barrier above
+    // (or by the kernel boundary when phases are launched separately).
+    if (blockIdx.x == 0) {
+      __syncthreads();
+      if (tid < world && !status.failed()) {
+        __threadfence_system();
+        uint64_t* flag = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ready_off) + rank;
+        st_release_sys(flag, a.peers.seq);
+      }
+    }
+  }
+
+  if (a.phases & kPhaseExchange) {
+    // ---- phase X: pull every rank's list and scatter-add it ----
+    for (int step = 0; step < world; ++step) {
+      const int p = (rank + step) % world;  // own list first: no waiting
+      __shared__ unsigned peer_count;
+      if (tid == 0) {
+        unsigned n = 0;
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ready_off) + p;
+        if (wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, p))
+          n = ld_cg_u32(a.peers.heap[p] + a.peers.slot_off);
+        peer_count = n < a.cap ? n : a.cap;
+      }
+      __syncthreads();
+      const unsigned n = peer_count;
+      const char* pv = a.peers.heap[p] + a.peers.slot_off + kSlotHeaderBytes;
+      const char* pi = pv + (size_t)a.cap * 4;
+      const unsigned groups = (n + 3) / 4;
+      for (unsigned gidx = blockIdx.x * kBlock + tid; gidx < groups; gidx += gridDim.x * kBlock) {
+        const uint4 v = ld_cg_u4(pv + (size_t)gidx * 16);
+        const uint4 ix = ld_cg_u4(pi + (size_t)gidx * 16);
+        const unsigned e = gidx * 4;
+        const unsigned lim = (unsigned)a.total;
+        if ((ix.x >= lim) | (e + 1 < n && ix.y >= lim) | (e + 2 < n && ix.z >= lim) | (e + 3 < n && ix.w >= lim)) {
+          status.fail(kBadArgument, p, (unsigned)a.peers.seq);  // corrupt index: skip, never dereference
+          continue;
+        }
+        atomicAdd(a.out + ix.x, __uint_as_float(v.x) * a.scale);
+        if (e + 1 < n) atomicAdd(a.out + ix.y, __uint_as_float(v.y) * a.scale);
+        if (e + 2 < n) atomicAdd(a.out + ix.z, __uint_as_float(v.z) * a.scale);
+        if (e + 3 < n) atomicAdd(a.out + ix.w, __uint_as_float(v.w) * a.scale);
+      }
+      __syncthreads();
+    }
+    // acknowledge: the peers may now reuse their slot of this parity
+    bar.sync();
+    if (blockIdx.x == 0 && tid < world && tid != rank && !status.failed()) {
+      uint64_t* ack = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ack_off) + rank;
+      st_release_sys(ack, a.peers.seq);
+    }
+  }
+}
+
+}  // namespace
+
+size_t sparse_slot_bytes(unsigned cap) { return kSlotHeaderBytes + (size_t)cap * 8; }
+size_t sparse_smem_bytes() { return sizeof(Smem); }
+
+int sparse_max_grid(int device, int sm_limit) {
+  static bool attr_set[64] = {};
+  if (device >= 0 && device < 64 && !attr_set[device]) {
+    cudaFuncSetAttribute(sparse_exchange_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+    attr_set[device] = true;
+  }
+  int per_sm = 0, sms = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sparse_exchange_kernel, kBlock, sizeof(Smem));
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
+  if (per_sm > 2) per_sm = 2;
+  return per_sm * sms;
+}
+
+cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t stream) {
+  cudaError_t err = cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream);
+  if (err != cudaSuccess) return err;
+  if (a.phases & kPhaseCompress) {
+    err = cudaMemsetAsync(a.state, 0, sizeof(SparseState) * (size_t)a.nseg, stream);
+    if (err != cudaSuccess) return err;
+  }
+  SparseArgs copy = a;
+  void* params[] = {&copy};
+  return cudaLaunchCooperativeKernel((const void*)sparse_exchange_kernel, dim3(grid), dim3(kBlock), params,
+                                     sizeof(Smem), stream);
+}
+
+}  // namespace grace

@@ -1,0 +1,1 @@
+from grace_b200.compressor.qsgd import QSGDCompressor, QSGDCompressor_CUDA  # noqa: F401

@@ -1,0 +1,1 @@
+from grace_b200.helper import grace_from_params  # noqa: F401
