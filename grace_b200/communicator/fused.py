@@ -1,0 +1,350 @@
+"""``FusedExchange``: one sm_100a kernel launch per gradient exchange.
+
+Where the library communicators (``Allgather`` and friends) run
+compensate -> compress -> memory.update -> collective -> W x decompress ->
+aggregate as a chain of framework ops and NCCL calls, this communicator hands
+the gradient, the error-feedback arenas and the peers' heap pointers to one
+cooperative kernel (``csrc/sparse_exchange.cu`` or ``csrc/quant_exchange.cu``)
+that does all of it, reading the other ranks' send slots over NVLink from
+inside the kernel.
+
+Supported pairs (anything else transparently uses the library ``Allgather``
+path, as does every call on CPU tensors):
+
+==================  =====================================  ==================
+compressor          memory                                 kernel
+==================  =====================================  ==================
+TopK, DGC           none / residual / dgc                  sparse (radix select)
+Threshold           none / residual                        sparse (threshold)
+QSGD (bucket 128,   none / residual                        quantised
+q < 128), TernGrad,
+natural, 8-bit,
+fp16, none
+signSGD, signum     none / residual                        quantised, vote
+EF-signSGD          efsignsgd                              quantised
+1-bit               none / residual                        quantised
+PowerSGD            powersgd                               low-rank (tcgen05)
+==================  =====================================  ==================
+
+Two granularities: ``step(tensor, name)`` (one tensor, API of the reference)
+and ``step_flat(flat, layout)`` (a whole bucket of named tensors in one launch,
+used by the DDP hook and ``DistributedOptimizer``).
+"""
+from __future__ import annotations
+
+import zlib
+from typing import Dict, List, Optional, Sequence
+
+import torch
+from torch import distributed as dist
+
+from ..core import Communicator
+from .. import compressor as C_
+from .. import memory as M_
+from ..compressor._common import topk_count
+from .allgather import Allgather
+
+
+def _name_seed(seed: int, name: str) -> int:
+    return ((seed & 0xFFFFFFFF) << 32) | (zlib.crc32(name.encode("utf8")) & 0xFFFFFFFF)
+
+
+class _Plan:
+    """Everything one layout needs: heap, channel, segment table, arenas."""
+
+    def __init__(self, owner: "FusedExchange", layout, kind: str):
+        from ..ops import exchange as X, native
+
+        Cn = native()
+        self.layout = layout
+        self.kind = kind
+        self.steps = 0
+        comp = owner.compressor
+        device = owner.device
+        nseg = len(layout.names)
+        self.ks = None
+        if kind == "sparse":
+            if isinstance(comp, C_.ThresholdCompressor):
+                self.mode = X.SPARSE_THRESHOLD
+                self.cap = X.sparse_capacity(layout, [], self.mode, owner.max_ratio)
+            else:
+                self.mode = X.SPARSE_TOPK
+                self.ks = [topk_count(n, comp.compress_ratio) for n in layout.numels]
+                self.cap = X.sparse_capacity(layout, self.ks, self.mode)
+            slot_bytes = Cn.sparse_slot_bytes(self.cap)
+        else:
+            self.codec = owner._codec
+            slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg)
+        heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 4096
+        self.heap = owner._make_heap(layout.key(), heap_bytes)
+        self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
+        self.segs = X.segments_to_device(layout, self.ks, device)
+        self.acc = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_acc else None
+        self.u = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_u else None
+        self.mom = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_mom else None
+        self.seed = _name_seed(owner.seed, "|".join(layout.names[:4]) + str(layout.total))
+
+
+class FusedExchange(Communicator):
+    def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
+                 group=None, inplace=True, max_ratio=1.0, exact=True, rank=None):
+        super().__init__(compressor, memory, world_size)
+        self.mode = mode
+        self.seed = int(seed)
+        self.timeout_ms = float(timeout_ms)
+        self.comm_sms = comm_sms
+        self.group = group
+        self.inplace = inplace
+        self.max_ratio = max_ratio
+        self.exact = exact
+        self.device = None
+        self._rank = rank
+        self._plans: Dict[tuple, _Plan] = {}
+        self._virtual = None
+        self._fallback = Allgather(compressor, memory, world_size)
+        self._resolve()
+
+    # ------------------------------------------------------------------
+    def _resolve(self):
+        comp, mem = self.compressor, self.memory
+        self._kind = None
+        self._codec = None
+        self._needs_acc = isinstance(mem, (M_.ResidualMemory, M_.EFSignSGDMemory, M_.DgcMemory))
+        self._needs_u = isinstance(mem, M_.DgcMemory)
+        self._needs_mom = isinstance(comp, C_.SignumCompressor)
+        from ..ops.exchange import CODEC
+
+        if isinstance(mem, M_.PowerSGDMemory) or isinstance(comp, C_.PowerSGDCompressor):
+            self._kind = "powersgd"
+        elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor)):
+            if isinstance(mem, M_.DgcMemory) and (mem.gradient_clipping or isinstance(comp, C_.ThresholdCompressor)):
+                self._kind = None
+            elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.DgcMemory)):
+                self._kind = "sparse"
+        elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.EFSignSGDMemory)):
+            table = [
+                (C_.QSGDCompressor, "qsgd"), (C_.TernGradCompressor, "terngrad"), (C_.NaturalCompressor, "natural"),
+                (C_.U8bitCompressor, "u8bit"), (C_.SignSGDCompressor, "sign"), (C_.SignumCompressor, "sign"),
+                (C_.EFSignSGDCompressor, "efsign"), (C_.OneBitCompressor, "onebit"), (C_.FP16Compressor, "fp16"),
+                (C_.NoneCompressor, "fp32"),
+            ]
+            for cls, key in table:
+                if isinstance(comp, cls):
+                    self._codec = CODEC[key]
+                    self._kind = "quant"
+                    break
+            if isinstance(comp, C_.QSGDCompressor) and (comp.bucket_size != 128 or comp.quantum_num >= 128):
+                self._kind = None
+
+    def supported(self, tensor: torch.Tensor) -> bool:
+        return self._kind in ("sparse", "quant") and tensor.is_cuda
+
+    # ------------------------------------------------------------------
+    def _make_heap(self, key, nbytes):
+        from ..parallel.symm import SymmetricHeap
+
+        if self._virtual is not None:
+            return self._virtual.heap_for(key, nbytes, self._rank)
+        return SymmetricHeap.create(nbytes, group=self.group, device=self.device)
+
+    def _plan(self, layout) -> _Plan:
+        key = layout.key()
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = _Plan(self, layout, self._kind)
+            self._plans[key] = plan
+        return plan
+
+    def _memory_coeffs(self, plan: _Plan):
+        mem = self.memory
+        first = plan.steps == 0
+        if isinstance(mem, M_.ResidualMemory):
+            return (0.0, 1.0) if first else (float(mem.beta), float(mem.gamma))
+        if isinstance(mem, M_.EFSignSGDMemory):
+            return (0.0, 1.0) if first else (1.0, float(mem.learning_rate))
+        return 0.0, 1.0
+
+    def _launch(self, plan: _Plan, g: torch.Tensor, out: torch.Tensor, phases: int, seq: Optional[int] = None) -> int:
+        from ..ops import exchange as X
+
+        comp = self.compressor
+        scale = (1.0 / self.world_size) if comp.average else 1.0
+        beta, gamma = self._memory_coeffs(plan)
+        plan.channel.poll()
+        if plan.kind == "sparse":
+            seq = X.run_sparse(
+                plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,
+                beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
+                threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
+                phases=phases, seq=seq)
+        else:
+            seq = X.run_quant(
+                plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,
+                quantum=int(getattr(comp, "quantum_num", 0)), deterministic=bool(getattr(comp, "deterministic", False)),
+                first_step=plan.steps == 0, beta=beta, gamma=gamma, mom_beta=float(getattr(comp, "momentum", 0.0)),
+                lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
+                phases=phases, seq=seq)
+        return seq
+
+    # ------------------------------------------------------------------
+    def step_flat(self, flat: torch.Tensor, layout, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Exchange a whole flat buffer of named gradients in one launch."""
+        from ..ops.exchange import PHASE_ALL
+
+        if self.device is None:
+            self.device = flat.device
+        plan = self._plan(layout)
+        out = flat if out is None else out
+        self._launch(plan, flat, out, PHASE_ALL)
+        plan.steps += 1
+        self._stats["steps"] += 1
+        return out
+
+    def _prepare(self, tensor: torch.Tensor):
+        flat = tensor.detach().reshape(-1)
+        if flat.dtype != torch.float32 or not flat.is_contiguous() or flat.data_ptr() % 16 != 0:
+            flat = flat.float().contiguous().clone()
+        return flat
+
+    def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:
+        if not self.supported(tensor):
+            return self._fallback.step(tensor, name)
+        from ..ops.exchange import FlatLayout
+
+        flat = self._prepare(tensor)
+        same = flat.data_ptr() == tensor.data_ptr()
+        out = flat if (self.inplace and same) else torch.empty_like(flat)
+        self.step_flat(flat, FlatLayout.single(name, flat.numel()), out)
+        return out.view(tensor.shape).to(tensor.dtype)
+
+    # split-phase: launch on the caller's current stream, hand back an event
+    def send_step(self, tensor: torch.Tensor, name: str):
+        if not self.supported(tensor):
+            return self._fallback.send_step(tensor, name)
+        out = self.step(tensor, name)
+        ev = torch.cuda.Event()
+        ev.record()
+        return ("fused", out, ev), None
+
+    def receive_step(self, handles, ctx) -> torch.Tensor:
+        if isinstance(handles, tuple) and len(handles) == 3 and handles[0] == "fused":
+            _, out, ev = handles
+            torch.cuda.current_stream().wait_event(ev)
+            return out
+        return self._fallback.receive_step(handles, ctx)
+
+    def send_receive(self, tensors, name, ctx):
+        return self._fallback.send_receive(tensors, name, ctx)
+
+    def check(self):
+        """Block until every launched exchange finished; raise on failure."""
+        for plan in self._plans.values():
+            plan.channel.check()
+
+    # ------------------------------------------------------------------
+    def state_dict(self):
+        if not self._plans:
+            return self._fallback.state_dict()
+        residuals, gradients, momentums = {}, {}, {}
+        for plan in self._plans.values():
+            lay = plan.layout
+            if plan.acc is not None:
+                target = gradients if plan.u is not None else residuals
+                for n, t in lay.slices(plan.acc).items():
+                    target[n] = t.clone()
+            if plan.u is not None:
+                for n, t in lay.slices(plan.u).items():
+                    residuals[n] = t.clone()
+            if plan.mom is not None:
+                for n, t in lay.slices(plan.mom).items():
+                    momentums[n] = t.clone()
+        mem = {"residuals": residuals}
+        if gradients:
+            mem["gradients"] = gradients
+        comp = self.compressor.state_dict()
+        if momentums:
+            comp["momentums"] = momentums
+        steps = {"|".join(map(str, k[1])) + ":" + "|".join(k[0][:2]): p.steps for k, p in self._plans.items()}
+        return {"compressor": comp, "memory": mem, "world_size": self.world_size, "fused_steps": steps}
+
+    def load_state_dict(self, state):
+        self._pending_state = state
+        self._fallback.load_state_dict(state)
+        for plan in self._plans.values():
+            self._restore_plan(plan, state)
+
+    def _restore_plan(self, plan: _Plan, state):
+        mem = state.get("memory", {})
+        lay = plan.layout
+        src_acc = mem.get("gradients" if plan.u is not None else "residuals", {})
+        if plan.acc is not None:
+            for n, t in lay.slices(plan.acc).items():
+                if n in src_acc:
+                    t.copy_(src_acc[n].reshape(-1))
+                    plan.steps = max(plan.steps, 1)
+        if plan.u is not None:
+            for n, t in lay.slices(plan.u).items():
+                if n in mem.get("residuals", {}):
+                    t.copy_(mem["residuals"][n].reshape(-1))
+        if plan.mom is not None:
+            for n, t in lay.slices(plan.mom).items():
+                if n in state.get("compressor", {}).get("momentums", {}):
+                    t.copy_(state["compressor"]["momentums"][n].reshape(-1))
+                    plan.steps = max(plan.steps, 1)
+        key = "|".join(map(str, lay.key()[1])) + ":" + "|".join(lay.key()[0][:2])
+        if key in state.get("fused_steps", {}):
+            plan.steps = int(state["fused_steps"][key])
+
+
+class VirtualWorld:
+    """W ``FusedExchange`` objects on ONE GPU, stepped phase by phase.
+
+    Ranks never wait on each other inside a kernel: all ranks run
+    compress+publish first, then all ranks run exchange, each as its own
+    launch on the same stream.  The protocol (flags, slots, acknowledgements,
+    sequence numbers) and the kernels are the ones a real multi-GPU run uses.
+    """
+
+    def __init__(self, world: int, make_comm, device=None):
+        self.world = world
+        self.device = torch.device(device if device is not None else "cuda")
+        self._heaps = {}
+        self.comms: List[FusedExchange] = []
+        for r in range(world):
+            c = make_comm(r)
+            c._virtual = self
+            c._rank = r
+            c.device = self.device
+            self.comms.append(c)
+
+    def heap_for(self, key, nbytes, rank):
+        from ..parallel.symm import SymmetricHeap
+
+        if key not in self._heaps:
+            self._heaps[key] = SymmetricHeap.virtual(nbytes, self.world, self.device)
+        return self._heaps[key][rank]
+
+    def step_flat(self, flats: Sequence[torch.Tensor], layout, outs: Optional[Sequence[torch.Tensor]] = None):
+        from ..ops.exchange import PHASE_COMPRESS, PHASE_EXCHANGE, PHASE_PUBLISH
+
+        outs = list(outs) if outs is not None else list(flats)
+        plans = [c._plan(layout) for c in self.comms]
+        seqs = []
+        for c, p, g, o in zip(self.comms, plans, flats, outs):
+            seqs.append(c._launch(p, g, o, PHASE_COMPRESS | PHASE_PUBLISH))
+        for c, p, g, o, s in zip(self.comms, plans, flats, outs, seqs):
+            c._launch(p, g, o, PHASE_EXCHANGE, seq=s)
+            p.steps += 1
+        return outs
+
+    def step(self, tensors: Sequence[torch.Tensor], name: str):
+        from ..ops.exchange import FlatLayout
+
+        flats = [c._prepare(t) for c, t in zip(self.comms, tensors)]
+        outs = [torch.empty_like(f) for f in flats]
+        self.step_flat(flats, FlatLayout.single(name, flats[0].numel()), outs)
+        return [o.view(t.shape) for o, t in zip(outs, tensors)]
+
+    def check(self):
+        for c in self.comms:
+            c.check()

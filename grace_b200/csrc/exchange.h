@@ -89,6 +89,7 @@ enum Codec : int {
   kCodecEFSign = 5,    // 1 bit + mean |x| per segment, scaled sum / lr
   kCodecOneBit = 6,    // 1 bit + two means per segment
   kCodecFP16 = 7,      // half cast, sum
+  kCodecFP32 = 8,      // no compression: one-shot all-gather-sum (small dense tensors)
 };
 
 struct QuantSegStats {   // per segment, device scratch (double for stable sums)

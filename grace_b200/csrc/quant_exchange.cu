@@ -48,6 +48,7 @@ template <> struct CodecTraits<kCodecSign>     { static constexpr bool stats = f
 template <> struct CodecTraits<kCodecEFSign>   { static constexpr bool stats = true;  static constexpr int bits = 1; };
 template <> struct CodecTraits<kCodecOneBit>   { static constexpr bool stats = true;  static constexpr int bits = 1; };
 template <> struct CodecTraits<kCodecFP16>     { static constexpr bool stats = false; static constexpr int bits = 16; };
+template <> struct CodecTraits<kCodecFP32>     { static constexpr bool stats = false; static constexpr int bits = 32; };
 
 __host__ __device__ inline size_t scalars_bytes(int nseg) { return ((size_t)nseg * 16 + 127) / 128 * 128; }
 __host__ __device__ inline size_t codes_bytes(int bits, long long total) { return (size_t)total * bits / 8; }
@@ -314,6 +315,10 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
             *reinterpret_cast<uint2*>(my_slot + off_codes + (size_t)i * 2) = w;
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
             dv[0] = f01.x; dv[1] = f01.y; dv[2] = f23.x; dv[3] = f23.y;
+          } else if (C == kCodecFP32) {
+            *reinterpret_cast<float4*>(my_slot + off_codes + (size_t)i * 4) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dv[j] = xv[j];
           }
           if (a.acc && valid) {
             float res[4];
@@ -412,6 +417,10 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
                 if (C == kCodecEFSign) sum[j] += bit ? s_peer[p].s0 : -s_peer[p].s0;
                 if (C == kCodecOneBit) sum[j] += bit ? s_peer[p].s0 : s_peer[p].s1;
               }
+            } else if (T::bits == 32) {
+              const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
+              sum[0] += __uint_as_float(w.x); sum[1] += __uint_as_float(w.y);
+              sum[2] += __uint_as_float(w.z); sum[3] += __uint_as_float(w.w);
             } else {  // fp16
               uint2 w;
               const char* q = slot + off_codes + (size_t)i * 2;
@@ -480,6 +489,7 @@ size_t quant_slot_bytes(int codec, long long total, int nseg) {
     case kCodecTernGrad: bits = 2; break;
     case kCodecSign: case kCodecEFSign: case kCodecOneBit: bits = 1; break;
     case kCodecFP16: bits = 16; break;
+    case kCodecFP32: bits = 32; break;
     default: bits = 8;
   }
   size_t bytes = kHeaderBytes + scalars_bytes(nseg) + codes_bytes(bits, total);
@@ -511,6 +521,7 @@ cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t str
     case kCodecEFSign: return launch_codec<kCodecEFSign>(a, grid, stream);
     case kCodecOneBit: return launch_codec<kCodecOneBit>(a, grid, stream);
     case kCodecFP16: return launch_codec<kCodecFP16>(a, grid, stream);
+    case kCodecFP32: return launch_codec<kCodecFP32>(a, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

@@ -1,0 +1,239 @@
+"""Launch plans for the fused exchange kernels.
+
+A ``FlatLayout`` describes how named gradients sit in one flat fp32 buffer
+(every tensor starts on a 128-element boundary).  An ``ExchangeChannel`` owns
+what one stream of exchanges needs on the symmetric heap: the ready/ack flag
+pads and two send slots (double buffered by sequence parity), plus the local
+scratch (histograms, per-segment state, barrier word, status block) and the
+error-feedback arenas.  ``run_sparse`` / ``run_quant`` fill the argument block
+and launch the cooperative kernel on the current stream.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import native
+from ..parallel.symm import SymmetricHeap
+
+PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
+SPARSE_TOPK, SPARSE_THRESHOLD = 0, 1
+CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8}
+
+STATUS_TEXT = {
+    0: "ok", 1: "timeout at a grid barrier", 2: "timeout waiting for a peer's data",
+    3: "timeout waiting for a peer's acknowledgement", 4: "send slot overflow", 5: "bad argument / corrupt index",
+    6: "timeout on an mbarrier",
+}
+ALIGN_ELEMS = 128
+
+
+class GraceCommError(RuntimeError):
+    """A fused exchange reported a failure (bounded wait expired, bad data)."""
+
+    def __init__(self, code: int, detail: int, seq: int, rank: int):
+        self.code, self.detail, self.seq, self.rank = code, detail, seq, rank
+        super().__init__(
+            "fused exchange failed on rank %d at sequence %d: %s (detail=%d)"
+            % (rank, seq, STATUS_TEXT.get(code, "code %d" % code), detail)
+        )
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclass
+class FlatLayout:
+    """Placement of named tensors in a flat buffer."""
+
+    names: List[str]
+    numels: List[int]
+    offsets: List[int] = field(default_factory=list)
+    total: int = 0
+
+    def __post_init__(self):
+        if not self.offsets:
+            off = 0
+            for n in self.numels:
+                self.offsets.append(off)
+                off += _round_up(n, ALIGN_ELEMS)
+            self.total = off
+        if self.total == 0 and self.numels:
+            self.total = _round_up(self.offsets[-1] + self.numels[-1], ALIGN_ELEMS)
+        if self.total >= 2 ** 31:
+            raise ValueError("flat buffers are indexed with 31 bits; split the bucket (%d elements)" % self.total)
+
+    @classmethod
+    def single(cls, name: str, numel: int) -> "FlatLayout":
+        return cls([name], [numel])
+
+    @classmethod
+    def from_named(cls, named: Sequence[Tuple[str, int]]) -> "FlatLayout":
+        return cls([n for n, _ in named], [int(c) for _, c in named])
+
+    def key(self) -> Tuple:
+        return (tuple(self.names), tuple(self.numels))
+
+    def segment_bytes(self, ks: Optional[Sequence[int]] = None) -> bytes:
+        ks = ks if ks is not None else [0] * len(self.names)
+        return b"".join(struct.pack("<qii", off, n, k) for off, n, k in zip(self.offsets, self.numels, ks))
+
+    def slices(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        return {n: flat[o : o + c] for n, o, c in zip(self.names, self.offsets, self.numels)}
+
+
+class ExchangeChannel:
+    """Flags + two send slots on the symmetric heap, and local scratch."""
+
+    def __init__(self, heap: SymmetricHeap, slot_bytes: int, nseg: int, timeout_ms: float = 10000.0,
+                 sm_limit: Optional[int] = None):
+        C = native()
+        self.heap = heap
+        self.device = heap.device
+        self.slot_bytes = _round_up(slot_bytes, 256)
+        self.flags_off = heap.alloc(2 * C.MAX_WORLD * 8)
+        self.ready_off = self.flags_off
+        self.ack_off = self.flags_off + C.MAX_WORLD * 8
+        self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+        self.seq = 0
+        self.timeout_ns = int(timeout_ms * 1e6)
+        self.sm_limit = sm_limit or 0
+        dev = self.device
+        self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
+        self.status_event: Optional[torch.cuda.Event] = None
+        self.hist = torch.zeros(max(1, nseg) * 4096, dtype=torch.int32, device=dev)
+        self.sparse_state = torch.zeros(max(1, nseg) * (C.SPARSE_STATE_BYTES // 4), dtype=torch.int32, device=dev)
+        self.quant_stats = torch.zeros(max(1, nseg) * C.QUANT_STATS_BYTES, dtype=torch.uint8, device=dev)
+
+    def next_seq(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    def slot_view(self, seq: int, numel: int, dtype, byte_offset: int = 0, rank: Optional[int] = None):
+        return self.heap.view(self.slot_off[seq & 1] + byte_offset, numel, dtype, rank)
+
+    # -- error surface ----------------------------------------------------
+    def post_status(self):
+        """Queue a copy of the status block to pinned memory (no sync)."""
+        self.status_host.copy_(self.status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.status_event = ev
+
+    def poll(self):
+        """Raise if the last finished launch reported a failure; never blocks."""
+        if self.status_event is not None and self.status_event.query():
+            self._raise_if_failed()
+
+    def check(self):
+        """Synchronise with the last launch and raise if it failed."""
+        if self.status_event is not None:
+            self.status_event.synchronize()
+            self._raise_if_failed()
+
+    def dropped(self) -> int:
+        self.check()
+        return int(self.status_host[3])
+
+    def _raise_if_failed(self):
+        code = int(self.status_host[0])
+        if code != 0:
+            detail, seq = int(self.status_host[1]), int(self.status_host[2])
+            raise GraceCommError(code, detail, seq, self.heap.rank)
+
+    def reset(self):
+        """Clear flags and status after an error (call on every rank, then barrier)."""
+        C = native()
+        torch.cuda.synchronize(self.device)
+        self.heap.view(self.flags_off, 2 * C.MAX_WORLD, torch.int64).zero_()
+        self.status.zero_()
+        self.hist.zero_()
+        self.sparse_state.zero_()
+        self.quant_stats.zero_()
+        self.seq = 0
+        self.status_event = None
+        if self.status_host is not None:
+            self.status_host.zero_()
+        torch.cuda.synchronize(self.device)
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def sparse_capacity(layout: FlatLayout, ks: Sequence[int], mode: int, max_ratio: float = 1.0) -> int:
+    if mode == SPARSE_TOPK:
+        cap = sum(ks)
+    else:
+        cap = int(sum(layout.numels) * max_ratio) + 16
+    return _round_up(max(cap, 16), 16)
+
+
+def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tensor, g: torch.Tensor,
+               acc: Optional[torch.Tensor], u: Optional[torch.Tensor], out: Optional[torch.Tensor], *, mode: int,
+               cap: int, beta: float = 1.0, gamma: float = 1.0, momentum: float = 0.0, threshold: float = 0.0,
+               scale: float = 1.0, levels: int = 3, phases: int = PHASE_ALL, seq: Optional[int] = None,
+               grid: Optional[int] = None) -> int:
+    C = native()
+    heap = channel.heap
+    if seq is None:
+        seq = channel.next_seq()
+    if grid is None:
+        grid = C.sparse_max_grid(heap.device.index, channel.sm_limit)
+    need = -(-layout.total // 2048)
+    grid = max(1, min(grid, max(need, 1)))
+    for t in (g, acc, u, out):
+        if t is not None:
+            assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    C.sparse_exchange(
+        _ptr(g), _ptr(acc), _ptr(u), _ptr(out), segs_dev.data_ptr(), len(layout.names), layout.total, mode, levels,
+        beta, gamma, momentum, threshold, scale, channel.hist.data_ptr(), channel.sparse_state.data_ptr(),
+        channel.barrier.data_ptr(), channel.status.data_ptr(), cap, phases, heap.rank, heap.world, seq,
+        channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
+        _stream_ptr(),
+    )
+    channel.post_status()
+    return seq
+
+
+def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tensor, g: torch.Tensor,
+              acc: Optional[torch.Tensor], mom: Optional[torch.Tensor], out: Optional[torch.Tensor], *, codec: int,
+              quantum: int = 0, deterministic: bool = False, first_step: bool = False, beta: float = 1.0,
+              gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
+              step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None) -> int:
+    C = native()
+    heap = channel.heap
+    if seq is None:
+        seq = channel.next_seq()
+    if grid is None:
+        grid = C.quant_max_grid(heap.device.index, channel.sm_limit)
+    need = -(-layout.total // 2048)
+    grid = max(1, min(grid, max(need, 1)))
+    for t in (g, acc, mom, out):
+        if t is not None:
+            assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    C.quant_exchange(
+        _ptr(g), _ptr(acc), _ptr(mom), _ptr(out), segs_dev.data_ptr(), len(layout.names), layout.total, codec, quantum,
+        int(deterministic), int(first_step), beta, gamma, mom_beta, lr, scale, seed & (2 ** 64 - 1), step & 0xFFFFFFFF,
+        channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
+        heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
+        grid, _stream_ptr(),
+    )
+    channel.post_status()
+    return seq
+
+
+def segments_to_device(layout: FlatLayout, ks: Optional[Sequence[int]], device) -> torch.Tensor:
+    raw = np.frombuffer(layout.segment_bytes(ks), dtype=np.uint8).copy()
+    return torch.from_numpy(raw).to(device)

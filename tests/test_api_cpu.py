@@ -1,0 +1,199 @@
+"""Factory, base-class contract, import paths, checkpointing, optimizer wrapper."""
+import warnings
+
+import pytest
+import torch
+
+import grace_b200
+from grace_b200 import grace_from_params
+
+
+def test_reference_import_paths():
+    from grace_dl.dist import Communicator, Compressor, Memory  # noqa: F401
+    from grace_dl.dist.communicator.all_to_all import AllToAll  # noqa: F401
+    from grace_dl.dist.communicator.allgather import Allgather
+    from grace_dl.dist.communicator.allreduce import Allreduce  # noqa: F401
+    from grace_dl.dist.communicator.broadcast import Broadcast  # noqa: F401
+    from grace_dl.dist.compressor.natural import NaturalCompressor_CUDA  # noqa: F401
+    from grace_dl.dist.compressor.qsgd import QSGDCompressor_CUDA  # noqa: F401
+    from grace_dl.dist.compressor.topk import TopKCompressor
+    from grace_dl.dist.helper import grace_from_params as g2
+    from grace_dl.dist.memory.residual import ResidualMemory
+    from grace_dl.torch.optimizer import DistributedOptimizer  # noqa: F401
+    from grace_dl.torch.helper import grace_from_params as g3  # noqa: F401
+
+    grc = Allgather(TopKCompressor(0.3), ResidualMemory(), 1)
+    out = grc.step(torch.randn(4, 5), "w")
+    assert out.shape == (4, 5)
+    assert g2 is grace_from_params
+
+
+COMPRESSORS = ["dgc", "efsignsgd", "fp16", "natural", "natural_cuda", "none", "onebit", "powersgd", "qsgd",
+               "qsgd_cuda", "randomk", "signsgd", "signum", "terngrad", "threshold", "topk", "u8bit", "adaq",
+               "inceptionn", "sketch"]
+
+
+@pytest.mark.parametrize("name", COMPRESSORS)
+def test_factory_builds_every_compressor(name):
+    mem = {"dgc": "dgc", "efsignsgd": "efsignsgd", "powersgd": "powersgd"}.get(name, "residual")
+    comm = "allreduce" if name in ("none", "fp16", "randomk", "powersgd") else "allgather"
+    grc = grace_from_params({"compressor": name, "memory": mem, "communicator": comm, "world_size": 1})
+    x = torch.randn(6, 50) * 0.01
+    for _ in range(2):
+        out = grc.step(x.clone(), "w")
+    assert out.shape == x.shape and torch.isfinite(out).all()
+    assert grc.stats()["steps"] == 2
+
+
+def test_factory_defaults_and_errors():
+    grc = grace_from_params({"world_size": 2})
+    assert type(grc).__name__ == "Allreduce" and type(grc.compressor).__name__ == "NoneCompressor"
+    assert type(grc.memory).__name__ == "NoneMemory" and grc.world_size == 2
+    assert grace_from_params({"compressor": "topk", "world_size": 1}).compressor.compress_ratio == 0.3
+    q = grace_from_params({"compressor": "qsgd", "world_size": 1}).compressor
+    assert q.quantum_num == 127 and q.bucket_size == 128
+    assert grace_from_params({"compressor": "signum", "world_size": 1}).compressor.momentum == 0.9
+    assert grace_from_params({"compressor": "threshold", "world_size": 1}).compressor.threshold == 0.01
+    assert grace_from_params({"compressor": "efsignsgd", "world_size": 1}).compressor.learning_rate == 0.1
+    p = grace_from_params({"compressor": "powersgd", "memory": "powersgd", "compress_rank": 4, "world_size": 3})
+    assert p.compressor.rank == 4 and p.compressor.world_size == 3 and p.memory.compress_rank == 4
+    b = grace_from_params({"compressor": "topk", "communicator": "broadcast", "world_size": 1})
+    assert b.rank == 0
+    for bad in ({"compressor": "nope"}, {"memory": "nope"}, {"communicator": "nope"}):
+        with pytest.raises(NotImplementedError):
+            grace_from_params({"world_size": 1, **bad})
+    with pytest.raises(KeyError):
+        grace_from_params({"compressor": "topk"})
+
+
+def test_send_receive_split_matches_step():
+    a = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather", "world_size": 1})
+    b = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather", "world_size": 1})
+    for i in range(3):
+        x = torch.randn(200)
+        h, ctx = a.send_step(x, "w")
+        torch.testing.assert_close(a.receive_step(h, ctx), b.step(x, "w"))
+
+
+def test_state_dict_roundtrip_resumes_identically():
+    def make():
+        return grace_from_params({"compressor": "signum", "memory": "residual", "communicator": "allgather",
+                                  "world_size": 1})
+
+    a = make()
+    xs = [torch.randn(300) for _ in range(4)]
+    a.step(xs[0], "w"); a.step(xs[1], "w")
+    state = a.state_dict()
+    assert set(state) >= {"compressor", "memory", "world_size"}
+    assert "residuals" in state["memory"] and "momentums" in state["compressor"]
+    b = make()
+    b.load_state_dict(state)
+    torch.testing.assert_close(a.step(xs[2], "w"), b.step(xs[2], "w"))
+    torch.testing.assert_close(a.memory.residuals["w"], b.memory.residuals["w"])
+    c = grace_from_params({"compressor": "signum", "memory": "residual", "communicator": "allgather", "world_size": 2})
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        c.load_state_dict(state)
+    assert w and not c.memory.residuals
+
+
+def test_checkpoint_files(tmp_path):
+    from grace_b200.utils.checkpoint import load_checkpoint, save_checkpoint
+
+    model = torch.nn.Linear(8, 4)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather", "world_size": 1})
+    for n, p in model.named_parameters():
+        grc.step(torch.randn_like(p), n)
+    save_checkpoint(str(tmp_path), model=model, optimizer=opt, grace=grc, rank=0, step=7)
+    assert (tmp_path / "grace_rank0.pt").exists() and (tmp_path / "model.pt").exists()
+    grc2 = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather", "world_size": 1})
+    meta = load_checkpoint(str(tmp_path), model=model, optimizer=opt, grace=grc2, rank=0)
+    assert meta["step"] == 7
+    for n in grc.memory.residuals:
+        torch.testing.assert_close(grc.memory.residuals[n], grc2.memory.residuals[n])
+
+
+# ---------------------------------------------------------------- optimizer wrapper
+class _FakeGrace:
+    def __init__(self):
+        self.sent, self.received = [], 0
+
+    def send_step(self, tensor, name):
+        self.sent.append(name)
+        return ("h", tensor * 2), name
+
+    def receive_step(self, handle, ctx):
+        self.received += 1
+        return handle[1]
+
+
+def _wrapped(passes=1, fake=None, named=True):
+    from grace_b200.parallel import DistributedOptimizer
+
+    model = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 2))
+    opt = torch.optim.SGD(model.parameters(), lr=0.0, momentum=0.9)
+    fake = fake or _FakeGrace()
+    d = DistributedOptimizer(opt, grace=fake, named_parameters=model.named_parameters() if named else None,
+                             backward_passes_per_step=passes, always_hook=True)
+    return model, d, fake
+
+
+def test_distributed_optimizer_contract():
+    model, d, fake = _wrapped()
+    assert isinstance(d, torch.optim.SGD) and type(d).__name__ == "SGD"
+    model(torch.randn(5, 4)).sum().backward()
+    assert sorted(fake.sent) == sorted(n for n, _ in model.named_parameters())
+    with pytest.raises(AssertionError):
+        d.zero_grad()  # exchanges in flight
+    grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+    d.step()
+    assert fake.received == 4
+    for n, p in model.named_parameters():
+        torch.testing.assert_close(p.grad, grads[n] * 2)  # grad replaced by the exchanged tensor
+    d.zero_grad()
+    # synchronize + skip_synchronize, and the warning on a redundant synchronize
+    model(torch.randn(5, 4)).sum().backward()
+    d.synchronize()
+    with d.skip_synchronize():
+        d.step()
+    model(torch.randn(5, 4)).sum().backward()
+    d.synchronize()
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        d.step()
+    assert any("skip_synchronize" in str(x.message) for x in w)
+
+
+def test_distributed_optimizer_accumulation_and_validation():
+    from grace_b200.parallel import DistributedOptimizer
+
+    model, d, fake = _wrapped(passes=2)
+    model(torch.randn(5, 4)).sum().backward()
+    assert fake.sent == []  # first pass only accumulates
+    model(torch.randn(5, 4)).sum().backward()
+    assert len(fake.sent) == 4
+    d.step()
+    d.set_backward_passes_per_step(1)
+    d.zero_grad()
+    model(torch.randn(5, 4)).sum().backward()
+    assert len(fake.sent) == 8
+    d.load_state_dict(d.state_dict())  # resets in-flight handles
+    d.zero_grad()
+    _, d2, fake2 = _wrapped(named=False)
+    assert sorted(d2._parameter_names.values())[0].startswith("allreduce.noname.")
+    m = torch.nn.Linear(2, 2)
+    o = torch.optim.SGD(m.parameters(), lr=0.1)
+    with pytest.raises(ValueError):
+        DistributedOptimizer(o, grace=fake, named_parameters=[("a", m.weight), ("a", m.bias)])
+    with pytest.raises(ValueError):
+        DistributedOptimizer(o, grace=fake, named_parameters=[("a", m.weight)])
+    with pytest.raises(ValueError):
+        DistributedOptimizer(o, grace=fake, named_parameters=["a", "b"])
+
+
+def test_missing_hooks_are_launched_at_synchronize():
+    model, d, fake = _wrapped()
+    model[0](torch.randn(5, 4)).sum().backward()  # second layer never gets a gradient hook call
+    d.step()
+    assert len(fake.sent) == 4

@@ -1,0 +1,197 @@
+"""GPU tests of the fused sparse exchange (TopK / DGC / Threshold) against plain
+PyTorch fp32 restatements of the same operations."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 31, 32, 33, 127, 128, 129, 2047, 2048, 2049, 6143, 6144, 6145, 100_003, (1 << 20) + 1]
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _rand(n, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(n, generator=g) * 1e-3).to(_dev())
+
+
+def _dense_topk(x, k):
+    _, idx = torch.topk(x.abs(), k, sorted=False)
+    out = torch.zeros_like(x)
+    out[idx] = x[idx]
+    return out
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_topk_select_matches_torch(n):
+    from grace_b200.ops.sparse import topk_select
+
+    x = _rand(n, seed=n)
+    for ratio in (0.001, 0.01, 0.3, 1.0):
+        k = max(1, int(n * ratio))
+        vals, idx = topk_select(x, k)
+        assert vals.numel() == k and idx.numel() == k
+        idx = idx.long()
+        assert idx.unique().numel() == k, "indices must be distinct"
+        assert torch.equal(vals, x[idx])
+        ref_vals, _ = torch.topk(x.abs(), k)
+        got = vals.abs().sort(descending=True).values
+        assert torch.equal(got, ref_vals), "selected magnitudes must be exactly the k largest"
+
+
+def test_topk_select_ties_and_zeros():
+    from grace_b200.ops.sparse import topk_select
+
+    x = torch.zeros(5000, device=_dev())
+    vals, idx = topk_select(x, 50)
+    assert idx.long().unique().numel() == 50 and torch.all(vals == 0)
+    x = torch.full((5000,), 0.25, device=_dev())
+    x[::7] = -0.25
+    vals, idx = topk_select(x, 123)
+    assert idx.long().unique().numel() == 123 and torch.all(vals.abs() == 0.25)
+    x = torch.zeros(4096, device=_dev())
+    x[[5, 77, 4095]] = torch.tensor([3.0, -4.0, 1.0], device=_dev())
+    vals, idx = topk_select(x, 2)
+    assert sorted(idx.tolist()) == [5, 77]
+
+
+def test_topk_select_approximate_mode():
+    from grace_b200.ops.sparse import topk_select
+
+    x = _rand(300_000, 5)
+    k = 3000
+    vals, idx = topk_select(x, k, exact=False)
+    assert idx.long().unique().numel() == k
+    kth = torch.topk(x.abs(), k).values[-1]
+    assert vals.abs().min() >= kth * (1 - 2.0 ** -14)
+
+
+def _world(W, params):
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.fused import VirtualWorld
+
+    def make(rank):
+        p = dict(params)
+        p.update(world_size=W, fused=True)
+        return grace_from_params(p)
+
+    return VirtualWorld(W, make, _dev())
+
+
+@pytest.mark.parametrize("W", [1, 2, 4])
+@pytest.mark.parametrize("n", [1000, 70_001])
+def test_topk_residual_exchange_matches_reference_semantics(W, n):
+    ratio = 0.01
+    k = max(1, int(n * ratio))
+    vw = _world(W, {"compressor": "topk", "memory": "residual", "communicator": "allgather", "compress_ratio": ratio})
+    residual = [torch.zeros(n, device=_dev()) for _ in range(W)]
+    for step in range(3):
+        grads = [_rand(n, seed=100 * step + r) for r in range(W)]
+        outs = vw.step(grads, "w")
+        vw.check()
+        expect = torch.zeros(n, device=_dev())
+        for r in range(W):
+            acc = residual[r] + grads[r]
+            sel = _dense_topk(acc, k)
+            residual[r] = acc - sel
+            expect += sel
+        expect /= W
+        for r in range(W):
+            torch.testing.assert_close(outs[r], expect, rtol=1e-6, atol=1e-9)
+            plan = next(iter(vw.comms[r]._plans.values()))
+            torch.testing.assert_close(plan.acc[:n], residual[r], rtol=0, atol=0)
+    # every rank produced bit-identical output
+    for r in range(1, W):
+        assert torch.equal(outs[0], outs[r])
+
+
+def test_dgc_momentum_correction_exchange():
+    W, n, ratio, m = 2, 50_000, 0.01, 0.9
+    k = max(1, int(n * ratio))
+    vw = _world(W, {"compressor": "dgc", "memory": "dgc", "communicator": "allgather", "compress_ratio": ratio,
+                    "momentum": m})
+    u = [torch.zeros(n, device=_dev()) for _ in range(W)]
+    v = [torch.zeros(n, device=_dev()) for _ in range(W)]
+    for step in range(3):
+        grads = [_rand(n, seed=7 * step + r) for r in range(W)]
+        outs = vw.step(grads, "w")
+        vw.check()
+        expect = torch.zeros(n, device=_dev())
+        for r in range(W):
+            u[r] = m * u[r] + grads[r]
+            v[r] = v[r] + u[r]
+            sel = _dense_topk(v[r], k)
+            keep = sel == 0
+            expect += sel
+            u[r] = u[r] * keep
+            v[r] = v[r] * keep
+        expect /= W
+        torch.testing.assert_close(outs[0], expect, rtol=1e-6, atol=1e-9)
+        plan = next(iter(vw.comms[0]._plans.values()))
+        torch.testing.assert_close(plan.acc[:n], v[0], rtol=1e-6, atol=1e-9)
+        torch.testing.assert_close(plan.u[:n], u[0], rtol=1e-6, atol=1e-9)
+
+
+def test_threshold_exchange():
+    W, n, thr = 2, 40_000, 2e-3
+    vw = _world(W, {"compressor": "threshold", "memory": "residual", "communicator": "allgather", "threshold": thr})
+    grads = [_rand(n, seed=r + 1) for r in range(W)]
+    outs = vw.step(grads, "w")
+    vw.check()
+    expect = torch.zeros(n, device=_dev())
+    for r in range(W):
+        t = min(thr, grads[r].max().item())
+        expect += torch.where(grads[r].abs() >= t, grads[r], torch.zeros_like(grads[r]))
+    torch.testing.assert_close(outs[0], expect / W, rtol=1e-6, atol=1e-9)
+
+
+def test_flat_multi_segment_topk():
+    from grace_b200.ops.exchange import FlatLayout
+
+    W, ratio = 2, 0.05
+    numels = [64, 300, 5000, 1, 128, 77_777]
+    layout = FlatLayout.from_named([("p%d" % i, n) for i, n in enumerate(numels)])
+    vw = _world(W, {"compressor": "topk", "memory": "residual", "communicator": "allgather", "compress_ratio": ratio})
+    flats = []
+    for r in range(W):
+        f = torch.zeros(layout.total, device=_dev())
+        for i, (o, n) in enumerate(zip(layout.offsets, layout.numels)):
+            f[o:o + n] = _rand(n, seed=10 * r + i)
+        flats.append(f)
+    ref_in = [f.clone() for f in flats]
+    outs = vw.step_flat(flats, layout)
+    vw.check()
+    expect = torch.zeros(layout.total, device=_dev())
+    for r in range(W):
+        for o, n in zip(layout.offsets, layout.numels):
+            k = max(1, int(n * ratio))
+            expect[o:o + n] += _dense_topk(ref_in[r][o:o + n], k)
+    torch.testing.assert_close(outs[0], expect / W, rtol=1e-6, atol=1e-9)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """A peer that never publishes: the exchange phase must give up after the
+    configured limit, leave an error status and keep the context usable."""
+    from grace_b200.ops.exchange import GraceCommError, PHASE_COMPRESS, PHASE_EXCHANGE, PHASE_PUBLISH
+
+    W, n = 2, 4096
+    vw = _world(W, {"compressor": "topk", "memory": "none", "communicator": "allgather", "compress_ratio": 0.01,
+                    "timeout_ms": 50})
+    from grace_b200.ops.exchange import FlatLayout
+
+    layout = FlatLayout.single("w", n)
+    g = [_rand(n, r) for r in range(W)]
+    c0 = vw.comms[0]
+    plan0 = c0._plan(layout)
+    vw.comms[1]._plan(layout)
+    # rank 0 compresses and publishes, rank 1 never does; rank 0 then waits for rank 1
+    seq = c0._launch(plan0, g[0], g[0].clone(), PHASE_COMPRESS | PHASE_PUBLISH)
+    c0._launch(plan0, g[0], g[0].clone(), PHASE_EXCHANGE, seq=seq)
+    with pytest.raises(GraceCommError) as err:
+        c0.check()
+    assert err.value.code == 2 and err.value.detail == 1
+    # the context is still alive
+    assert torch.ones(4, device=_dev()).sum().item() == 4
