@@ -12,7 +12,8 @@ only).  With ``e`` the biased exponent and ``eb = 127 + int(log10(bound/2))``,
 A fixed point code is the sign bit followed by the top bits of
 ``|x| * 2**(width-1)`` (|x| < 1), i.e. the significand shifted right by
 ``127 - e`` with its hidden one made explicit.  The class of every element is
-packed four per byte.  Payload: ``(fp32[], int16[], uint8[], uint8 classes)``.
+packed four per byte.  Payload: ``(fp32[], 16-bit codes as byte pairs, uint8[],
+uint8 classes)`` (byte tensors travel on every backend).
 """
 import math
 
@@ -64,7 +65,7 @@ class INCEPTIONNCompressor(Compressor):
         cls = torch.where((e >= self.exp_mid) & (e < 127), torch.full_like(e, 2), cls)
         cls = torch.where(e >= 127, torch.full_like(e, 3), cls)
         v32 = flat[cls == 3]
-        v16 = self._fixed(flat[cls == 2], 16).to(torch.int16)
+        v16 = self._fixed(flat[cls == 2], 16).to(torch.int16).view(torch.uint8)  # two bytes per code
         v8 = self._fixed(flat[cls == 1], 8).to(torch.uint8)
         return (v32, v16, v8, pack2(cls)), tensor.shape
 
@@ -74,6 +75,6 @@ class INCEPTIONNCompressor(Compressor):
         cls = unpack2(packed, numel)
         out = torch.zeros(numel, dtype=torch.float32, device=packed.device)
         out[cls == 3] = v32
-        out[cls == 2] = self._unfixed(v16, 16)
+        out[cls == 2] = self._unfixed(v16.contiguous().view(torch.int16), 16)
         out[cls == 1] = self._unfixed(v8, 8)
         return out.view(ctx)
