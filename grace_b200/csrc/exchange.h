@@ -128,6 +128,53 @@ size_t quant_slot_bytes(int codec, long long total, int nseg);
 int quant_max_grid(int device, int sm_limit);
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
 
+// -------------------------------------------------------------- low rank ----
+// One matrix (n x m, row-major) of a PowerSGD launch.  All offsets in floats.
+struct LowRankMatrix {
+  long long g_off;   // start of the matrix in the flat gradient / accumulator buffers
+  int n, m;
+  int p_off;         // row-major [n][16] block inside the P regions
+  int q_off;         // row-major [m][16] block inside the Q regions
+  int pt_off;        // [16][n] block inside pt_orth
+  int qt_off;        // [16][m] block inside qt
+  int item1_begin;   // first stage-1 work item (prefix sum over matrices)
+  int item2_begin;   // first stage-2 work item
+};
+
+enum LowRankMap : int { kMapG1 = 0, kMapA1 = 1, kMapM2 = 2, kMapQt = 3, kMapPt = 4, kMapsPerMatrix = 5 };
+
+struct CUtensorMap_st;
+
+struct LowRankArgs {
+  const float* g;          // flat gradients
+  float* acc;              // flat accumulator / residual (used when has_memory)
+  float* out;              // flat output (may alias g)
+  const LowRankMatrix* mats;
+  const CUtensorMap_st* maps;  // nmat * kMapsPerMatrix tensor maps in device memory (64-byte aligned)
+  int nmat;
+  int rank;                // actual rank r <= 8 (buffers are padded to 16 columns)
+  int has_memory;
+  int divisor;             // world size (P and Q are averaged)
+  int items_s1, items_s2;
+  int p_floats, q_floats;  // sizes of the P and Q regions (multiples of 4)
+  float* p_mean;           // [p_floats]
+  float* q_mean;           // [q_floats]
+  float* pt_orth;          // sum_n 16*n
+  float* qt;               // sum_m 16*m: Q^T, persistent across steps (warm start)
+  double* gram;            // nmat * 256
+  unsigned* barrier;
+  unsigned* status;
+  unsigned long long ready2_off;  // second flag pad (Q); peers.ready_off is the first (P)
+  int phases;
+  int part;                // 0 = whole exchange; 1, 2, 3 = that part only (one-GPU emulation)
+  PeerTable peers;
+};
+
+size_t lowrank_smem_bytes();
+int lowrank_max_grid(int device, int sm_limit);
+cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream);
+int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m);
+
 // ------------------------------------------------------------------- sgd ----
 struct SgdTensor {
   float* p;
