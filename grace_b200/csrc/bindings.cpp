@@ -115,6 +115,37 @@ PYBIND11_MODULE(_C, m) {
           check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
         });
 
+  // ---- fused PowerSGD (tcgen05) ----
+  m.def("lowrank_smem_bytes", &lowrank_smem_bytes);
+  m.def("lowrank_max_grid", &lowrank_max_grid);
+  m.attr("LOWRANK_MATRIX_BYTES") = sizeof(LowRankMatrix);
+  m.attr("TENSOR_MAP_BYTES") = 128;
+  m.attr("MAPS_PER_MATRIX") = (int)kMapsPerMatrix;
+  m.def("lowrank_encode_maps", [](uintptr_t host_out, uintptr_t g, uintptr_t acc, uintptr_t qt, uintptr_t pt, int n, int mm) {
+    const int rc = lowrank_encode_maps(ptr<void>(host_out), ptr<const float>(g), ptr<float>(acc), ptr<const float>(qt),
+                                       ptr<const float>(pt), n, mm);
+    if (rc != 0) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(rc));
+  });
+  m.def("powersgd_exchange",
+        [](uintptr_t g, uintptr_t acc, uintptr_t out, uintptr_t mats, uintptr_t maps, int nmat, int rank_r,
+           int has_memory, int divisor, int items_s1, int items_s2, int p_floats, int q_floats, uintptr_t p_mean,
+           uintptr_t q_mean, uintptr_t pt_orth, uintptr_t qt, uintptr_t gram, uintptr_t barrier, uintptr_t status,
+           unsigned long long ready2_off, int part, int rank, int world, unsigned long long seq,
+           unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
+           unsigned long long ack_off, unsigned long long slot_off, int grid, uintptr_t stream) {
+          LowRankArgs a{};
+          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.out = ptr<float>(out);
+          a.mats = ptr<const LowRankMatrix>(mats); a.maps = ptr<const CUtensorMap_st>(maps); a.nmat = nmat;
+          a.rank = rank_r; a.has_memory = has_memory; a.divisor = divisor; a.items_s1 = items_s1; a.items_s2 = items_s2;
+          a.p_floats = p_floats; a.q_floats = q_floats; a.p_mean = ptr<float>(p_mean); a.q_mean = ptr<float>(q_mean);
+          a.pt_orth = ptr<float>(pt_orth); a.qt = ptr<float>(qt); a.gram = ptr<double>(gram);
+          a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status); a.ready2_off = ready2_off;
+          a.phases = kPhaseAll; a.part = part;
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
+          if (rank_r < 1 || rank_r > 8 || nmat < 1) throw std::invalid_argument("rank must be in [1,8], nmat >= 1");
+          check(launch_powersgd(a, grid, reinterpret_cast<cudaStream_t>(stream)), "powersgd_exchange");
+        });
+
   // ---- fused SGD ----
   m.def("fused_sgd", [](uintptr_t p, uintptr_t g, uintptr_t buf, long long numel, float lr, float momentum,
                         float dampening, float weight_decay, int nesterov, int first_step, int zero_grad,

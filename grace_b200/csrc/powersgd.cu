@@ -295,12 +295,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
     }
   }
   __syncthreads();
-  step_counter = __shfl_sync(0xffffffffu, tid == 0 ? p_step : 0u, 0);
-  // all threads need the same counter: broadcast through shared memory
-  __shared__ unsigned s_steps;
-  if (tid == 0) s_steps = p_step;
-  __syncthreads();
-  step_counter = s_steps;
+  step_counter = c_step;  // uniform: every thread consumed the same steps
 }
 
 // Mean over ranks of a [rows x 16] region; optional Gram matrix per matrix.
@@ -318,17 +313,18 @@ __device__ void reduce_region(const LowRankArgs& a, size_t region_off, float* __
   }
 }
 
-__device__ bool publish_and_wait(const LowRankArgs& a, const Status& status, unsigned long long ready_off) {
+__device__ bool publish_and_wait(const LowRankArgs& a, const Status& status, unsigned long long ready_off,
+                                 bool do_publish, bool do_wait) {
   // called by all threads of all CTAs after a grid barrier
   __shared__ int s_ok;
   const int tid = threadIdx.x, rank = a.peers.rank, world = a.peers.world;
   if (tid == 0) s_ok = 1;
   __syncthreads();
-  if (blockIdx.x == 0 && tid < world && (a.phases & kPhasePublish) && !status.failed()) {
+  if (blockIdx.x == 0 && tid < world && do_publish && !status.failed()) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint64_t*>(a.peers.heap[tid] + ready_off) + rank, a.peers.seq);
   }
-  if (a.phases & kPhaseExchange) {
+  if (do_wait) {
     if (tid < world) {
       const uint64_t* flag = reinterpret_cast<const uint64_t*>(a.peers.heap[rank] + ready_off) + tid;
       if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid)) s_ok = 0;
@@ -397,9 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
 
   if (part1 || part2) {
     // publish P (part 1) / wait for the peers' P (part 2)
-    LowRankArgs b = a;
-    b.phases = (part1 ? kPhasePublish : 0) | (part2 ? kPhaseExchange : 0);
-    ok = publish_and_wait(b, status, a.peers.ready_off) && ok && !status.failed();
+    ok = publish_and_wait(a, status, a.peers.ready_off, part1, part2) && ok && !status.failed();
   }
 
   if (part2) {
@@ -483,9 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   }
 
   if (part2 || part3) {
-    LowRankArgs b = a;
-    b.phases = (part2 ? kPhasePublish : 0) | (part3 ? kPhaseExchange : 0);
-    ok = publish_and_wait(b, status, a.ready2_off) && ok && !status.failed();
+    ok = publish_and_wait(a, status, a.ready2_off, part2, part3) && ok && !status.failed();
   }
 
   if (part3) {
@@ -600,13 +592,27 @@ cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream)
 //   Qt : Q^T [16][m], box 32 x 16;  Pt : P^T [16][n], box 32 x 16
 int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m) {
   CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_out);
-  auto enc = [](CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+  // The driver entry point is looked up at run time so that the extension does
+  // not link against libcuda (it must import on machines without a driver).
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode_fn = nullptr;
+  if (!encode_fn) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+      return -1;
+    encode_fn = reinterpret_cast<EncodeFn>(fn);
+  }
+  EncodeFn cuTensorMapEncodeTiled_rt = encode_fn;
+  auto enc = [cuTensorMapEncodeTiled_rt](CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
                 uint32_t box_outer) -> CUresult {
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {inner * 4};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    return cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
+    return cuTensorMapEncodeTiled_rt(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };

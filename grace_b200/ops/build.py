@@ -84,7 +84,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
     tmp = BUILD / ("_C.tmp" + EXT_SUFFIX)
-    cmd = [_nvcc(), "-shared", "-cudart", "shared", *ARCH_FLAGS, "-o", str(tmp), *map(str, objs), "-lcuda"]
+    cmd = [_nvcc(), "-shared", "-cudart", "shared", *ARCH_FLAGS, "-o", str(tmp), *map(str, objs)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (res.stdout, res.stderr))
