@@ -157,7 +157,7 @@ def build_ours(cfg, device, world):
     params = dict(cfg["grace"])
     params.update(world_size=world, fused=True)
     grc = grace_b200.grace_from_params(params)
-    fused_flat = getattr(grc, "_kind", None) in ("sparse", "quant")
+    fused_flat = getattr(grc, "_kind", None) in ("sparse", "quant", "powersgd")
     if fused_flat:
         flat = FlatParams(named, bucket_bytes=cfg.get("bucket_bytes"))
         opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, flat=flat)

@@ -137,6 +137,8 @@ class FusedExchange(Communicator):
                 self._kind = None
 
     def supported(self, tensor: torch.Tensor) -> bool:
+        if self._kind == "powersgd":
+            return tensor.is_cuda and int(getattr(self.compressor, "rank", 1)) <= 8
         return self._kind in ("sparse", "quant") and tensor.is_cuda
 
     # ------------------------------------------------------------------
@@ -151,7 +153,18 @@ class FusedExchange(Communicator):
         key = layout.key()
         plan = self._plans.get(key)
         if plan is None:
-            plan = _Plan(self, layout, self._kind)
+            if self._kind == "powersgd":
+                from ..ops.lowrank import LowRankPlan
+
+                plan = LowRankPlan(self._make_heap, layout, layout.shape_list(), int(self.compressor.rank),
+                                   self.world_size, isinstance(self.memory, M_.PowerSGDMemory), self.device,
+                                   seed=self.seed, timeout_ms=self.timeout_ms, sm_limit=self.comm_sms)
+                plan.kind = "powersgd"
+                pending = getattr(self, "_pending_state", None)
+                if pending:
+                    self._restore_plan(plan, pending)
+            else:
+                plan = _Plan(self, layout, self._kind)
             self._plans[key] = plan
         return plan
 
@@ -195,7 +208,13 @@ class FusedExchange(Communicator):
             self.device = flat.device
         plan = self._plan(layout)
         out = flat if out is None else out
-        self._launch(plan, flat, out, PHASE_ALL)
+        if plan.kind == "powersgd":
+            if plan.matrices:
+                plan.channel.poll()
+                plan.launch(flat, out)
+            plan.launch_dense(flat, out)
+        else:
+            self._launch(plan, flat, out, PHASE_ALL)
         plan.steps += 1
         self._stats["steps"] += 1
         return out
@@ -214,7 +233,7 @@ class FusedExchange(Communicator):
         flat = self._prepare(tensor)
         same = flat.data_ptr() == tensor.data_ptr()
         out = flat if (self.inplace and same) else torch.empty_like(flat)
-        self.step_flat(flat, FlatLayout.single(name, flat.numel()), out)
+        self.step_flat(flat, FlatLayout.single(name, flat.numel(), tensor.shape), out)
         return out.view(tensor.shape).to(tensor.dtype)
 
     # split-phase: launch on the caller's current stream, hand back an event
@@ -239,15 +258,26 @@ class FusedExchange(Communicator):
     def check(self):
         """Block until every launched exchange finished; raise on failure."""
         for plan in self._plans.values():
-            plan.channel.check()
+            if plan.kind == "powersgd":
+                plan.check()
+            else:
+                plan.channel.check()
 
     # ------------------------------------------------------------------
     def state_dict(self):
         if not self._plans:
             return self._fallback.state_dict()
         residuals, gradients, momentums = {}, {}, {}
+        q_memory = {}
         for plan in self._plans.values():
             lay = plan.layout
+            if plan.kind == "powersgd":
+                if plan.acc is not None:
+                    for n, t in lay.slices(plan.acc).items():
+                        residuals[n] = t.clone()
+                if plan.matrices:
+                    q_memory.update(plan.q_memory())
+                continue
             if plan.acc is not None:
                 target = gradients if plan.u is not None else residuals
                 for n, t in lay.slices(plan.acc).items():
@@ -264,6 +294,8 @@ class FusedExchange(Communicator):
         comp = self.compressor.state_dict()
         if momentums:
             comp["momentums"] = momentums
+        if q_memory:
+            comp["q_memory"] = q_memory
         steps = {"|".join(map(str, k[1])) + ":" + "|".join(k[0][:2]): p.steps for k, p in self._plans.items()}
         return {"compressor": comp, "memory": mem, "world_size": self.world_size, "fused_steps": steps}
 
@@ -276,6 +308,14 @@ class FusedExchange(Communicator):
     def _restore_plan(self, plan: _Plan, state):
         mem = state.get("memory", {})
         lay = plan.layout
+        if plan.kind == "powersgd":
+            if plan.acc is not None:
+                for n, t in lay.slices(plan.acc).items():
+                    if n in mem.get("residuals", {}):
+                        t.copy_(mem["residuals"][n].reshape(-1))
+            if plan.matrices:
+                plan.load_q_memory(state.get("compressor", {}).get("q_memory", {}))
+            return
         src_acc = mem.get("gradients" if plan.u is not None else "residuals", {})
         if plan.acc is not None:
             for n, t in lay.slices(plan.acc).items():
@@ -308,6 +348,8 @@ class VirtualWorld:
     def __init__(self, world: int, make_comm, device=None):
         self.world = world
         self.device = torch.device(device if device is not None else "cuda")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self._heaps = {}
         self.comms: List[FusedExchange] = []
         for r in range(world):
@@ -329,6 +371,19 @@ class VirtualWorld:
 
         outs = list(outs) if outs is not None else list(flats)
         plans = [c._plan(layout) for c in self.comms]
+        if plans[0].kind == "powersgd":
+            if plans[0].matrices:
+                seqs = [p.launch(g, o, part=1) for p, g, o in zip(plans, flats, outs)]
+                for part in (2, 3):
+                    for p, g, o, s in zip(plans, flats, outs, seqs):
+                        p.launch(g, o, part=part, seq=s)
+            if plans[0].dense:
+                seqs = [p.launch_dense(g, o, PHASE_COMPRESS | PHASE_PUBLISH) for p, g, o in zip(plans, flats, outs)]
+                for p, g, o, s in zip(plans, flats, outs, seqs):
+                    p.launch_dense(g, o, PHASE_EXCHANGE, seq=s)
+            for p in plans:
+                p.steps += 1
+            return outs
         seqs = []
         for c, p, g, o in zip(self.comms, plans, flats, outs):
             seqs.append(c._launch(p, g, o, PHASE_COMPRESS | PHASE_PUBLISH))
@@ -342,7 +397,7 @@ class VirtualWorld:
 
         flats = [c._prepare(t) for c, t in zip(self.comms, tensors)]
         outs = [torch.empty_like(f) for f in flats]
-        self.step_flat(flats, FlatLayout.single(name, flats[0].numel()), outs)
+        self.step_flat(flats, FlatLayout.single(name, flats[0].numel(), tensors[0].shape), outs)
         return [o.view(t.shape) for o, t in zip(outs, tensors)]
 
     def check(self):

@@ -16,8 +16,11 @@
 //   O   orthogonalise P: Cholesky factor of the Gram matrix in fp64, P R^-1
 //       (what modified Gram-Schmidt computes in exact arithmetic), written
 //       transposed for the next stage;
-//   S2  Q = M'^T * P: A = M' tile as an MN-major operand (4 boxes of 32 columns
-//       x 32 rows), B = P^T tile [16 x 32] K-major, D [128 x 16] in TMEM;
+//   S2  Q = M'^T * P: TMA brings 32 rows x 128 columns of M' (four unswizzled
+//       boxes); the CTA transposes them in shared memory into a K-major
+//       128B-swizzled A tile [128 x 32] (the TF32 MMA returns zeros for an
+//       MN-major A operand on this part, so the transpose is done by hand),
+//       B = P^T tile [16 x 32] K-major, D [128 x 16] in TMEM;
 //   R2  publish; wait; Q = mean over ranks; kept as next step's warm start;
 //   S3  out = P Q^T (rank-r outer products on CUDA cores), R = M' - out.
 //
@@ -50,11 +53,10 @@ constexpr unsigned kTmemCols = 32;
 // [4,6), a_format [7,10), b_format [10,13), a_major 15, b_major 16, N>>3
 // [17,23), M>>4 [24,29))
 constexpr uint32_t kIdescS1 = (1u << 4) | (2u << 7) | (2u << 10) | ((kRankPad >> 3) << 17) | ((kTileRows >> 4) << 24);
-constexpr uint32_t kIdescS2 = kIdescS1 | (1u << 15);  // A is MN-major
 
 struct __align__(1024) SmemLayout {
   unsigned char a[kStages][kATileBytes];   // gradient tile, becomes the A operand
-  unsigned char r[kStages][kATileBytes];   // residual tile (stage 1 only)
+  unsigned char r[kStages][kATileBytes];   // stage 1: residual tile; stage 2: unswizzled M' boxes before the transpose
   unsigned char b[kStages][kBTileBytes];   // Q^T / P^T tile
   unsigned long long full[kStages];
   unsigned long long mma_done[kStages];
@@ -193,8 +195,8 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       tma_load_2d(sm.b[slot], maps + kMapQt, p_kt * kTileK, 0, &sm.full[slot]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)  // four boxes of 32 columns x 32 rows: the MN-major A operand
-        tma_load_2d(sm.a[slot] + j * 4096, maps + kMapM2, pit.blk * kTileRows + j * 32, p_kt * kTileK, &sm.full[slot]);
+      for (int j = 0; j < 4; ++j)  // four unswizzled boxes of 32 columns x 32 rows of M'
+        tma_load_2d(sm.r[slot] + j * 4096, maps + kMapM2, pit.blk * kTileRows + j * 32, p_kt * kTileK, &sm.full[slot]);
       tma_load_2d(sm.b[slot], maps + kMapPt, p_kt * kTileK, 0, &sm.full[slot]);
     }
     (void)M;
@@ -226,6 +228,25 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       }
       fence_async_smem();  // generic-proxy writes -> visible to the TMA store and the MMA
     }
+    if (STAGE == 2 && ok) {
+      // transpose: staging[j][k][mi] (k = row of M', 32 per tile; m = 32*j + mi) -> A[m][k], K-major with the
+      // 128-byte swizzle (16-byte chunk index XOR row % 8).  One 4 x 4 block per thread.
+      const int kq = tid & 7, mq = tid >> 3;          // k / 4 and m / 4
+      const int j = mq >> 3, mi4 = (mq & 7) * 4;
+      const unsigned char* st = sm.r[slot] + j * 4096 + mi4 * 4;
+      float4 rowv[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) rowv[kk] = *reinterpret_cast<const float4*>(st + (kq * 4 + kk) * 128);
+      const float t[4][4] = {{rowv[0].x, rowv[1].x, rowv[2].x, rowv[3].x}, {rowv[0].y, rowv[1].y, rowv[2].y, rowv[3].y},
+                             {rowv[0].z, rowv[1].z, rowv[2].z, rowv[3].z}, {rowv[0].w, rowv[1].w, rowv[2].w, rowv[3].w}};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int mrow = mq * 4 + e;
+        *reinterpret_cast<float4*>(sm.a[slot] + mrow * 128 + ((kq ^ (mrow & 7)) << 4)) =
+            make_float4(t[e][0], t[e][1], t[e][2], t[e][3]);
+      }
+      fence_async_smem();
+    }
     if (!ok) sm.bail = 1;
     __syncthreads();
     if (sm.bail) break;
@@ -240,11 +261,9 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       const uint32_t a_addr = smem_u32(sm.a[slot]), b_addr = smem_u32(sm.b[slot]);
 #pragma unroll
       for (int kk = 0; kk < kTileK / 8; ++kk) {
-        uint64_t adesc, bdesc;
-        if (STAGE == 1) adesc = smem_desc(a_addr + kk * 32, 16, 1024);        // K-major: 32 B per K step
-        else adesc = smem_desc(a_addr + kk * 1024, 4096, 1024);                // MN-major: 8 rows per K step
-        bdesc = smem_desc(b_addr + kk * 32, 16, 1024);
-        umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdescS1 : kIdescS2, !(c_kt == cit.kt0 && kk == 0));
+        const uint64_t adesc = smem_desc(a_addr + kk * 32, 16, 1024);   // K-major: 32 B per K step of 8
+        const uint64_t bdesc = smem_desc(b_addr + kk * 32, 16, 1024);
+        umma_tf32(tmem_d, adesc, bdesc, kIdescS1, !(c_kt == cit.kt0 && kk == 0));
       }
       umma_commit(&sm.mma_done[slot]);
       if (last_kt) umma_commit(&sm.item_done);
@@ -588,7 +607,7 @@ cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream)
 // Host: encode the five tensor maps of one matrix.
 //   G1 : gradient, box 32 x 128 (stage-1 A operand)
 //   A1 : accumulator, box 32 x 128 (residual load, M' store)
-//   M2 : M' (accumulator, or gradient without memory), box 32 x 32 (stage-2 A operand)
+//   M2 : M' (accumulator, or gradient without memory), box 32 x 32, not swizzled (transposed by the CTA in stage 2)
 //   Qt : Q^T [16][m], box 32 x 16;  Pt : P^T [16][n], box 32 x 16
 int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m) {
   CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_out);
@@ -607,19 +626,19 @@ int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float*
   }
   EncodeFn cuTensorMapEncodeTiled_rt = encode_fn;
   auto enc = [cuTensorMapEncodeTiled_rt](CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                uint32_t box_outer) -> CUresult {
+                uint32_t box_outer, bool swizzle = true) -> CUresult {
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {inner * 4};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     return cuTensorMapEncodeTiled_rt(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
-                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
   CUresult r;
   if ((r = enc(maps + kMapG1, g, m, n, 32, 128)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapA1, acc ? acc : g, m, n, 32, 128)) != CUDA_SUCCESS) return (int)r;
-  if ((r = enc(maps + kMapM2, acc ? acc : g, m, n, 32, 32)) != CUDA_SUCCESS) return (int)r;
+  if ((r = enc(maps + kMapM2, acc ? acc : g, m, n, 32, 32, false)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapQt, qt, m, kRankPad, 32, 16)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapPt, pt, n, kRankPad, 32, 16)) != CUDA_SUCCESS) return (int)r;
   return 0;

@@ -55,6 +55,7 @@ class FlatLayout:
     numels: List[int]
     offsets: List[int] = field(default_factory=list)
     total: int = 0
+    shapes: Optional[List[Tuple[int, ...]]] = None   # original tensor shapes (PowerSGD needs rows x cols)
 
     def __post_init__(self):
         if not self.offsets:
@@ -69,8 +70,10 @@ class FlatLayout:
             raise ValueError("flat buffers are indexed with 31 bits; split the bucket (%d elements)" % self.total)
 
     @classmethod
-    def single(cls, name: str, numel: int) -> "FlatLayout":
-        return cls([name], [numel])
+    def single(cls, name: str, numel: int, shape=None) -> "FlatLayout":
+        lay = cls([name], [numel])
+        lay.shapes = [tuple(shape)] if shape is not None else None
+        return lay
 
     @classmethod
     def from_named(cls, named: Sequence[Tuple[str, int]]) -> "FlatLayout":
@@ -78,6 +81,9 @@ class FlatLayout:
 
     def key(self) -> Tuple:
         return (tuple(self.names), tuple(self.numels))
+
+    def shape_list(self):
+        return self.shapes if self.shapes is not None else [(n,) for n in self.numels]
 
     def segment_bytes(self, ks: Optional[Sequence[int]] = None) -> bytes:
         ks = ks if ks is not None else [0] * len(self.names)

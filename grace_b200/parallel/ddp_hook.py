@@ -45,8 +45,9 @@ class GraceDDPHook:
             offsets.append(off)
             aligned = aligned and off % ALIGN_ELEMS == 0
         total = (bucket.buffer().numel() + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
-        info = dict(names=names, numels=numels, offsets=offsets, aligned=aligned,
-                    layout=FlatLayout(names, numels, offsets, total) if aligned else FlatLayout(names, numels))
+        layout = FlatLayout(names, numels, offsets, total) if aligned else FlatLayout(names, numels)
+        layout.shapes = [tuple(p.shape) for p in params]
+        info = dict(names=names, numels=numels, offsets=offsets, aligned=aligned, layout=layout)
         self._layouts[idx] = info
         return info
 
@@ -54,7 +55,7 @@ class GraceDDPHook:
         buf = bucket.buffer()
         fut: torch.futures.Future = torch.futures.Future()
         fused = hasattr(self.grc, "step_flat") and buf.is_cuda and buf.dtype == torch.float32 \
-            and getattr(self.grc, "_kind", None) in ("sparse", "quant")
+            and getattr(self.grc, "_kind", None) in ("sparse", "quant", "powersgd")
         if not fused:
             for p, g in zip(bucket.parameters(), bucket.gradients()):
                 name = self.names.get(id(p), "param")

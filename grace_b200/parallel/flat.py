@@ -31,10 +31,12 @@ def _dense_view(flat: torch.Tensor, offset: int, like: torch.Tensor) -> torch.Te
 class Bucket:
     """A contiguous range of the flat buffers with its own layout."""
 
-    def __init__(self, index: int, start: int, end: int, names: List[str], numels: List[int], offsets: List[int]):
+    def __init__(self, index: int, start: int, end: int, names: List[str], numels: List[int], offsets: List[int],
+                 shapes=None):
         self.index = index
         self.start, self.end = start, end
         self.layout = FlatLayout(names, numels, [o - start for o in offsets], end - start)
+        self.layout.shapes = shapes
         self.pending = 0
 
 
@@ -50,6 +52,7 @@ class FlatParams:
         self.names = [n for n, _ in named]
         self.params = [p for _, p in named]
         self.layout = FlatLayout.from_named([(n, p.numel()) for n, p in named])
+        self.layout.shapes = [tuple(p.shape) for _, p in named]
         self.flat_p = torch.zeros(self.layout.total, dtype=torch.float32, device=dev)
         self.flat_g = torch.zeros(self.layout.total, dtype=torch.float32, device=dev)
         with torch.no_grad():
@@ -67,7 +70,7 @@ class FlatParams:
     def _make_buckets(self, bucket_bytes: Optional[int]) -> List[Bucket]:
         lay = self.layout
         if not bucket_bytes:
-            return [Bucket(0, 0, lay.total, list(lay.names), list(lay.numels), list(lay.offsets))]
+            return [Bucket(0, 0, lay.total, list(lay.names), list(lay.numels), list(lay.offsets), list(lay.shapes))]
         limit = max(ALIGN_ELEMS, bucket_bytes // 4)
         buckets: List[Bucket] = []
         # gradients arrive roughly last parameter first: cut buckets from the end
@@ -78,7 +81,8 @@ class FlatParams:
             while j > 0 and (end - lay.offsets[j - 1] <= limit or j == idx):
                 j -= 1
             start = lay.offsets[j]
-            buckets.append(Bucket(len(buckets), start, end, lay.names[j:idx], lay.numels[j:idx], lay.offsets[j:idx]))
+            buckets.append(Bucket(len(buckets), start, end, lay.names[j:idx], lay.numels[j:idx], lay.offsets[j:idx],
+                                  lay.shapes[j:idx]))
             idx, end = j, start
         return buckets
 

@@ -1,0 +1,114 @@
+"""GPU tests of the fused PowerSGD exchange (tcgen05 / TMEM / TMA kernel) against a
+plain PyTorch fp32 restatement of the same algorithm started from the same Q."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _world(W, rank_r, memory="powersgd"):
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.fused import VirtualWorld
+
+    def make(rank):
+        return grace_from_params({"compressor": "powersgd", "memory": memory, "communicator": "allreduce",
+                                  "compress_rank": rank_r, "world_size": W, "fused": True, "timeout_ms": 3000})
+
+    return VirtualWorld(W, make, _dev())
+
+
+def _orth(p):
+    from grace_b200.compressor.powersgd import orthogonalize
+
+    p = p.clone().double()
+    orthogonalize(p)
+    return p.float()
+
+
+def _reference(mats, q0, W):
+    """mats: list over ranks of (n x m) matrices M'; returns out, P_orth, Q_mean."""
+    p = sum(m.double() @ q0.double() for m in mats) / W
+    p = _orth(p.float()).double()
+    q = sum(m.double().t() @ p for m in mats) / W
+    return (p @ q.t()).float(), p.float(), q.float()
+
+
+@pytest.mark.parametrize("n,m,r", [(256, 512, 4), (128, 32, 1), (100, 36, 2), (1024, 2080, 4), (4096, 1024, 8)])
+@pytest.mark.parametrize("W", [1, 2])
+def test_single_matrix_matches_reference(n, m, r, W):
+    vw = _world(W, r, memory="none")
+    gen = torch.Generator().manual_seed(n * 7 + m)
+    # low-rank signal + noise so that the projection is well conditioned
+    base = torch.randn(n, 6, generator=gen) @ torch.randn(6, m, generator=gen)
+    mats = [(base + 0.1 * torch.randn(n, m, generator=gen)).to(_dev()) for _ in range(W)]
+    outs = vw.step([x.clone() for x in mats], "w")
+    vw.check()
+    plan = next(iter(vw.comms[0]._plans.values()))
+    assert len(plan.matrices) == 1
+    q0 = None
+    # the kernel started from the plan's Q^T; recover what it was: re-create it
+    from grace_b200.ops.lowrank import orthogonal_init
+    import zlib
+
+    q0 = orthogonal_init(m, r, vw.comms[0].seed ^ zlib.crc32(b"w"), _dev())
+    ref, p_ref, q_ref = _reference(mats, q0, W)
+    err = ((outs[0] - ref).norm() / ref.norm()).item()
+    assert err < 5e-3, err   # TF32 operands
+    for k in range(1, W):
+        assert torch.equal(outs[0], outs[k])
+    # the warm-start Q kept by the plan is the averaged Q
+    q_kept = plan.q_memory()["w"]
+    assert ((q_kept - q_ref).norm() / q_ref.norm()).item() < 5e-3
+
+
+def test_error_feedback_identity_and_dense_side_channel():
+    from grace_b200.ops.exchange import FlatLayout
+
+    W, r = 2, 4
+    vw = _world(W, r)
+    shapes = [(64, 16, 3, 3), (64,), (256, 300), (10, 7), (512, 256)]
+    numels = [int(torch.tensor(s).prod()) for s in shapes]
+    layout = FlatLayout.from_named([("p%d" % i, n) for i, n in enumerate(numels)])
+    layout.shapes = shapes
+    prev = [torch.zeros(layout.total, device=_dev()) for _ in range(W)]
+    for step in range(3):
+        gen = torch.Generator().manual_seed(step)
+        flats = [(torch.randn(layout.total, generator=gen) * 0.1).to(_dev()) for _ in range(W)]
+        for f in flats:  # keep the padding gaps at zero like a real flat gradient buffer
+            mask = torch.zeros(layout.total, dtype=torch.bool, device=_dev())
+            for o, c in zip(layout.offsets, layout.numels):
+                mask[o:o + c] = True
+            f.mul_(mask)
+        grads = [f.clone() for f in flats]
+        outs = vw.step_flat(flats, layout)
+        vw.check()
+        plans = [next(iter(c._plans.values())) for c in vw.comms]
+        assert [m[0] for m in plans[0].matrices] == ["p0", "p2", "p4"]
+        for rk in range(W):
+            acc = plans[rk].acc
+            for name, off, n, m in plans[rk].matrices:
+                sl = slice(off, off + n * m)
+                # residual + transmitted approximation == gradient + previous residual
+                torch.testing.assert_close(acc[sl] + outs[rk][sl], grads[rk][sl] + prev[rk][sl], rtol=1e-5, atol=1e-6)
+            prev[rk] = acc.clone()
+        # 1-D and odd tensors: plain mean over ranks
+        for i in (1, 3):
+            o, c = layout.offsets[i], layout.numels[i]
+            torch.testing.assert_close(outs[0][o:o + c], sum(g[o:o + c] for g in grads) / W, rtol=1e-6, atol=1e-7)
+        assert torch.equal(outs[0], outs[1])
+
+
+def test_warm_start_converges_on_a_low_rank_matrix():
+    vw = _world(1, 4, memory="none")
+    gen = torch.Generator().manual_seed(3)
+    m = (torch.randn(512, 4, generator=gen) @ torch.randn(4, 768, generator=gen)).to(_dev())
+    err = []
+    for _ in range(3):
+        (out,) = vw.step([m.clone()], "w")
+        err.append(((out - m).norm() / m.norm()).item())
+    vw.check()
+    assert err[-1] < 3e-3 and err[-1] <= err[0] + 1e-6, err
