@@ -229,7 +229,8 @@ def build_reference(cfg, device, world):
         import torchvision
 
         model = getattr(torchvision.models, cfg["model"])(weights=None).to(device)
-        model = model.to(memory_format=torch.channels_last)
+        if g["compressor"] != "powersgd":  # the reference's PowerSGD calls .view() on the gradient: needs NCHW weights
+            model = model.to(memory_format=torch.channels_last)
     opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
 
     def step(batch, amp):
@@ -302,8 +303,16 @@ def main():
 
     # ---- device-resident inputs: kernel-side number ----
     batches = [make_batch(cfg, device, seed=1000 * rank + i) for i in range(2)]
-    for i in range(args.warmup):
-        step(batches[i % 2], amp)
+    try:
+        for i in range(args.warmup):
+            step(batches[i % 2], amp)
+        torch.cuda.synchronize()
+    except Exception as e:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "unavailable": "%s during warm-up: %s" % (
+                type(e).__name__, str(e).splitlines()[0][:200])}))
+        dist.destroy_process_group()
+        return 0
     barrier_sync()
     sampler = ClockSampler(local)
     if rank == 0:

@@ -1,0 +1,191 @@
+#!/usr/bin/env python
+"""Compressed-exchange microbenchmark (no model).
+
+fp32 gradients of 1M .. 256M elements drawn from N(0, 1e-3) with seed = rank;
+TopK 1 %, DGC 0.1 %, QSGD 8-bit, EF-signSGD (majority-style scaled vote),
+natural compression, each with its error-feedback memory, and PowerSGD rank 4
+on 4096 x 4096.  Measures compensate + compress + exchange + decompress for
+
+    --impl ours       one fused kernel per exchange (FusedExchange)
+    --impl library    this package's torch.distributed communicators
+    --impl reference  the unmodified reference under baseline/_ref (NCCL)
+
+Device-timed with CUDA events, max over ranks; L2 is flushed between timed
+iterations (a 256 MiB write).  For the fused path the achieved time is also
+reported as a fraction of the roofline
+
+    max( minimal HBM bytes / measured copy bandwidth ,
+         compressed bytes received / 770 GB/s per direction )
+
+with the copy bandwidth taken from MEASURED_PEAKS.json when present.
+
+    python benchmarks/microbench.py --sizes 1,4,16,64,256 --iters 5
+    python -m torch.distributed.run --nproc-per-node 8 benchmarks/microbench.py ...
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+NVLINK_GBS = 770.0
+
+CASES = {
+    "topk1": dict(compressor="topk", memory="residual", communicator="allgather", compress_ratio=0.01),
+    "dgc01": dict(compressor="dgc", memory="dgc", communicator="allgather", compress_ratio=0.001, momentum=0.9),
+    "qsgd8": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127),
+    "efsign": dict(compressor="efsignsgd", memory="efsignsgd", communicator="allgather", lr=0.1),
+    "natural": dict(compressor="natural", memory="residual", communicator="allgather"),
+    "powersgd4": dict(compressor="powersgd", memory="powersgd", communicator="allreduce", compress_rank=4,
+                      use_memory=True),
+}
+
+
+def hbm_gbs():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def roofline_ms(case, n, world, bw):
+    """(hbm_bytes, link_bytes) -> ms.  Minimal traffic of the fused algorithm."""
+    if case in ("topk1", "dgc01"):
+        ratio = 0.01 if case == "topk1" else 0.001
+        per_elem = 20 if case == "topk1" else 28          # g,r read; r,out write; one re-read (+u read/write for DGC)
+        hbm = per_elem * n
+        link = (world - 1) * ratio * n * 8
+    elif case in ("qsgd8", "natural"):
+        hbm = (12 + 1 + world + 4) * n                       # g,r read, r write, code write, W code reads, out write
+        link = (world - 1) * n * (1 + 4.0 / 128)
+    elif case == "efsign":
+        hbm = (12 + 8 + 4) * n + (1 + world) * n / 8
+        link = (world - 1) * n / 8
+    else:  # powersgd on sqrt(n) x sqrt(n)
+        hbm = 28 * n
+        side = int(n ** 0.5)
+        link = (world - 1) * 2 * side * 16 * 4
+    return max(hbm / (bw * 1e9), link / (NVLINK_GBS * 1e9)) * 1e3, hbm, link
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes", default="1,4,16,64", help="millions of elements (2^20)")
+    ap.add_argument("--cases", default=",".join(CASES))
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "library", "reference"])
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29541")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    bw, bw_src = hbm_gbs()
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    if args.impl == "reference":
+        for mod in [m for m in sys.modules if m.startswith("grace_dl")]:
+            del sys.modules[mod]
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+
+    def build(case):
+        p = dict(CASES[case])
+        p["world_size"] = world
+        if args.impl == "ours":
+            import grace_b200
+
+            p["fused"] = True
+            return grace_b200.grace_from_params(p)
+        if args.impl == "library":
+            import grace_b200
+
+            return grace_b200.grace_from_params(p)
+        # reference: construct the classes directly where its helper cannot
+        if case == "dgc01":
+            from grace_dl.dist.communicator.allgather import Allgather
+            from grace_dl.dist.compressor.dgc import DgcCompressor
+            from grace_dl.dist.memory.dgc import DgcMemory
+
+            return Allgather(DgcCompressor(p["compress_ratio"]), DgcMemory(0.9, False, world), world)
+        if case == "powersgd4":
+            from grace_dl.dist.communicator.allreduce import Allreduce
+            from grace_dl.dist.compressor.powersgd import PowerSGDCompressor
+            from grace_dl.dist.memory.powersgd import PowerSGDMemory
+
+            comp = PowerSGDCompressor(rank=4, use_memory=True, world_size=world)
+            return Allreduce(comp, PowerSGDMemory(comp.q_memory, 4), world)
+        if case == "natural":
+            raise RuntimeError("reference natural compression needs cupy (not installed)")
+        from grace_dl.dist.helper import grace_from_params
+
+        return grace_from_params(p)
+
+    rows = []
+    for case in args.cases.split(","):
+        for size_m in [int(s) for s in args.sizes.split(",")]:
+            n = size_m << 20
+            if case == "powersgd4":
+                if size_m != 16:
+                    continue
+                shape = (4096, 4096)
+            else:
+                shape = (n,)
+            try:
+                grc = build(case)
+            except Exception as e:
+                if rank == 0:
+                    print(json.dumps({"case": case, "impl": args.impl, "unavailable": str(e)[:120]}))
+                break
+            gen = torch.Generator(device=dev).manual_seed(rank)
+            base = torch.randn(shape, generator=gen, device=dev) * 1e-3
+            times = []
+            try:
+                for it in range(args.warmup + args.iters):
+                    g = base.clone()
+                    flush.fill_(float(it))
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    out = grc.step(g, "w")
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if it >= args.warmup:
+                        times.append(e0.elapsed_time(e1))
+                if hasattr(grc, "check"):
+                    grc.check()
+            except Exception as e:
+                if rank == 0:
+                    print(json.dumps({"case": case, "impl": args.impl, "size_m": size_m,
+                                      "error": "%s: %s" % (type(e).__name__, str(e).splitlines()[0][:160])}))
+                continue
+            t = torch.tensor([sorted(times)[len(times) // 2]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+            roof, hbm, link = roofline_ms(case, n, world, bw)
+            row = {"case": case, "impl": args.impl, "size_m": size_m, "n_gpus": world, "ms": round(ms, 4),
+                   "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / ms, 3) if args.impl == "ours" else None,
+                   "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
+                   "timing": "cuda events, median of %d, max over ranks, L2 flushed" % args.iters}
+            rows.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+            del grc, base, out, g
+            torch.cuda.empty_cache()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

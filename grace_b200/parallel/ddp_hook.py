@@ -51,7 +51,7 @@ class GraceDDPHook:
         self._layouts[idx] = info
         return info
 
-    def __call__(self, state, bucket) -> torch.futures.Future:
+    def __call__(self, state, bucket):  # returns torch.futures.Future[torch.Tensor]
         buf = bucket.buffer()
         fut: torch.futures.Future = torch.futures.Future()
         fused = hasattr(self.grc, "step_flat") and buf.is_cuda and buf.dtype == torch.float32 \
@@ -93,5 +93,9 @@ class GraceDDPHook:
 def register_grace_hook(ddp_model, grc):
     """Install GRACE as the gradient communication of a DDP-wrapped model."""
     hook = GraceDDPHook(grc, list(ddp_model.module.named_parameters()))
-    ddp_model.register_comm_hook(None, hook)
+
+    def grace_comm_hook(state, bucket):  # DDP wants a plain function (it logs hook.__name__)
+        return hook(state, bucket)
+
+    ddp_model.register_comm_hook(None, grace_comm_hook)
     return hook

@@ -180,3 +180,32 @@ def test_heartbeat_detects_a_rank_that_left():
     res = _run(_failure_detection, 2)
     assert res[1] == "left"
     assert res[0] == [1]
+
+
+def _ddp_hook(rank, world):
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    from grace_b200 import grace_from_params
+    from grace_b200.parallel.ddp_hook import register_grace_hook
+
+    torch.manual_seed(0)
+    model = DDP(torch.nn.Sequential(torch.nn.Linear(20, 30), torch.nn.ReLU(), torch.nn.Linear(30, 5)))
+    grc = grace_from_params({"compressor": "none", "memory": "none", "communicator": "allreduce", "world_size": world})
+    register_grace_hook(model, grc)
+    ref = torch.nn.Sequential(torch.nn.Linear(20, 30), torch.nn.ReLU(), torch.nn.Linear(30, 5))
+    ref.load_state_dict(model.module.state_dict())
+    g = torch.Generator().manual_seed(rank)
+    x = torch.randn(8, 20, generator=g)
+    model(x).sum().backward()
+    ref(x).sum().backward()
+    worst = 0.0
+    for p, q in zip(model.module.parameters(), ref.parameters()):
+        expect = q.grad.clone()
+        dist.all_reduce(expect)
+        worst = max(worst, (p.grad - expect / world).abs().max().item())
+    return worst
+
+
+def test_ddp_comm_hook_averages_like_allreduce():
+    res = _run(_ddp_hook, 2)
+    assert res[0] < 1e-6 and res[1] < 1e-6
