@@ -97,6 +97,7 @@ class FusedExchange(Communicator):
         self.inplace = inplace
         self.max_ratio = max_ratio
         self.exact = exact
+        self.nvtx = True
         self.device = None
         self._rank = rank
         self._plans: Dict[tuple, _Plan] = {}
@@ -208,6 +209,11 @@ class FusedExchange(Communicator):
             self.device = flat.device
         plan = self._plan(layout)
         out = flat if out is None else out
+        nvtx = self.nvtx and flat.is_cuda
+        if nvtx:
+            torch.cuda.nvtx.range_push("grace.exchange.%s" % plan.kind)
+        self._stats["dense_bytes"] += 4 * sum(layout.numels)
+        self._stats["payload_bytes"] += self._payload_bytes(plan)
         if plan.kind == "powersgd":
             if plan.matrices:
                 plan.channel.poll()
@@ -217,7 +223,18 @@ class FusedExchange(Communicator):
             self._launch(plan, flat, out, PHASE_ALL)
         plan.steps += 1
         self._stats["steps"] += 1
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
         return out
+
+    def _payload_bytes(self, plan) -> int:
+        """Bytes this rank publishes per exchange of ``plan`` (what a peer pulls)."""
+        if plan.kind == "sparse":
+            return 8 * (sum(plan.ks) if plan.ks else plan.cap)
+        if plan.kind == "quant":
+            return int(plan.channel.slot_bytes)
+        dense = 4 * plan.dense_layout.total if plan.dense else 0
+        return 4 * (plan.p_floats + plan.q_floats) * self.compressor.rank // 16 + dense
 
     def _prepare(self, tensor: torch.Tensor):
         flat = tensor.detach().reshape(-1)

@@ -67,7 +67,7 @@ PYBIND11_MODULE(_C, m) {
   // ---- sizes / occupancy ----
   m.def("sparse_slot_bytes", &sparse_slot_bytes);
   m.def("sparse_max_grid", &sparse_max_grid);
-  m.def("quant_slot_bytes", &quant_slot_bytes);
+  m.def("quant_slot_bytes", &quant_slot_bytes, py::arg("codec"), py::arg("total"), py::arg("nseg"), py::arg("alltoall_world") = 0);
   m.def("quant_max_grid", &quant_max_grid);
   m.def("sgd_table_chunk", &sgd_table_chunk);
   m.attr("SEGMENT_BYTES") = sizeof(Segment);
@@ -102,8 +102,9 @@ PYBIND11_MODULE(_C, m) {
            float scale, unsigned long long seed, unsigned step, uintptr_t stats, uintptr_t barrier, uintptr_t status,
            int phases, int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
-           unsigned long long slot_off, int grid, uintptr_t stream) {
+           unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off) {
           QuantArgs a{};
+          a.alltoall = alltoall; a.ready2_off = ready2_off;
           a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
           a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.codec = codec; a.quantum = quantum;
           a.deterministic = deterministic; a.first_step = first_step; a.beta = beta; a.gamma = gamma;

@@ -41,6 +41,7 @@ enum Phase : int {
   kPhasePublish = 2,   // release the slot to the peers
   kPhaseExchange = 4,  // wait for peers, pull, decode, aggregate, acknowledge
   kPhaseAll = 7,
+  kPhaseReduce = 8,    // two-phase ("alltoall") mode only: reduce my chunk, re-encode, publish again
 };
 
 // ---------------------------------------------------------------- sparse ----
@@ -121,10 +122,13 @@ struct QuantArgs {
   unsigned* barrier;
   unsigned* status;
   int phases;
+  int alltoall;          // 1: compressed reduce-scatter + compressed all-gather (QSGD, natural, fp16, fp32)
+  unsigned long long ready2_off;  // flag pad of the second publication (alltoall mode)
   PeerTable peers;
 };
 
-size_t quant_slot_bytes(int codec, long long total, int nseg);
+// alltoall_world > 0 adds the second region (one re-encoded chunk per rank) used by the two-phase mode.
+size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world = 0);
 int quant_max_grid(int device, int sm_limit);
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
 

@@ -53,6 +53,12 @@ template <> struct CodecTraits<kCodecFP32>     { static constexpr bool stats = f
 __host__ __device__ inline size_t scalars_bytes(int nseg) { return ((size_t)nseg * 16 + 127) / 128 * 128; }
 __host__ __device__ inline size_t codes_bytes(int bits, long long total) { return (size_t)total * bits / 8; }
 
+__host__ __device__ inline size_t region1_bytes(int codec, int bits, long long total, int nseg) {
+  size_t b = kHeaderBytes + scalars_bytes(nseg) + codes_bytes(bits, total);
+  if (codec == kCodecQSGD) b += (size_t)(total / 128) * 4;
+  return (b + 255) / 256 * 256;
+}
+
 struct SegScalars { float s0, s1, s2, s3; };
 
 // Turn the reduced statistics of a segment into the scalars that travel.
@@ -350,6 +356,163 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
     }
   }
 
+  constexpr bool kTwoPhaseCodec = C == kCodecQSGD || C == kCodecNatural || C == kCodecFP16 || C == kCodecFP32;
+  if (kTwoPhaseCodec && a.alltoall) {
+    // ---- two-phase mode: compressed reduce-scatter, re-encode, compressed all-gather ----
+    // Rank j owns the contiguous chunk j of 128-element groups.  Region 2 of every
+    // slot holds that rank's re-encoded chunk: codes, then (QSGD) one norm per group.
+    const long long groups_total = a.total >> 7;
+    const long long chunk_groups = (groups_total + world - 1) / world;
+    const size_t off2_codes = region1_bytes(C, T::bits, a.total, a.nseg);
+    const size_t off2_norms = off2_codes + codes_bytes(T::bits, chunk_groups * 128);
+    __shared__ int s_ready2;
+    if (a.phases & kPhaseReduce) {
+      if (tid == 0) s_ready2 = 1;
+      __syncthreads();
+      if (tid < world) {
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ready_off) + tid;
+        if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid)) s_ready2 = 0;
+      }
+      __syncthreads();
+      const long long g_begin = chunk_groups * rank;
+      const long long g_end = g_begin + chunk_groups < groups_total ? g_begin + chunk_groups : groups_total;
+      if (s_ready2) {
+        for (long long grp = g_begin + (long long)blockIdx.x * kWarps + warp; grp < g_end; grp += (long long)gridDim.x * kWarps) {
+          const long long i = (grp << 7) + 4 * lane;
+          float xv[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int p = 0; p < world; ++p) {
+            const char* slot = a.peers.heap[p] + a.peers.slot_off;
+            if (T::bits == 8) {
+              const unsigned word = ld_cg_u32(slot + off_codes + (size_t)i);
+              float dq = 0.f;
+              if (C == kCodecQSGD) dq = ld_cg_f32(slot + off_norms + (size_t)grp * 4) / (float)a.quantum;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const unsigned byte = (word >> (8 * j)) & 0xffu;
+                if (C == kCodecQSGD) xv[j] += dq * (float)(int)(signed char)byte;
+                else xv[j] += natural_decode(byte);
+              }
+            } else if (T::bits == 32) {
+              const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
+              xv[0] += __uint_as_float(w.x); xv[1] += __uint_as_float(w.y);
+              xv[2] += __uint_as_float(w.z); xv[3] += __uint_as_float(w.w);
+            } else {
+              uint2 w;
+              const char* q = slot + off_codes + (size_t)i * 2;
+              asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(q));
+              const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w.x));
+              const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w.y));
+              xv[0] += f01.x; xv[1] += f01.y; xv[2] += f23.x; xv[3] += f23.y;
+            }
+          }
+          // re-encode the reduced group (a second lossy step, with its own random stream)
+          const size_t li = (size_t)((grp - g_begin) << 7) + 4 * lane;   // element index inside my chunk
+          if (C == kCodecQSGD) {
+            const Philox4 rnd = philox_group((uint64_t)(i >> 2), a.step, 1u, a.seed);
+            const unsigned rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+            float sq = warp_sum(xv[0] * xv[0] + xv[1] * xv[1] + xv[2] * xv[2] + xv[3] * xv[3]);
+            const float norm = sqrtf(sq);
+            const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f;
+            unsigned word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lf = qn * fabsf(xv[j]);
+              const float fl = floorf(lf);
+              const float level = fminf(fl + ((u01(rw[j]) < lf - fl) ? 1.f : 0.f), 127.f);
+              const int code = xv[j] < 0.f ? -(int)level : (int)level;
+              word |= ((unsigned)code & 0xffu) << (8 * j);
+            }
+            *reinterpret_cast<unsigned*>(my_slot + off2_codes + li) = word;
+            if (lane == 0) *reinterpret_cast<float*>(my_slot + off2_norms + (size_t)(grp - g_begin) * 4) = norm;
+          } else if (C == kCodecNatural) {
+            const Philox4 rnd = philox_group((uint64_t)(i >> 2), a.step, 1u, a.seed);
+            const unsigned rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+            unsigned word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const unsigned bits = __float_as_uint(xv[j]);
+              const unsigned biased = (bits >> 23) & 0xffu;
+              const unsigned mant = bits & 0x7fffffu;
+              const bool up = a.deterministic ? mant > 0x400000u : u01(rw[j]) < (float)mant * 1.1920928955078125e-07f;
+              int c7 = (int)biased + (up ? 1 : 0) - 17;
+              c7 = c7 < 0 ? 0 : (c7 > 127 ? 127 : c7);
+              if (biased == 0) c7 = 0;
+              word |= ((unsigned)c7 | ((bits >> 24) & 0x80u)) << (8 * j);
+            }
+            *reinterpret_cast<unsigned*>(my_slot + off2_codes + li) = word;
+          } else if (C == kCodecFP32) {
+            *reinterpret_cast<float4*>(my_slot + off2_codes + li * 4) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+          } else {
+            __half2 h01 = __floats2half2_rn(xv[0], xv[1]);
+            __half2 h23 = __floats2half2_rn(xv[2], xv[3]);
+            uint2 w;
+            w.x = *reinterpret_cast<unsigned*>(&h01);
+            w.y = *reinterpret_cast<unsigned*>(&h23);
+            *reinterpret_cast<uint2*>(my_slot + off2_codes + li * 2) = w;
+          }
+        }
+      }
+      bar.sync();
+      if (blockIdx.x == 0 && tid < world && !status.failed()) {
+        __threadfence_system();
+        uint64_t* flag = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.ready2_off) + rank;
+        st_release_sys(flag, a.peers.seq);
+      }
+    }
+    if (a.phases & kPhaseExchange) {
+      if (tid == 0) s_ready2 = 1;
+      __syncthreads();
+      if (tid < world) {
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.ready2_off) + tid;
+        if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid)) s_ready2 = 0;
+      }
+      __syncthreads();
+      if (s_ready2 && lo < hi) {
+        for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+          for (long long gb = b0 + 128ll * warp; gb < e0; gb += 128ll * kWarps) {
+            const long long i = gb + 4 * lane;
+            int valid = 0;
+            if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+            const long long grp = gb >> 7;
+            const int owner = (int)(grp / chunk_groups);
+            const long long lg = grp - (long long)owner * chunk_groups;
+            const size_t li = (size_t)(lg << 7) + 4 * lane;
+            const char* slot = a.peers.heap[owner] + a.peers.slot_off;
+            float ov[4];
+            if (T::bits == 8) {
+              const unsigned word = ld_cg_u32(slot + off2_codes + li);
+              float dq = 0.f;
+              if (C == kCodecQSGD) dq = ld_cg_f32(slot + off2_norms + (size_t)lg * 4) / (float)a.quantum;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const unsigned byte = (word >> (8 * j)) & 0xffu;
+                ov[j] = (C == kCodecQSGD ? dq * (float)(int)(signed char)byte : natural_decode(byte)) * a.scale;
+              }
+            } else if (T::bits == 32) {
+              const uint4 w = ld_cg_u4(slot + off2_codes + li * 4);
+              ov[0] = __uint_as_float(w.x) * a.scale; ov[1] = __uint_as_float(w.y) * a.scale;
+              ov[2] = __uint_as_float(w.z) * a.scale; ov[3] = __uint_as_float(w.w) * a.scale;
+            } else {
+              uint2 w;
+              const char* q = slot + off2_codes + li * 2;
+              asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(q));
+              const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w.x));
+              const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w.y));
+              ov[0] = f01.x * a.scale; ov[1] = f01.y * a.scale; ov[2] = f23.x * a.scale; ov[3] = f23.y * a.scale;
+            }
+            if (valid) store4(a.out, i, valid, ov);
+          }
+        });
+      }
+      bar.sync();
+      if (blockIdx.x == 0 && tid < world && tid != rank && !status.failed()) {
+        uint64_t* ack = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ack_off) + rank;
+        st_release_sys(ack, a.peers.seq);
+      }
+    }
+    return;
+  }
+
   if (a.phases & kPhaseExchange) {
     // every CTA polls its own (local) copy of the peers' flags
     __shared__ int s_ready;
@@ -483,7 +646,7 @@ void build_u8_edges(float* e) {
 
 }  // namespace
 
-size_t quant_slot_bytes(int codec, long long total, int nseg) {
+size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world) {
   int bits = 8;
   switch (codec) {
     case kCodecTernGrad: bits = 2; break;
@@ -492,8 +655,12 @@ size_t quant_slot_bytes(int codec, long long total, int nseg) {
     case kCodecFP32: bits = 32; break;
     default: bits = 8;
   }
-  size_t bytes = kHeaderBytes + scalars_bytes(nseg) + codes_bytes(bits, total);
-  if (codec == kCodecQSGD) bytes += (size_t)(total / 128) * 4;
+  size_t bytes = region1_bytes(codec, bits, total, nseg);
+  if (alltoall_world > 0) {
+    const long long groups = total / 128;
+    const long long chunk_groups = (groups + alltoall_world - 1) / alltoall_world;
+    bytes += codes_bytes(bits, chunk_groups * 128) + (size_t)chunk_groups * 4;
+  }
   return (bytes + 255) / 256 * 256;
 }
 
