@@ -74,7 +74,9 @@ class _Plan:
             slot_bytes = Cn.sparse_slot_bytes(self.cap)
         else:
             self.codec = owner._codec
-            slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg)
+            self.alltoall = owner.mode == "alltoall" and self.codec in (X.CODEC["qsgd"], X.CODEC["natural"],
+                                                                        X.CODEC["fp16"], X.CODEC["fp32"])
+            slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg, owner.world_size if self.alltoall else 0)
         heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 4096
         self.heap = owner._make_heap(layout.key(), heap_bytes)
         self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
@@ -197,7 +199,8 @@ class FusedExchange(Communicator):
                 quantum=int(getattr(comp, "quantum_num", 0)), deterministic=bool(getattr(comp, "deterministic", False)),
                 first_step=plan.steps == 0, beta=beta, gamma=gamma, mom_beta=float(getattr(comp, "momentum", 0.0)),
                 lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
-                phases=phases, seq=seq)
+                phases=phases | (X.PHASE_REDUCE if (plan.alltoall and phases == X.PHASE_ALL) else 0), seq=seq,
+                alltoall=plan.alltoall)
         return seq
 
     # ------------------------------------------------------------------
@@ -404,6 +407,11 @@ class VirtualWorld:
         seqs = []
         for c, p, g, o in zip(self.comms, plans, flats, outs):
             seqs.append(c._launch(p, g, o, PHASE_COMPRESS | PHASE_PUBLISH))
+        if getattr(plans[0], "alltoall", False):
+            from ..ops.exchange import PHASE_REDUCE
+
+            for c, p, g, o, s in zip(self.comms, plans, flats, outs, seqs):
+                c._launch(p, g, o, PHASE_REDUCE, seq=s)
         for c, p, g, o, s in zip(self.comms, plans, flats, outs, seqs):
             c._launch(p, g, o, PHASE_EXCHANGE, seq=s)
             p.steps += 1

@@ -539,26 +539,40 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
               for (int c = 0; c < 8; ++c)
                 q[e][c] = (e < valid && c < a.rank) ? a.q_mean[M.q_off + (size_t)(col + e) * kRankPad + c] : 0.f;
             const int rows = min(32, M.n - rb * 32);
-            for (int rr = 0; rr < rows; ++rr) {
-              const size_t base = (size_t)M.g_off + (size_t)(rb * 32 + rr) * M.m + col;
-              float o[4];
+            const bool vec = valid == 4 && (M.m & 3) == 0;
+            for (int r0 = 0; r0 < rows; r0 += 4) {
+              // four rows per trip: issue the loads of M' first, then compute and store
+              float4 mv[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float s = 0.f;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) s += sm.prow[rr][c] * q[e][c];
-                o[e] = s;
+              for (int u = 0; u < 4; ++u) {
+                mv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r0 + u < rows && a.has_memory && vec)
+                  mv[u] = *reinterpret_cast<const float4*>(src + (size_t)M.g_off + (size_t)(rb * 32 + r0 + u) * M.m + col);
               }
-              if (valid == 4 && (M.m & 3) == 0) {
-                const float4 mv = *reinterpret_cast<const float4*>(src + base);
-                if (a.has_memory)
-                  *reinterpret_cast<float4*>(a.acc + base) = make_float4(mv.x - o[0], mv.y - o[1], mv.z - o[2], mv.w - o[3]);
-                *reinterpret_cast<float4*>(a.out + base) = make_float4(o[0], o[1], o[2], o[3]);
-              } else {
-                for (int e = 0; e < valid; ++e) {
-                  const float mv = src[base + e];
-                  if (a.has_memory) a.acc[base + e] = mv - o[e];
-                  a.out[base + e] = o[e];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int rr = r0 + u;
+                if (rr >= rows) break;
+                const size_t base = (size_t)M.g_off + (size_t)(rb * 32 + rr) * M.m + col;
+                float o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float s = 0.f;
+#pragma unroll
+                  for (int c = 0; c < 8; ++c) s += sm.prow[rr][c] * q[e][c];
+                  o[e] = s;
+                }
+                if (vec) {
+                  if (a.has_memory)
+                    *reinterpret_cast<float4*>(a.acc + base) =
+                        make_float4(mv[u].x - o[0], mv[u].y - o[1], mv[u].z - o[2], mv[u].w - o[3]);
+                  *reinterpret_cast<float4*>(a.out + base) = make_float4(o[0], o[1], o[2], o[3]);
+                } else {
+                  for (int e = 0; e < valid; ++e) {
+                    const float m1 = src[base + e];
+                    if (a.has_memory) a.acc[base + e] = m1 - o[e];
+                    a.out[base + e] = o[e];
+                  }
                 }
               }
             }

@@ -38,6 +38,7 @@ constexpr int kBlock = 512;
 constexpr int kWarps = kBlock / 32;
 constexpr int kIterElems = kBlock * 4;
 constexpr unsigned kHeaderBytes = 128;
+constexpr int kU = 4;  // groups per warp trip whose loads are issued up front
 
 template <int C> struct CodecTraits;
 template <> struct CodecTraits<kCodecQSGD>     { static constexpr bool stats = false; static constexpr int bits = 8; };
@@ -104,7 +105,7 @@ __device__ __forceinline__ float natural_decode(unsigned code) {
 }
 
 template <int C>
-__global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs a) {
+__global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantArgs a) {
   using T = CodecTraits<C>;
   __shared__ double red_d[kWarps][4];
   __shared__ unsigned long long red_c[kWarps];
@@ -201,20 +202,35 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
             *reinterpret_cast<float4*>(my_slot + kHeaderBytes + (size_t)s * 16) = make_float4(sc.s0, sc.s1, sc.s2, sc.s3);
         }
         // b0 is a multiple of 128: every warp step covers one whole code group
-        for (long long gb = b0 + 128ll * warp; gb < e0; gb += 128ll * kWarps) {
-          const long long i = gb + 4 * lane;
-          int valid = 0;
-          if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-          float av[4] = {0.f, 0.f, 0.f, 0.f};
-          if (T::stats) {
-            if (valid) load4(src, i, valid, av);
-          } else if (valid) {
-            float gv[4], rv[4] = {0.f, 0.f, 0.f, 0.f};
-            load4(a.g, i, valid, gv);
-            if (a.acc && a.beta != 0.f) load4(a.acc, i, valid, rv);
+        for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
+          // prefetch: all loads of kU groups are issued before the first encode
+          float pav[kU][4];
+          int pvalid[kU];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[j] + a.gamma * gv[j];
+          for (int q = 0; q < kU; ++q) {
+            const long long pi = gb0 + 128ll * kWarps * q + 4 * lane;
+            pvalid[q] = pi < e0 ? ((e0 - pi) >= 4 ? 4 : (int)(e0 - pi)) : 0;
+            float gv[4] = {0.f, 0.f, 0.f, 0.f}, rv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (pvalid[q]) {
+              if (T::stats) {
+                load4(src, pi, pvalid[q], gv);
+              } else {
+                load4(a.g, pi, pvalid[q], gv);
+                if (a.acc && a.beta != 0.f) load4(a.acc, pi, pvalid[q], rv);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pav[q][j] = T::stats ? gv[j] : a.beta * rv[j] + a.gamma * gv[j];
           }
+#pragma unroll
+          for (int q = 0; q < kU; ++q) {
+          const long long gb = gb0 + 128ll * kWarps * q;
+          if (gb >= e0) break;  // warp-uniform
+          const long long i = gb + 4 * lane;
+          const int valid = pvalid[q];
+          float av[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) av[j] = pav[q][j];
           float xv[4];  // what is encoded (momentum for signum, else acc)
 #pragma unroll
           for (int j = 0; j < 4; ++j) xv[j] = av[j];
@@ -331,6 +347,7 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
 #pragma unroll
             for (int j = 0; j < 4; ++j) res[j] = av[j] - dv[j];
             store4(a.acc, i, valid, res);
+          }
           }
         }
       });
@@ -533,74 +550,101 @@ __global__ void __launch_bounds__(kBlock) quant_exchange_kernel(const QuantArgs 
           }
           __syncthreads();
         }
-        for (long long gb = b0 + 128ll * warp; gb < e0; gb += 128ll * kWarps) {
-          const long long i = gb + 4 * lane;
-          int valid = 0;
-          if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-          const size_t group = (size_t)(gb >> 7);
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
-          int votes[4] = {0, 0, 0, 0};
+        for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
+          // kU groups per warp trip; for every peer the kU loads are issued before they are consumed
+          float sum[kU][4];
+          int votes[kU][4];
+#pragma unroll
+          for (int q = 0; q < kU; ++q)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { sum[q][j] = 0.f; votes[q][j] = 0; }
           for (int p = 0; p < world; ++p) {
             const char* slot = a.peers.heap[p] + a.peers.slot_off;
-            if (T::bits == 8) {
-              const unsigned word = ld_cg_u32(slot + off_codes + (size_t)i);
-              float dq = 0.f;
-              if (C == kCodecQSGD) dq = ld_cg_f32(slot + off_norms + group * 4) / (float)a.quantum;
+            unsigned w0[kU], w1[kU];
+            float dq[kU];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const unsigned byte = (word >> (8 * j)) & 0xffu;
-                if (C == kCodecQSGD) sum[j] += dq * (float)(int)(signed char)byte;
-                if (C == kCodecNatural) sum[j] += natural_decode(byte);
-                if (C == kCodecU8bit) {
-                  const int code = (int)(signed char)byte;
-                  const int ab = code < 0 ? -code : code;
-                  const float sg = code > 0 ? 1.f : (code < 0 ? -1.f : 0.f);
-                  sum[j] += s_edges[ab] * s_peer[p].s0 * sg;
+            for (int q = 0; q < kU; ++q) {
+              const long long gb = gb0 + 128ll * kWarps * q;
+              const long long i = gb + 4 * lane;
+              const size_t group = (size_t)(gb >> 7);
+              w0[q] = 0; w1[q] = 0; dq[q] = 0.f;
+              if (gb >= e0) continue;
+              if (T::bits == 8) {
+                w0[q] = ld_cg_u32(slot + off_codes + (size_t)i);
+                if (C == kCodecQSGD) dq[q] = ld_cg_f32(slot + off_norms + group * 4);
+              } else if (T::bits == 2) {
+                if (lane < 8) w0[q] = ld_cg_u32(slot + off_codes + group * 32 + lane * 4);
+              } else if (T::bits == 1) {
+                if (lane < 4) w0[q] = ld_cg_u32(slot + off_codes + group * 16 + lane * 4);
+              } else if (T::bits == 16) {
+                const char* ptr16 = slot + off_codes + (size_t)i * 2;
+                asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w0[q]), "=r"(w1[q]) : "l"(ptr16));
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < kU; ++q) {
+              const long long gb = gb0 + 128ll * kWarps * q;
+              if (gb >= e0) continue;  // warp-uniform
+              if (T::bits == 8) {
+                const float d = dq[q] / (float)a.quantum;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned byte = (w0[q] >> (8 * j)) & 0xffu;
+                  if (C == kCodecQSGD) sum[q][j] += d * (float)(int)(signed char)byte;
+                  if (C == kCodecNatural) sum[q][j] += natural_decode(byte);
+                  if (C == kCodecU8bit) {
+                    const int code = (int)(signed char)byte;
+                    const int ab = code < 0 ? -code : code;
+                    const float sg = code > 0 ? 1.f : (code < 0 ? -1.f : 0.f);
+                    sum[q][j] += s_edges[ab] * s_peer[p].s0 * sg;
+                  }
                 }
-              }
-            } else if (T::bits == 2) {
-              // 8 words per group: 4 "non-zero" ballots then 4 "negative" ballots
-              unsigned w = 0;
-              if (lane < 8) w = ld_cg_u32(slot + off_codes + group * 32 + lane * 4);
+              } else if (T::bits == 2) {
+                // 8 words per group: 4 "non-zero" ballots then 4 "negative" ballots
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const unsigned nz = __shfl_sync(0xffffffffu, w, j);
-                const unsigned ng = __shfl_sync(0xffffffffu, w, 4 + j);
-                const float s0 = s_peer[p].s0;
-                if ((nz >> lane) & 1u) sum[j] += ((ng >> lane) & 1u) ? -s0 : s0;
-              }
-            } else if (T::bits == 1) {
-              unsigned w = 0;
-              if (lane < 4) w = ld_cg_u32(slot + off_codes + group * 16 + lane * 4);
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned nz = __shfl_sync(0xffffffffu, w0[q], j);
+                  const unsigned ng = __shfl_sync(0xffffffffu, w0[q], 4 + j);
+                  const float s0 = s_peer[p].s0;
+                  if ((nz >> lane) & 1u) sum[q][j] += ((ng >> lane) & 1u) ? -s0 : s0;
+                }
+              } else if (T::bits == 1) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const unsigned bits = __shfl_sync(0xffffffffu, w, j);
-                const bool bit = (bits >> lane) & 1u;
-                if (C == kCodecSign) votes[j] += bit ? 1 : -1;
-                if (C == kCodecEFSign) sum[j] += bit ? s_peer[p].s0 : -s_peer[p].s0;
-                if (C == kCodecOneBit) sum[j] += bit ? s_peer[p].s0 : s_peer[p].s1;
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned bits = __shfl_sync(0xffffffffu, w0[q], j);
+                  const bool bit = (bits >> lane) & 1u;
+                  if (C == kCodecSign) votes[q][j] += bit ? 1 : -1;
+                  if (C == kCodecEFSign) sum[q][j] += bit ? s_peer[p].s0 : -s_peer[p].s0;
+                  if (C == kCodecOneBit) sum[q][j] += bit ? s_peer[p].s0 : s_peer[p].s1;
+                }
+              } else if (T::bits == 32) {
+                const long long i = gb + 4 * lane;
+                const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
+                sum[q][0] += __uint_as_float(w.x); sum[q][1] += __uint_as_float(w.y);
+                sum[q][2] += __uint_as_float(w.z); sum[q][3] += __uint_as_float(w.w);
+              } else {  // fp16
+                const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w0[q]));
+                const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w1[q]));
+                sum[q][0] += f01.x; sum[q][1] += f01.y; sum[q][2] += f23.x; sum[q][3] += f23.y;
               }
-            } else if (T::bits == 32) {
-              const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
-              sum[0] += __uint_as_float(w.x); sum[1] += __uint_as_float(w.y);
-              sum[2] += __uint_as_float(w.z); sum[3] += __uint_as_float(w.w);
-            } else {  // fp16
-              uint2 w;
-              const char* q = slot + off_codes + (size_t)i * 2;
-              asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(q));
-              const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w.x));
-              const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w.y));
-              sum[0] += f01.x; sum[1] += f01.y; sum[2] += f23.x; sum[3] += f23.y;
             }
           }
-          float ov[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (C == kCodecSign) ov[j] = votes[j] >= 0 ? 1.f : -1.f;
-            else if (C == kCodecEFSign) ov[j] = sum[j] / a.lr;
-            else ov[j] = sum[j] * a.scale;
+          for (int q = 0; q < kU; ++q) {
+            const long long gb = gb0 + 128ll * kWarps * q;
+            if (gb >= e0) continue;
+            const long long i = gb + 4 * lane;
+            int valid = 0;
+            if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+            float ov[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (C == kCodecSign) ov[j] = votes[q][j] >= 0 ? 1.f : -1.f;
+              else if (C == kCodecEFSign) ov[j] = sum[q][j] / a.lr;
+              else ov[j] = sum[q][j] * a.scale;
+            }
+            if (valid) store4(a.out, i, valid, ov);
           }
-          if (valid) store4(a.out, i, valid, ov);
         }
       });
     }

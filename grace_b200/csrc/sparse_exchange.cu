@@ -32,6 +32,7 @@ constexpr int kBlock = 512;
 constexpr int kBins = 4096;
 constexpr int kStageCap = 8192;           // staged (value, index) pairs per CTA
 constexpr int kIterElems = kBlock * 4;    // elements per CTA iteration
+constexpr int kUnroll = 4;                // 16-byte loads in flight per thread and array
 constexpr unsigned kSlotHeaderBytes = 128;
 
 __device__ __forceinline__ unsigned ordered_bits(float f) {
@@ -111,7 +112,7 @@ __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseStat
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(kBlock) sparse_exchange_kernel(const SparseArgs a) {
+__global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const SparseArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const Status status{a.status};
@@ -146,31 +147,46 @@ __global__ void __launch_bounds__(kBlock) sparse_exchange_kernel(const SparseArg
     if (lo < hi) {
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         float tmax = -INFINITY;
-        for (long long i = b0 + 4ll * tid; i < e0; i += kIterElems) {
-          const int valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-          float gv[4], rv[4] = {0.f, 0.f, 0.f, 0.f}, av[4];
-          load4(a.g, i, valid, gv);
-          if (a.u) {
-            float uv[4];
-            load4(a.u, i, valid, uv);
-            load4(a.acc, i, valid, rv);
+        const bool read_acc = a.u || (a.acc && a.beta != 0.f);
+        for (long long base = b0 + 4ll * tid; base < e0; base += (long long)kUnroll * kIterElems) {
+          // issue every load of the trip before the first dependent instruction
+          int valid[kUnroll];
+          float gv[kUnroll][4], rv[kUnroll][4], uv[kUnroll][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { uv[j] = a.momentum * uv[j] + gv[j]; av[j] = rv[j] + uv[j]; }
-            store4(a.u, i, valid, uv);
-          } else {
-            if (a.acc && a.beta != 0.f) load4(a.acc, i, valid, rv);
+          for (int q = 0; q < kUnroll; ++q) {
+            const long long i = base + (long long)q * kIterElems;
+            valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[j] + a.gamma * gv[j];
+            for (int j = 0; j < 4; ++j) { rv[q][j] = 0.f; uv[q][j] = 0.f; gv[q][j] = 0.f; }
+            if (valid[q]) {
+              load4(a.g, i, valid[q], gv[q]);
+              if (read_acc) load4(a.acc, i, valid[q], rv[q]);
+              if (a.u) load4(a.u, i, valid[q], uv[q]);
+            }
           }
-          if (a.acc) store4(a.acc, i, valid, av);
-          if (a.out) { const float z[4] = {0.f, 0.f, 0.f, 0.f}; store4(a.out, i, valid, z); }
-          if (topk) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (j < valid) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
-          } else {
+          for (int q = 0; q < kUnroll; ++q) {
+            if (!valid[q]) continue;
+            const long long i = base + (long long)q * kIterElems;
+            float av[4];
+            if (a.u) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) if (j < valid) tmax = fmaxf(tmax, av[j]);
+              for (int j = 0; j < 4; ++j) { uv[q][j] = a.momentum * uv[q][j] + gv[q][j]; av[j] = rv[q][j] + uv[q][j]; }
+              store4(a.u, i, valid[q], uv[q]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[q][j] + a.gamma * gv[q][j];
+            }
+            if (a.acc) store4(a.acc, i, valid[q], av);
+            if (a.out) { const float z[4] = {0.f, 0.f, 0.f, 0.f}; store4(a.out, i, valid[q], z); }
+            if (topk) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (j < valid[q]) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) if (j < valid[q]) tmax = fmaxf(tmax, av[j]);
+            }
           }
         }
         if (topk) {
@@ -205,15 +221,23 @@ __global__ void __launch_bounds__(kBlock) sparse_exchange_kernel(const SparseArg
           if (ok && lo < hi) {
             for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
               const unsigned prefix = a.state[s].prefix;
-              for (long long i = b0 + 4ll * tid; i < e0; i += kIterElems) {
-                const int valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-                float av[4];
-                load4(src, i, valid, av);
+              for (long long base = b0 + 4ll * tid; base < e0; base += (long long)kUnroll * kIterElems) {
+                int valid[kUnroll];
+                float av[kUnroll][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const unsigned key = __float_as_uint(av[j]) & 0x7fffffffu;
-                  if (j < valid && (key >> shift_prefix) == prefix)
-                    atomicAdd(&sm.hist[(key >> shift_digit) & digit_mask], 1u);
+                for (int q = 0; q < kUnroll; ++q) {
+                  const long long i = base + (long long)q * kIterElems;
+                  valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
+                  if (valid[q]) load4(src, i, valid[q], av[q]);
+                }
+#pragma unroll
+                for (int q = 0; q < kUnroll; ++q) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (j >= valid[q]) continue;
+                    const unsigned key = __float_as_uint(av[q][j]) & 0x7fffffffu;
+                    if ((key >> shift_prefix) == prefix) atomicAdd(&sm.hist[(key >> shift_digit) & digit_mask], 1u);
+                  }
                 }
               }
               flush_hist(sm, a.hist + (size_t)s * kBins);
@@ -258,62 +282,64 @@ __global__ void __launch_bounds__(kBlock) sparse_exchange_kernel(const SparseArg
         float thr = a.threshold;
         if (!topk) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));
         const long long span = e0 - b0;
-        const long long iters = (span + kIterElems - 1) / kIterElems;
-        for (long long it = 0; it < iters; ++it) {
-          // at most 3 * 2048 pairs are staged between flushes (capacity 8192)
-          if (since_flush == 3) { __syncthreads(); flush_stage(); since_flush = 0; }
-          ++since_flush;
-          const long long i = b0 + it * kIterElems + 4ll * tid;
-          int valid = 0;
-          if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-          float av[4] = {0.f, 0.f, 0.f, 0.f};
-          if (valid) load4(src, i, valid, av);
-          unsigned mask = 0;
+        const long long trips = (span + (long long)kUnroll * kIterElems - 1) / ((long long)kUnroll * kIterElems);
+        for (long long trip = 0; trip < trips; ++trip) {
+          // a trip stages at most kUnroll * 2048 = 8192 pairs, the capacity of the staging buffer
+          if (since_flush) { __syncthreads(); flush_stage(); since_flush = 0; }
+          since_flush = 1;
+          const long long base = b0 + trip * (long long)kUnroll * kIterElems + 4ll * tid;
+          int valid[kUnroll];
+          float avs[kUnroll][4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (j >= valid) continue;
-            bool sel;
-            if (topk) {
-              const unsigned kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
-              sel = kp > pivot;
-              if (kp == pivot) sel = atomicAdd(&a.state[s].tie_taken, 1u) < need;
-            } else {
-              sel = fabsf(av[j]) >= thr;
-            }
-            if (sel) mask |= 1u << j;
-          }
-          const unsigned cnt = __popc(mask);
-          // warp-aggregated reservation in the staging buffer
-          unsigned incl = cnt;
+          for (int q = 0; q < kUnroll; ++q) {
+            const long long i = base + (long long)q * kIterElems;
+            valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
 #pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const unsigned n = __shfl_up_sync(0xffffffffu, incl, o);
-            if ((tid & 31) >= o) incl += n;
+            for (int j = 0; j < 4; ++j) avs[q][j] = 0.f;
+            if (valid[q]) load4(src, i, valid[q], avs[q]);
           }
-          const unsigned wtotal = __shfl_sync(0xffffffffu, incl, 31);
-          unsigned wbase = 0;
-          if ((tid & 31) == 31 && wtotal) wbase = atomicAdd(&sm.stage_count, wtotal);
-          wbase = __shfl_sync(0xffffffffu, wbase, 31);
-          unsigned pos = wbase + incl - cnt;
-          if (mask) {
-            float zv[4];
+#pragma unroll
+          for (int q = 0; q < kUnroll; ++q) {
+            const long long i = base + (long long)q * kIterElems;
+            const float (&av)[4] = avs[q];
+            unsigned mask = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              zv[j] = av[j];
-              if (mask & (1u << j)) {
-                sm.stage.val[pos] = av[j];
-                sm.stage.idx[pos] = (int)(i + j);
-                ++pos;
-                zv[j] = 0.f;
+              if (j >= valid[q]) continue;
+              bool sel;
+              if (topk) {
+                const unsigned kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
+                sel = kp > pivot;
+                if (kp == pivot) sel = atomicAdd(&a.state[s].tie_taken, 1u) < need;
+              } else {
+                sel = fabsf(av[j]) >= thr;
               }
+              if (sel) mask |= 1u << j;
             }
-            if (a.acc) {
+            const unsigned cnt = __popc(mask);
+            // warp-aggregated reservation in the staging buffer
+            unsigned incl = cnt;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) if (mask & (1u << j)) a.acc[i + j] = 0.f;
+            for (int o = 1; o < 32; o <<= 1) {
+              const unsigned n = __shfl_up_sync(0xffffffffu, incl, o);
+              if ((tid & 31) >= o) incl += n;
             }
-            if (a.u) {
+            const unsigned wtotal = __shfl_sync(0xffffffffu, incl, 31);
+            unsigned wbase = 0;
+            if ((tid & 31) == 31 && wtotal) wbase = atomicAdd(&sm.stage_count, wtotal);
+            wbase = __shfl_sync(0xffffffffu, wbase, 31);
+            unsigned pos = wbase + incl - cnt;
+            if (mask) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) if (mask & (1u << j)) a.u[i + j] = 0.f;
+              for (int j = 0; j < 4; ++j) {
+                if (mask & (1u << j)) {
+                  sm.stage.val[pos] = av[j];
+                  sm.stage.idx[pos] = (int)(i + j);
+                  ++pos;
+                  if (a.acc) a.acc[i + j] = 0.f;
+                  if (a.u) a.u[i + j] = 0.f;
+                }
+              }
             }
           }
         }

@@ -21,6 +21,7 @@ from . import native
 from ..parallel.symm import SymmetricHeap
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
+PHASE_REDUCE = 8  # two-phase (alltoall) mode: reduce my chunk, re-encode, publish again
 SPARSE_TOPK, SPARSE_THRESHOLD = 0, 1
 CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8}
 
@@ -106,6 +107,7 @@ class ExchangeChannel:
         self.ready_off = self.flags_off
         self.ack_off = self.flags_off + C.MAX_WORLD * 8
         self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+        self.ready2_off = heap.alloc(C.MAX_WORLD * 8) if heap.free_bytes >= C.MAX_WORLD * 8 + 256 else 0
         self.seq = 0
         self.timeout_ns = int(timeout_ms * 1e6)
         self.sm_limit = sm_limit or 0
@@ -159,6 +161,8 @@ class ExchangeChannel:
         C = native()
         torch.cuda.synchronize(self.device)
         self.heap.view(self.flags_off, 2 * C.MAX_WORLD, torch.int64).zero_()
+        if self.ready2_off:
+            self.heap.view(self.ready2_off, C.MAX_WORLD, torch.int64).zero_()
         self.status.zero_()
         self.hist.zero_()
         self.sparse_state.zero_()
@@ -217,7 +221,8 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
               acc: Optional[torch.Tensor], mom: Optional[torch.Tensor], out: Optional[torch.Tensor], *, codec: int,
               quantum: int = 0, deterministic: bool = False, first_step: bool = False, beta: float = 1.0,
               gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
-              step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None) -> int:
+              step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None,
+              alltoall: bool = False) -> int:
     C = native()
     heap = channel.heap
     if seq is None:
@@ -234,7 +239,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         int(deterministic), int(first_step), beta, gamma, mom_beta, lr, scale, seed & (2 ** 64 - 1), step & 0xFFFFFFFF,
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
-        grid, _stream_ptr(),
+        grid, _stream_ptr(), int(alltoall), channel.ready2_off,
     )
     channel.post_status()
     return seq

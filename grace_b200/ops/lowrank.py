@@ -106,7 +106,7 @@ class LowRankPlan:
             slot_bytes = (self.p_floats + self.q_floats) * 4
             self.heap = heap_factory(("lowrank",) + layout.key(), 2 * ((slot_bytes + 255) // 256 * 256) + 8192)
             self.channel = ExchangeChannel(self.heap, slot_bytes, 1, timeout_ms, sm_limit)
-            self.ready2_off = self.heap.alloc(C.MAX_WORLD * 8)
+            self.ready2_off = self.channel.ready2_off or self.heap.alloc(C.MAX_WORLD * 8)
             self.maps = None
             self._maps_key = None
         # ---- dense side channel for everything that is not a matrix ----

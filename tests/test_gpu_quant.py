@@ -196,3 +196,66 @@ def test_codec_exchange_matches_python_compressor(name, memory, extra, W):
             assert torch.equal(outs[0], outs[r])
         if hasattr(refs[0].memory, "residuals") and name in ("natural",):
             torch.testing.assert_close(_plan(vw, 0).acc[:n], refs[0].memory.residuals["w"].to(_dev()), rtol=1e-5, atol=1e-8)
+
+
+def _a2a_world(W, params):
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.fused import VirtualWorld
+
+    def make(rank):
+        p = dict(params)
+        p.update(world_size=W, fused=True, communicator="alltoall")
+        return grace_from_params(p)
+
+    return VirtualWorld(W, make, _dev())
+
+
+@pytest.mark.parametrize("W", [2, 3, 4])
+def test_two_phase_mode_dense_and_natural(W):
+    """Compressed reduce-scatter + all-gather: exact for the dense codec, and equal to
+    decode -> sum -> re-encode -> decode for deterministic natural compression."""
+    from grace_b200.compressor.natural import natural_decode, natural_encode
+
+    n = 50_001
+    grads = [_rand(n, 11 * r + 1, scale=1e-2) for r in range(W)]
+    vw = _a2a_world(W, {"compressor": "none", "memory": "none"})
+    assert vw.comms[0].mode == "alltoall"
+    outs = vw.step([g.clone() for g in grads], "w")
+    vw.check()
+    assert next(iter(vw.comms[0]._plans.values())).alltoall
+    torch.testing.assert_close(outs[0], sum(grads) / W, rtol=1e-6, atol=1e-9)
+    for r in range(1, W):
+        assert torch.equal(outs[0], outs[r])
+
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.fused import VirtualWorld
+
+    def make(rank):
+        c = grace_from_params({"compressor": "natural", "memory": "none", "communicator": "alltoall",
+                               "world_size": W, "fused": True})
+        c.compressor.deterministic = True
+        return c
+
+    vw = VirtualWorld(W, make, _dev())
+    outs = vw.step([g.clone() for g in grads], "w")
+    vw.check()
+
+    def det_code(x):
+        prob = ((x.view(torch.int32) & 0x7FFFFF) > 0x400000)
+        return natural_encode(x, torch.where(prob, 0.0, 1.0).to(x.device))
+
+    total = sum(natural_decode(det_code(g.cpu())) for g in grads)
+    expect = natural_decode(det_code(total.contiguous())) / W
+    torch.testing.assert_close(outs[0].cpu(), expect, rtol=0, atol=0)
+
+
+def test_two_phase_mode_qsgd_close_to_mean():
+    W, n = 4, 100_000
+    grads = [_rand(n, 5 * r + 2, scale=1e-2) for r in range(W)]
+    vw = _a2a_world(W, {"compressor": "qsgd", "memory": "residual", "quantum_num": 127})
+    outs = vw.step([g.clone() for g in grads], "w")
+    vw.check()
+    mean = sum(grads) / W
+    assert ((outs[0] - mean).norm() / mean.norm()).item() < 0.12
+    for r in range(1, W):
+        assert torch.equal(outs[0], outs[r])
