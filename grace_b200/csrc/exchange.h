@@ -67,7 +67,10 @@ struct SparseArgs {
   float beta, gamma, momentum, threshold;
   float scale;        // factor applied while aggregating (1/W when averaging)
   unsigned* hist;     // nseg * 4096, zero on entry, left zero on exit
-  SparseState* state; // nseg
+  SparseState* state; // nseg + 1 (the extra entry holds the candidate counters), zeroed by the launcher
+  float* cand_val;    // candidate list of the fast select path (nullable)
+  int* cand_idx;
+  unsigned cand_cap;  // capacity of the candidate list in entries (0 disables the fast path)
   unsigned* barrier;  // one word, zeroed by the launcher
   unsigned* status;   // 4 words
   unsigned cap;       // slot capacity in entries (multiple of 16)

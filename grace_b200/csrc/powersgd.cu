@@ -40,7 +40,7 @@ namespace grace {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kStages = 4;
+constexpr int kStages = 4;             // 4 x (16 + 16 + 2) KiB of tiles in flight per CTA, one CTA per SM
 constexpr int kTileRows = 128;          // MMA M
 constexpr int kTileK = 32;              // fp32 elements per 128-byte swizzle row
 constexpr int kRankPad = 16;            // MMA N
@@ -48,6 +48,8 @@ constexpr int kATileBytes = kTileRows * kTileK * 4;   // 16 KiB
 constexpr int kBTileBytes = kRankPad * kTileK * 4;    // 2 KiB
 constexpr int kKTilesPerItem = 16;      // split-K granularity: 512 columns (S1) / 512 rows (S2)
 constexpr unsigned kTmemCols = 32;
+constexpr int kMaxRank = 8;              // ranks 1..8 (buffers are padded to kRankPad columns)
+constexpr int kS3Rows = 64;             // rows per stage-3 work item
 
 // instruction descriptor: D=f32, A=B=tf32, N=16, M=128 (bit layout: c_format
 // [4,6), a_format [7,10), b_format [10,13), a_major 15, b_major 16, N>>3
@@ -63,9 +65,9 @@ struct __align__(1024) SmemLayout {
   unsigned long long item_done;
   unsigned tmem_base;
   int bail;
-  double gram[kRankPad][kRankPad];
-  double rinv[kRankPad][kRankPad];
-  float prow[32][kRankPad];
+  double gram[kMaxRank][kMaxRank];
+  double rinv[kMaxRank][kMaxRank];
+  float prow[kS3Rows][kMaxRank];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -213,7 +215,6 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
   }
 
   while (c_valid) {
-    if (tid == 0) produce();
     const unsigned slot = c_step % kStages;
     bool ok = mbar_wait(&sm.full[slot], (c_step / kStages) & 1, a.peers.timeout_ns, status, 200 + slot);
     if (add_residual && ok) {
@@ -231,7 +232,12 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
     if (STAGE == 2 && ok) {
       // transpose: staging[j][k][mi] (k = row of M', 32 per tile; m = 32*j + mi) -> A[m][k], K-major with the
       // 128-byte swizzle (16-byte chunk index XOR row % 8).  One 4 x 4 block per thread.
-      const int kq = tid & 7, mq = tid >> 3;          // k / 4 and m / 4
+      // Thread -> block mapping chosen so that both sides are free of bank conflicts: the eight
+      // lanes of a quarter warp read eight different 16-byte chunks of the staging rows, and their
+      // swizzled destination chunks (kq ^ row % 8) are eight different values as well.
+      const int l8 = tid & 7, rest = tid >> 3;
+      const int mq = (rest & 3) * 8 + l8;             // m / 4
+      const int kq = (l8 >> 1) ^ (rest >> 2);         // k / 4
       const int j = mq >> 3, mi4 = (mq & 7) * 4;
       const unsigned char* st = sm.r[slot] + j * 4096 + mi4 * 4;
       float4 rowv[4];
@@ -267,6 +273,9 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       }
       umma_commit(&sm.mma_done[slot]);
       if (last_kt) umma_commit(&sm.item_done);
+      // refill the slot used one step ago: its MMAs were issued a whole iteration earlier, so the
+      // wait inside produce() rarely stalls
+      produce();
     }
     ++c_step;
     if (last_kt) {
@@ -425,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       // Gram: one thread per row, shared-memory fp64 accumulation per matrix
       for (int mat = 0; mat < a.nmat; ++mat) {
         const LowRankMatrix& M = a.mats[mat];
-        for (int i = tid; i < kRankPad * kRankPad; i += kThreads) (&sm.gram[0][0])[i] = 0.0;
+        for (int i = tid; i < kMaxRank * kMaxRank; i += kThreads) (&sm.gram[0][0])[i] = 0.0;
         __syncthreads();
         for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
           const float* pr = a.p_mean + M.p_off + (size_t)row * kRankPad;
@@ -439,9 +448,10 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
               if (d < a.rank) atomicAdd(&sm.gram[c][d], (double)v[c] * (double)v[d]);
         }
         __syncthreads();
-        if (tid < kRankPad * kRankPad) {
-          const int c = tid / kRankPad, d = tid % kRankPad;
-          if (c <= d && d < a.rank && sm.gram[c][d] != 0.0) atomicAdd(&a.gram[(size_t)mat * 256 + tid], sm.gram[c][d]);
+        if (tid < kMaxRank * kMaxRank) {
+          const int c = tid / kMaxRank, d = tid % kMaxRank;
+          if (c <= d && d < a.rank && sm.gram[c][d] != 0.0)
+            atomicAdd(&a.gram[(size_t)mat * 256 + c * kRankPad + d], sm.gram[c][d]);
         }
         __syncthreads();
       }
@@ -516,16 +526,16 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
           for (int c = 0; c < a.rank; ++c) a.qt[M.qt_off + (size_t)c * M.m + j] = qr[c];
         }
       }
-      // S3: out = P Q^T, residual = M' - out.  Item = 32 rows x 1024 columns.
+      // S3: out = P Q^T, residual = M' - out.  Item = kS3Rows rows x 1024 columns.
       for (int mat = 0; mat < a.nmat; ++mat) {
         const LowRankMatrix& M = a.mats[mat];
         const float* __restrict__ src = a.has_memory ? a.acc : a.g;
-        const int row_blocks = (M.n + 31) / 32, col_blocks = (M.m + 1023) / 1024;
+        const int row_blocks = (M.n + kS3Rows - 1) / kS3Rows, col_blocks = (M.m + 1023) / 1024;
         for (int item = blockIdx.x; item < row_blocks * col_blocks; item += gridDim.x) {
           const int rb = item / col_blocks, cb = item % col_blocks;
           __syncthreads();
-          for (int i = tid; i < 32 * kRankPad; i += kThreads) {
-            const int rr = i / kRankPad, c = i % kRankPad, row = rb * 32 + rr;
+          for (int i = tid; i < kS3Rows * kMaxRank; i += kThreads) {
+            const int rr = i / kMaxRank, c = i % kMaxRank, row = rb * kS3Rows + rr;
             sm.prow[rr][c] = (row < M.n && c < a.rank) ? a.pt_orth[M.pt_off + (size_t)c * M.n + row] : 0.f;
           }
           __syncthreads();
@@ -534,26 +544,32 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
             const int valid = min(4, M.m - col);
             float q[4][8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-#pragma unroll
-              for (int c = 0; c < 8; ++c)
-                q[e][c] = (e < valid && c < a.rank) ? a.q_mean[M.q_off + (size_t)(col + e) * kRankPad + c] : 0.f;
-            const int rows = min(32, M.n - rb * 32);
+            for (int e = 0; e < 4; ++e) {
+              float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+              if (e < valid) {   // columns >= rank of q_mean are zero
+                const float4* qp = reinterpret_cast<const float4*>(a.q_mean + M.q_off + (size_t)(col + e) * kRankPad);
+                lo4 = qp[0];
+                if (a.rank > 4) hi4 = qp[1];
+              }
+              q[e][0] = lo4.x; q[e][1] = lo4.y; q[e][2] = lo4.z; q[e][3] = lo4.w;
+              q[e][4] = hi4.x; q[e][5] = hi4.y; q[e][6] = hi4.z; q[e][7] = hi4.w;
+            }
+            const int rows = min(kS3Rows, M.n - rb * kS3Rows);
             const bool vec = valid == 4 && (M.m & 3) == 0;
-            for (int r0 = 0; r0 < rows; r0 += 4) {
-              // four rows per trip: issue the loads of M' first, then compute and store
-              float4 mv[4];
+            for (int r0 = 0; r0 < rows; r0 += 8) {
+              // eight rows per trip: issue the loads of M' first, then compute and store
+              float4 mv[8];
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
+              for (int u = 0; u < 8; ++u) {
                 mv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (r0 + u < rows && a.has_memory && vec)
-                  mv[u] = *reinterpret_cast<const float4*>(src + (size_t)M.g_off + (size_t)(rb * 32 + r0 + u) * M.m + col);
+                  mv[u] = *reinterpret_cast<const float4*>(src + (size_t)M.g_off + (size_t)(rb * kS3Rows + r0 + u) * M.m + col);
               }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
+              for (int u = 0; u < 8; ++u) {
                 const int rr = r0 + u;
                 if (rr >= rows) break;
-                const size_t base = (size_t)M.g_off + (size_t)(rb * 32 + rr) * M.m + col;
+                const size_t base = (size_t)M.g_off + (size_t)(rb * kS3Rows + rr) * M.m + col;
                 float o[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {

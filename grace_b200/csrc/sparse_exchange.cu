@@ -32,6 +32,9 @@ constexpr int kBlock = 512;
 constexpr int kBins = 4096;
 constexpr int kStageCap = 8192;           // staged (value, index) pairs per CTA
 constexpr int kIterElems = kBlock * 4;    // elements per CTA iteration
+constexpr int kCandStage = 4096;          // staged pivot-bin candidates per CTA
+constexpr int kWarpStage = kStageCap / (kBlock / 32);   // 512 staged picks per warp
+constexpr int kWarpCand = kCandStage / (kBlock / 32);   // 256 staged candidates per warp
 constexpr int kUnroll = 4;                // 16-byte loads in flight per thread and array
 constexpr unsigned kSlotHeaderBytes = 128;
 
@@ -44,6 +47,8 @@ __device__ __forceinline__ float from_ordered_bits(unsigned b) {
   return __uint_as_float((b & 0x80000000u) ? (b & 0x7fffffffu) : ~b);
 }
 
+template <bool B> struct Bool { static constexpr bool value = B; };
+
 struct Smem {
   union {
     unsigned hist[kBins];
@@ -52,8 +57,10 @@ struct Smem {
       int idx[kStageCap];
     } stage;
   };
-  unsigned stage_count;
-  unsigned flush_base;
+  float cand_val[kCandStage];   // keys of the pivot bin awaiting refinement (fast path), kWarpCand per warp
+  int cand_idx[kCandStage];
+  unsigned wcnt[kBlock / 32];   // entries staged by each warp
+  unsigned ccnt[kBlock / 32];
   unsigned scan[kBlock / 32 + 1];
   unsigned pick[4];
 };
@@ -73,7 +80,7 @@ __device__ __forceinline__ void flush_hist(Smem& sm, unsigned* __restrict__ ghis
 // Suffix-scan one segment's histogram and pick the bin holding the `need`-th
 // largest key.  All threads of the CTA take part; the histogram is left zero.
 __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseState* __restrict__ st, unsigned need,
-                              int bits) {
+                              int bits, unsigned* cand_total = nullptr) {
   constexpr int kPer = kBins / kBlock;  // 8 bins per thread
   const int t = threadIdx.x;
   unsigned c[kPer];
@@ -105,6 +112,7 @@ __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseStat
         st->prefix = (st->prefix << bits) | (unsigned)(t * kPer + j);
         st->need = need - cum;
         st->tie_taken = 0;
+        if (cand_total) atomicAdd(cand_total, c[j]);
       }
       cum += c[j];
     }
@@ -148,14 +156,15 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         float tmax = -INFINITY;
         const bool read_acc = a.u || (a.acc && a.beta != 0.f);
-        for (long long base = b0 + 4ll * tid; base < e0; base += (long long)kUnroll * kIterElems) {
+        auto trip_a = [&](auto full_tag, long long base) {
+          constexpr bool kFull = decltype(full_tag)::value;   // all kUnroll vectors fully inside the range
           // issue every load of the trip before the first dependent instruction
           int valid[kUnroll];
           float gv[kUnroll][4], rv[kUnroll][4], uv[kUnroll][4];
 #pragma unroll
           for (int q = 0; q < kUnroll; ++q) {
             const long long i = base + (long long)q * kIterElems;
-            valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
+            valid[q] = kFull ? 4 : (i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) { rv[q][j] = 0.f; uv[q][j] = 0.f; gv[q][j] = 0.f; }
             if (valid[q]) {
@@ -182,12 +191,18 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             if (topk) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (j < valid[q]) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
+                if (kFull || j < valid[q]) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
             } else {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) if (j < valid[q]) tmax = fmaxf(tmax, av[j]);
+              for (int j = 0; j < 4; ++j) if (kFull || j < valid[q]) tmax = fmaxf(tmax, av[j]);
             }
           }
+        };
+        {
+          const long long trip_elems = (long long)kUnroll * kIterElems;
+          long long base = b0 + 4ll * tid;
+          for (; base + trip_elems - 4ll * tid <= e0; base += trip_elems) trip_a(Bool<true>{}, base);
+          for (; base < e0; base += trip_elems) trip_a(Bool<false>{}, base);
         }
         if (topk) {
           flush_hist(sm, a.hist + (size_t)s * kBins);
@@ -200,19 +215,30 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
     // zero the padding gaps of the output (between segments) is unnecessary:
     // nothing ever writes there.
     bool ok = bar.sync();
+    bool fast = false;
+    SparseState* const extra = a.state + a.nseg;  // [prefix] = candidate total, [need] = candidate cursor
 
     if (topk) {
       // ---- radix select: levels of 12, 12 and 7 key bits ----
+      // Fast path (exact mode): when the pivot bins of the first level are small enough, the
+      // compaction pass also collects their keys into a candidate list and the remaining two levels
+      // run on that list only: two streaming passes over the tensor instead of four.
       const int nlevels = a.levels;
       for (int level = 0; level < nlevels; ++level) {
         const int bits = level == 2 ? 7 : 12;
         if (ok) {
           for (int s = blockIdx.x; s < a.nseg; s += gridDim.x) {
             const unsigned need = level == 0 ? (unsigned)a.segs[s].k : a.state[s].need;
-            pivot_segment(sm, a.hist + (size_t)s * kBins, &a.state[s], need, bits);
+            pivot_segment(sm, a.hist + (size_t)s * kBins, &a.state[s], need, bits,
+                          level == 0 ? &extra->prefix : nullptr);
           }
         }
         ok = bar.sync();
+        if (level == 0 && nlevels == 3 && a.cand_cap) {
+          // extra->prefix now holds the exact number of keys in the pivot bins of all segments
+          fast = ld_acquire_gpu(&extra->prefix) <= a.cand_cap;
+          if (fast) break;
+        }
         if (level + 1 < nlevels) {
           // histogram of the next digit among keys that match the prefix
           const int shift_prefix = level == 0 ? 19 : 7;
@@ -249,51 +275,67 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
     }
 
     // ---- phase B: compaction into the send slot + error-feedback update ----
+    // Every warp stages its picks in its own slice of shared memory and flushes it by itself
+    // (one global atomic per flush, coalesced copies): the streaming loop has no CTA barrier.
     __syncthreads();
-    if (tid == 0) sm.stage_count = 0;
-    __syncthreads();
-    const int key_shift = topk ? (a.levels == 3 ? 0 : (a.levels == 2 ? 7 : 19)) : 0;
-    auto flush_stage = [&]() {
-      // called by all threads; copies the staged pairs to the slot (coalesced)
-      const unsigned n = sm.stage_count;
-      if (tid == 0) sm.flush_base = n ? atomicAdd(&my_hdr[0], n) : 0u;
-      __syncthreads();
-      const unsigned base = sm.flush_base;
-      for (unsigned e = tid; e < n; e += kBlock) {
+    const int key_shift = topk ? (fast ? 19 : (a.levels == 3 ? 0 : (a.levels == 2 ? 7 : 19))) : 0;
+    const int lane = tid & 31, warp = tid >> 5;
+    const unsigned lane_lt = (1u << lane) - 1u;
+    float* const w_val = sm.stage.val + warp * kWarpStage;
+    int* const w_idx = sm.stage.idx + warp * kWarpStage;
+    float* const c_val = sm.cand_val + warp * kWarpCand;
+    int* const c_idx = sm.cand_idx + warp * kWarpCand;
+    if (lane == 0) { sm.wcnt[warp] = 0; sm.ccnt[warp] = 0; }
+    __syncwarp();
+    auto flush_warp = [&]() {
+      __syncwarp();
+      const unsigned wcount = sm.wcnt[warp];
+      unsigned base = 0;
+      if (lane == 0 && wcount) base = atomicAdd(&my_hdr[0], wcount);
+      base = __shfl_sync(0xffffffffu, base, 0);
+      for (unsigned e = lane; e < wcount; e += 32) {
         const unsigned pos = base + e;
         if (pos < a.cap) {
-          my_vals[pos] = sm.stage.val[e];
-          my_idx[pos] = sm.stage.idx[e];
+          my_vals[pos] = w_val[e];
+          my_idx[pos] = w_idx[e];
         } else {
           // no room: give the value back to the residual so nothing is lost
-          if (a.acc) a.acc[sm.stage.idx[e]] = sm.stage.val[e];
+          if (a.acc) a.acc[w_idx[e]] = w_val[e];
           atomicAdd(&a.status[3], 1u);
         }
       }
-      __syncthreads();
-      if (tid == 0) sm.stage_count = 0;
-      __syncthreads();
+      __syncwarp();
+      if (lane == 0) sm.wcnt[warp] = 0;
+      __syncwarp();
     };
-    unsigned since_flush = 0;
+    auto flush_warp_cand = [&]() {
+      __syncwarp();
+      const unsigned ccount = sm.ccnt[warp];
+      unsigned base = 0;
+      if (lane == 0 && ccount) base = atomicAdd(&extra->need, ccount);
+      base = __shfl_sync(0xffffffffu, base, 0);
+      for (unsigned e = lane; e < ccount; e += 32) {
+        const unsigned pos = base + e;
+        if (pos < a.cand_cap) { a.cand_val[pos] = c_val[e]; a.cand_idx[pos] = c_idx[e]; }
+      }
+      __syncwarp();
+      if (lane == 0) sm.ccnt[warp] = 0;
+      __syncwarp();
+    };
     if (ok && lo < hi) {
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         const unsigned pivot = a.state[s].prefix;
         const unsigned need = a.state[s].need;
         float thr = a.threshold;
         if (!topk) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));
-        const long long span = e0 - b0;
-        const long long trips = (span + (long long)kUnroll * kIterElems - 1) / ((long long)kUnroll * kIterElems);
-        for (long long trip = 0; trip < trips; ++trip) {
-          // a trip stages at most kUnroll * 2048 = 8192 pairs, the capacity of the staging buffer
-          if (since_flush) { __syncthreads(); flush_stage(); since_flush = 0; }
-          since_flush = 1;
-          const long long base = b0 + trip * (long long)kUnroll * kIterElems + 4ll * tid;
+        auto trip_b = [&](auto full_tag, long long base) {
+          constexpr bool kFull = decltype(full_tag)::value;
           int valid[kUnroll];
           float avs[kUnroll][4];
 #pragma unroll
           for (int q = 0; q < kUnroll; ++q) {
             const long long i = base + (long long)q * kIterElems;
-            valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
+            valid[q] = kFull ? 4 : (i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) avs[q][j] = 0.f;
             if (valid[q]) load4(src, i, valid[q], avs[q]);
@@ -302,52 +344,116 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           for (int q = 0; q < kUnroll; ++q) {
             const long long i = base + (long long)q * kIterElems;
             const float (&av)[4] = avs[q];
-            unsigned mask = 0;
+            // a warp adds at most 128 entries per step to either stage
+            __syncwarp();
+            if (sm.wcnt[warp] + 128 > kWarpStage) flush_warp();
+            if (fast && sm.ccnt[warp] + 128 > kWarpCand) flush_warp_cand();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (j >= valid[q]) continue;
-              bool sel;
+              if (!kFull && j >= valid[q]) continue;
+              bool hit;  // rare: this element is picked or is a candidate
+              unsigned kp = 0;
               if (topk) {
-                const unsigned kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
-                sel = kp > pivot;
-                if (kp == pivot) sel = atomicAdd(&a.state[s].tie_taken, 1u) < need;
+                kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
+                hit = kp >= pivot;
               } else {
-                sel = fabsf(av[j]) >= thr;
+                hit = fabsf(av[j]) >= thr;
               }
-              if (sel) mask |= 1u << j;
-            }
-            const unsigned cnt = __popc(mask);
-            // warp-aggregated reservation in the staging buffer
-            unsigned incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-              const unsigned n = __shfl_up_sync(0xffffffffu, incl, o);
-              if ((tid & 31) >= o) incl += n;
-            }
-            const unsigned wtotal = __shfl_sync(0xffffffffu, incl, 31);
-            unsigned wbase = 0;
-            if ((tid & 31) == 31 && wtotal) wbase = atomicAdd(&sm.stage_count, wtotal);
-            wbase = __shfl_sync(0xffffffffu, wbase, 31);
-            unsigned pos = wbase + incl - cnt;
-            if (mask) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (mask & (1u << j)) {
-                  sm.stage.val[pos] = av[j];
-                  sm.stage.idx[pos] = (int)(i + j);
-                  ++pos;
+              if (hit) {
+                bool sel = true;
+                if (topk && kp == pivot) {
+                  sel = false;
+                  if (fast) {  // decided later, on the candidate list
+                    const unsigned pos = atomicAdd(&sm.ccnt[warp], 1u);
+                    c_val[pos] = av[j];
+                    c_idx[pos] = (int)(i + j);
+                  } else {
+                    sel = atomicAdd(&a.state[s].tie_taken, 1u) < need;
+                  }
+                }
+                if (sel) {
+                  const unsigned pos = atomicAdd(&sm.wcnt[warp], 1u);
+                  w_val[pos] = av[j];
+                  w_idx[pos] = (int)(i + j);
                   if (a.acc) a.acc[i + j] = 0.f;
                   if (a.u) a.u[i + j] = 0.f;
                 }
               }
             }
           }
-        }
+        };
+        const long long trip_elems = (long long)kUnroll * kIterElems;
+        long long base = b0 + 4ll * tid;
+        for (; base + trip_elems - 4ll * tid <= e0; base += trip_elems) trip_b(Bool<true>{}, base);
+        // the guarded tail must be executed by whole warps together (flush checks are warp-wide)
+        for (long long wb = base - 4ll * lane; wb < e0; wb += trip_elems) trip_b(Bool<false>{}, wb + 4ll * lane);
       });
     }
-    __syncthreads();
-    flush_stage();
+    flush_warp();
+    if (fast) flush_warp_cand();
     ok = bar.sync();
+    if (fast) {
+      // ---- refinement on the candidate list: 12-bit and 7-bit levels, then the final picks ----
+      const unsigned ncand = min(ld_acquire_gpu(&extra->need), a.cand_cap);
+      const unsigned gtid = blockIdx.x * kBlock + tid, gstride = gridDim.x * kBlock;
+      auto seg_of = [&](int idx) {
+        int lo_s = 0, hi_s = a.nseg;
+        while (lo_s + 1 < hi_s) {
+          const int m = (lo_s + hi_s) >> 1;
+          if (a.segs[m].offset <= idx) lo_s = m; else hi_s = m;
+        }
+        return lo_s;
+      };
+      for (int level = 1; level < 3; ++level) {
+        if (ok) {
+          for (unsigned e = gtid; e < ncand; e += gstride) {
+            const unsigned key = __float_as_uint(a.cand_val[e]) & 0x7fffffffu;
+            const int sg = seg_of(a.cand_idx[e]);
+            if (level == 1) atomicAdd(&a.hist[(size_t)sg * kBins + ((key >> 7) & 0xfffu)], 1u);
+            else if ((key >> 7) == a.state[sg].prefix) atomicAdd(&a.hist[(size_t)sg * kBins + (key & 0x7fu)], 1u);
+          }
+        }
+        ok = bar.sync();
+        if (ok) {
+          for (int sg = blockIdx.x; sg < a.nseg; sg += gridDim.x)
+            pivot_segment(sm, a.hist + (size_t)sg * kBins, &a.state[sg], a.state[sg].need, level == 2 ? 7 : 12);
+        }
+        ok = bar.sync();
+      }
+      if (ok) {
+        for (unsigned e0 = blockIdx.x * kBlock; e0 < ncand; e0 += gstride) {   // warp-uniform trip count
+          const unsigned e = e0 + tid;
+          bool sel = false;
+          float v = 0.f;
+          int idx = 0;
+          if (e < ncand) {
+            v = a.cand_val[e];
+            idx = a.cand_idx[e];
+            const unsigned key = __float_as_uint(v) & 0x7fffffffu;
+            const int sg = seg_of(idx);
+            const unsigned thr_key = a.state[sg].prefix;
+            sel = key > thr_key;
+            if (key == thr_key) sel = atomicAdd(&a.state[sg].tie_taken, 1u) < a.state[sg].need;
+          }
+          const unsigned ballot = __ballot_sync(0xffffffffu, sel);
+          unsigned wbase = 0;
+          if ((tid & 31) == 0 && ballot) wbase = atomicAdd(&my_hdr[0], __popc(ballot));
+          wbase = __shfl_sync(0xffffffffu, wbase, 0);
+          if (sel) {
+            const unsigned pos = wbase + __popc(ballot & ((1u << (tid & 31)) - 1u));
+            if (pos < a.cap) {
+              my_vals[pos] = v;
+              my_idx[pos] = idx;
+              if (a.acc) a.acc[idx] = 0.f;
+              if (a.u) a.u[idx] = 0.f;
+            } else {
+              atomicAdd(&a.status[3], 1u);
+            }
+          }
+        }
+      }
+      ok = bar.sync();
+    }
     if (blockIdx.x == 0 && tid == 0) {
       // clamp the published count to the capacity
       const unsigned n = my_hdr[0];
@@ -371,8 +477,10 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
 
   if (a.phases & kPhaseExchange) {
     // ---- phase X: pull every rank's list and scatter-add it ----
-    for (int step = 0; step < world; ++step) {
-      const int p = (rank + step) % world;  // own list first: no waiting
+    // Lists are applied in rank order 0..W-1 on every rank, with a grid barrier between
+    // lists when more than two ranks contribute: floating-point addition is not
+    // associative, and all replicas must end up with bit-identical gradients.
+    for (int p = 0; p < world; ++p) {
       __shared__ unsigned peer_count;
       if (tid == 0) {
         unsigned n = 0;
@@ -401,6 +509,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         if (e + 3 < n) atomicAdd(a.out + ix.w, __uint_as_float(v.w) * a.scale);
       }
       __syncthreads();
+      if (world > 2 && p + 1 < world) bar.sync();
     }
     // acknowledge: the peers may now reuse their slot of this parity
     bar.sync();
@@ -434,7 +543,7 @@ cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t s
   cudaError_t err = cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream);
   if (err != cudaSuccess) return err;
   if (a.phases & kPhaseCompress) {
-    err = cudaMemsetAsync(a.state, 0, sizeof(SparseState) * (size_t)a.nseg, stream);
+    err = cudaMemsetAsync(a.state, 0, sizeof(SparseState) * (size_t)(a.nseg + 1), stream);
     if (err != cudaSuccess) return err;
   }
   SparseArgs copy = a;

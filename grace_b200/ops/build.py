@@ -94,10 +94,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 def ensure_built() -> Path:
-    """Build if the library is missing or older than its sources."""
+    """Build if the library is missing or older than its sources.  Several
+    ranks may start at once: an exclusive file lock makes one of them build
+    while the others wait and then find the library current."""
     if is_current():
         return TARGET
-    return build()
+    import fcntl
+
+    BUILD.mkdir(exist_ok=True)
+    with open(BUILD / "build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if is_current():
+                return TARGET
+            return build()
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
 
 
 if __name__ == "__main__":

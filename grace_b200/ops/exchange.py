@@ -117,7 +117,8 @@ class ExchangeChannel:
         self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
         self.status_event: Optional[torch.cuda.Event] = None
         self.hist = torch.zeros(max(1, nseg) * 4096, dtype=torch.int32, device=dev)
-        self.sparse_state = torch.zeros(max(1, nseg) * (C.SPARSE_STATE_BYTES // 4), dtype=torch.int32, device=dev)
+        self.sparse_state = torch.zeros((max(1, nseg) + 1) * (C.SPARSE_STATE_BYTES // 4), dtype=torch.int32, device=dev)
+        self.cand = None  # candidate list of the fast top-k path, allocated by run_sparse on first use
         self.quant_stats = torch.zeros(max(1, nseg) * C.QUANT_STATS_BYTES, dtype=torch.uint8, device=dev)
 
     def next_seq(self) -> int:
@@ -206,12 +207,19 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
     for t in (g, acc, u, out):
         if t is not None:
             assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    cand_cap = 0
+    if mode == SPARSE_TOPK and levels == 3 and (phases & PHASE_COMPRESS):
+        if channel.cand is None:
+            channel.cand_cap = max(65536, layout.total // 8)
+            channel.cand = torch.empty(2 * channel.cand_cap, dtype=torch.int32, device=channel.device)
+        cand_cap = channel.cand_cap
     C.sparse_exchange(
         _ptr(g), _ptr(acc), _ptr(u), _ptr(out), segs_dev.data_ptr(), len(layout.names), layout.total, mode, levels,
         beta, gamma, momentum, threshold, scale, channel.hist.data_ptr(), channel.sparse_state.data_ptr(),
         channel.barrier.data_ptr(), channel.status.data_ptr(), cap, phases, heap.rank, heap.world, seq,
         channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
-        _stream_ptr(),
+        _stream_ptr(), channel.cand.data_ptr() if cand_cap else 0,
+        (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
     )
     channel.post_status()
     return seq

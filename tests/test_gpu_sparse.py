@@ -195,3 +195,36 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     assert err.value.code == 2 and err.value.detail == 1
     # the context is still alive
     assert torch.ones(4, device=_dev()).sum().item() == 4
+
+
+def test_dense_overlap_is_bit_identical_across_ranks():
+    """Many indices chosen by three or more ranks: the aggregate must still be
+    bit-identical on every rank (lists are applied in rank order)."""
+    W, n = 4, 200_000
+    vw = _world(W, {"compressor": "topk", "memory": "none", "communicator": "allgather", "compress_ratio": 0.4})
+    grads = [_rand(n, seed=900 + r) for r in range(W)]
+    outs = vw.step(grads, "w")
+    vw.check()
+    expect = torch.zeros(n, device=_dev())
+    k = int(n * 0.4)
+    for r in range(W):  # same order as the kernel: rank 0 first
+        expect += _dense_topk(grads[r], k) * (1.0 / W)
+    for r in range(W):
+        assert torch.equal(outs[r], expect)
+
+
+@pytest.mark.parametrize("n,ratio", [(3_000_000, 0.001), (500_000, 0.5), (8192, 0.01)])
+def test_fast_select_path_large_and_small(n, ratio):
+    """Sizes / ratios on both sides of the candidate-list capacity."""
+    from grace_b200.ops.sparse import topk_select
+
+    x = _rand(n, seed=n)
+    k = max(1, int(n * ratio))
+    vals, idx = topk_select(x, k)
+    assert idx.long().unique().numel() == k
+    assert torch.equal(vals, x[idx.long()])
+    assert torch.equal(vals.abs().sort(descending=True).values, torch.topk(x.abs(), k).values)
+    heavy = torch.full((300_000,), 0.5, device=_dev())   # every key in one bin: falls back to the full passes
+    heavy[:1000] = 2.0
+    vals, idx = topk_select(heavy, 5000)
+    assert idx.long().unique().numel() == 5000 and (vals == 2.0).sum() == 1000
