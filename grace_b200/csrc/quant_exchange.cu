@@ -550,6 +550,64 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
           }
           __syncthreads();
         }
+        if (T::bits == 8 && world > 1) {
+          // 8-bit codes, remote peers: one 16-byte load brings 16 codes, a warp covers 512 elements per load
+          // instruction (remote reads over NVLink need large requests in flight); kX such loads per
+          // peer are issued before the first one is consumed.
+          constexpr int kX = 2;
+          for (long long w0 = b0 + 512ll * warp; w0 < e0; w0 += 512ll * kWarps * kX) {
+            float acc16[kX][16];
+#pragma unroll
+            for (int q = 0; q < kX; ++q)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc16[q][j] = 0.f;
+            for (int p = 0; p < world; ++p) {
+              const char* slot = a.peers.heap[p] + a.peers.slot_off;
+              uint4 cw[kX];
+              float dq[kX];
+#pragma unroll
+              for (int q = 0; q < kX; ++q) {
+                const long long i = w0 + 512ll * kWarps * q + 16 * lane;
+                cw[q] = make_uint4(0u, 0u, 0u, 0u);
+                dq[q] = 0.f;
+                if (i < e0) {
+                  cw[q] = ld_cg_u4(slot + off_codes + (size_t)i);
+                  if (C == kCodecQSGD) dq[q] = ld_cg_f32(slot + off_norms + (size_t)(i >> 7) * 4);
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < kX; ++q) {
+                const unsigned words[4] = {cw[q].x, cw[q].y, cw[q].z, cw[q].w};
+                const float d = dq[q] / (float)a.quantum;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                  if (C == kCodecQSGD) acc16[q][j] += d * (float)(int)(signed char)byte;
+                  if (C == kCodecNatural) acc16[q][j] += natural_decode(byte);
+                  if (C == kCodecU8bit) {
+                    const int code = (int)(signed char)byte;
+                    const int ab = code < 0 ? -code : code;
+                    const float sg = code > 0 ? 1.f : (code < 0 ? -1.f : 0.f);
+                    acc16[q][j] += s_edges[ab] * s_peer[p].s0 * sg;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < kX; ++q) {
+              const long long i = w0 + 512ll * kWarps * q + 16 * lane;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const long long iv = i + 4 * v;
+                if (iv >= e0) continue;
+                const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
+                const float ov[4] = {acc16[q][4 * v] * a.scale, acc16[q][4 * v + 1] * a.scale,
+                                     acc16[q][4 * v + 2] * a.scale, acc16[q][4 * v + 3] * a.scale};
+                store4(a.out, iv, valid, ov);
+              }
+            }
+          }
+        } else
         for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
           // kU groups per warp trip; for every peer the kU loads are issued before they are consumed
           float sum[kU][4];
