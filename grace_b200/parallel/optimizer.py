@@ -263,10 +263,12 @@ def DistributedOptimizer(optimizer, grace=None, named_parameters=None, compressi
     obj = cls.__new__(cls)
     cls.__init__(obj, optimizer.param_groups, named_parameters, grace, compression, backward_passes_per_step, op,
                  gradient_predivide_factor, num_groups, flat, always_hook)
-    # keep what the wrapped optimizer had already set up beyond the base class
-    # (per-parameter state, flat buffers of FusedSGD, ...)
-    base_keys = set(obj.__dict__.keys())
+    # keep what the wrapped optimizer had already set up (per-parameter state, flat buffers and
+    # momentum of FusedSGD, ...): everything except what this wrapper itself owns
+    own = {"param_groups", "defaults", "_grace", "_compression", "_parameter_names", "backward_passes_per_step",
+           "_allreduce_delay", "op", "gradient_predivide_factor", "_num_groups", "_handles", "_grad_accs",
+           "_requires_update", "_synchronized", "_should_synchronize", "_flat", "_bucket_events", "_side_stream"}
     for key, value in optimizer.__dict__.items():
-        if key == "state" or key not in base_keys:
+        if key not in own and not key.startswith("_optimizer_") and not key.startswith("_zero_grad_profile"):
             obj.__dict__[key] = value
     return obj

@@ -197,3 +197,16 @@ def test_missing_hooks_are_launched_at_synchronize():
     model[0](torch.randn(5, 4)).sum().backward()  # second layer never gets a gradient hook call
     d.step()
     assert len(fake.sent) == 4
+
+
+def test_wrapper_keeps_the_wrapped_optimizers_own_attributes():
+    from grace_b200.optim import FusedSGD
+    from grace_b200.parallel import DistributedOptimizer
+
+    m = torch.nn.Linear(3, 2)
+    opt = FusedSGD(m.parameters(), lr=0.1, momentum=0.9)
+    opt.grad_scale = 0.5
+    marker = object()
+    opt.flat = marker
+    d = DistributedOptimizer(opt, grace=_FakeGrace(), named_parameters=m.named_parameters(), always_hook=True)
+    assert d.flat is marker and d.grad_scale == 0.5 and d.param_groups[0]["lr"] == 0.1
