@@ -64,7 +64,19 @@ class _Plan:
         nseg = len(layout.names)
         self.ks = None
         if kind == "sparse":
-            if isinstance(comp, C_.ThresholdCompressor):
+            self.kprefix = self.seg_seed = None
+            if isinstance(comp, C_.RandomKCompressor):
+                self.mode = X.SPARSE_RANDOMK
+                self.ks = [topk_count(n, comp.compress_ratio) for n in layout.numels]
+                self.cap = X.sparse_capacity(layout, self.ks, self.mode)
+                prefix = [0]
+                for k in self.ks:
+                    prefix.append(prefix[-1] + k)
+                self.kprefix = torch.tensor(prefix, dtype=torch.int32, device=device)
+                seeds = [_name_seed(owner.seed, n) for n in layout.names]
+                self.seg_seed = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in seeds],
+                                             dtype=torch.int64, device=device)
+            elif isinstance(comp, C_.ThresholdCompressor):
                 self.mode = X.SPARSE_THRESHOLD
                 self.cap = X.sparse_capacity(layout, [], self.mode, owner.max_ratio)
             else:
@@ -81,7 +93,10 @@ class _Plan:
         self.heap = owner._make_heap(layout.key(), heap_bytes)
         self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
         self.segs = X.segments_to_device(layout, self.ks, device)
-        self.acc = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_acc else None
+        # the sparse kernel zeroes the output while it reads the gradient: when both alias (in-place
+        # exchange) the accumulator is where later passes re-read the values, so it always exists there
+        need_acc = owner._needs_acc or kind == "sparse"
+        self.acc = torch.zeros(layout.total, dtype=torch.float32, device=device) if need_acc else None
         self.u = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_u else None
         self.mom = torch.zeros(layout.total, dtype=torch.float32, device=device) if owner._needs_mom else None
         self.seed = _name_seed(owner.seed, "|".join(layout.names[:4]) + str(layout.total))
@@ -119,7 +134,7 @@ class FusedExchange(Communicator):
 
         if isinstance(mem, M_.PowerSGDMemory) or isinstance(comp, C_.PowerSGDCompressor):
             self._kind = "powersgd"
-        elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor)):
+        elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor, C_.RandomKCompressor)):
             if isinstance(mem, M_.DgcMemory) and (mem.gradient_clipping or isinstance(comp, C_.ThresholdCompressor)):
                 self._kind = None
             elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.DgcMemory)):
@@ -192,7 +207,7 @@ class FusedExchange(Communicator):
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,
                 beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
                 threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
-                phases=phases, seq=seq)
+                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps)
         else:
             seq = X.run_quant(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,

@@ -45,7 +45,7 @@ enum Phase : int {
 };
 
 // ---------------------------------------------------------------- sparse ----
-enum SparseMode : int { kSparseTopK = 0, kSparseThreshold = 1 };
+enum SparseMode : int { kSparseTopK = 0, kSparseThreshold = 1, kSparseRandomK = 2 };
 
 struct SparseState {       // per segment, device scratch
   unsigned prefix;         // selected key prefix after each radix level
@@ -71,6 +71,10 @@ struct SparseArgs {
   float* cand_val;    // candidate list of the fast select path (nullable)
   int* cand_idx;
   unsigned cand_cap;  // capacity of the candidate list in entries (0 disables the fast path)
+  // Random-k: every rank draws the same positions from Philox(seed of the tensor, step), so only values travel.
+  const int* kprefix;               // nseg + 1 prefix sums of k (entry e belongs to the segment with kprefix[s] <= e)
+  const unsigned long long* seg_seed;  // nseg seeds (derived from the tensor names, identical on every rank)
+  unsigned rk_step;                 // per-plan step counter (part of the Philox counter)
   unsigned* barrier;  // one word, zeroed by the launcher
   unsigned* status;   // 4 words
   unsigned cap;       // slot capacity in entries (multiple of 16)

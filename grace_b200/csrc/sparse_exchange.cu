@@ -22,6 +22,7 @@
 // memory/dgc.py:21-39.
 #include "common.cuh"
 #include "exchange.h"
+#include "philox.cuh"
 #include "segments.cuh"
 
 namespace grace {
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   const long long hi = lo + chunk < a.total ? lo + chunk : a.total;
   const float* __restrict__ src = a.acc ? a.acc : a.g;
   const bool topk = a.mode == kSparseTopK;
+  const bool randomk = a.mode == kSparseRandomK;
 
   if (a.phases & kPhaseCompress) {
     // Before overwriting the slot of parity (seq & 1): every peer must have
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         }
         if (topk) {
           flush_hist(sm, a.hist + (size_t)s * kBins);
-        } else {
+        } else if (!randomk) {
           tmax = warp_max(tmax);
           if ((tid & 31) == 0 && tmax > -INFINITY) atomicMax(&a.state[s].max_bits, ordered_bits(tmax));
         }
@@ -322,7 +324,34 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       if (lane == 0) sm.ccnt[warp] = 0;
       __syncwarp();
     };
-    if (ok && lo < hi) {
+    if (ok && randomk) {
+      // ---- random-k: gather the agreed positions; the residual is zeroed there after a barrier
+      //      (positions are drawn with replacement, duplicates must all read the same value) ----
+      const int total_k = a.kprefix[a.nseg];
+      auto locate = [&](int e, int& sgm) {
+        int lo_s = 0, hi_s = a.nseg;
+        while (lo_s + 1 < hi_s) {
+          const int m = (lo_s + hi_s) >> 1;
+          if (a.kprefix[m] <= e) lo_s = m; else hi_s = m;
+        }
+        sgm = lo_s;
+      };
+      for (int e = blockIdx.x * kBlock + tid; e < total_k; e += gridDim.x * kBlock) {
+        int sgm;
+        locate(e, sgm);
+        const unsigned j = (unsigned)(e - a.kprefix[sgm]);
+        const Philox4 r4 = philox_group((uint64_t)(j >> 2), a.rk_step, 7u, a.seg_seed[sgm]);
+        const unsigned word = (j & 3) == 0 ? r4.x : ((j & 3) == 1 ? r4.y : ((j & 3) == 2 ? r4.z : r4.w));
+        const long long idx = a.segs[sgm].offset + (long long)(word % (unsigned)a.segs[sgm].numel);
+        my_vals[e] = src[idx];
+        my_idx[e] = (int)idx;
+      }
+      ok = bar.sync();
+      if (ok && a.acc)
+        for (int e = blockIdx.x * kBlock + tid; e < total_k; e += gridDim.x * kBlock) a.acc[my_idx[e]] = 0.f;
+      if (blockIdx.x == 0 && tid == 0) my_hdr[0] = (unsigned)total_k;
+    }
+    if (ok && lo < hi && !randomk) {
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         const unsigned pivot = a.state[s].prefix;
         const unsigned need = a.state[s].need;
@@ -477,6 +506,31 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
 
   if (a.phases & kPhaseExchange) {
     // ---- phase X: pull every rank's list and scatter-add it ----
+    if (randomk) {
+      __shared__ int s_rk_ok;
+      if (tid == 0) s_rk_ok = 1;
+      __syncthreads();
+      if (tid < world) {
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ready_off) + tid;
+        if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid)) s_rk_ok = 0;
+      }
+      __syncthreads();
+      const int total_k = a.kprefix[a.nseg];
+      if (s_rk_ok) {
+        for (int e = blockIdx.x * kBlock + tid; e < total_k; e += gridDim.x * kBlock) {
+          float sum = 0.f;
+          for (int p = 0; p < world; ++p)
+            sum += ld_cg_f32(a.peers.heap[p] + a.peers.slot_off + kSlotHeaderBytes + (size_t)e * 4);
+          a.out[my_idx[e]] = sum * a.scale;   // duplicates of a position write the same value
+        }
+      }
+      bar.sync();
+      if (blockIdx.x == 0 && tid < world && tid != rank && !status.failed()) {
+        uint64_t* ack = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ack_off) + rank;
+        st_release_sys(ack, a.peers.seq);
+      }
+      return;
+    }
     // Lists are applied in rank order 0..W-1 on every rank, with a grid barrier between
     // lists when more than two ranks contribute: floating-point addition is not
     // associative, and all replicas must end up with bit-identical gradients.

@@ -22,7 +22,7 @@ from ..parallel.symm import SymmetricHeap
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
 PHASE_REDUCE = 8  # two-phase (alltoall) mode: reduce my chunk, re-encode, publish again
-SPARSE_TOPK, SPARSE_THRESHOLD = 0, 1
+SPARSE_TOPK, SPARSE_THRESHOLD, SPARSE_RANDOMK = 0, 1, 2
 CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8}
 
 STATUS_TEXT = {
@@ -184,7 +184,7 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 
 
 def sparse_capacity(layout: FlatLayout, ks: Sequence[int], mode: int, max_ratio: float = 1.0) -> int:
-    if mode == SPARSE_TOPK:
+    if mode in (SPARSE_TOPK, SPARSE_RANDOMK):
         cap = sum(ks)
     else:
         cap = int(sum(layout.numels) * max_ratio) + 16
@@ -195,7 +195,8 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
                acc: Optional[torch.Tensor], u: Optional[torch.Tensor], out: Optional[torch.Tensor], *, mode: int,
                cap: int, beta: float = 1.0, gamma: float = 1.0, momentum: float = 0.0, threshold: float = 0.0,
                scale: float = 1.0, levels: int = 3, phases: int = PHASE_ALL, seq: Optional[int] = None,
-               grid: Optional[int] = None) -> int:
+               grid: Optional[int] = None, kprefix: Optional[torch.Tensor] = None,
+               seg_seed: Optional[torch.Tensor] = None, rk_step: int = 0) -> int:
     C = native()
     heap = channel.heap
     if seq is None:
@@ -220,6 +221,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
         _stream_ptr(), channel.cand.data_ptr() if cand_cap else 0,
         (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
+        _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF,
     )
     channel.post_status()
     return seq

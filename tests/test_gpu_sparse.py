@@ -228,3 +228,49 @@ def test_fast_select_path_large_and_small(n, ratio):
     heavy[:1000] = 2.0
     vals, idx = topk_select(heavy, 5000)
     assert idx.long().unique().numel() == 5000 and (vals == 2.0).sum() == 1000
+
+
+def test_randomk_same_positions_on_all_ranks_and_mean_of_values():
+    W, n, ratio = 3, 50_000, 0.02
+    k = int(n * ratio)
+    vw = _world(W, {"compressor": "randomk", "memory": "residual", "communicator": "allreduce", "compress_ratio": ratio})
+    assert vw.comms[0]._kind == "sparse"
+    residual = [torch.zeros(n, device=_dev()) for _ in range(W)]
+    prev_idx = None
+    for step in range(2):
+        grads = [_rand(n, seed=40 * step + r) for r in range(W)]
+        outs = vw.step(grads, "w")
+        vw.check()
+        plans = [next(iter(c._plans.values())) for c in vw.comms]
+        seq = plans[0].channel.seq
+        idx = [p.channel.slot_view(seq, k, torch.int32, 128 + p.cap * 4).long() for p in plans]
+        for r in range(1, W):
+            assert torch.equal(idx[0], idx[r]), "every rank must draw the same positions"
+        assert idx[0].min() >= 0 and idx[0].max() < n
+        if prev_idx is not None:
+            assert not torch.equal(prev_idx, idx[0])  # the step is part of the counter
+        prev_idx = idx[0].clone()
+        expect = torch.zeros(n, device=_dev())
+        acc = [residual[r] + grads[r] for r in range(W)]
+        expect[idx[0]] = sum(a[idx[0]] for a in acc) / W
+        for r in range(W):
+            torch.testing.assert_close(outs[r], expect, rtol=1e-6, atol=1e-9)
+            res = acc[r].clone()
+            res[idx[0]] = 0
+            residual[r] = res
+            torch.testing.assert_close(plans[r].acc[:n], res, rtol=0, atol=0)
+
+
+def test_in_place_exchange_without_memory():
+    """out aliases the gradient and there is no error-feedback memory."""
+    from grace_b200 import grace_from_params
+
+    n, ratio = 30_000, 0.01
+    grc = grace_from_params({"compressor": "topk", "memory": "none", "communicator": "allgather", "world_size": 1,
+                             "compress_ratio": ratio, "fused": True})
+    x = _rand(n, 3)
+    expect = _dense_topk(x, int(n * ratio))
+    out = grc.step(x, "w")
+    grc.check()
+    assert out.data_ptr() == x.data_ptr()
+    torch.testing.assert_close(out, expect, rtol=0, atol=0)
