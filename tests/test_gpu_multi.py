@@ -121,3 +121,59 @@ def test_fused_exchange_matches_library_over_real_gpus():
                 assert worst < 0.2, (comp, worst)
             else:
                 assert worst < 1e-5, (comp, worst)
+
+
+def _timeout_entry(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from grace_b200 import grace_from_params
+        from grace_b200.ops.exchange import GraceCommError
+
+        store = dist.distributed_c10d._get_default_store()
+        grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                                 "world_size": world, "fused": True, "compress_ratio": 0.01, "timeout_ms": 500})
+        x = torch.randn(100_000, device=dev) * 1e-3
+        for _ in range(2):                       # two healthy steps
+            grc.step(x.clone(), "w")
+        grc.check()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 1:
+            # leaves between steps: nothing of its own in flight, it just never launches step 3
+            store.wait(["rank0_done"])
+            ret[rank] = "left"
+        else:
+            grc.step(x.clone(), "w")             # the peer never publishes: bounded wait expires
+            try:
+                grc.check()
+                ret[rank] = "no error"
+            except GraceCommError as e:
+                ret[rank] = (e.code, e.detail)
+            # the context is still usable
+            ret["alive"] = float(torch.ones(8, device=dev).sum())
+            store.set("rank0_done", "1")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_peer_that_stops_launching_is_reported_as_timeout():
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _port()
+        procs = [ctx.Process(target=_timeout_entry, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        for p in procs:
+            assert p.exitcode == 0, "rank exited with %s" % p.exitcode
+        res = dict(ret)
+    assert res[1] == "left"
+    assert res[0] == (2, 1)          # timeout waiting for peer 1's data
+    assert res["alive"] == 8.0
