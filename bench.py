@@ -258,6 +258,8 @@ def main():
     ap.add_argument("--config", default="resnet50_dgc", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (invalidates the headline)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--bucket-mb", type=float, default=None,
+                    help="exchange gradients in buckets of this size from backward hooks (overlap); default one bucket")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -271,6 +273,8 @@ def main():
     cfg = dict(CONFIGS[args.config])
     if args.batch:
         cfg["batch"] = args.batch
+    if args.bucket_mb:
+        cfg["bucket_bytes"] = int(args.bucket_mb * (1 << 20))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -2,7 +2,7 @@
 """Compressed-exchange microbenchmark (no model).
 
 fp32 gradients of 1M .. 256M elements drawn from N(0, 1e-3) with seed = rank;
-TopK 1 %, DGC 0.1 %, QSGD 8-bit, EF-signSGD (majority-style scaled vote),
+TopK 1 %, DGC 0.1 %, QSGD 8-bit (all-gather and two-phase "alltoall" mode), EF-signSGD (majority-style scaled vote),
 natural compression, each with its error-feedback memory, and PowerSGD rank 4
 on 4096 x 4096.  Measures compensate + compress + exchange + decompress for
 
@@ -38,6 +38,7 @@ CASES = {
     "topk1": dict(compressor="topk", memory="residual", communicator="allgather", compress_ratio=0.01),
     "dgc01": dict(compressor="dgc", memory="dgc", communicator="allgather", compress_ratio=0.001, momentum=0.9),
     "qsgd8": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127),
+    "qsgd8_a2a": dict(compressor="qsgd", memory="residual", communicator="alltoall", quantum_num=127),
     "efsign": dict(compressor="efsignsgd", memory="efsignsgd", communicator="allgather", lr=0.1),
     "natural": dict(compressor="natural", memory="residual", communicator="allgather"),
     "powersgd4": dict(compressor="powersgd", memory="powersgd", communicator="allreduce", compress_rank=4,
@@ -62,6 +63,9 @@ def roofline_ms(case, n, world, bw):
     elif case in ("qsgd8", "natural"):
         hbm = (12 + 1 + world + 4) * n                       # g,r read, r write, code write, W code reads, out write
         link = (world - 1) * n * (1 + 4.0 / 128)
+    elif case == "qsgd8_a2a":
+        hbm = 19 * n                                         # encode 13 B, reduce my chunk 1 + 1/W B, gather 1 + 4 B
+        link = 2.0 * (world - 1) / world * n * (1 + 4.0 / 128)
     elif case == "efsign":
         hbm = (12 + 8 + 4) * n + (1 + world) * n / 8
         link = (world - 1) * n / 8

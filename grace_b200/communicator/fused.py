@@ -178,11 +178,11 @@ class FusedExchange(Communicator):
                                    self.world_size, isinstance(self.memory, M_.PowerSGDMemory), self.device,
                                    seed=self.seed, timeout_ms=self.timeout_ms, sm_limit=self.comm_sms)
                 plan.kind = "powersgd"
-                pending = getattr(self, "_pending_state", None)
-                if pending:
-                    self._restore_plan(plan, pending)
             else:
                 plan = _Plan(self, layout, self._kind)
+            pending = getattr(self, "_pending_state", None)
+            if pending:  # a checkpoint was loaded before this layout was first used
+                self._restore_plan(plan, pending)
             self._plans[key] = plan
         return plan
 
@@ -289,6 +289,19 @@ class FusedExchange(Communicator):
 
     def send_receive(self, tensors, name, ctx):
         return self._fallback.send_receive(tensors, name, ctx)
+
+    def reset(self):
+        """After a ``GraceCommError``: clear flags, sequence numbers and scratch of every plan.
+        Call it on every rank, then synchronise the ranks on the host (``dist.barrier()``) before
+        the next exchange.  Error-feedback state is kept."""
+        for plan in self._plans.values():
+            if plan.kind == "powersgd":
+                if plan.matrices:
+                    plan.channel.reset()
+                if plan.dense:
+                    plan.dense_channel.reset()
+            else:
+                plan.channel.reset()
 
     def check(self):
         """Block until every launched exchange finished; raise on failure."""

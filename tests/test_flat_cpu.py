@@ -1,0 +1,61 @@
+"""Flat layouts, buckets and the flat SGD path on CPU tensors."""
+import torch
+
+from grace_b200.ops.exchange import ALIGN_ELEMS, FlatLayout
+from grace_b200.parallel.flat import FlatParams
+
+
+def test_flat_layout_alignment_and_segments():
+    lay = FlatLayout.from_named([("a", 5), ("b", 128), ("c", 300)])
+    assert lay.offsets == [0, 128, 256] and lay.total == 256 + 384
+    assert all(o % ALIGN_ELEMS == 0 for o in lay.offsets)
+    raw = lay.segment_bytes([1, 2, 3])
+    assert len(raw) == 3 * 16
+    flat = torch.arange(lay.total, dtype=torch.float32)
+    sl = lay.slices(flat)
+    assert sl["b"][0] == 128 and sl["c"].numel() == 300
+    assert FlatLayout.single("x", 7, (7,)).shape_list() == [(7,)]
+
+
+def test_flat_params_views_and_buckets():
+    model = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3), torch.nn.BatchNorm2d(8), torch.nn.Flatten(),
+                                torch.nn.Linear(8 * 6 * 6, 10))
+    model = model.to(memory_format=torch.channels_last)
+    before = [p.detach().clone() for p in model.parameters()]
+    flat = FlatParams(model.named_parameters(), bucket_bytes=4096)
+    for p, b in zip(model.parameters(), before):
+        assert torch.equal(p.detach(), b)                       # values and logical layout preserved
+        assert p.grad is not None and p.grad.shape == p.shape
+    assert flat.check_views()
+    out = model(torch.randn(2, 3, 8, 8)).sum()
+    out.backward()
+    assert flat.check_views(), "backward must accumulate into the flat gradient buffer"
+    assert flat.flat_g.abs().sum() > 0
+    # buckets tile the flat buffer from the end (gradients arrive last layer first)
+    assert flat.buckets[0].end == flat.layout.total and flat.buckets[-1].start == 0
+    covered = sorted((b.start, b.end) for b in flat.buckets)
+    assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+    names = [n for b in flat.buckets for n in b.layout.names]
+    assert sorted(names) == sorted(flat.names)
+    assert flat.buckets[0].layout.shapes is not None
+    flat.zero_grad()
+    assert flat.flat_g.abs().sum() == 0
+
+
+def test_fused_sgd_flat_cpu_fallback_matches_torch():
+    from grace_b200.optim import FusedSGD
+
+    torch.manual_seed(0)
+    m1 = torch.nn.Linear(6, 4)
+    m2 = torch.nn.Linear(6, 4)
+    m2.load_state_dict(m1.state_dict())
+    flat = FlatParams(m1.named_parameters())
+    a = FusedSGD(m1.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-3, flat=flat)
+    b = torch.optim.SGD(m2.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-3)
+    for _ in range(3):
+        x = torch.randn(5, 6)
+        a.zero_grad(); b.zero_grad()
+        m1(x).sum().backward(); m2(x).sum().backward()
+        a.step(); b.step()
+    for p, q in zip(m1.parameters(), m2.parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-6, atol=1e-6)
