@@ -123,6 +123,7 @@ PYBIND11_MODULE(_C, m) {
   // ---- fused PowerSGD (tcgen05) ----
   m.def("lowrank_smem_bytes", &lowrank_smem_bytes);
   m.def("lowrank_max_grid", &lowrank_max_grid);
+  m.def("lowrank_occupancy", &lowrank_occupancy);
   m.attr("LOWRANK_MATRIX_BYTES") = sizeof(LowRankMatrix);
   m.attr("TENSOR_MAP_BYTES") = 128;
   m.attr("MAPS_PER_MATRIX") = (int)kMapsPerMatrix;

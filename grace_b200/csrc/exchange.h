@@ -183,6 +183,7 @@ struct LowRankArgs {
 
 size_t lowrank_smem_bytes();
 int lowrank_max_grid(int device, int sm_limit);
+int lowrank_occupancy(int dynamic_smem_bytes);
 cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream);
 int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m);
 

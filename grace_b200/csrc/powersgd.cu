@@ -40,7 +40,7 @@ namespace grace {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kStages = 4;             // 4 x (16 + 16 + 2) KiB of tiles in flight per CTA, one CTA per SM
+constexpr int kStages = 6;             // 6 x (16 + 16 + 2) KiB ring per CTA (one CTA per SM: the runtime reports one resident CTA for this kernel at any shared-memory size)
 constexpr int kTileRows = 128;          // MMA M
 constexpr int kTileK = 32;              // fp32 elements per 128-byte swizzle row
 constexpr int kRankPad = 16;            // MMA N
@@ -48,6 +48,7 @@ constexpr int kATileBytes = kTileRows * kTileK * 4;   // 16 KiB
 constexpr int kBTileBytes = kRankPad * kTileK * 4;    // 2 KiB
 constexpr int kKTilesPerItem = 16;      // split-K granularity: 512 columns (S1) / 512 rows (S2)
 constexpr unsigned kTmemCols = 32;
+constexpr int kProducerThread = 32;      // lane 0 of warp 1: TMA loads and stores
 constexpr int kMaxRank = 8;              // ranks 1..8 (buffers are padded to kRankPad columns)
 constexpr int kS3Rows = 64;             // rows per stage-3 work item
 
@@ -116,6 +117,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
 }
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -176,7 +178,9 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
   int p_kt = p_valid ? pit.kt0 : 0, c_kt = c_valid ? cit.kt0 : 0;
   unsigned p_step = step_counter, c_step = step_counter;
 
-  auto produce = [&]() {  // thread 0 only: issue the TMA loads of the next (item, k-tile)
+  // Two single-thread roles run side by side after each CTA barrier: thread 0 issues the MMAs,
+  // thread kProducerThread issues the TMA store of M' and refills the ring.
+  auto produce = [&]() {  // producer thread only: issue the TMA loads of the next (item, k-tile)
     if (!p_valid) return;
     const unsigned slot = p_step % kStages;
     if (p_step >= kStages) {
@@ -186,7 +190,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
         p_valid = false;
         return;
       }
-      tma_wait_read0();
+      tma_wait_read1();  // all of this thread's stores except the newest one have read their tile
     }
     const LowRankMatrix& M = a.mats[pit.mat];
     const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)pit.mat * kMapsPerMatrix;
@@ -210,13 +214,17 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
     }
   };
 
-  if (tid == 0) {
+  if (tid == kProducerThread) {
     for (int i = 0; i < kStages - 1; ++i) produce();
   }
 
+  long long t_wait = 0, t_work = 0, t_sync = 0, t_issue = 0, t_prod = 0, t_epi = 0;
+  const bool prof = (a.part & 0x100) && blockIdx.x == 0 && tid == 0;
   while (c_valid) {
     const unsigned slot = c_step % kStages;
+    long long t0 = prof ? clock64() : 0;
     bool ok = mbar_wait(&sm.full[slot], (c_step / kStages) & 1, a.peers.timeout_ns, status, 200 + slot);
+    if (prof) { const long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; }
     if (add_residual && ok) {
       float4* pa = reinterpret_cast<float4*>(sm.a[slot]);
       const float4* pr = reinterpret_cast<const float4*>(sm.r[slot]);
@@ -254,15 +262,22 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       fence_async_smem();
     }
     if (!ok) sm.bail = 1;
+    if (prof) { const long long t1 = clock64(); t_work += t1 - t0; t0 = t1; }
     __syncthreads();
+    if (prof) { const long long t1 = clock64(); t_sync += t1 - t0; t0 = t1; }
     if (sm.bail) break;
     const bool last_kt = (c_kt + 1 >= cit.kt1);
-    if (tid == 0) {
-      const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)cit.mat * kMapsPerMatrix;
+    if (tid == kProducerThread) {
       if (add_residual) {  // M' goes back to the accumulator buffer
+        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)cit.mat * kMapsPerMatrix;
         tma_store_2d(maps + kMapA1, c_kt * kTileK, cit.blk * kTileRows, sm.a[slot]);
         tma_commit();
       }
+      // refill the slot used one step ago: its MMAs were issued a whole iteration earlier, so the
+      // wait inside produce() rarely stalls
+      produce();
+    }
+    if (tid == 0) {
       tc_fence_after();
       const uint32_t a_addr = smem_u32(sm.a[slot]), b_addr = smem_u32(sm.b[slot]);
 #pragma unroll
@@ -273,9 +288,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       }
       umma_commit(&sm.mma_done[slot]);
       if (last_kt) umma_commit(&sm.item_done);
-      // refill the slot used one step ago: its MMAs were issued a whole iteration earlier, so the
-      // wait inside produce() rarely stalls
-      produce();
+      if (prof) { const long long t1 = clock64(); t_issue += t1 - t0; t0 = t1; }
     }
     ++c_step;
     if (last_kt) {
@@ -310,12 +323,18 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       c_item += gridDim.x;
       c_valid = decode_item(a, STAGE, c_item, cit);
       c_kt = c_valid ? cit.kt0 : 0;
+      if (prof) { const long long t1 = clock64(); t_epi += t1 - t0; t0 = t1; }
     } else {
       ++c_kt;
     }
   }
+  if (prof) {
+    unsigned* w = a.status + 8 + (STAGE - 1) * 8;
+    w[0] = (unsigned)(t_wait >> 4); w[1] = (unsigned)(t_work >> 4); w[2] = (unsigned)(t_sync >> 4);
+    w[3] = (unsigned)(t_issue >> 4); w[4] = (unsigned)(t_prod >> 4); w[5] = (unsigned)(t_epi >> 4); w[6] = c_step;
+  }
   // drain: every issued load must land and every store must finish before smem is reused
-  if (tid == 0) {
+  if (tid == kProducerThread) {
     tma_wait_all0();
     while (c_step < p_step && !sm.bail) {  // loads issued ahead of a bail-out
       mbar_wait(&sm.full[c_step % kStages], (c_step / kStages) & 1, a.peers.timeout_ns, status, 400);
@@ -396,9 +415,10 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   //   everything, the split launches of the one-GPU emulation run
   //   [S1 | publish P] [reduce P, O, S2 | publish Q] [reduce Q, S3] as three
   //   launches selected by a.part (0 = all, 1..3 = that part only).
-  const bool part1 = a.part == 0 || a.part == 1;
-  const bool part2 = a.part == 0 || a.part == 2;
-  const bool part3 = a.part == 0 || a.part == 3;
+  const int part = a.part & 0xff;   // bit 8 of a.part asks CTA 0 to record per-phase cycle counts
+  const bool part1 = part == 0 || part == 1;
+  const bool part2 = part == 0 || part == 2;
+  const bool part3 = part == 0 || part == 3;
   bool ok = true;
 
   if (part1) {
@@ -600,7 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
 
   // ---- teardown ----
   __syncthreads();
-  if (tid == 0) tma_wait_all0();
+  if (tid == kProducerThread) tma_wait_all0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
@@ -623,6 +643,17 @@ int lowrank_max_grid(int device, int sm_limit) {
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
   if (per_sm > 1) per_sm = 1;
   return per_sm * sms;
+}
+
+// Resident CTAs per SM the runtime reports for a given dynamic shared-memory size (tuning aid).
+int lowrank_occupancy(int dynamic_smem_bytes) {
+  cudaFuncSetAttribute(powersgd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_smem_bytes);
+  int per_sm = -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, powersgd_kernel, kThreads, dynamic_smem_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return per_sm;
 }
 
 cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream) {

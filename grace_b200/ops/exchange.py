@@ -113,8 +113,8 @@ class ExchangeChannel:
         self.sm_limit = sm_limit or 0
         dev = self.device
         self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
-        self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
+        self.status = torch.zeros(32, dtype=torch.int32, device=dev)   # [0..3] error block, [8..] optional phase counters
+        self.status_host = torch.zeros(32, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
         self.status_event: Optional[torch.cuda.Event] = None
         self.hist = torch.zeros(max(1, nseg) * 4096, dtype=torch.int32, device=dev)
         self.sparse_state = torch.zeros((max(1, nseg) + 1) * (C.SPARSE_STATE_BYTES // 4), dtype=torch.int32, device=dev)
