@@ -550,6 +550,85 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
           }
           __syncthreads();
         }
+        if ((T::bits == 1 || T::bits == 2) && world > 1) {
+          // Bit-packed codes, remote peers: lane l fetches the whole code block of group g0 + l with
+          // 16-byte loads (all loads of up to four peers in flight), then the blocks are handed round
+          // with shuffles so that every group is decoded and stored by the full warp (coalesced).
+          constexpr int kWordsPerGroup = T::bits * 4;     // 4 words (1 bit) or 8 words (2 bits)
+          constexpr int kPeerChunk = T::bits == 2 ? 2 : 4;   // peers whose loads are in flight together
+          for (long long g0 = (b0 >> 7) + 32ll * warp; (g0 << 7) < e0; g0 += 32ll * kWarps) {
+            const long long my_group = g0 + lane;
+            const bool have = (my_group << 7) < e0;
+            // this lane's 4 elements of each of the 32 groups would need 128 accumulators,
+            // so the groups are processed in four rounds of eight
+#pragma unroll 1
+            for (int round = 0; round < 4; ++round) {
+              float acc[8][4];
+              int votes[8][4];
+#pragma unroll
+              for (int gi = 0; gi < 8; ++gi)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { acc[gi][j] = 0.f; votes[gi][j] = 0; }
+              for (int p0 = 0; p0 < world; p0 += kPeerChunk) {
+                unsigned w[kPeerChunk][kWordsPerGroup];
+#pragma unroll
+                for (int pp = 0; pp < kPeerChunk; ++pp) {
+#pragma unroll
+                  for (int k = 0; k < kWordsPerGroup; ++k) w[pp][k] = 0u;
+                  // lanes 8*round .. 8*round+7 own the groups of this round
+                  if (p0 + pp < world && have && (lane >> 3) == round) {
+                    const char* src_blk = a.peers.heap[p0 + pp] + a.peers.slot_off + off_codes +
+                                          (size_t)my_group * (kWordsPerGroup * 4);
+                    const uint4 v0 = ld_cg_u4(src_blk);
+                    w[pp][0] = v0.x; w[pp][1] = v0.y; w[pp][2] = v0.z; w[pp][3] = v0.w;
+                    if (T::bits == 2) {
+                      const uint4 v1 = ld_cg_u4(src_blk + 16);
+                      w[pp][4] = v1.x; w[pp][5] = v1.y; w[pp][6] = v1.z; w[pp][7] = v1.w;
+                    }
+                  }
+                }
+#pragma unroll
+                for (int pp = 0; pp < kPeerChunk; ++pp) {
+                  if (p0 + pp >= world) break;
+                  const SegScalars sp = s_peer[p0 + pp];
+#pragma unroll
+                  for (int gi = 0; gi < 8; ++gi) {
+                    const int owner = round * 8 + gi;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const unsigned b0w = __shfl_sync(0xffffffffu, w[pp][j], owner);
+                      const bool bit = (b0w >> lane) & 1u;
+                      if (T::bits == 2) {
+                        const unsigned ngw = __shfl_sync(0xffffffffu, w[pp][4 + j], owner);
+                        if (bit) acc[gi][j] += ((ngw >> lane) & 1u) ? -sp.s0 : sp.s0;
+                      } else {
+                        if (C == kCodecSign) votes[gi][j] += bit ? 1 : -1;
+                        if (C == kCodecEFSign) acc[gi][j] += bit ? sp.s0 : -sp.s0;
+                        if (C == kCodecOneBit) acc[gi][j] += bit ? sp.s0 : sp.s1;
+                      }
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int gi = 0; gi < 8; ++gi) {
+                const long long gb = (g0 + round * 8 + gi) << 7;
+                if (gb >= e0) break;  // warp-uniform
+                const long long i = gb + 4 * lane;
+                int valid = 0;
+                if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+                float ov[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (C == kCodecSign) ov[j] = votes[gi][j] >= 0 ? 1.f : -1.f;
+                  else if (C == kCodecEFSign) ov[j] = acc[gi][j] / a.lr;
+                  else ov[j] = acc[gi][j] * a.scale;
+                }
+                if (valid) store4(a.out, i, valid, ov);
+              }
+            }
+          }
+        } else
         if (T::bits == 8 && world > 1) {
           // 8-bit codes, remote peers: one 16-byte load brings 16 codes, a warp covers 512 elements per load
           // instruction (remote reads over NVLink need large requests in flight); kX such loads per
