@@ -394,34 +394,63 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
       const long long g_begin = chunk_groups * rank;
       const long long g_end = g_begin + chunk_groups < groups_total ? g_begin + chunk_groups : groups_total;
       if (s_ready2) {
-        for (long long grp = g_begin + (long long)blockIdx.x * kWarps + warp; grp < g_end; grp += (long long)gridDim.x * kWarps) {
-          const long long i = (grp << 7) + 4 * lane;
-          float xv[4] = {0.f, 0.f, 0.f, 0.f};
+        const long long wstride = (long long)gridDim.x * kWarps;
+        for (long long grp0 = g_begin + (long long)blockIdx.x * kWarps + warp; grp0 < g_end; grp0 += wstride * kU) {
+          // kU groups per warp trip; per peer, the kU loads are issued before they are consumed
+          float xs[kU][4];
+#pragma unroll
+          for (int q = 0; q < kU; ++q)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xs[q][j] = 0.f;
           for (int p = 0; p < world; ++p) {
             const char* slot = a.peers.heap[p] + a.peers.slot_off;
-            if (T::bits == 8) {
-              const unsigned word = ld_cg_u32(slot + off_codes + (size_t)i);
-              float dq = 0.f;
-              if (C == kCodecQSGD) dq = ld_cg_f32(slot + off_norms + (size_t)grp * 4) / (float)a.quantum;
+            uint4 w4[kU];
+            float dqs[kU];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const unsigned byte = (word >> (8 * j)) & 0xffu;
-                if (C == kCodecQSGD) xv[j] += dq * (float)(int)(signed char)byte;
-                else xv[j] += natural_decode(byte);
+            for (int q = 0; q < kU; ++q) {
+              const long long grp = grp0 + wstride * q;
+              const long long i = (grp << 7) + 4 * lane;
+              w4[q] = make_uint4(0u, 0u, 0u, 0u);
+              dqs[q] = 0.f;
+              if (grp >= g_end) continue;
+              if (T::bits == 8) {
+                w4[q].x = ld_cg_u32(slot + off_codes + (size_t)i);
+                if (C == kCodecQSGD) dqs[q] = ld_cg_f32(slot + off_norms + (size_t)grp * 4);
+              } else if (T::bits == 32) {
+                w4[q] = ld_cg_u4(slot + off_codes + (size_t)i * 4);
+              } else {
+                const char* q16 = slot + off_codes + (size_t)i * 2;
+                asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w4[q].x), "=r"(w4[q].y) : "l"(q16));
               }
-            } else if (T::bits == 32) {
-              const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
-              xv[0] += __uint_as_float(w.x); xv[1] += __uint_as_float(w.y);
-              xv[2] += __uint_as_float(w.z); xv[3] += __uint_as_float(w.w);
-            } else {
-              uint2 w;
-              const char* q = slot + off_codes + (size_t)i * 2;
-              asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(q));
-              const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w.x));
-              const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w.y));
-              xv[0] += f01.x; xv[1] += f01.y; xv[2] += f23.x; xv[3] += f23.y;
+            }
+#pragma unroll
+            for (int q = 0; q < kU; ++q) {
+              if (T::bits == 8) {
+                const float d = dqs[q] / (float)a.quantum;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned byte = (w4[q].x >> (8 * j)) & 0xffu;
+                  if (C == kCodecQSGD) xs[q][j] += d * (float)(int)(signed char)byte;
+                  else xs[q][j] += natural_decode(byte);
+                }
+              } else if (T::bits == 32) {
+                xs[q][0] += __uint_as_float(w4[q].x); xs[q][1] += __uint_as_float(w4[q].y);
+                xs[q][2] += __uint_as_float(w4[q].z); xs[q][3] += __uint_as_float(w4[q].w);
+              } else {
+                const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w4[q].x));
+                const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w4[q].y));
+                xs[q][0] += f01.x; xs[q][1] += f01.y; xs[q][2] += f23.x; xs[q][3] += f23.y;
+              }
             }
           }
+#pragma unroll
+          for (int q = 0; q < kU; ++q) {
+          const long long grp = grp0 + wstride * q;
+          if (grp >= g_end) break;  // warp-uniform
+          const long long i = (grp << 7) + 4 * lane;
+          float xv[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[j] = xs[q][j];
           // re-encode the reduced group (a second lossy step, with its own random stream)
           const size_t li = (size_t)((grp - g_begin) << 7) + 4 * lane;   // element index inside my chunk
           if (C == kCodecQSGD) {
@@ -467,6 +496,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
             w.y = *reinterpret_cast<unsigned*>(&h23);
             *reinterpret_cast<uint2*>(my_slot + off2_codes + li * 2) = w;
           }
+          }
         }
       }
       bar.sync();
@@ -486,38 +516,55 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
       __syncthreads();
       if (s_ready2 && lo < hi) {
         for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
-          for (long long gb = b0 + 128ll * warp; gb < e0; gb += 128ll * kWarps) {
-            const long long i = gb + 4 * lane;
-            int valid = 0;
-            if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-            const long long grp = gb >> 7;
-            const int owner = (int)(grp / chunk_groups);
-            const long long lg = grp - (long long)owner * chunk_groups;
-            const size_t li = (size_t)(lg << 7) + 4 * lane;
-            const char* slot = a.peers.heap[owner] + a.peers.slot_off;
-            float ov[4];
-            if (T::bits == 8) {
-              const unsigned word = ld_cg_u32(slot + off2_codes + li);
-              float dq = 0.f;
-              if (C == kCodecQSGD) dq = ld_cg_f32(slot + off2_norms + (size_t)lg * 4) / (float)a.quantum;
+          for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
+            uint4 w4[kU];
+            float dqs[kU];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const unsigned byte = (word >> (8 * j)) & 0xffu;
-                ov[j] = (C == kCodecQSGD ? dq * (float)(int)(signed char)byte : natural_decode(byte)) * a.scale;
+            for (int q = 0; q < kU; ++q) {
+              const long long gb = gb0 + 128ll * kWarps * q;
+              w4[q] = make_uint4(0u, 0u, 0u, 0u);
+              dqs[q] = 0.f;
+              if (gb >= e0) continue;
+              const long long grp = gb >> 7;
+              const int owner = (int)(grp / chunk_groups);
+              const long long lg = grp - (long long)owner * chunk_groups;
+              const size_t li = (size_t)(lg << 7) + 4 * lane;
+              const char* slot = a.peers.heap[owner] + a.peers.slot_off;
+              if (T::bits == 8) {
+                w4[q].x = ld_cg_u32(slot + off2_codes + li);
+                if (C == kCodecQSGD) dqs[q] = ld_cg_f32(slot + off2_norms + (size_t)lg * 4);
+              } else if (T::bits == 32) {
+                w4[q] = ld_cg_u4(slot + off2_codes + li * 4);
+              } else {
+                const char* q16 = slot + off2_codes + li * 2;
+                asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w4[q].x), "=r"(w4[q].y) : "l"(q16));
               }
-            } else if (T::bits == 32) {
-              const uint4 w = ld_cg_u4(slot + off2_codes + li * 4);
-              ov[0] = __uint_as_float(w.x) * a.scale; ov[1] = __uint_as_float(w.y) * a.scale;
-              ov[2] = __uint_as_float(w.z) * a.scale; ov[3] = __uint_as_float(w.w) * a.scale;
-            } else {
-              uint2 w;
-              const char* q = slot + off2_codes + li * 2;
-              asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(q));
-              const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w.x));
-              const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w.y));
-              ov[0] = f01.x * a.scale; ov[1] = f01.y * a.scale; ov[2] = f23.x * a.scale; ov[3] = f23.y * a.scale;
             }
-            if (valid) store4(a.out, i, valid, ov);
+#pragma unroll
+            for (int q = 0; q < kU; ++q) {
+              const long long gb = gb0 + 128ll * kWarps * q;
+              if (gb >= e0) break;  // warp-uniform
+              const long long i = gb + 4 * lane;
+              int valid = 0;
+              if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+              float ov[4];
+              if (T::bits == 8) {
+                const float d = dqs[q] / (float)a.quantum;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned byte = (w4[q].x >> (8 * j)) & 0xffu;
+                  ov[j] = (C == kCodecQSGD ? d * (float)(int)(signed char)byte : natural_decode(byte)) * a.scale;
+                }
+              } else if (T::bits == 32) {
+                ov[0] = __uint_as_float(w4[q].x) * a.scale; ov[1] = __uint_as_float(w4[q].y) * a.scale;
+                ov[2] = __uint_as_float(w4[q].z) * a.scale; ov[3] = __uint_as_float(w4[q].w) * a.scale;
+              } else {
+                const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w4[q].x));
+                const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w4[q].y));
+                ov[0] = f01.x * a.scale; ov[1] = f01.y * a.scale; ov[2] = f23.x * a.scale; ov[3] = f23.y * a.scale;
+              }
+              if (valid) store4(a.out, i, valid, ov);
+            }
           }
         });
       }
