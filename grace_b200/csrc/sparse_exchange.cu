@@ -4,16 +4,26 @@
 // of named gradients (segments):
 //   A   acc = beta*residual + gamma*g   (DGC: u = m*u + g, v += u, acc = v),
 //       store acc as the new residual, zero the output, histogram the top 12
-//       magnitude bits per segment;
-//   P1..P3 / A2, A3   radix select of the k-th largest magnitude per segment,
-//       entirely on device (12 + 12 + 7 key bits);
-//   B   compaction of (value, flat index) into this rank's send slot through a
-//       shared-memory staging buffer, zeroing the residual (and DGC u, v) at
-//       the selected positions, which is the whole error-feedback update;
+//       magnitude bits per segment (shared-memory histograms, one flush per
+//       segment and CTA);
+//   P1  per segment, the bin holding the k-th largest magnitude (device-side
+//       suffix scan, no host round trip);
+//   B   one more streaming pass: everything above the pivot bin goes straight
+//       to this rank's send slot, the keys inside the pivot bin go to a small
+//       candidate list; picks are staged per warp in shared memory and flushed
+//       with one global atomic per flush; the residual (and DGC u, v) is zeroed
+//       at the picked positions, which is the whole error-feedback update;
+//   P2, P3  the remaining 12 + 7 key bits are resolved on the candidate list
+//       only (if the pivot bins hold more keys than the list, the kernel falls
+//       back to two more passes over the tensor); exactly k entries come out;
 //   publish   st.release.sys of the sequence number into every peer's flag pad;
-//   X   for every rank: bounded wait for its flag, stream its list with
-//       ld.global.cg over NVLink and red.global.add.f32 into the dense output
-//       scaled by 1/W; then acknowledge so the slot can be reused.
+//   X   for every rank in rank order: bounded wait for its flag, stream its
+//       list with ld.global.cg over NVLink and red.global.add.f32 into the
+//       dense output scaled by 1/W (a grid barrier separates the lists when
+//       W > 2 so that all replicas get bit-identical sums); then acknowledge
+//       so the slot can be reused.
+// Threshold mode skips the select; random-k mode draws the positions from
+// Philox so that only values travel.
 //
 // What it replaces in the reference: ATen topk / nonzero / scatter_, the
 // rdxtopk extension with its three blocking copies per digit
@@ -63,7 +73,6 @@ struct Smem {
   unsigned wcnt[kBlock / 32];   // entries staged by each warp
   unsigned ccnt[kBlock / 32];
   unsigned scan[kBlock / 32 + 1];
-  unsigned pick[4];
 };
 
 __device__ __forceinline__ void flush_hist(Smem& sm, unsigned* __restrict__ ghist) {

@@ -2,7 +2,7 @@
 
 Some users of the library cannot allocate device memory where they need a
 top-k: a plug-in living inside a host application that owns the allocator, code
-inside a memory-planned region whose budget is already spent, a latency-bound
+inside a memory-planned region that has already handed out every byte it reserved, a latency-bound
 loop where ``cudaMalloc`` would stall the device.  For them the library exports
 one C symbol whose scratch lives in a static device array.  This test calls it
 through ``ctypes`` exactly as such a caller would (raw pointers, no Python
