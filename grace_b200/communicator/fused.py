@@ -120,6 +120,9 @@ class FusedExchange(Communicator):
         self._plans: Dict[tuple, _Plan] = {}
         self._virtual = None
         self._fallback = Allgather(compressor, memory, world_size)
+        from ..utils.faults import FaultPlan
+
+        self._faults = FaultPlan.from_env()
         self._resolve()
 
     # ------------------------------------------------------------------
@@ -202,6 +205,9 @@ class FusedExchange(Communicator):
         scale = (1.0 / self.world_size) if comp.average else 1.0
         beta, gamma = self._memory_coeffs(plan)
         plan.channel.poll()
+        if self._faults.action and (phases & X.PHASE_PUBLISH) and self._faults.hits(
+                "skip_publish", plan.heap.rank, plan.steps):
+            phases &= ~X.PHASE_PUBLISH  # host-side fault injection: this rank "forgets" to publish
         if plan.kind == "sparse":
             seq = X.run_sparse(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,

@@ -6,7 +6,9 @@ norms and residuals are per tensor), so the hook builds, once per bucket index,
 a segment table from ``bucket.parameters()`` and runs the fused exchange kernel
 over the bucket on a side stream; the returned future resolves to the bucket
 buffer holding the aggregated gradients.  With a library communicator (or on
-CPU) the hook falls back to ``grc.step`` per parameter.
+CPU) the hook falls back to ``grc.step`` per parameter.  DDP re-partitions its
+buckets once, after the first iteration; error-feedback state collected during
+that first iteration belongs to the old partition and is not carried over.
 
 The reference has no DDP integration: its "DDP" example is a Python loop over
 ``model.named_parameters()`` after ``backward()`` with no overlap
@@ -31,10 +33,12 @@ class GraceDDPHook:
 
     def _layout_for(self, bucket):
         idx = bucket.index()
-        if idx in self._layouts:
-            return self._layouts[idx]
         params = bucket.parameters()
         grads = bucket.gradients()
+        # DDP re-partitions its buckets after the first iteration: the cache key is the bucket's content
+        key = (idx, tuple(id(p) for p in params))
+        if key in self._layouts:
+            return self._layouts[key]
         base = bucket.buffer().data_ptr()
         names, numels, offsets = [], [], []
         aligned = base % 16 == 0
@@ -48,7 +52,8 @@ class GraceDDPHook:
         layout = FlatLayout(names, numels, offsets, total) if aligned else FlatLayout(names, numels)
         layout.shapes = [tuple(p.shape) for p in params]
         info = dict(names=names, numels=numels, offsets=offsets, aligned=aligned, layout=layout)
-        self._layouts[idx] = info
+        info["key"] = key
+        self._layouts[key] = info
         return info
 
     def __call__(self, state, bucket):  # returns torch.futures.Future[torch.Tensor]
@@ -73,11 +78,10 @@ class GraceDDPHook:
                 self.grc.step_flat(buf, layout)
             else:
                 # DDP packs tensors back to back: stage into an aligned buffer
-                idx = bucket.index()
-                stage = self._staging.get(idx)
+                stage = self._staging.get(info["key"])
                 if stage is None:
                     stage = torch.zeros(layout.total, dtype=torch.float32, device=buf.device)
-                    self._staging[idx] = stage
+                    self._staging[info["key"]] = stage
                 for g, off, n in zip(bucket.gradients(), layout.offsets, layout.numels):
                     stage[off:off + n].copy_(g.reshape(-1))
                 self.grc.step_flat(stage, layout)

@@ -274,3 +274,32 @@ def test_in_place_exchange_without_memory():
     grc.check()
     assert out.data_ptr() == x.data_ptr()
     torch.testing.assert_close(out, expect, rtol=0, atol=0)
+
+
+def test_injected_skip_publish_surfaces_as_timeout_on_the_peer(monkeypatch):
+    """GRACE_FAULT makes rank 1 skip its publication at step 1: rank 0 must report a
+    bounded-wait timeout for peer 1 (host-side injection, nothing faults on the GPU)."""
+    from grace_b200.ops.exchange import GraceCommError
+
+    monkeypatch.setenv("GRACE_FAULT", "skip_publish:rank1:step1")
+    W, n = 2, 8192
+    vw = _world(W, {"compressor": "topk", "memory": "residual", "communicator": "allgather", "compress_ratio": 0.01,
+                    "timeout_ms": 50})
+    vw.step([_rand(n, r) for r in range(W)], "w")     # step 0: healthy
+    vw.check()
+    vw.step([_rand(n, 10 + r) for r in range(W)], "w")  # step 1: rank 1 does not publish
+    with pytest.raises(GraceCommError) as err:
+        vw.comms[0].check()
+    assert err.value.code == 2 and err.value.detail == 1
+    for c in vw.comms:  # recovery: clear flags and sequence numbers, then carry on
+        try:
+            c.check()
+        except GraceCommError:
+            pass
+        c.reset()
+    monkeypatch.delenv("GRACE_FAULT")
+    for c in vw.comms:
+        c._faults.action = ""
+    outs = vw.step([_rand(n, 20 + r) for r in range(W)], "w")
+    vw.check()
+    assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
