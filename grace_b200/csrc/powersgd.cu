@@ -218,7 +218,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
     for (int i = 0; i < kStages - 1; ++i) produce();
   }
 
-  long long t_wait = 0, t_work = 0, t_sync = 0, t_issue = 0, t_prod = 0, t_epi = 0;
+  long long t_wait = 0, t_work = 0, t_sync = 0, t_issue = 0, t_fence = 0, t_commit = 0;
   const bool prof = (a.part & 0x100) && blockIdx.x == 0 && tid == 0;
   while (c_valid) {
     const unsigned slot = c_step % kStages;
@@ -279,6 +279,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
     }
     if (tid == 0) {
       tc_fence_after();
+      if (prof) { const long long t1 = clock64(); t_fence += t1 - t0; t0 = t1; }
       const uint32_t a_addr = smem_u32(sm.a[slot]), b_addr = smem_u32(sm.b[slot]);
 #pragma unroll
       for (int kk = 0; kk < kTileK / 8; ++kk) {
@@ -286,9 +287,10 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
         const uint64_t bdesc = smem_desc(b_addr + kk * 32, 16, 1024);
         umma_tf32(tmem_d, adesc, bdesc, kIdescS1, !(c_kt == cit.kt0 && kk == 0));
       }
+      if (prof) { const long long t1 = clock64(); t_issue += t1 - t0; t0 = t1; }
       umma_commit(&sm.mma_done[slot]);
       if (last_kt) umma_commit(&sm.item_done);
-      if (prof) { const long long t1 = clock64(); t_issue += t1 - t0; t0 = t1; }
+      if (prof) { const long long t1 = clock64(); t_commit += t1 - t0; t0 = t1; }
     }
     ++c_step;
     if (last_kt) {
@@ -323,7 +325,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       c_item += gridDim.x;
       c_valid = decode_item(a, STAGE, c_item, cit);
       c_kt = c_valid ? cit.kt0 : 0;
-      if (prof) { const long long t1 = clock64(); t_epi += t1 - t0; t0 = t1; }
+      if (prof) { const long long t1 = clock64(); t_commit += t1 - t0; t0 = t1; }
     } else {
       ++c_kt;
     }
@@ -331,7 +333,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
   if (prof) {
     unsigned* w = a.status + 8 + (STAGE - 1) * 8;
     w[0] = (unsigned)(t_wait >> 4); w[1] = (unsigned)(t_work >> 4); w[2] = (unsigned)(t_sync >> 4);
-    w[3] = (unsigned)(t_issue >> 4); w[4] = (unsigned)(t_prod >> 4); w[5] = (unsigned)(t_epi >> 4); w[6] = c_step;
+    w[3] = (unsigned)(t_issue >> 4); w[4] = (unsigned)(t_fence >> 4); w[5] = (unsigned)(t_commit >> 4); w[6] = c_step;
   }
   // drain: every issued load must land and every store must finish before smem is reused
   if (tid == kProducerThread) {
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   //   everything, the split launches of the one-GPU emulation run
   //   [S1 | publish P] [reduce P, O, S2 | publish Q] [reduce Q, S3] as three
   //   launches selected by a.part (0 = all, 1..3 = that part only).
-  const int part = a.part & 0xff;   // bit 8 of a.part asks CTA 0 to record per-phase cycle counts
+  const int part = a.part & 0xff;   // bit 8 of a.part asks CTA 0 to record per-phase cycle counts in status[8..]: wait, smem work, barrier, MMA issue, fence, commit + epilogue, steps (units of 16 cycles)
   const bool part1 = part == 0 || part == 1;
   const bool part2 = part == 0 || part == 2;
   const bool part3 = part == 0 || part == 3;
