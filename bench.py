@@ -140,6 +140,38 @@ def forward_loss(model, cfg, batch, amp):
 
 
 # ----------------------------------------------------------------------------- arms
+def build_ours_loop(cfg, device, world):
+    """Drop-in usage: the reference's training loop with this package's fused communicator."""
+    import torch
+
+    import grace_b200
+    from grace_b200 import models
+
+    torch.manual_seed(0)
+    model = getattr(models, cfg["model"])().to(device)
+    if cfg["model"] in ("resnet50", "resnet20"):
+        model = model.to(memory_format=torch.channels_last)
+    params = dict(cfg["grace"])
+    params.update(world_size=world, fused=True)
+    grc = grace_b200.grace_from_params(params)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    named = list(model.named_parameters())
+
+    def step(batch, amp):
+        opt.zero_grad()
+        loss = forward_loss(model, cfg, batch, amp)
+        loss.backward()
+        for name, p in named:
+            if p.grad is not None:
+                new = grc.step(p.grad.data, name)
+                if new.data_ptr() != p.grad.data_ptr():
+                    p.grad.data.copy_(new.view_as(p.grad))
+        opt.step()
+        return loss
+
+    return step, len(named), grc
+
+
 def build_ours(cfg, device, world):
     import torch
 
@@ -258,6 +290,9 @@ def main():
     ap.add_argument("--config", default="resnet50_dgc", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (invalidates the headline)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--api", default="optimizer", choices=["optimizer", "loop"],
+                    help="ours: DistributedOptimizer over flat buckets (default) or the reference-style "
+                         "per-parameter grc.step loop with torch.optim.SGD (drop-in usage)")
     ap.add_argument("--bucket-mb", type=float, default=None,
                     help="exchange gradients in buckets of this size from backward hooks (overlap); default one bucket")
     args = ap.parse_args()
@@ -293,6 +328,8 @@ def main():
     try:
         if args.impl == "reference":
             step, launches, grc = build_reference(cfg, device, world)
+        elif args.api == "loop":
+            step, launches, grc = build_ours_loop(cfg, device, world)
         else:
             step, launches, grc = build_ours(cfg, device, world)
     except Exception as e:
@@ -379,7 +416,7 @@ def main():
             "metric": "training samples/sec (%s)" % args.config, "value": value, "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"],
-            "data": "synthetic N(0,1) inputs, uniform labels, random-init weights", "impl": args.impl,
+            "data": "synthetic N(0,1) inputs, uniform labels, random-init weights", "impl": args.impl, "api": args.api,
             "config": {"model": cfg["model"], "global_batch": cfg["batch"] * world,
                        "seq_len": cfg.get("seq"), "parallelism": "dp%d" % world, "compression": cfg["grace"],
                        "l2": "inputs and activations exceed L2 (batch %.0f MB)" % (

@@ -118,6 +118,7 @@ class FusedExchange(Communicator):
         self.device = None
         self._rank = rank
         self._plans: Dict[tuple, _Plan] = {}
+        self._single_layouts = {}
         self._virtual = None
         self._fallback = Allgather(compressor, memory, world_size)
         from ..utils.faults import FaultPlan
@@ -171,7 +172,9 @@ class FusedExchange(Communicator):
         return SymmetricHeap.create(nbytes, group=self.group, device=self.device)
 
     def _plan(self, layout) -> _Plan:
-        key = layout.key()
+        key = getattr(layout, "_key", None)
+        if key is None:
+            key = layout._key = layout.key()
         plan = self._plans.get(key)
         if plan is None:
             if self._kind == "powersgd":
@@ -274,7 +277,11 @@ class FusedExchange(Communicator):
         flat = self._prepare(tensor)
         same = flat.data_ptr() == tensor.data_ptr()
         out = flat if (self.inplace and same) else torch.empty_like(flat)
-        self.step_flat(flat, FlatLayout.single(name, flat.numel(), tensor.shape), out)
+        lkey = (name, flat.numel(), tuple(tensor.shape))
+        layout = self._single_layouts.get(lkey)
+        if layout is None:
+            layout = self._single_layouts[lkey] = FlatLayout.single(name, flat.numel(), tensor.shape)
+        self.step_flat(flat, layout, out)
         return out.view(tensor.shape).to(tensor.dtype)
 
     # split-phase: launch on the caller's current stream, hand back an event

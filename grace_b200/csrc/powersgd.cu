@@ -50,6 +50,7 @@ constexpr int kKTilesPerItem = 16;      // split-K granularity: 512 columns (S1)
 constexpr unsigned kTmemCols = 32;
 constexpr int kProducerThread = 32;      // lane 0 of warp 1: TMA loads and stores
 constexpr int kMaxRank = 8;              // ranks 1..8 (buffers are padded to kRankPad columns)
+constexpr int kS3Trip = 16;             // rows whose loads are in flight together in stage 3
 constexpr int kS3Rows = 64;             // rows per stage-3 work item
 
 // instruction descriptor: D=f32, A=B=tf32, N=16, M=128 (bit layout: c_format
@@ -578,17 +579,17 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
             }
             const int rows = min(kS3Rows, M.n - rb * kS3Rows);
             const bool vec = valid == 4 && (M.m & 3) == 0;
-            for (int r0 = 0; r0 < rows; r0 += 8) {
-              // eight rows per trip: issue the loads of M' first, then compute and store
-              float4 mv[8];
+            for (int r0 = 0; r0 < rows; r0 += kS3Trip) {
+              // kS3Trip rows per trip: issue the loads of M' first, then compute and store
+              float4 mv[kS3Trip];
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
+              for (int u = 0; u < kS3Trip; ++u) {
                 mv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (r0 + u < rows && a.has_memory && vec)
                   mv[u] = *reinterpret_cast<const float4*>(src + (size_t)M.g_off + (size_t)(rb * kS3Rows + r0 + u) * M.m + col);
               }
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
+              for (int u = 0; u < kS3Trip; ++u) {
                 const int rr = r0 + u;
                 if (rr >= rows) break;
                 const size_t base = (size_t)M.g_off + (size_t)(rb * kS3Rows + rr) * M.m + col;

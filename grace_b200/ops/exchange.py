@@ -109,6 +109,8 @@ class ExchangeChannel:
         self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
         self.ready2_off = heap.alloc(C.MAX_WORLD * 8) if heap.free_bytes >= C.MAX_WORLD * 8 + 256 else 0
         self.seq = 0
+        self._grids = {}
+        self._events = [None, None]
         self.timeout_ns = int(timeout_ms * 1e6)
         self.sm_limit = sm_limit or 0
         dev = self.device
@@ -125,6 +127,16 @@ class ExchangeChannel:
         self.seq += 1
         return self.seq
 
+    def max_grid(self, kind: str) -> int:
+        """Largest co-resident grid of a kernel family on this device (cached)."""
+        g = self._grids.get(kind)
+        if g is None:
+            C = native()
+            fn = C.sparse_max_grid if kind == "sparse" else C.quant_max_grid
+            g = fn(self.heap.device.index, self.sm_limit)
+            self._grids[kind] = g
+        return g
+
     def slot_view(self, seq: int, numel: int, dtype, byte_offset: int = 0, rank: Optional[int] = None):
         return self.heap.view(self.slot_off[seq & 1] + byte_offset, numel, dtype, rank)
 
@@ -132,7 +144,10 @@ class ExchangeChannel:
     def post_status(self):
         """Queue a copy of the status block to pinned memory (no sync)."""
         self.status_host.copy_(self.status, non_blocking=True)
-        ev = torch.cuda.Event()
+        slot = self.seq & 1                      # two events, reused alternately
+        ev = self._events[slot]
+        if ev is None:
+            ev = self._events[slot] = torch.cuda.Event()
         ev.record()
         self.status_event = ev
 
@@ -202,7 +217,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
     if seq is None:
         seq = channel.next_seq()
     if grid is None:
-        grid = C.sparse_max_grid(heap.device.index, channel.sm_limit)
+        grid = channel.max_grid("sparse")
     need = -(-layout.total // 2048)
     grid = max(1, min(grid, max(need, 1)))
     for t in (g, acc, u, out):
@@ -238,7 +253,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
     if seq is None:
         seq = channel.next_seq()
     if grid is None:
-        grid = C.quant_max_grid(heap.device.index, channel.sm_limit)
+        grid = channel.max_grid("quant")
     need = -(-layout.total // 2048)
     grid = max(1, min(grid, max(need, 1)))
     for t in (g, acc, mom, out):
