@@ -26,6 +26,10 @@ EF-signSGD          efsignsgd                              quantised
 PowerSGD            powersgd                               low-rank (tcgen05)
 ==================  =====================================  ==================
 
+Threshold compression has a data-dependent payload: the send slot holds at most
+``max_ratio`` (default 0.25) of the elements; what does not fit stays in the
+residual (counted by ``channel.dropped()``).
+
 Two granularities: ``step(tensor, name)`` (one tensor, API of the reference)
 and ``step_flat(flat, layout)`` (a whole bucket of named tensors in one launch,
 used by the DDP hook and ``DistributedOptimizer``).
@@ -104,7 +108,7 @@ class _Plan:
 
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
-                 group=None, inplace=True, max_ratio=1.0, exact=True, rank=None):
+                 group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None):
         super().__init__(compressor, memory, world_size)
         self.mode = mode
         self.seed = int(seed)
@@ -114,6 +118,7 @@ class FusedExchange(Communicator):
         self.inplace = inplace
         self.max_ratio = max_ratio
         self.exact = exact
+        self.monitor = monitor   # optional utils.faults.HeartbeatMonitor: checked before every launch
         self.nvtx = True
         self.device = None
         self._rank = rank
@@ -139,7 +144,7 @@ class FusedExchange(Communicator):
         if isinstance(mem, M_.PowerSGDMemory) or isinstance(comp, C_.PowerSGDCompressor):
             self._kind = "powersgd"
         elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor, C_.RandomKCompressor)):
-            if isinstance(mem, M_.DgcMemory) and (mem.gradient_clipping or isinstance(comp, C_.ThresholdCompressor)):
+            if isinstance(mem, M_.DgcMemory) and isinstance(comp, (C_.ThresholdCompressor, C_.RandomKCompressor)):
                 self._kind = None
             elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.DgcMemory)):
                 self._kind = "sparse"
@@ -192,6 +197,17 @@ class FusedExchange(Communicator):
             self._plans[key] = plan
         return plan
 
+    def _clip_bounds(self, plan: _Plan, g: torch.Tensor) -> torch.Tensor:
+        """DGC gradient clipping: per tensor, ``sqrt(mean over ranks of sum(g^2))``
+        (``grace_dl/torch/memory/dgc.py:16-19``); the kernel clamps element-wise."""
+        views = list(plan.layout.slices(g).values())
+        sq = torch.stack(torch._foreach_norm(views)).pow(2)
+        if self._virtual is None and dist.is_available() and dist.is_initialized() and self.world_size > 1:
+            dist.all_reduce(sq, group=self.group)
+            sq = sq / self.world_size
+        plan.clip = sq.sqrt().float().contiguous()   # kept alive until the kernel has read it
+        return plan.clip
+
     def _memory_coeffs(self, plan: _Plan):
         mem = self.memory
         first = plan.steps == 0
@@ -208,6 +224,9 @@ class FusedExchange(Communicator):
         scale = (1.0 / self.world_size) if comp.average else 1.0
         beta, gamma = self._memory_coeffs(plan)
         plan.channel.poll()
+        clip = None
+        if plan.kind == "sparse" and getattr(self.memory, "gradient_clipping", False) and (phases & X.PHASE_COMPRESS):
+            clip = self._clip_bounds(plan, g)
         if self._faults.action and (phases & X.PHASE_PUBLISH) and self._faults.hits(
                 "skip_publish", plan.heap.rank, plan.steps):
             phases &= ~X.PHASE_PUBLISH  # host-side fault injection: this rank "forgets" to publish
@@ -216,7 +235,7 @@ class FusedExchange(Communicator):
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,
                 beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
                 threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
-                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps)
+                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps, clip=clip)
         else:
             seq = X.run_quant(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,
@@ -234,6 +253,12 @@ class FusedExchange(Communicator):
 
         if self.device is None:
             self.device = flat.device
+        if self.monitor is not None:
+            self.monitor.beat(force=False)
+            dead = self.monitor.dead_ranks()
+            if dead:
+                raise RuntimeError("grace: ranks %s stopped sending heartbeats; not launching an exchange "
+                                   "that could only time out" % dead)
         plan = self._plan(layout)
         out = flat if out is None else out
         nvtx = self.nvtx and flat.is_cuda

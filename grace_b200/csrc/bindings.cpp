@@ -84,8 +84,9 @@ PYBIND11_MODULE(_C, m) {
            unsigned long long seq, unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps,
            unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
-           uintptr_t seg_seed, unsigned rk_step) {
+           uintptr_t seg_seed, unsigned rk_step, uintptr_t clip) {
           SparseArgs a{};
+          a.clip = ptr<const float>(clip);
           a.kprefix = ptr<const int>(kprefix); a.seg_seed = ptr<const unsigned long long>(seg_seed); a.rk_step = rk_step;
           if (mode == kSparseRandomK && (!kprefix || !seg_seed)) throw std::invalid_argument("random-k needs kprefix and seeds");
           a.cand_val = ptr<float>(cand_val); a.cand_idx = ptr<int>(cand_idx); a.cand_cap = cand_val ? cand_cap : 0;

@@ -75,6 +75,7 @@ struct SparseArgs {
   const int* kprefix;               // nseg + 1 prefix sums of k (entry e belongs to the segment with kprefix[s] <= e)
   const unsigned long long* seg_seed;  // nseg seeds (derived from the tensor names, identical on every rank)
   unsigned rk_step;                 // per-plan step counter (part of the Philox counter)
+  const float* clip;                // nseg clamp bounds applied to g before compensation (DGC clipping), nullable
   unsigned* barrier;  // one word, zeroed by the launcher
   unsigned* status;   // 4 words
   unsigned cap;       // slot capacity in entries (multiple of 16)

@@ -167,6 +167,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         float tmax = -INFINITY;
         const bool read_acc = a.u || (a.acc && a.beta != 0.f);
+        const float clip = a.clip ? a.clip[s] : INFINITY;   // element-wise clamp of the incoming gradient
         auto trip_a = [&](auto full_tag, long long base) {
           constexpr bool kFull = decltype(full_tag)::value;   // all kUnroll vectors fully inside the range
           // issue every load of the trip before the first dependent instruction
@@ -189,6 +190,10 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             if (!valid[q]) continue;
             const long long i = base + (long long)q * kIterElems;
             float av[4];
+            if (a.clip) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) gv[q][j] = fminf(fmaxf(gv[q][j], -clip), clip);
+            }
             if (a.u) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) { uv[q][j] = a.momentum * uv[q][j] + gv[q][j]; av[j] = rv[q][j] + uv[q][j]; }

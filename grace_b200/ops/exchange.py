@@ -211,7 +211,8 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
                cap: int, beta: float = 1.0, gamma: float = 1.0, momentum: float = 0.0, threshold: float = 0.0,
                scale: float = 1.0, levels: int = 3, phases: int = PHASE_ALL, seq: Optional[int] = None,
                grid: Optional[int] = None, kprefix: Optional[torch.Tensor] = None,
-               seg_seed: Optional[torch.Tensor] = None, rk_step: int = 0) -> int:
+               seg_seed: Optional[torch.Tensor] = None, rk_step: int = 0,
+               clip: Optional[torch.Tensor] = None) -> int:
     C = native()
     heap = channel.heap
     if seq is None:
@@ -236,7 +237,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
         _stream_ptr(), channel.cand.data_ptr() if cand_cap else 0,
         (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
-        _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF,
+        _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF, _ptr(clip),
     )
     channel.post_status()
     return seq

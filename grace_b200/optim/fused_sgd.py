@@ -126,6 +126,48 @@ class FusedSGD(torch.optim.Optimizer):
         self._steps += 1
         return loss
 
+    # -- checkpoint: the flat momentum buffer is exported in torch.optim.SGD's format -------------
+    def _flat_slices(self, flat_tensor):
+        fp = self.flat
+        by_id = {id(p): (off, p) for p, off in zip(fp.params, fp.layout.offsets)}
+        out = []
+        for group in self.param_groups:
+            for p in group["params"]:
+                off, _ = by_id.get(id(p), (None, None))
+                out.append(None if off is None else flat_tensor[off : off + p.numel()])
+        return out
+
+    def state_dict(self):
+        sd = super().state_dict()
+        if self.flat is not None and self._flat_buf is not None:
+            from ..parallel.flat import _dense_view
+
+            idx = 0
+            for group in self.param_groups:
+                for p in group["params"]:
+                    off = dict((id(q), o) for q, o in zip(self.flat.params, self.flat.layout.offsets)).get(id(p))
+                    if off is not None:
+                        sd["state"].setdefault(idx, {})["momentum_buffer"] = _dense_view(
+                            self._flat_buf, off, p.data).clone()
+                    idx += 1
+        return sd
+
+    def load_state_dict(self, state_dict):
+        super().load_state_dict(state_dict)
+        if self.flat is None:
+            return
+        from ..parallel.flat import _dense_view
+
+        found = False
+        buf = torch.zeros_like(self.flat.flat_p)
+        for p, off in zip(self.flat.params, self.flat.layout.offsets):
+            st = self.state.get(p, {})
+            if "momentum_buffer" in st and st["momentum_buffer"] is not None:
+                _dense_view(buf, off, p.data).copy_(st.pop("momentum_buffer"))
+                found = True
+        if found:
+            self._flat_buf = buf
+
     def zero_grad(self, set_to_none: bool = False):
         if self.flat is not None:
             if not self.zero_grad_in_step:

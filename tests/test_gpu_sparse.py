@@ -303,3 +303,21 @@ def test_injected_skip_publish_surfaces_as_timeout_on_the_peer(monkeypatch):
     outs = vw.step([_rand(n, 20 + r) for r in range(W)], "w")
     vw.check()
     assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
+
+
+def test_dgc_with_gradient_clipping_runs_fused():
+    from grace_b200 import grace_from_params
+
+    n, ratio = 20_000, 0.01
+    grc = grace_from_params({"compressor": "dgc", "memory": "dgc", "communicator": "allgather", "world_size": 1,
+                             "compress_ratio": ratio, "momentum": 0.9, "gradient_clipping": True, "fused": True})
+    assert grc._kind == "sparse"
+    x = _rand(n, 8)
+    x[:5] = 1.0          # (with one rank the bound is the tensor's own L2 norm, which no element exceeds)
+    bound = x.pow(2).sum().sqrt()
+    out = grc.step(x.clone(), "w")
+    grc.check()
+    clipped = x.clamp(-bound, bound)
+    expect = _dense_topk(clipped, int(n * ratio))
+    torch.testing.assert_close(out, expect, rtol=1e-6, atol=1e-9)
+    assert out.abs().max() <= bound + 1e-6
