@@ -93,7 +93,7 @@ class _Plan:
             self.alltoall = owner.mode == "alltoall" and self.codec in (X.CODEC["qsgd"], X.CODEC["natural"],
                                                                         X.CODEC["fp16"], X.CODEC["fp32"])
             slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg, owner.world_size if self.alltoall else 0)
-        heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 4096
+        heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 8192
         self.heap = owner._make_heap(layout.key(), heap_bytes)
         self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
         self.segs = X.segments_to_device(layout, self.ks, device)

@@ -10,6 +10,7 @@ and launch the cooperative kernel on the current stream.
 """
 from __future__ import annotations
 
+import os
 import struct
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -31,6 +32,8 @@ STATUS_TEXT = {
     6: "timeout on an mbarrier",
 }
 ALIGN_ELEMS = 128
+GUARD_BYTES = 256
+GUARD_PATTERN = 0xA5
 
 
 class GraceCommError(RuntimeError):
@@ -106,7 +109,20 @@ class ExchangeChannel:
         self.flags_off = heap.alloc(2 * C.MAX_WORLD * 8)
         self.ready_off = self.flags_off
         self.ack_off = self.flags_off + C.MAX_WORLD * 8
-        self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+        # GRACE_GUARD=1: poison-filled guard bands around both send slots, checked by check()
+        # (stands in for a memory checker: a kernel writing outside its slot is caught on the host)
+        self.guard = bool(os.environ.get("GRACE_GUARD")) and heap.free_bytes >= 2 * self.slot_bytes + 4 * GUARD_BYTES
+        self.guard_off = []
+        if self.guard:
+            self.guard_off.append(heap.alloc(GUARD_BYTES))
+        self.slot_off = [heap.alloc(self.slot_bytes)]
+        if self.guard:
+            self.guard_off.append(heap.alloc(GUARD_BYTES))
+        self.slot_off.append(heap.alloc(self.slot_bytes))
+        if self.guard:
+            self.guard_off.append(heap.alloc(GUARD_BYTES))
+            for off in self.guard_off:
+                heap.view(off, GUARD_BYTES, torch.uint8).fill_(GUARD_PATTERN)
         self.ready2_off = heap.alloc(C.MAX_WORLD * 8) if heap.free_bytes >= C.MAX_WORLD * 8 + 256 else 0
         self.seq = 0
         self._grids = {}
@@ -161,6 +177,15 @@ class ExchangeChannel:
         if self.status_event is not None:
             self.status_event.synchronize()
             self._raise_if_failed()
+        if self.guard:
+            self.verify_guards()
+
+    def verify_guards(self):
+        for off in self.guard_off:
+            band = self.heap.view(off, GUARD_BYTES, torch.uint8)
+            if not bool((band == GUARD_PATTERN).all()):
+                raise RuntimeError("grace: guard band at heap offset %d was overwritten (a kernel wrote outside "
+                                   "its send slot)" % off)
 
     def dropped(self) -> int:
         self.check()

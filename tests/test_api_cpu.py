@@ -210,3 +210,27 @@ def test_wrapper_keeps_the_wrapped_optimizers_own_attributes():
     opt.flat = marker
     d = DistributedOptimizer(opt, grace=_FakeGrace(), named_parameters=m.named_parameters(), always_hook=True)
     assert d.flat is marker and d.grad_scale == 0.5 and d.param_groups[0]["lr"] == 0.1
+
+
+def test_metrics_helpers(tmp_path):
+    import json
+
+    from grace_b200.utils.metrics import DeviceTimer, JsonlLogger, TableLogger, ThroughputMeter
+
+    with DeviceTimer("cpu") as t:
+        sum(range(1000))
+    assert t.ms >= 0
+    m = ThroughputMeter()
+    m.update(256, 100.0); m.update(256, 100.0)
+    assert abs(m.rate() - 2560.0) < 1e-6
+    log = JsonlLogger(str(tmp_path / "log.jsonl"))
+    log.log(step=1, loss=0.5)
+    rec = json.loads(open(tmp_path / "log.jsonl").read().splitlines()[0])
+    assert rec["step"] == 1 and rec["rank"] == 0
+    text = TableLogger().append({"epoch": 1, "loss": 0.25})
+    assert "epoch" in text and "0.2500" in text
+    grc = grace_from_params({"compressor": "topk", "memory": "none", "communicator": "allgather", "world_size": 1,
+                             "compress_ratio": 0.1})
+    grc.step(torch.randn(1000), "w")
+    s = grc.stats()
+    assert s["steps"] == 1 and 4.9 < s["compression_ratio"] < 5.1

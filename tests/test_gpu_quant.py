@@ -283,3 +283,17 @@ def test_fused_state_dict_resume_is_bit_identical():
     assert torch.equal(out_a, out_b)
     pa, pb = next(iter(a._plans.values())), next(iter(b._plans.values()))
     assert torch.equal(pa.acc, pb.acc)
+
+
+def test_guard_bands_stay_intact(monkeypatch):
+    """GRACE_GUARD=1 surrounds the send slots with poison bytes; every codec must leave them alone."""
+    monkeypatch.setenv("GRACE_GUARD", "1")
+    n = 12_345
+    for name, memory in (("qsgd", "residual"), ("terngrad", "none"), ("signsgd", "none"), ("topk", "residual"),
+                         ("fp16", "none")):
+        vw = _world(2, {"compressor": name, "memory": memory, "communicator": "allgather", "compress_ratio": 0.05,
+                        "quantum_num": 64})
+        vw.step([_rand(n, r) for r in range(2)], "w")
+        plan = _plan(vw)
+        assert plan.channel.guard and len(plan.channel.guard_off) == 3
+        vw.check()   # raises if a guard band changed
