@@ -209,3 +209,27 @@ def _ddp_hook(rank, world):
 def test_ddp_comm_hook_averages_like_allreduce():
     res = _run(_ddp_hook, 2)
     assert res[0] < 1e-6 and res[1] < 1e-6
+
+
+def _hvd_api(rank, world):
+    import grace_b200.parallel.hvd as hvd
+
+    assert hvd.size() == world and hvd.rank() == rank
+    t = torch.full((4,), float(rank + 1))
+    h = hvd.allreduce_async_(t, average=True)
+    assert hvd.synchronize(h) is t and torch.allclose(t, torch.full((4,), (1 + world) * world / 2 / world))
+    g = hvd.allgather(torch.arange(rank + 1, dtype=torch.float32))
+    model = torch.nn.Linear(3, 2)
+    with torch.no_grad():
+        model.weight.fill_(float(rank))
+    hvd.broadcast_parameters(model.state_dict(), root_rank=0)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1 * (rank + 1), momentum=0.9)
+    hvd.broadcast_optimizer_state(opt, root_rank=0)
+    return g.tolist(), float(model.weight.abs().sum()), opt.param_groups[0]["lr"]
+
+
+def test_horovod_style_helpers():
+    res = _run(_hvd_api, 2)
+    for r in (0, 1):
+        gathered, wsum, lr = res[r]
+        assert gathered == [0.0, 0.0, 1.0] and wsum == 0.0 and abs(lr - 0.1) < 1e-12
