@@ -51,11 +51,10 @@ class NaturalCompressor(StochasticMixin, Compressor):
 
             return [_quant.natural_compress(flat, name, self.deterministic)], tensor.shape
         if self.deterministic:
-            # the reference keeps the larger power when 2|m|-1 > 0.5
-            u = torch.full_like(flat, 0.5)
+            # the reference keeps the larger power when 2|m|-1 > 0.5: u = 0 forces "up", u = 1 "down"
             bits = flat.contiguous().view(torch.int32)
             prob = (bits & 0x7FFFFF).float() * (2.0 ** -23)
-            u = torch.where(prob > 0.5, torch.zeros_like(u), torch.ones_like(u))
+            u = torch.where(prob > 0.5, torch.zeros_like(flat), torch.ones_like(flat))
         else:
             u = self._uniform(flat, name)
         return [natural_encode(flat, u)], tensor.shape

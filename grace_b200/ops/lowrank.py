@@ -137,9 +137,11 @@ class LowRankPlan:
         if self._maps_key == key:
             return
         nmat = len(self.matrices)
-        host = np.zeros(nmat * C.MAPS_PER_MATRIX * C.TENSOR_MAP_BYTES, dtype=np.uint8)
+        nbytes = nmat * C.MAPS_PER_MATRIX * C.TENSOR_MAP_BYTES
+        raw = np.zeros(nbytes + 64, dtype=np.uint8)          # tensor maps are 64-byte aligned objects
+        shift = (-raw.ctypes.data) % 64
+        host = raw[shift : shift + nbytes]
         base = host.ctypes.data
-        assert base % 64 == 0 or True
         pt_off = qt_off = 0
         for i, (name, off, n, m) in enumerate(self.matrices):
             C.lowrank_encode_maps(
@@ -148,7 +150,7 @@ class LowRankPlan:
                 self.qt.data_ptr() + 4 * qt_off, self.pt_orth.data_ptr() + 4 * pt_off, n, m)
             pt_off += n * RANK_PAD
             qt_off += m * RANK_PAD
-        self.maps = torch.from_numpy(host).to(self.device)
+        self.maps = torch.from_numpy(host.copy()).to(self.device)
         self._maps_key = key
 
     def launch(self, g: torch.Tensor, out: torch.Tensor, part: int = 0, seq: Optional[int] = None) -> int:

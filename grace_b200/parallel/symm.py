@@ -60,7 +60,7 @@ class SymmetricHeap:
         self._imported = imported   # pointers to unmap at close
         self._cursor = 0
         self._closed = False
-        weakref.finalize(self, SymmetricHeap._release, list(owned), list(imported))
+        self._finalizer = weakref.finalize(self, SymmetricHeap._release, list(owned), list(imported))
 
     # -- construction -----------------------------------------------------
     @classmethod
@@ -151,5 +151,8 @@ class SymmetricHeap:
             pass
 
     def close(self):
+        """Unmap the peers' regions and free this rank's region now (all kernels using the heap must
+        have finished on every rank: synchronise and barrier first)."""
         if not self._closed:
             self._closed = True
+            self._finalizer()
