@@ -84,8 +84,11 @@ PYBIND11_MODULE(_C, m) {
            unsigned long long seq, unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps,
            unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
-           uintptr_t seg_seed, unsigned rk_step, uintptr_t clip) {
+           uintptr_t seg_seed, unsigned rk_step, uintptr_t clip, uintptr_t tile_start, uintptr_t tile_cur,
+           uintptr_t scan_tmp, uintptr_t sort_pair, uintptr_t stage_pair) {
           SparseArgs a{};
+          a.tile_start = ptr<unsigned>(tile_start); a.tile_cur = ptr<unsigned>(tile_cur); a.scan_tmp = ptr<unsigned>(scan_tmp);
+          a.sort_pair = ptr<uint2>(sort_pair); a.stage_pair = ptr<uint2>(stage_pair);
           a.clip = ptr<const float>(clip);
           a.kprefix = ptr<const int>(kprefix); a.seg_seed = ptr<const unsigned long long>(seg_seed); a.rk_step = rk_step;
           if (mode == kSparseRandomK && (!kprefix || !seg_seed)) throw std::invalid_argument("random-k needs kprefix and seeds");

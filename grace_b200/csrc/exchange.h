@@ -76,6 +76,14 @@ struct SparseArgs {
   const unsigned long long* seg_seed;  // nseg seeds (derived from the tensor names, identical on every rank)
   unsigned rk_step;                 // per-plan step counter (part of the Philox counter)
   const float* clip;                // nseg clamp bounds applied to g before compensation (DGC clipping), nullable
+  // Tile-bucketed decode (nullable: then every list is scatter-added with red.global): the received
+  // (value, index) pairs are counting-sorted by (8192-element output tile, source rank) into sort_pair;
+  // each tile is then built in shared memory in rank order and written once, densely.
+  unsigned* tile_start;             // tiles * world + 1 (zero on entry; holds exclusive prefix sums afterwards)
+  unsigned* tile_cur;               // tiles * world running cursors
+  unsigned* scan_tmp;               // one word per CTA
+  uint2* sort_pair;                 // world * cap entries of (value bits, index)
+  uint2* stage_pair;                // world * cap: local copy of the peers' lists, made while counting
   unsigned* barrier;  // one word, zeroed by the launcher
   unsigned* status;   // 4 words
   unsigned cap;       // slot capacity in entries (multiple of 16)

@@ -46,6 +46,8 @@ constexpr int kIterElems = kBlock * 4;    // elements per CTA iteration
 constexpr int kCandStage = 4096;          // staged pivot-bin candidates per CTA
 constexpr int kWarpStage = kStageCap / (kBlock / 32);   // 512 staged picks per warp
 constexpr int kWarpCand = kCandStage / (kBlock / 32);   // 256 staged candidates per warp
+constexpr int kTileShift = 13;             // decode tiles of 8192 output elements (32 KiB of shared memory)
+constexpr int kTileElems = 1 << kTileShift;
 constexpr int kUnroll = 4;                // 16-byte loads in flight per thread and array
 constexpr unsigned kSlotHeaderBytes = 128;
 
@@ -150,6 +152,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   const float* __restrict__ src = a.acc ? a.acc : a.g;
   const bool topk = a.mode == kSparseTopK;
   const bool randomk = a.mode == kSparseRandomK;
+  const bool dense_decode = a.tile_start != nullptr && !randomk && a.out != nullptr;  // tile-bucketed decode
 
   if (a.phases & kPhaseCompress) {
     // Before overwriting the slot of parity (seq & 1): every peer must have
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
               for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[q][j] + a.gamma * gv[q][j];
             }
             if (a.acc) store4(a.acc, i, valid[q], av);
-            if (a.out) { const float z[4] = {0.f, 0.f, 0.f, 0.f}; store4(a.out, i, valid[q], z); }
+            if (a.out && !dense_decode) { const float z[4] = {0.f, 0.f, 0.f, 0.f}; store4(a.out, i, valid[q], z); }
             if (topk) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
@@ -536,6 +539,251 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           for (int p = 0; p < world; ++p)
             sum += ld_cg_f32(a.peers.heap[p] + a.peers.slot_off + kSlotHeaderBytes + (size_t)e * 4);
           a.out[my_idx[e]] = sum * a.scale;   // duplicates of a position write the same value
+        }
+      }
+      bar.sync();
+      if (blockIdx.x == 0 && tid < world && tid != rank && !status.failed()) {
+        uint64_t* ack = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ack_off) + rank;
+        st_release_sys(ack, a.peers.seq);
+      }
+      return;
+    }
+    if (dense_decode) {
+      // ---- tile-bucketed decode ----
+      const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
+      const unsigned nbins = (unsigned)(tiles * world);
+      const unsigned gtid = blockIdx.x * kBlock + tid, gstride = gridDim.x * kBlock;
+      const unsigned lim = (unsigned)a.total;
+      __shared__ unsigned s_n[kMaxWorld];
+      __shared__ unsigned s_scan[kBlock / 32];
+      __shared__ unsigned s_carry;
+      // D0: counters must start from zero (the previous exchange left prefix sums there)
+      for (unsigned b = gtid; b <= nbins; b += gstride) a.tile_start[b] = 0;
+      if (tid < world) {
+        unsigned n = 0;
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ready_off) + tid;
+        if (wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid))
+          n = ld_cg_u32(a.peers.heap[tid] + a.peers.slot_off);
+        s_n[tid] = n < a.cap ? n : a.cap;
+      }
+      bool okx = bar.sync();
+      // D1: count the pairs per (tile, source rank); a warp merges its increments per bin
+      // The first traversal (counting) keeps a copy of every remote list in local memory, so that the
+      // second one (placement) does not cross NVLink again; each thread re-reads what it wrote itself.
+      auto for_each_pair = [&](auto second, auto&& fn) {
+        constexpr bool kSecond = decltype(second)::value;
+        for (int p = 0; p < world; ++p) {
+          const unsigned n = s_n[p];
+          const char* pv = a.peers.heap[p] + a.peers.slot_off + kSlotHeaderBytes;
+          const char* pi = pv + (size_t)a.cap * 4;
+          const unsigned groups = (n + 3) / 4;
+          const unsigned trips = (groups + gstride - 1) / gstride;   // uniform trip count: warp collectives inside
+          auto fetch = [&](unsigned gidx, uint4& v, uint4& ix) {
+            v = make_uint4(0u, 0u, 0u, 0u);
+            ix = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+            if (gidx >= groups) return;
+            uint4* local = reinterpret_cast<uint4*>(a.stage_pair + (size_t)p * a.cap + (size_t)gidx * 4);
+            if (kSecond && p != rank) {
+              const uint4 lo = local[0], hi = local[1];
+              v = make_uint4(lo.x, lo.z, hi.x, hi.z);
+              ix = make_uint4(lo.y, lo.w, hi.y, hi.w);
+            } else {
+              v = ld_cg_u4(pv + (size_t)gidx * 16);
+              ix = ld_cg_u4(pi + (size_t)gidx * 16);
+            }
+          };
+          auto consume = [&](unsigned gidx, const uint4& v, const uint4& ix) {
+            if (!kSecond && p != rank && gidx < groups) {
+              uint4* local = reinterpret_cast<uint4*>(a.stage_pair + (size_t)p * a.cap + (size_t)gidx * 4);
+              local[0] = make_uint4(v.x, ix.x, v.y, ix.y);
+              local[1] = make_uint4(v.z, ix.z, v.w, ix.w);
+            }
+            const unsigned e = gidx * 4;
+            const unsigned idx4[4] = {ix.x, ix.y, ix.z, ix.w};
+            const unsigned val4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const bool live = gidx < groups && e + j < n;
+              if (live && idx4[j] >= lim) status.fail(kBadArgument, p, (unsigned)a.peers.seq);  // corrupt index
+              const bool use = live && idx4[j] < lim;
+              const unsigned bin = use ? (idx4[j] >> kTileShift) * (unsigned)world + (unsigned)p : 0xffffffffu;
+              // lanes with the same bin elect a leader that touches the counter once
+              const unsigned peers_mask = __match_any_sync(0xffffffffu, bin);
+              fn(use, bin, peers_mask, idx4[j], val4[j]);
+            }
+          };
+          for (unsigned t = 0; t < trips; t += 2) {   // two groups in flight per thread
+            const unsigned g0 = t * gstride + gtid, g1 = g0 + gstride;
+            uint4 v0, i0, v1, i1;
+            fetch(g0, v0, i0);
+            if (t + 1 < trips) fetch(g1, v1, i1);
+            consume(g0, v0, i0);
+            if (t + 1 < trips) consume(g1, v1, i1);
+          }
+        }
+      };
+      const unsigned lane_id = tid & 31;
+      if (okx) {
+        for_each_pair(Bool<false>{}, [&](bool use, unsigned bin, unsigned mask, unsigned, unsigned) {
+          if (use && lane_id == (unsigned)(__ffs(mask) - 1)) atomicAdd(&a.tile_start[bin], (unsigned)__popc(mask));
+        });
+      }
+      okx = bar.sync();
+      // D2: exclusive prefix sum over the bins (CTA-chunked two-level scan)
+      const unsigned chunk_bins = (nbins + gridDim.x - 1) / gridDim.x;
+      const unsigned cb0 = blockIdx.x * chunk_bins, cb1 = min(cb0 + chunk_bins, nbins);
+      auto block_sum = [&](unsigned v) {
+        v = (unsigned)warp_sum((int)v);
+        if ((tid & 31) == 0) s_scan[tid >> 5] = v;
+        __syncthreads();
+        unsigned tot = 0;
+        for (int w = 0; w < kBlock / 32; ++w) tot += s_scan[w];
+        __syncthreads();
+        return tot;
+      };
+      if (okx) {
+        unsigned part = 0;
+        for (unsigned b = cb0 + tid; b < cb1; b += kBlock) part += __ldcg(a.tile_start + b);
+        const unsigned tot = block_sum(part);
+        if (tid == 0) a.scan_tmp[blockIdx.x] = tot;
+      }
+      okx = bar.sync();
+      if (okx) {
+        unsigned part = 0;
+        for (unsigned c = tid; c < blockIdx.x; c += kBlock) part += __ldcg(a.scan_tmp + c);
+        unsigned running = block_sum(part);   // pairs in all earlier chunks
+        if (tid == 0) s_carry = running;
+        __syncthreads();
+        for (unsigned b0 = cb0; b0 < cb1; b0 += kBlock) {
+          const unsigned b = b0 + tid;
+          const unsigned c = b < cb1 ? __ldcg(a.tile_start + b) : 0u;
+          // block-wide exclusive scan of c
+          unsigned incl = c;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const unsigned nb = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((tid & 31) >= o) incl += nb;
+          }
+          if ((tid & 31) == 31) s_scan[tid >> 5] = incl;
+          __syncthreads();
+          unsigned before = 0;
+          for (int w = 0; w < (tid >> 5); ++w) before += s_scan[w];
+          const unsigned excl = s_carry + before + incl - c;
+          if (b < cb1) { a.tile_start[b] = excl; a.tile_cur[b] = excl; }
+          __syncthreads();
+          if (tid == kBlock - 1) s_carry = excl + c;
+          __syncthreads();
+        }
+        if (blockIdx.x == gridDim.x - 1 && tid == 0) a.tile_start[nbins] = s_carry;  // sentinel = total pairs
+      }
+      okx = bar.sync();
+      // D3: move every pair to its (tile, source rank) block
+      if (okx) {
+        for_each_pair(Bool<true>{}, [&](bool use, unsigned bin, unsigned mask, unsigned idx, unsigned val) {
+          unsigned base = 0;
+          const unsigned leader = (unsigned)(__ffs(mask) - 1);
+          if (use && lane_id == leader) base = atomicAdd(&a.tile_cur[bin], (unsigned)__popc(mask));
+          base = __shfl_sync(0xffffffffu, base, leader);   // every lane takes part; only members of `mask` use it
+          if (use) {
+            const unsigned pos = base + __popc(mask & ((1u << lane_id) - 1u));
+            a.sort_pair[pos] = make_uint2(val, idx);
+          }
+        });
+      }
+      okx = bar.sync();
+      // D4: build the output in shared memory, kGroup tiles (64 KiB) at a time, source ranks in order
+      // 0..W-1 (within one rank's block the indices are distinct, so plain adds suffice), then one dense,
+      // coalesced write.  The block boundaries of the next unit are fetched while the current one is built.
+      if (okx) {
+        constexpr int kR = 8;                        // pairs per thread and chunk
+        constexpr int kGroup = 2;                    // tiles per unit: stage.val and stage.idx hold one each
+        static_assert(kGroup == 2 && kGroup * kMaxWorld <= 32, "block_of() assumes two tiles and at most 32 blocks per unit");
+        constexpr int kUnitElems = kGroup * kTileElems;
+        __shared__ unsigned s_b[3][kGroup * kMaxWorld + 1];
+        float* tile = sm.stage.val;                  // val[8192] and idx[8192] are adjacent: 16384 floats
+        const long long units = (tiles + kGroup - 1) / kGroup;
+        const unsigned ubins = kGroup * (unsigned)world;
+        const unsigned w = (unsigned)world;
+        auto fetch_bounds = [&](long long u) {       // boundaries past the last tile repeat the sentinel
+          const unsigned b = (unsigned)u * ubins + tid;
+          return __ldcg(a.tile_start + (b < nbins ? b : nbins));
+        };
+        auto load_chunk = [&](uint2 (&pr)[kR], unsigned j0, unsigned s1) {
+#pragma unroll
+          for (int r = 0; r < kR; ++r) {
+            const unsigned j = j0 + r * kBlock + tid;
+            pr[r] = j < s1 ? __ldcg(a.sort_pair + j) : make_uint2(0u, 0u);
+          }
+        };
+        long long u = blockIdx.x;
+        if (tid <= ubins) {
+          if (u < units) s_b[0][tid] = fetch_bounds(u);
+          if (u + gridDim.x < units) s_b[1][tid] = fetch_bounds(u + gridDim.x);
+        }
+        __syncthreads();
+        uint2 pr[kR], prn[kR];
+        if (u < units) load_chunk(pr, s_b[0][0], s_b[0][ubins]);
+        int cur = 0;
+        for (; u < units; u += gridDim.x) {
+          const int nxt = cur == 2 ? 0 : cur + 1, nn = nxt == 2 ? 0 : nxt + 1;
+          // boundaries two units ahead and the first chunk of the next unit travel while this one is built
+          unsigned nb = 0;
+          if (u + 2 * (long long)gridDim.x < units && tid <= ubins) nb = fetch_bounds(u + 2 * (long long)gridDim.x);
+          if (u + gridDim.x < units) load_chunk(prn, s_b[nxt][0], s_b[nxt][ubins]);
+          for (int i = tid * 4; i < kUnitElems; i += kBlock * 4)
+            *reinterpret_cast<float4*>(tile + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+          __syncthreads();
+          const unsigned* bnd = s_b[cur];
+          const unsigned s0 = bnd[0], s1 = bnd[ubins];
+          for (unsigned j0 = s0; j0 < s1; j0 += kBlock * kR) {
+            if (j0 != s0) load_chunk(pr, j0, s1);
+            int src[kR];
+            const unsigned jlast = min(j0 + kBlock * kR, s1) - 1;
+            // block of position j: the last q with bnd[q] <= j (ubins <= 32: five halving steps)
+            auto block_of = [&](unsigned j) {
+              unsigned lo = 0;
+#pragma unroll
+              for (unsigned step = 16; step > 0; step >>= 1) {
+                const unsigned q = lo + step;
+                if (q < ubins && bnd[q] <= j) lo = q;
+              }
+              return lo;
+            };
+            const unsigned b_first = block_of(j0), b_last = block_of(jlast);
+            // one tile in the chunk: only its ranks; several tiles: every rank
+            const bool one_tile = (b_first >= w) == (b_last >= w);
+            const int p_first = one_tile ? (int)(b_first >= w ? b_first - w : b_first) : 0;
+            const int p_last = one_tile ? (int)(b_last >= w ? b_last - w : b_last) : world - 1;
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+              const unsigned j = j0 + r * kBlock + tid;
+              const unsigned bin = block_of(j);
+              src[r] = j < s1 ? (int)(bin >= w ? bin - w : bin) : -1;
+            }
+            for (int p = p_first; p <= p_last; ++p) {
+#pragma unroll
+              for (int r = 0; r < kR; ++r)
+                if (src[r] == p) {   // product rounded first, as in the scatter-add decode
+                  float* slot = tile + (pr[r].y & (kUnitElems - 1));
+                  *slot = __fadd_rn(*slot, __fmul_rn(__uint_as_float(pr[r].x), a.scale));
+                }
+              __syncthreads();
+            }
+          }
+          const long long base = u * kUnitElems;
+          for (int i = tid * 4; i < kUnitElems; i += kBlock * 4) {
+            const long long gi = base + i;
+            if (gi + 4 <= a.total) {
+              *reinterpret_cast<float4*>(a.out + gi) = *reinterpret_cast<const float4*>(tile + i);
+            } else {
+              for (int j = 0; j < 4; ++j) if (gi + j < a.total) a.out[gi + j] = tile[i + j];
+            }
+          }
+          if (tid <= ubins) s_b[nn][tid] = nb;
+#pragma unroll
+          for (int r = 0; r < kR; ++r) pr[r] = prn[r];
+          __syncthreads();
+          cur = nxt;
         }
       }
       bar.sync();

@@ -321,3 +321,54 @@ def test_dgc_with_gradient_clipping_runs_fused():
     expect = _dense_topk(clipped, int(n * ratio))
     torch.testing.assert_close(out, expect, rtol=1e-6, atol=1e-9)
     assert out.abs().max() <= bound + 1e-6
+
+
+@pytest.mark.parametrize("W", [1, 2, 4])
+@pytest.mark.parametrize("n,ratio", [(200_000, 0.4), (70_001, 0.01), (5000, 0.05)])
+def test_tile_bucketed_decode_matches_scatter_decode(monkeypatch, W, n, ratio):
+    """The counting-sort decode (pairs bucketed per 8192-element tile and source rank, tiles built in shared
+    memory) must give the bits of the rank-ordered scatter-add, on consecutive exchanges of one channel."""
+    import grace_b200.ops.exchange as X
+
+    monkeypatch.setattr(X, "TILE_DECODE_DEFAULT", True)
+    monkeypatch.setattr(X, "TILE_DECODE_MIN_ELEMS", 0)
+    monkeypatch.setattr(X, "TILE_DECODE_MIN_DENSITY", 0.0)
+    vw = _world(W, {"compressor": "topk", "memory": "none", "communicator": "allgather", "compress_ratio": ratio})
+    k = max(1, int(n * ratio))
+    for step in range(3):
+        grads = [_rand(n, seed=40 * step + r) for r in range(W)]
+        outs = vw.step(grads, "w")
+        vw.check()
+        plan = next(iter(vw.comms[0]._plans.values()))
+        assert plan.channel._tile is not None and plan.channel._tile[1] is not None   # the new path really ran
+        expect = torch.zeros(n, device=_dev())
+        for r in range(W):
+            expect += _dense_topk(grads[r], k) * (1.0 / W)
+        for r in range(W):
+            assert torch.equal(outs[r], expect)
+
+
+def test_tile_bucketed_decode_threshold_and_segments(monkeypatch):
+    import grace_b200.ops.exchange as X
+    from grace_b200.ops.exchange import FlatLayout
+
+    monkeypatch.setattr(X, "TILE_DECODE_DEFAULT", True)
+    monkeypatch.setattr(X, "TILE_DECODE_MIN_ELEMS", 0)
+    monkeypatch.setattr(X, "TILE_DECODE_MIN_DENSITY", 0.0)
+    W = 2
+    vw = _world(W, {"compressor": "threshold", "memory": "none", "communicator": "allgather", "threshold": 2e-3})
+    names, numels = ["a", "b", "c"], [9000, 130, 20_000]
+    lay = FlatLayout(names, numels)
+    flats = []
+    for r in range(W):
+        f = torch.zeros(lay.total, device=_dev())
+        for i, (o, m) in enumerate(zip(lay.offsets, numels)):
+            f[o : o + m] = _rand(m, seed=7 * r + i)
+        flats.append(f)
+    outs = vw.step_flat([f.clone() for f in flats], lay)
+    vw.check()
+    expect = torch.zeros(lay.total, device=_dev())
+    for r in range(W):
+        expect += torch.where(flats[r].abs() >= 2e-3, flats[r], torch.zeros_like(flats[r])) * (1.0 / W)
+    for r in range(W):
+        assert torch.equal(outs[r], expect)
