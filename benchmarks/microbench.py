@@ -41,6 +41,9 @@ CASES = {
     "qsgd8_a2a": dict(compressor="qsgd", memory="residual", communicator="alltoall", quantum_num=127),
     "efsign": dict(compressor="efsignsgd", memory="efsignsgd", communicator="allgather", lr=0.1),
     "natural": dict(compressor="natural", memory="residual", communicator="allgather"),
+    # uncompressed mean: "dense" = one-shot peer loads + two-phase option, "dense_nvls" = NVSwitch multicast kernel
+    "dense": dict(compressor="none", memory="none", communicator="alltoall"),
+    "dense_nvls": dict(compressor="none", memory="none", communicator="allreduce", nvls=True),
     "powersgd4": dict(compressor="powersgd", memory="powersgd", communicator="allreduce", compress_rank=4,
                       use_memory=True),
 }
@@ -66,6 +69,11 @@ def roofline_ms(case, n, world, bw):
     elif case == "qsgd8_a2a":
         hbm = 19 * n                                         # encode 13 B, reduce my chunk 1 + 1/W B, gather 1 + 4 B
         link = 2.0 * (world - 1) / world * n * (1 + 4.0 / 128)
+    elif case in ("dense", "dense_nvls"):
+        hbm = 8 * n                                          # read g, write the mean
+        # multicast: every GPU receives the other ranks' share of its slice plus the broadcast of the rest;
+        # two-phase peer loads: reduce-scatter + all-gather
+        link = (2.0 if case == "dense" else 1.0) * (world - 1) / world * n * 4
     elif case == "efsign":
         hbm = (12 + 8 + 4) * n + (1 + world) * n / 8
         link = (world - 1) * n / 8
@@ -115,6 +123,9 @@ def main():
         if args.impl == "library":
             import grace_b200
 
+            p.pop("nvls", None)
+            if case.startswith("dense"):
+                p["communicator"] = "allreduce"
             return grace_b200.grace_from_params(p)
         # reference: construct the classes directly where its helper cannot
         if case == "dgc01":
@@ -134,6 +145,9 @@ def main():
             raise RuntimeError("reference natural compression needs cupy (not installed)")
         from grace_dl.dist.helper import grace_from_params
 
+        p.pop("nvls", None)
+        if case.startswith("dense"):
+            p["communicator"] = "allreduce"
         return grace_from_params(p)
 
     rows = []

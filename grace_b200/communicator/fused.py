@@ -87,7 +87,9 @@ class _Plan:
                 self.mode = X.SPARSE_TOPK
                 self.ks = [topk_count(n, comp.compress_ratio) for n in layout.numels]
                 self.cap = X.sparse_capacity(layout, self.ks, self.mode)
-            slot_bytes = Cn.sparse_slot_bytes(self.cap)
+            # tile-ordered lists (sender sorts by output tile, receivers build dense tiles): same decision on every rank
+            self.tile = X.tile_decode_wanted(layout.total, self.cap, owner.world_size, self.mode)
+            slot_bytes = Cn.sparse_slot_bytes(self.cap, layout.total if self.tile else 0)
         else:
             self.codec = owner._codec
             self.alltoall = owner.mode == "alltoall" and self.codec in (X.CODEC["qsgd"], X.CODEC["natural"],
@@ -235,7 +237,8 @@ class FusedExchange(Communicator):
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,
                 beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
                 threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
-                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps, clip=clip)
+                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps, clip=clip,
+                tile_decode=plan.tile)
         else:
             seq = X.run_quant(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,

@@ -65,7 +65,7 @@ PYBIND11_MODULE(_C, m) {
   });
 
   // ---- sizes / occupancy ----
-  m.def("sparse_slot_bytes", &sparse_slot_bytes);
+  m.def("sparse_slot_bytes", &sparse_slot_bytes, pybind11::arg("cap"), pybind11::arg("tiled_total") = 0);
   m.def("sparse_max_grid", &sparse_max_grid);
   m.def("quant_slot_bytes", &quant_slot_bytes, py::arg("codec"), py::arg("total"), py::arg("nseg"), py::arg("alltoall_world") = 0);
   m.def("quant_max_grid", &quant_max_grid);
@@ -85,10 +85,9 @@ PYBIND11_MODULE(_C, m) {
            unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
            uintptr_t seg_seed, unsigned rk_step, uintptr_t clip, uintptr_t tile_start, uintptr_t tile_cur,
-           uintptr_t scan_tmp, uintptr_t sort_pair, uintptr_t stage_pair) {
+           uintptr_t scan_tmp) {
           SparseArgs a{};
           a.tile_start = ptr<unsigned>(tile_start); a.tile_cur = ptr<unsigned>(tile_cur); a.scan_tmp = ptr<unsigned>(scan_tmp);
-          a.sort_pair = ptr<uint2>(sort_pair); a.stage_pair = ptr<uint2>(stage_pair);
           a.clip = ptr<const float>(clip);
           a.kprefix = ptr<const int>(kprefix); a.seg_seed = ptr<const unsigned long long>(seg_seed); a.rk_step = rk_step;
           if (mode == kSparseRandomK && (!kprefix || !seg_seed)) throw std::invalid_argument("random-k needs kprefix and seeds");
@@ -122,6 +121,22 @@ PYBIND11_MODULE(_C, m) {
           a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
           if (total % 128 != 0) throw std::invalid_argument("total must be a multiple of 128");
           check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
+        });
+
+  // ---- dense all-reduce over the NVSwitch multicast mapping ----
+  m.def("dense_max_grid", &dense_max_grid);
+  m.def("dense_allreduce",
+        [](uintptr_t g, uintptr_t out, uintptr_t symm, uintptr_t mc, long long total, float scale, uintptr_t barrier,
+           uintptr_t status, unsigned long long ready2_off, int rank, int world, unsigned long long seq,
+           unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
+           unsigned long long ack_off, int grid, uintptr_t stream) {
+          DenseArgs a{};
+          a.g = ptr<const float>(g); a.out = ptr<float>(out); a.symm = ptr<float>(symm); a.mc = ptr<float>(mc);
+          a.total = total; a.scale = scale; a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status);
+          a.ready2_off = ready2_off;
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, 0);
+          if ((g | out | symm | mc) % 16 != 0) throw std::invalid_argument("dense_allreduce: pointers must be 16-byte aligned");
+          check(launch_dense_allreduce(a, grid, reinterpret_cast<cudaStream_t>(stream)), "dense_allreduce");
         });
 
   // ---- fused PowerSGD (tcgen05) ----

@@ -76,14 +76,13 @@ struct SparseArgs {
   const unsigned long long* seg_seed;  // nseg seeds (derived from the tensor names, identical on every rank)
   unsigned rk_step;                 // per-plan step counter (part of the Philox counter)
   const float* clip;                // nseg clamp bounds applied to g before compensation (DGC clipping), nullable
-  // Tile-bucketed decode (nullable: then every list is scatter-added with red.global): the received
-  // (value, index) pairs are counting-sorted by (8192-element output tile, source rank) into sort_pair;
-  // each tile is then built in shared memory in rank order and written once, densely.
-  unsigned* tile_start;             // tiles * world + 1 (zero on entry; holds exclusive prefix sums afterwards)
-  unsigned* tile_cur;               // tiles * world running cursors
+  // Tile-ordered exchange (nullable: then lists travel unordered and are scatter-added with red.global):
+  // the sender orders its list by 8192-element output tile into a second pair of arrays in the slot,
+  // followed by a directory of tile offsets; receivers build whole tiles in shared memory.  The slot
+  // must then be sized with sparse_slot_bytes(cap, total).  Local scratch of the ordering step:
+  unsigned* tile_start;             // tiles + 1 counters / prefix sums
+  unsigned* tile_cur;               // tiles running cursors
   unsigned* scan_tmp;               // one word per CTA
-  uint2* sort_pair;                 // world * cap entries of (value bits, index)
-  uint2* stage_pair;                // world * cap: local copy of the peers' lists, made while counting
   unsigned* barrier;  // one word, zeroed by the launcher
   unsigned* status;   // 4 words
   unsigned cap;       // slot capacity in entries (multiple of 16)
@@ -91,7 +90,7 @@ struct SparseArgs {
   PeerTable peers;
 };
 
-size_t sparse_slot_bytes(unsigned cap);
+size_t sparse_slot_bytes(unsigned cap, long long tiled_total = 0);
 size_t sparse_smem_bytes();
 int sparse_max_grid(int device, int sm_limit);
 cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t stream);
@@ -147,6 +146,25 @@ struct QuantArgs {
 size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world = 0);
 int quant_max_grid(int device, int sm_limit);
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
+
+// ------------------------------------------------------------ dense NVLS ----
+// Uncompressed all-reduce over the NVSwitch multicast mapping of a symmetric buffer
+// (dense_allreduce.cu).  `symm` is this rank's copy of the buffer, `mc` the multicast
+// address of the same buffer; `g` / `out` may equal `symm` (no staging copies then).
+struct DenseArgs {
+  const float* g;
+  float* out;
+  float* symm;
+  float* mc;
+  long long total;                // floats, multiple of 4
+  float scale;                    // applied to the sum (1/W for the mean)
+  unsigned* barrier;
+  unsigned* status;
+  unsigned long long ready2_off;  // flag pad of the second rendezvous
+  PeerTable peers;
+};
+int dense_max_grid(int device, int sm_limit);
+cudaError_t launch_dense_allreduce(const DenseArgs& a, int grid, cudaStream_t stream);
 
 // -------------------------------------------------------------- low rank ----
 // One matrix (n x m, row-major) of a PowerSGD launch.  All offsets in floats.

@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   const float* __restrict__ src = a.acc ? a.acc : a.g;
   const bool topk = a.mode == kSparseTopK;
   const bool randomk = a.mode == kSparseRandomK;
-  const bool dense_decode = a.tile_start != nullptr && !randomk && a.out != nullptr;  // tile-bucketed decode
+  const bool dense_decode = a.tile_start != nullptr && !randomk;  // tile-ordered lists and decode
 
   if (a.phases & kPhaseCompress) {
     // Before overwriting the slot of parity (seq & 1): every peer must have
@@ -162,6 +162,10 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     if (blockIdx.x == 0 && tid == 0) { my_hdr[0] = 0; my_hdr[1] = 0; }
+    if (dense_decode) {   // tile counters of the ordering step; many grid barriers lie between here and their use
+      const long long nb1 = ((a.total + kTileElems - 1) >> kTileShift) + 1;
+      for (long long b = (long long)blockIdx.x * kBlock + tid; b < nb1; b += (long long)gridDim.x * kBlock) a.tile_start[b] = 0;
+    }
     for (int b = tid; b < kBins; b += kBlock) sm.hist[b] = 0;
     __syncthreads();
 
@@ -500,6 +504,112 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       }
       ok = bar.sync();
     }
+    if (dense_decode) {
+      // ---- order the list by output tile (counting sort of this rank's own picks, all in local memory) and
+      //      publish a directory of tile offsets: the receivers then build whole tiles without any sorting ----
+      const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
+      const unsigned nbins = (unsigned)tiles;
+      const unsigned gtid = blockIdx.x * kBlock + tid, gstride = gridDim.x * kBlock;
+      const unsigned n_mine = min(ld_cg_u32(my_hdr), a.cap);   // every pick is counted: a grid barrier lies behind us
+      float* const s_vals = my_vals + 2 * (size_t)a.cap;       // second pair of arrays in the slot: the ordered list
+      int* const s_idx = reinterpret_cast<int*>(s_vals + a.cap);
+      unsigned* const dir = reinterpret_cast<unsigned*>(s_vals + 2 * (size_t)a.cap);
+      __shared__ unsigned s_scan[kBlock / 32];
+      __shared__ unsigned s_carry;
+      const unsigned lane_id = tid & 31;
+      const unsigned groups = (n_mine + 3) / 4;
+      const unsigned trips = (groups + gstride - 1) / gstride;   // uniform trip count: warp collectives inside
+      auto for_each_mine = [&](auto&& fn) {
+        for (unsigned t = 0; t < trips; ++t) {
+          const unsigned gidx = t * gstride + gtid;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u), ix = make_uint4(0u, 0u, 0u, 0u);
+          if (gidx < groups) {
+            v = ld_cg_u4(my_vals + (size_t)gidx * 4);
+            ix = ld_cg_u4(my_idx + (size_t)gidx * 4);
+          }
+          const unsigned idx4[4] = {ix.x, ix.y, ix.z, ix.w};
+          const unsigned val4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool use = gidx < groups && gidx * 4 + j < n_mine && idx4[j] < (unsigned)a.total;
+            const unsigned bin = use ? idx4[j] >> kTileShift : 0xffffffffu;
+            // lanes with the same tile elect a leader that touches the counter once
+            const unsigned mask = __match_any_sync(0xffffffffu, bin);
+            fn(use, bin, mask, idx4[j], val4[j]);
+          }
+        }
+      };
+      // S1: count the picks per tile (the counters were zeroed at the start of the kernel)
+      if (ok) {
+        for_each_mine([&](bool use, unsigned bin, unsigned mask, unsigned, unsigned) {
+          if (use && lane_id == (unsigned)(__ffs(mask) - 1)) atomicAdd(&a.tile_start[bin], (unsigned)__popc(mask));
+        });
+      }
+      ok = bar.sync();
+      // S2: exclusive prefix sum over the tiles (CTA-chunked two-level scan) -> directory
+      const unsigned chunk_bins = (nbins + gridDim.x - 1) / gridDim.x;
+      const unsigned cb0 = blockIdx.x * chunk_bins, cb1 = min(cb0 + chunk_bins, nbins);
+      auto block_sum = [&](unsigned v) {
+        v = (unsigned)warp_sum((int)v);
+        if ((tid & 31) == 0) s_scan[tid >> 5] = v;
+        __syncthreads();
+        unsigned tot = 0;
+        for (int w = 0; w < kBlock / 32; ++w) tot += s_scan[w];
+        __syncthreads();
+        return tot;
+      };
+      if (ok) {
+        unsigned part = 0;
+        for (unsigned b = cb0 + tid; b < cb1; b += kBlock) part += __ldcg(a.tile_start + b);
+        const unsigned tot = block_sum(part);
+        if (tid == 0) a.scan_tmp[blockIdx.x] = tot;
+      }
+      ok = bar.sync();
+      if (ok) {
+        unsigned part = 0;
+        for (unsigned c = tid; c < blockIdx.x; c += kBlock) part += __ldcg(a.scan_tmp + c);
+        unsigned running = block_sum(part);   // pairs in all earlier chunks
+        if (tid == 0) s_carry = running;
+        __syncthreads();
+        for (unsigned b0 = cb0; b0 < cb1; b0 += kBlock) {
+          const unsigned b = b0 + tid;
+          const unsigned c = b < cb1 ? __ldcg(a.tile_start + b) : 0u;
+          // block-wide exclusive scan of c
+          unsigned incl = c;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const unsigned nb = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((tid & 31) >= o) incl += nb;
+          }
+          if ((tid & 31) == 31) s_scan[tid >> 5] = incl;
+          __syncthreads();
+          unsigned before = 0;
+          for (int w = 0; w < (tid >> 5); ++w) before += s_scan[w];
+          const unsigned excl = s_carry + before + incl - c;
+          if (b < cb1) { a.tile_start[b] = excl; a.tile_cur[b] = excl; dir[b] = excl; }
+          __syncthreads();
+          if (tid == kBlock - 1) s_carry = excl + c;
+          __syncthreads();
+        }
+        if (blockIdx.x == gridDim.x - 1 && tid == 0) { a.tile_start[nbins] = s_carry; dir[nbins] = s_carry; }  // sentinel = list length
+      }
+      ok = bar.sync();
+      // S3: move every pick to its tile's block of the ordered list
+      if (ok) {
+        for_each_mine([&](bool use, unsigned bin, unsigned mask, unsigned idx, unsigned val) {
+          unsigned base = 0;
+          const unsigned leader = (unsigned)(__ffs(mask) - 1);
+          if (use && lane_id == leader) base = atomicAdd(&a.tile_cur[bin], (unsigned)__popc(mask));
+          base = __shfl_sync(0xffffffffu, base, leader);   // every lane takes part; only members of `mask` use it
+          if (use) {
+            const unsigned pos = base + __popc(mask & ((1u << lane_id) - 1u));
+            s_vals[pos] = __uint_as_float(val);
+            s_idx[pos] = (int)idx;
+          }
+        });
+      }
+      ok = bar.sync();
+    }
     if (blockIdx.x == 0 && tid == 0) {
       // clamp the published count to the capacity
       const unsigned n = my_hdr[0];
@@ -548,17 +658,19 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       }
       return;
     }
-    if (dense_decode) {
-      // ---- tile-bucketed decode ----
-      const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
-      const unsigned nbins = (unsigned)(tiles * world);
-      const unsigned gtid = blockIdx.x * kBlock + tid, gstride = gridDim.x * kBlock;
-      const unsigned lim = (unsigned)a.total;
+    if (dense_decode && a.out) {
+      // ---- tile-ordered decode: every peer's list arrives sorted by 8192-element output tile with a
+      //      directory of tile offsets, so each CTA builds whole output tiles in shared memory (source
+      //      ranks in order 0..W-1) and writes them once, densely; nothing is scattered to global memory ----
+      constexpr int kR = 8;                          // pairs per thread and chunk
+      constexpr int kGroup = 2;                      // tiles per unit: stage.val and stage.idx hold one each
+      constexpr int kUnitElems = kGroup * kTileElems;
       __shared__ unsigned s_n[kMaxWorld];
-      __shared__ unsigned s_scan[kBlock / 32];
-      __shared__ unsigned s_carry;
-      // D0: counters must start from zero (the previous exchange left prefix sums there)
-      for (unsigned b = gtid; b <= nbins; b += gstride) a.tile_start[b] = 0;
+      __shared__ unsigned s_b[3][kMaxWorld][2];      // per unit (ring of 3) and peer: first and one-past-last entry
+      __shared__ unsigned s_pref[3][kMaxWorld + 1];  // running sum of the peers' range lengths
+      const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
+      const long long units = (tiles + kGroup - 1) / kGroup;
+      const size_t sorted_off = kSlotHeaderBytes + (size_t)a.cap * 8, dir_off = sorted_off + (size_t)a.cap * 8;
       if (tid < world) {
         unsigned n = 0;
         const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ready_off) + tid;
@@ -566,206 +678,98 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           n = ld_cg_u32(a.peers.heap[tid] + a.peers.slot_off);
         s_n[tid] = n < a.cap ? n : a.cap;
       }
-      bool okx = bar.sync();
-      // D1: count the pairs per (tile, source rank); a warp merges its increments per bin
-      // The first traversal (counting) keeps a copy of every remote list in local memory, so that the
-      // second one (placement) does not cross NVLink again; each thread re-reads what it wrote itself.
-      auto for_each_pair = [&](auto second, auto&& fn) {
-        constexpr bool kSecond = decltype(second)::value;
-        for (int p = 0; p < world; ++p) {
-          const unsigned n = s_n[p];
-          const char* pv = a.peers.heap[p] + a.peers.slot_off + kSlotHeaderBytes;
-          const char* pi = pv + (size_t)a.cap * 4;
-          const unsigned groups = (n + 3) / 4;
-          const unsigned trips = (groups + gstride - 1) / gstride;   // uniform trip count: warp collectives inside
-          auto fetch = [&](unsigned gidx, uint4& v, uint4& ix) {
-            v = make_uint4(0u, 0u, 0u, 0u);
-            ix = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
-            if (gidx >= groups) return;
-            uint4* local = reinterpret_cast<uint4*>(a.stage_pair + (size_t)p * a.cap + (size_t)gidx * 4);
-            if (kSecond && p != rank) {
-              const uint4 lo = local[0], hi = local[1];
-              v = make_uint4(lo.x, lo.z, hi.x, hi.z);
-              ix = make_uint4(lo.y, lo.w, hi.y, hi.w);
-            } else {
-              v = ld_cg_u4(pv + (size_t)gidx * 16);
-              ix = ld_cg_u4(pi + (size_t)gidx * 16);
-            }
-          };
-          auto consume = [&](unsigned gidx, const uint4& v, const uint4& ix) {
-            if (!kSecond && p != rank && gidx < groups) {
-              uint4* local = reinterpret_cast<uint4*>(a.stage_pair + (size_t)p * a.cap + (size_t)gidx * 4);
-              local[0] = make_uint4(v.x, ix.x, v.y, ix.y);
-              local[1] = make_uint4(v.z, ix.z, v.w, ix.w);
-            }
-            const unsigned e = gidx * 4;
-            const unsigned idx4[4] = {ix.x, ix.y, ix.z, ix.w};
-            const unsigned val4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const bool live = gidx < groups && e + j < n;
-              if (live && idx4[j] >= lim) status.fail(kBadArgument, p, (unsigned)a.peers.seq);  // corrupt index
-              const bool use = live && idx4[j] < lim;
-              const unsigned bin = use ? (idx4[j] >> kTileShift) * (unsigned)world + (unsigned)p : 0xffffffffu;
-              // lanes with the same bin elect a leader that touches the counter once
-              const unsigned peers_mask = __match_any_sync(0xffffffffu, bin);
-              fn(use, bin, peers_mask, idx4[j], val4[j]);
-            }
-          };
-          for (unsigned t = 0; t < trips; t += 2) {   // two groups in flight per thread
-            const unsigned g0 = t * gstride + gtid, g1 = g0 + gstride;
-            uint4 v0, i0, v1, i1;
-            fetch(g0, v0, i0);
-            if (t + 1 < trips) fetch(g1, v1, i1);
-            consume(g0, v0, i0);
-            if (t + 1 < trips) consume(g1, v1, i1);
-          }
-        }
-      };
-      const unsigned lane_id = tid & 31;
-      if (okx) {
-        for_each_pair(Bool<false>{}, [&](bool use, unsigned bin, unsigned mask, unsigned, unsigned) {
-          if (use && lane_id == (unsigned)(__ffs(mask) - 1)) atomicAdd(&a.tile_start[bin], (unsigned)__popc(mask));
-        });
-      }
-      okx = bar.sync();
-      // D2: exclusive prefix sum over the bins (CTA-chunked two-level scan)
-      const unsigned chunk_bins = (nbins + gridDim.x - 1) / gridDim.x;
-      const unsigned cb0 = blockIdx.x * chunk_bins, cb1 = min(cb0 + chunk_bins, nbins);
-      auto block_sum = [&](unsigned v) {
-        v = (unsigned)warp_sum((int)v);
-        if ((tid & 31) == 0) s_scan[tid >> 5] = v;
-        __syncthreads();
-        unsigned tot = 0;
-        for (int w = 0; w < kBlock / 32; ++w) tot += s_scan[w];
-        __syncthreads();
-        return tot;
-      };
-      if (okx) {
-        unsigned part = 0;
-        for (unsigned b = cb0 + tid; b < cb1; b += kBlock) part += __ldcg(a.tile_start + b);
-        const unsigned tot = block_sum(part);
-        if (tid == 0) a.scan_tmp[blockIdx.x] = tot;
-      }
-      okx = bar.sync();
-      if (okx) {
-        unsigned part = 0;
-        for (unsigned c = tid; c < blockIdx.x; c += kBlock) part += __ldcg(a.scan_tmp + c);
-        unsigned running = block_sum(part);   // pairs in all earlier chunks
-        if (tid == 0) s_carry = running;
-        __syncthreads();
-        for (unsigned b0 = cb0; b0 < cb1; b0 += kBlock) {
-          const unsigned b = b0 + tid;
-          const unsigned c = b < cb1 ? __ldcg(a.tile_start + b) : 0u;
-          // block-wide exclusive scan of c
-          unsigned incl = c;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const unsigned nb = __shfl_up_sync(0xffffffffu, incl, o);
-            if ((tid & 31) >= o) incl += nb;
-          }
-          if ((tid & 31) == 31) s_scan[tid >> 5] = incl;
-          __syncthreads();
-          unsigned before = 0;
-          for (int w = 0; w < (tid >> 5); ++w) before += s_scan[w];
-          const unsigned excl = s_carry + before + incl - c;
-          if (b < cb1) { a.tile_start[b] = excl; a.tile_cur[b] = excl; }
-          __syncthreads();
-          if (tid == kBlock - 1) s_carry = excl + c;
-          __syncthreads();
-        }
-        if (blockIdx.x == gridDim.x - 1 && tid == 0) a.tile_start[nbins] = s_carry;  // sentinel = total pairs
-      }
-      okx = bar.sync();
-      // D3: move every pair to its (tile, source rank) block
-      if (okx) {
-        for_each_pair(Bool<true>{}, [&](bool use, unsigned bin, unsigned mask, unsigned idx, unsigned val) {
-          unsigned base = 0;
-          const unsigned leader = (unsigned)(__ffs(mask) - 1);
-          if (use && lane_id == leader) base = atomicAdd(&a.tile_cur[bin], (unsigned)__popc(mask));
-          base = __shfl_sync(0xffffffffu, base, leader);   // every lane takes part; only members of `mask` use it
-          if (use) {
-            const unsigned pos = base + __popc(mask & ((1u << lane_id) - 1u));
-            a.sort_pair[pos] = make_uint2(val, idx);
-          }
-        });
-      }
-      okx = bar.sync();
-      // D4: build the output in shared memory, kGroup tiles (64 KiB) at a time, source ranks in order
-      // 0..W-1 (within one rank's block the indices are distinct, so plain adds suffice), then one dense,
-      // coalesced write.  The block boundaries of the next unit are fetched while the current one is built.
-      if (okx) {
-        constexpr int kR = 8;                        // pairs per thread and chunk
-        constexpr int kGroup = 2;                    // tiles per unit: stage.val and stage.idx hold one each
-        static_assert(kGroup == 2 && kGroup * kMaxWorld <= 32, "block_of() assumes two tiles and at most 32 blocks per unit");
-        constexpr int kUnitElems = kGroup * kTileElems;
-        __shared__ unsigned s_b[3][kGroup * kMaxWorld + 1];
+      __syncthreads();
+      if (!status.failed()) {
         float* tile = sm.stage.val;                  // val[8192] and idx[8192] are adjacent: 16384 floats
-        const long long units = (tiles + kGroup - 1) / kGroup;
-        const unsigned ubins = kGroup * (unsigned)world;
-        const unsigned w = (unsigned)world;
-        auto fetch_bounds = [&](long long u) {       // boundaries past the last tile repeat the sentinel
-          const unsigned b = (unsigned)u * ubins + tid;
-          return __ldcg(a.tile_start + (b < nbins ? b : nbins));
+        auto fetch_bound = [&](long long u) {        // thread 2p+k: entry k (0: first, 1: end) of peer p
+          const int p = tid >> 1;
+          long long t = u * kGroup + (tid & 1) * kGroup;
+          if (t > tiles) t = tiles;
+          const unsigned d = ld_cg_u32(a.peers.heap[p] + a.peers.slot_off + dir_off + (size_t)t * 4);
+          return d < s_n[p] ? d : s_n[p];            // a directory can never point past the list
         };
-        auto load_chunk = [&](uint2 (&pr)[kR], unsigned j0, unsigned s1) {
+        auto prefix_of = [&](int ring) {             // warp 0: running sum of range lengths
+          if (tid < 32) {
+            unsigned len = 0;
+            if (tid < world) {
+              const unsigned d0 = s_b[ring][tid][0], d1 = s_b[ring][tid][1];
+              len = d1 > d0 ? d1 - d0 : 0u;
+            }
+            unsigned incl = len;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const unsigned nb = __shfl_up_sync(0xffffffffu, incl, o);
+              if (tid >= o) incl += nb;
+            }
+            if (tid < world) s_pref[ring][tid + 1] = incl;
+            if (tid == 0) s_pref[ring][0] = 0;
+          }
+        };
+        // pairs j0 + r * kBlock + tid of a unit's concatenated ranges (rank-major), fetched from the peers
+        auto load_chunk = [&](uint2 (&pr)[kR], int (&src)[kR], int ring, unsigned j0) {
+          const unsigned total_len = s_pref[ring][world];
 #pragma unroll
           for (int r = 0; r < kR; ++r) {
             const unsigned j = j0 + r * kBlock + tid;
-            pr[r] = j < s1 ? __ldcg(a.sort_pair + j) : make_uint2(0u, 0u);
+            src[r] = -1;
+            pr[r] = make_uint2(0u, 0u);
+            if (j < total_len) {
+              int p = 0;                             // last p with pref[p] <= j (world <= 16: four halving steps)
+#pragma unroll
+              for (int step = 8; step > 0; step >>= 1)
+                if (p + step < world && s_pref[ring][p + step] <= j) p += step;
+              const size_t e = (size_t)s_b[ring][p][0] + (j - s_pref[ring][p]);
+              const char* pv = a.peers.heap[p] + a.peers.slot_off + sorted_off;
+              pr[r].x = ld_cg_u32(pv + e * 4);
+              pr[r].y = ld_cg_u32(pv + ((size_t)a.cap + e) * 4);
+              src[r] = p;
+            }
           }
         };
         long long u = blockIdx.x;
-        if (tid <= ubins) {
-          if (u < units) s_b[0][tid] = fetch_bounds(u);
-          if (u + gridDim.x < units) s_b[1][tid] = fetch_bounds(u + gridDim.x);
+        if (tid < 2 * world) {
+          if (u < units) s_b[0][tid >> 1][tid & 1] = fetch_bound(u);
+          if (u + gridDim.x < units) s_b[1][tid >> 1][tid & 1] = fetch_bound(u + gridDim.x);
         }
         __syncthreads();
+        if (u < units) prefix_of(0);
+        if (u + gridDim.x < units) prefix_of(1);
+        __syncthreads();
         uint2 pr[kR], prn[kR];
-        if (u < units) load_chunk(pr, s_b[0][0], s_b[0][ubins]);
+        int src[kR], srcn[kR];
+        if (u < units) load_chunk(pr, src, 0, 0u);
         int cur = 0;
         for (; u < units; u += gridDim.x) {
           const int nxt = cur == 2 ? 0 : cur + 1, nn = nxt == 2 ? 0 : nxt + 1;
-          // boundaries two units ahead and the first chunk of the next unit travel while this one is built
+          const bool more = u + gridDim.x < units, more2 = u + 2 * (long long)gridDim.x < units;
+          // the directory entries two units ahead and the first chunk of the next unit travel while this one is built
           unsigned nb = 0;
-          if (u + 2 * (long long)gridDim.x < units && tid <= ubins) nb = fetch_bounds(u + 2 * (long long)gridDim.x);
-          if (u + gridDim.x < units) load_chunk(prn, s_b[nxt][0], s_b[nxt][ubins]);
+          if (more2 && tid < 2 * world) nb = fetch_bound(u + 2 * (long long)gridDim.x);
+          if (more) load_chunk(prn, srcn, nxt, 0u);
           for (int i = tid * 4; i < kUnitElems; i += kBlock * 4)
             *reinterpret_cast<float4*>(tile + i) = make_float4(0.f, 0.f, 0.f, 0.f);
           __syncthreads();
-          const unsigned* bnd = s_b[cur];
-          const unsigned s0 = bnd[0], s1 = bnd[ubins];
-          for (unsigned j0 = s0; j0 < s1; j0 += kBlock * kR) {
-            if (j0 != s0) load_chunk(pr, j0, s1);
-            int src[kR];
-            const unsigned jlast = min(j0 + kBlock * kR, s1) - 1;
-            // block of position j: the last q with bnd[q] <= j (ubins <= 32: five halving steps)
-            auto block_of = [&](unsigned j) {
-              unsigned lo = 0;
+          const unsigned total_len = s_pref[cur][world];
+          for (unsigned j0 = 0; j0 < total_len; j0 += kBlock * kR) {
+            if (j0 != 0) load_chunk(pr, src, cur, j0);
+            // ranks present in this chunk (uniform over the CTA)
+            const unsigned jlast = min(j0 + kBlock * kR, total_len) - 1;
+            int p_first = 0, p_last = 0;
 #pragma unroll
-              for (unsigned step = 16; step > 0; step >>= 1) {
-                const unsigned q = lo + step;
-                if (q < ubins && bnd[q] <= j) lo = q;
-              }
-              return lo;
-            };
-            const unsigned b_first = block_of(j0), b_last = block_of(jlast);
-            // one tile in the chunk: only its ranks; several tiles: every rank
-            const bool one_tile = (b_first >= w) == (b_last >= w);
-            const int p_first = one_tile ? (int)(b_first >= w ? b_first - w : b_first) : 0;
-            const int p_last = one_tile ? (int)(b_last >= w ? b_last - w : b_last) : world - 1;
-#pragma unroll
-            for (int r = 0; r < kR; ++r) {
-              const unsigned j = j0 + r * kBlock + tid;
-              const unsigned bin = block_of(j);
-              src[r] = j < s1 ? (int)(bin >= w ? bin - w : bin) : -1;
+            for (int step = 8; step > 0; step >>= 1) {
+              if (p_first + step < world && s_pref[cur][p_first + step] <= j0) p_first += step;
+              if (p_last + step < world && s_pref[cur][p_last + step] <= jlast) p_last += step;
             }
             for (int p = p_first; p <= p_last; ++p) {
 #pragma unroll
               for (int r = 0; r < kR; ++r)
-                if (src[r] == p) {   // product rounded first, as in the scatter-add decode
-                  float* slot = tile + (pr[r].y & (kUnitElems - 1));
-                  *slot = __fadd_rn(*slot, __fmul_rn(__uint_as_float(pr[r].x), a.scale));
+                if (src[r] == p) {
+                  if ((long long)(pr[r].y >> (kTileShift + 1)) != u) {   // not an index of this unit: corrupt list
+                    status.fail(kBadArgument, p, (unsigned)a.peers.seq);
+                  } else {   // product rounded first, as in the scatter-add decode
+                    float* slot = tile + (pr[r].y & (kUnitElems - 1));
+                    *slot = __fadd_rn(*slot, __fmul_rn(__uint_as_float(pr[r].x), a.scale));
+                  }
                 }
               __syncthreads();
             }
@@ -779,9 +783,11 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
               for (int j = 0; j < 4; ++j) if (gi + j < a.total) a.out[gi + j] = tile[i + j];
             }
           }
-          if (tid <= ubins) s_b[nn][tid] = nb;
+          if (more2 && tid < 2 * world) s_b[nn][tid >> 1][tid & 1] = nb;
 #pragma unroll
-          for (int r = 0; r < kR; ++r) pr[r] = prn[r];
+          for (int r = 0; r < kR; ++r) { pr[r] = prn[r]; src[r] = srcn[r]; }
+          __syncthreads();
+          if (more2) prefix_of(nn);
           __syncthreads();
           cur = nxt;
         }
@@ -838,7 +844,14 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
 
 }  // namespace
 
-size_t sparse_slot_bytes(unsigned cap) { return kSlotHeaderBytes + (size_t)cap * 8; }
+size_t sparse_slot_bytes(unsigned cap, long long tiled_total) {
+  size_t bytes = kSlotHeaderBytes + (size_t)cap * 8;
+  if (tiled_total > 0) {   // tile-ordered copy of the list + directory (one entry per tile and a sentinel)
+    const size_t tiles = (size_t)((tiled_total + kTileElems - 1) >> kTileShift);
+    bytes += (size_t)cap * 8 + (tiles + 1 + 3) / 4 * 16;
+  }
+  return bytes;
+}
 size_t sparse_smem_bytes() { return sizeof(Smem); }
 
 int sparse_max_grid(int device, int sm_limit) {

@@ -13,6 +13,10 @@ codecs of ``grace_dl/tensorflow/helper.py`` (``adaq``, ``inceptionn``,
     to the memory).
 ``seed``, ``timeout_ms``, ``comm_sms``
     forwarded to the fused exchange.
+``nvls`` (bool, default False; needs ``fused``)
+    with the ``none`` compressor and no memory, average through the NVSwitch
+    multicast mapping (``communicator/nvls.py``) where it is available; the
+    fused peer-load exchange stays the fallback.
 
 Unknown names raise ``NotImplementedError`` as in the reference.
 """
@@ -95,9 +99,15 @@ def grace_from_params(params: Dict[str, Any]):
         from .communicator.fused import FusedExchange
 
         mode = "alltoall" if comm_name == "alltoall" else "allgather"
-        return FusedExchange(
+        fused = FusedExchange(
             comp, mem, _world(params), mode=mode,
             seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
             comm_sms=params.get("comm_sms"), group=params.get("group"),
         )
+        if params.get("nvls", False) and comp_name == "none" and mem_name == "none":
+            from .communicator.nvls import NvlsAllreduce
+
+            return NvlsAllreduce(comp, mem, _world(params), fallback=fused, group=params.get("group"),
+                                 timeout_ms=params.get("timeout_ms", 10000), comm_sms=params.get("comm_sms"))
+        return fused
     return _COMMUNICATORS[comm_name](comp, mem, params)

@@ -154,23 +154,14 @@ class ExchangeChannel:
             self._grids[kind] = g
         return g
 
-    def tile_scratch(self, total: int, cap: int):
-        """Scratch of the tile-bucketed sparse decode, or None when the scatter-add decode is the better choice."""
-        key = (total, cap)
-        if self._tile is None or self._tile[0] != key:
-            world = self.heap.world
-            bins = -(-total // TILE_ELEMS) * world
-            pair_bytes = 16 * world * cap
-            if (total < TILE_DECODE_MIN_ELEMS or pair_bytes > TILE_DECODE_MAX_BYTES
-                    or world * cap < TILE_DECODE_MIN_DENSITY * total):
-                self._tile = (key, None)
-            else:
-                dev = self.device
-                self._tile = (key, (torch.zeros(bins + 1, dtype=torch.int32, device=dev),
-                                    torch.empty(bins, dtype=torch.int32, device=dev),
-                                    torch.empty(self.max_grid("sparse"), dtype=torch.int32, device=dev),
-                                    torch.empty(world * cap, 2, dtype=torch.int32, device=dev),
-                                    torch.empty(world * cap if world > 1 else 1, 2, dtype=torch.int32, device=dev)))
+    def tile_scratch(self, total: int):
+        """Local scratch of the tile-ordering step of the sparse exchange (counters, cursors, scan words)."""
+        if self._tile is None or self._tile[0] != total:
+            tiles = -(-total // TILE_ELEMS)
+            dev = self.device
+            self._tile = (total, (torch.zeros(tiles + 1, dtype=torch.int32, device=dev),
+                                  torch.empty(tiles, dtype=torch.int32, device=dev),
+                                  torch.empty(self.max_grid("sparse"), dtype=torch.int32, device=dev)))
         return self._tile[1]
 
     def slot_view(self, seq: int, numel: int, dtype, byte_offset: int = 0, rank: Optional[int] = None):
@@ -243,17 +234,29 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
-# The tile-bucketed decode of the sparse exchange (counting sort of the received pairs by output tile,
-# tiles built in shared memory, one dense write) beats the scatter-add decode once the output no longer
-# fits the L2 cache AND the ranks together deliver a few percent of its elements: measured on one B200
-# with 8 lists of 1 % of 256 Mi elements the exchange phase takes 0.94 ms against 1.02 ms and the compress
-# phase 0.77 ms against 0.98 ms (it no longer zero-fills the output); at 0.1 % it loses (0.55 against 0.19 ms).
-# GRACE_TILE_DECODE=0 turns it off, =force turns it on for every size.
+# Tile-ordered sparse exchange: the sender orders its (value, index) list by 8192-element output tile and
+# publishes a directory of tile offsets; receivers build whole output tiles in shared memory (ranks in order)
+# and write them once, densely, instead of scatter-adding every entry into global memory.  It pays once the
+# output no longer fits the L2 cache AND the ranks together deliver a percent or two of its elements; below
+# that the scattered adds are cheaper than the dense write.  Measured on one B200 with 8 lists of 256 Mi
+# elements each (compress + exchange phase of one rank): 1 % per list 1.27 ms against 2.00 ms, 0.1 % per list
+# 1.13 against 1.08 ms; 2 lists of 1 %: 1.15 against 1.25 ms; 8 lists of 1 % of 32 Mi: 0.29 against 0.35 ms.  GRACE_TILE_DECODE=0 turns it off, =force turns it on
+# for every size.  Every rank must decide alike (the slot layout depends on it): the rule uses only the
+# layout, the capacity and the world size.
 _TILE_ENV = os.environ.get("GRACE_TILE_DECODE", "1")
 TILE_DECODE_DEFAULT = _TILE_ENV != "0"
 TILE_DECODE_MIN_ELEMS = 0 if _TILE_ENV == "force" else 1 << 24
-TILE_DECODE_MIN_DENSITY = 0.0 if _TILE_ENV == "force" else 1.0 / 32     # world * capacity / elements
-TILE_DECODE_MAX_BYTES = 2 << 30
+TILE_DECODE_MIN_DENSITY = 0.0 if _TILE_ENV == "force" else 1.0 / 64     # world * capacity / elements
+TILE_DECODE_MAX_DENSITY = 0.5                                            # above this the lists outweigh the tiles
+
+
+def tile_decode_wanted(total: int, cap: int, world: int, mode: int) -> bool:
+    if not TILE_DECODE_DEFAULT or mode == SPARSE_RANDOMK:
+        return False
+    return (total >= TILE_DECODE_MIN_ELEMS and world * cap >= TILE_DECODE_MIN_DENSITY * total
+            and cap <= TILE_DECODE_MAX_DENSITY * total)
+
+
 TILE_ELEMS = 8192
 
 
@@ -271,16 +274,16 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
                scale: float = 1.0, levels: int = 3, phases: int = PHASE_ALL, seq: Optional[int] = None,
                grid: Optional[int] = None, kprefix: Optional[torch.Tensor] = None,
                seg_seed: Optional[torch.Tensor] = None, rk_step: int = 0,
-               clip: Optional[torch.Tensor] = None, tile_decode: Optional[bool] = None) -> int:
+               clip: Optional[torch.Tensor] = None, tile_decode: bool = False) -> int:
+    """``tile_decode``: the slot was sized with ``sparse_slot_bytes(cap, total)`` and every rank orders its list
+    by output tile (see ``tile_decode_wanted``)."""
     C = native()
     heap = channel.heap
     if seq is None:
         seq = channel.next_seq()
     if grid is None:
         grid = channel.max_grid("sparse")
-    if tile_decode is None:
-        tile_decode = TILE_DECODE_DEFAULT
-    td = channel.tile_scratch(layout.total, cap) if (tile_decode and mode != SPARSE_RANDOMK and out is not None) else None
+    td = channel.tile_scratch(layout.total) if (tile_decode and mode != SPARSE_RANDOMK) else None
     need = -(-layout.total // 2048)
     grid = max(1, min(grid, max(need, 1)))
     for t in (g, acc, u, out):
@@ -301,7 +304,6 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
         _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF, _ptr(clip),
         td[0].data_ptr() if td else 0, td[1].data_ptr() if td else 0, td[2].data_ptr() if td else 0,
-        td[3].data_ptr() if td else 0, td[4].data_ptr() if td else 0,
     )
     channel.post_status()
     return seq

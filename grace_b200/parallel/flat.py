@@ -41,7 +41,11 @@ class Bucket:
 
 
 class FlatParams:
-    def __init__(self, named_parameters: Iterable[Tuple[str, torch.nn.Parameter]], bucket_bytes: Optional[int] = None):
+    def __init__(self, named_parameters: Iterable[Tuple[str, torch.nn.Parameter]], bucket_bytes: Optional[int] = None,
+                 grad_buffer=None):
+        """``grad_buffer``: optional fp32 tensor, or a callable ``numel -> tensor or None``, that provides the
+        storage of the flat gradient buffer (e.g. ``NvlsAllreduce.buffer`` so that gradients are reduced in place
+        through the multicast mapping)."""
         named = [(n, p) for n, p in named_parameters if p.requires_grad]
         if not named:
             raise ValueError("no trainable parameters")
@@ -54,7 +58,16 @@ class FlatParams:
         self.layout = FlatLayout.from_named([(n, p.numel()) for n, p in named])
         self.layout.shapes = [tuple(p.shape) for _, p in named]
         self.flat_p = torch.zeros(self.layout.total, dtype=torch.float32, device=dev)
-        self.flat_g = torch.zeros(self.layout.total, dtype=torch.float32, device=dev)
+        if callable(grad_buffer):
+            grad_buffer = grad_buffer(self.layout.total)
+        if grad_buffer is not None:
+            if (grad_buffer.dtype != torch.float32 or grad_buffer.numel() < self.layout.total
+                    or grad_buffer.device != dev or grad_buffer.data_ptr() % 16):
+                raise ValueError("grad_buffer must be a 16-byte aligned fp32 tensor on %s with at least %d elements"
+                                 % (dev, self.layout.total))
+            self.flat_g = grad_buffer.reshape(-1)[: self.layout.total].zero_()
+        else:
+            self.flat_g = torch.zeros(self.layout.total, dtype=torch.float32, device=dev)
         with torch.no_grad():
             for p, off in zip(self.params, self.layout.offsets):
                 view = _dense_view(self.flat_p, off, p.data)

@@ -1,0 +1,123 @@
+"""Dense all-reduce through the NVSwitch multicast mapping (``multimem.ld_reduce`` / ``multimem.st``), one
+process per GPU.  Every rank records its findings and leaves through a common barrier, so no process exits
+while the others still use the multicast object.  Skipped with fewer than two GPUs or without multicast."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _guard(res, label, fn, default):
+    """Run a rank-local step; on an exception record it and carry on, so that every rank still takes part in
+    the collectives that follow (no rank may stop half way while the others wait for it)."""
+    try:
+        return fn()
+    except Exception:  # noqa: BLE001
+        res.setdefault("error", "%s: %s" % (label, traceback.format_exc()))
+        return default
+
+
+def _body(rank, world, dev):
+    from grace_b200 import grace_from_params
+
+    res = {}
+    grc = grace_from_params({"compressor": "none", "memory": "none", "communicator": "allreduce", "world_size": world,
+                             "fused": True, "nvls": True, "timeout_ms": 5000})
+    n = 1_000_000
+    buf = grc.buffer(n)          # collective; returns None on every rank alike when there is no multicast
+    if buf is None:
+        return {"unavailable": True}
+    # 1. a tensor outside the symmetric buffer (staged by the kernel), several exchanges in a row
+    worst = 0.0
+    for step in range(4):
+        g = torch.Generator().manual_seed(31 * step + rank)
+        x = torch.randn(n, generator=g).to(dev)
+        ref = x.clone()
+        dist.all_reduce(ref)
+        ref /= world
+        got = _guard(res, "staged", lambda: grc.step(x.clone(), "w"), torch.zeros_like(x))
+        _guard(res, "check", grc.check, None)
+        worst = max(worst, ((got - ref).abs().max() / ref.abs().max()).item())
+        gathered = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got)
+        res["same_%d" % step] = all(torch.equal(gathered[0], t) for t in gathered)
+    res["staged_err"] = worst
+    # 2. gradients that live in the symmetric buffer: reduced in place, no staging
+    g = torch.Generator().manual_seed(500 + rank)
+    x = torch.randn(n, generator=g).to(dev)
+    ref = x.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    buf.copy_(x)
+    out = _guard(res, "inplace", lambda: grc.step_flat(buf), buf)
+    _guard(res, "check", grc.check, None)
+    res["inplace_same_storage"] = out.data_ptr() == buf.data_ptr()
+    res["inplace_err"] = ((buf - ref).abs().max() / ref.abs().max()).item()
+    # 3. exact arithmetic: rank r contributes (r + 1) everywhere -> mean (W + 1) / 2
+    buf.fill_(float(rank + 1))
+    _guard(res, "exact", lambda: grc.step_flat(buf), None)
+    _guard(res, "check", grc.check, None)
+    res["exact"] = bool((buf == (world + 1) / 2.0).all())
+    # 4. small tensors take the fallback and still average
+    small = torch.full((1000,), float(rank), device=dev)
+    got = grc.step(small, "s")
+    res["small"] = bool(torch.allclose(got, torch.full_like(got, (world - 1) / 2.0)))
+    res["launches"] = grc.stats()["nvls_launches"]
+    return res
+
+
+def _entry(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        ret[rank] = _body(rank, world, dev)
+    except Exception:  # noqa: BLE001 - reported by the parent; the rank still leaves through the barrier
+        ret[rank] = {"error": traceback.format_exc()}
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_multicast_allreduce_matches_library_allreduce():
+    world = min(torch.cuda.device_count(), 8)
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _port()
+        procs = [ctx.Process(target=_entry, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(600)
+        for p in procs:
+            assert p.exitcode == 0, "rank exited with %s" % p.exitcode
+        res = dict(ret)
+    if all(r.get("unavailable") for r in res.values()):
+        pytest.skip("no NVSwitch multicast on this machine")
+    for rank in range(world):
+        r = res[rank]
+        assert "error" not in r, r.get("error")
+        assert r["staged_err"] < 1e-6 and r["inplace_err"] < 1e-6, r
+        assert all(r["same_%d" % s] for s in range(4)), "ranks disagree"
+        assert r["inplace_same_storage"] and r["exact"] and r["small"], r
+        assert r["launches"] == 6, r

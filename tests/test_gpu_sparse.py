@@ -326,8 +326,9 @@ def test_dgc_with_gradient_clipping_runs_fused():
 @pytest.mark.parametrize("W", [1, 2, 4])
 @pytest.mark.parametrize("n,ratio", [(200_000, 0.4), (70_001, 0.01), (5000, 0.05)])
 def test_tile_bucketed_decode_matches_scatter_decode(monkeypatch, W, n, ratio):
-    """The counting-sort decode (pairs bucketed per 8192-element tile and source rank, tiles built in shared
-    memory) must give the bits of the rank-ordered scatter-add, on consecutive exchanges of one channel."""
+    """The tile-ordered exchange (sender orders its list by 8192-element output tile and publishes a directory;
+    receivers build dense tiles in shared memory) must give the bits of the rank-ordered scatter-add, on
+    consecutive exchanges of one channel."""
     import grace_b200.ops.exchange as X
 
     monkeypatch.setattr(X, "TILE_DECODE_DEFAULT", True)
@@ -340,7 +341,7 @@ def test_tile_bucketed_decode_matches_scatter_decode(monkeypatch, W, n, ratio):
         outs = vw.step(grads, "w")
         vw.check()
         plan = next(iter(vw.comms[0]._plans.values()))
-        assert plan.channel._tile is not None and plan.channel._tile[1] is not None   # the new path really ran
+        assert plan.tile and plan.channel._tile is not None   # the tile-ordered path really ran
         expect = torch.zeros(n, device=_dev())
         for r in range(W):
             expect += _dense_topk(grads[r], k) * (1.0 / W)
