@@ -43,7 +43,10 @@ CASES = {
     "natural": dict(compressor="natural", memory="residual", communicator="allgather"),
     # uncompressed mean: "dense" = one-shot peer loads + two-phase option, "dense_nvls" = NVSwitch multicast kernel
     "dense": dict(compressor="none", memory="none", communicator="alltoall"),
-    "dense_nvls": dict(compressor="none", memory="none", communicator="allreduce", nvls=True),
+    "dense_nvls": dict(compressor="none", memory="none", communicator="allreduce", nvls=True, nvls_min_world=2),
+    # same, with the gradient living in the symmetric buffer (FlatParams(grad_buffer=...)): no staging copies
+    "dense_nvls_inplace": dict(compressor="none", memory="none", communicator="allreduce", nvls=True,
+                               nvls_min_world=2),
     "powersgd4": dict(compressor="powersgd", memory="powersgd", communicator="allreduce", compress_rank=4,
                       use_memory=True),
 }
@@ -69,11 +72,11 @@ def roofline_ms(case, n, world, bw):
     elif case == "qsgd8_a2a":
         hbm = 19 * n                                         # encode 13 B, reduce my chunk 1 + 1/W B, gather 1 + 4 B
         link = 2.0 * (world - 1) / world * n * (1 + 4.0 / 128)
-    elif case in ("dense", "dense_nvls"):
+    elif case in ("dense", "dense_nvls", "dense_nvls_inplace"):
         hbm = 8 * n                                          # read g, write the mean
-        # multicast: every GPU receives the other ranks' share of its slice plus the broadcast of the rest;
-        # two-phase peer loads: reduce-scatter + all-gather
-        link = (2.0 if case == "dense" else 1.0) * (world - 1) / world * n * 4
+        # two-phase peer loads: reduce-scatter + all-gather; multicast: all W copies of every slice leave through
+        # the switch once (the requester's own copy included) plus the broadcast of this rank's slice
+        link = (2.0 * (world - 1) / world if case == "dense" else 1.0 + 1.0 / world) * n * 4
     elif case == "efsign":
         hbm = (12 + 8 + 4) * n + (1 + world) * n / 8
         link = (world - 1) * n / 8
@@ -124,6 +127,7 @@ def main():
             import grace_b200
 
             p.pop("nvls", None)
+            p.pop("nvls_min_world", None)
             if case.startswith("dense"):
                 p["communicator"] = "allreduce"
             return grace_b200.grace_from_params(p)
@@ -146,6 +150,7 @@ def main():
         from grace_dl.dist.helper import grace_from_params
 
         p.pop("nvls", None)
+        p.pop("nvls_min_world", None)
         if case.startswith("dense"):
             p["communicator"] = "allreduce"
         return grace_from_params(p)
@@ -169,15 +174,18 @@ def main():
             gen = torch.Generator(device=dev).manual_seed(rank)
             base = torch.randn(shape, generator=gen, device=dev) * 1e-3
             times = []
+            resident = None
+            if case.endswith("_inplace") and args.impl == "ours" and hasattr(grc, "buffer"):
+                resident = grc.buffer(n)
             try:
                 for it in range(args.warmup + args.iters):
-                    g = base.clone()
+                    g = base.clone() if resident is None else resident.copy_(base)
                     flush.fill_(float(it))
                     dist.barrier()
                     torch.cuda.synchronize()
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                    out = grc.step(g, "w")
+                    out = grc.step(g, "w") if resident is None else grc.step_flat(g)
                     e1.record()
                     torch.cuda.synchronize()
                     if it >= args.warmup:

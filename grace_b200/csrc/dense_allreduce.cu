@@ -2,8 +2,10 @@
 // ("two-shot" in one kernel): every rank reduces its own 1/W slice with
 // multimem.ld_reduce (the switch pulls the slice from all W GPUs and adds in
 // flight) and broadcasts the scaled sum with multimem.st (the switch writes it
-// into all W copies).  Per GPU and direction this moves about N*4 bytes, against
-// 2*(W-1)/W*N*4 for a ring and (W-1)*N*4 for a one-shot gather.
+// into all W copies).  Per GPU and direction this moves (1 + 1/W)*N*4 bytes (a
+// multimem load fetches the requester's own copy through the switch too), against
+// 2*(W-1)/W*N*4 for a ring or a two-phase peer-load exchange and (W-1)*N*4 for a
+// one-shot gather: it wins from four ranks on and loses at two.
 //
 //   P0  copy the local gradient into the symmetric buffer (skipped when the
 //       caller's tensor already lives there)
@@ -68,7 +70,13 @@ __global__ void __launch_bounds__(kBlock, 1) dense_allreduce_kernel(const DenseA
   // P0: stage the local gradient
   if (a.g != a.symm) {
     const float4* g4 = reinterpret_cast<const float4*>(a.g);
-    for (long long i = gtid; i < n4; i += gstride) symm4[i] = __ldcs(g4 + i);
+    for (long long i0 = gtid; i0 < n4; i0 += gstride * kInFlight) {   // kInFlight loads ahead of the stores
+      float4 t[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) if (i0 + u * gstride < n4) t[u] = __ldcs(g4 + i0 + u * gstride);
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) if (i0 + u * gstride < n4) symm4[i0 + u * gstride] = t[u];
+    }
   }
   bool ok = bar.sync();
   // P1
@@ -78,13 +86,21 @@ __global__ void __launch_bounds__(kBlock, 1) dense_allreduce_kernel(const DenseA
     const long long chunk4 = (n4 + a.peers.world - 1) / a.peers.world;
     const long long lo = chunk4 * a.peers.rank;
     const long long hi = lo + chunk4 < n4 ? lo + chunk4 : n4;
-    for (long long i0 = lo + gtid; i0 < hi; i0 += gstride * kInFlight) {
-      float4 v[kInFlight];
+    // software pipeline: the loads of the next batch are in flight while this batch is scaled and stored
+    const long long step = gstride * kInFlight;
+    float4 v[kInFlight];
+    auto issue = [&](long long i0, float4 (&dst)[kInFlight]) {
 #pragma unroll
       for (int u = 0; u < kInFlight; ++u) {
         const long long i = i0 + u * gstride;
-        if (i < hi) v[u] = multimem_ld_reduce_add(mc4 + i);
+        if (i < hi) dst[u] = multimem_ld_reduce_add(mc4 + i);
       }
+    };
+    long long i0 = lo + gtid;
+    if (i0 < hi) issue(i0, v);
+    for (; i0 < hi; i0 += step) {
+      float4 nv[kInFlight];
+      if (i0 + step < hi) issue(i0 + step, nv);
 #pragma unroll
       for (int u = 0; u < kInFlight; ++u) {
         const long long i = i0 + u * gstride;
@@ -93,6 +109,8 @@ __global__ void __launch_bounds__(kBlock, 1) dense_allreduce_kernel(const DenseA
           multimem_st(mc4 + i, v[u]);
         }
       }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) v[u] = nv[u];
     }
   }
   __threadfence_system();   // the multicast stores are ordered before the flag that follows the barrier
@@ -102,9 +120,15 @@ __global__ void __launch_bounds__(kBlock, 1) dense_allreduce_kernel(const DenseA
   // P4: hand the result to the caller (L1 is not coherent with the switch's writes: read through L2)
   if (ok && a.out != a.symm) {
     float4* out4 = reinterpret_cast<float4*>(a.out);
-    for (long long i = gtid; i < n4; i += gstride) {
-      const uint4 v = ld_cg_u4(symm4 + i);
-      out4[i] = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+    for (long long i0 = gtid; i0 < n4; i0 += gstride * kInFlight) {
+      uint4 t[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) if (i0 + u * gstride < n4) t[u] = ld_cg_u4(symm4 + i0 + u * gstride);
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u)
+        if (i0 + u * gstride < n4)
+          out4[i0 + u * gstride] = make_float4(__uint_as_float(t[u].x), __uint_as_float(t[u].y), __uint_as_float(t[u].z),
+                                               __uint_as_float(t[u].w));
     }
   }
 }

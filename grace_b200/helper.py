@@ -15,8 +15,9 @@ codecs of ``grace_dl/tensorflow/helper.py`` (``adaq``, ``inceptionn``,
     forwarded to the fused exchange.
 ``nvls`` (bool, default False; needs ``fused``)
     with the ``none`` compressor and no memory, average through the NVSwitch
-    multicast mapping (``communicator/nvls.py``) where it is available; the
-    fused peer-load exchange stays the fallback.
+    multicast mapping (``communicator/nvls.py``) where it is available and the
+    job has at least ``nvls_min_world`` (default 4) ranks; the fused peer-load
+    exchange stays the fallback.
 
 Unknown names raise ``NotImplementedError`` as in the reference.
 """
@@ -108,6 +109,7 @@ def grace_from_params(params: Dict[str, Any]):
             from .communicator.nvls import NvlsAllreduce
 
             return NvlsAllreduce(comp, mem, _world(params), fallback=fused, group=params.get("group"),
-                                 timeout_ms=params.get("timeout_ms", 10000), comm_sms=params.get("comm_sms"))
+                                 timeout_ms=params.get("timeout_ms", 10000), comm_sms=params.get("comm_sms"),
+                                 min_world=params.get("nvls_min_world", 4))
         return fused
     return _COMMUNICATORS[comm_name](comp, mem, params)

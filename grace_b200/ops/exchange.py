@@ -246,7 +246,7 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 _TILE_ENV = os.environ.get("GRACE_TILE_DECODE", "1")
 TILE_DECODE_DEFAULT = _TILE_ENV != "0"
 TILE_DECODE_MIN_ELEMS = 0 if _TILE_ENV == "force" else 1 << 24
-TILE_DECODE_MIN_DENSITY = 0.0 if _TILE_ENV == "force" else 1.0 / 64     # world * capacity / elements
+TILE_DECODE_MIN_DENSITY = 0.0 if _TILE_ENV == "force" else 1.0 / 32     # world * capacity / elements
 TILE_DECODE_MAX_DENSITY = 0.5                                            # above this the lists outweigh the tiles
 
 

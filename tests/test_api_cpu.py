@@ -234,3 +234,34 @@ def test_metrics_helpers(tmp_path):
     grc.step(torch.randn(1000), "w")
     s = grc.stats()
     assert s["steps"] == 1 and 4.9 < s["compression_ratio"] < 5.1
+
+
+def test_tile_ordered_exchange_rule_is_a_pure_function_of_layout_capacity_and_world():
+    """Every rank must size its send slot alike, so the rule may only look at (elements, capacity, world, mode)."""
+    import grace_b200.ops.exchange as X
+
+    n = 256 << 20
+    k = n // 100
+    assert X.tile_decode_wanted(n, k, 8, X.SPARSE_TOPK)          # 8 lists of 1 %: dense tiles win
+    assert not X.tile_decode_wanted(n, k, 1, X.SPARSE_TOPK)      # one list: scattered adds win
+    assert not X.tile_decode_wanted(n, n // 1000, 8, X.SPARSE_TOPK)
+    assert not X.tile_decode_wanted(1 << 20, 1 << 14, 8, X.SPARSE_TOPK)   # fits the L2 cache
+    assert not X.tile_decode_wanted(n, k, 8, X.SPARSE_RANDOMK)   # random-k sends no indices at all
+
+
+def test_nvls_option_falls_back_cleanly_without_multicast():
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.nvls import NvlsAllreduce
+
+    grc = grace_from_params({"compressor": "none", "memory": "none", "communicator": "allreduce", "world_size": 1,
+                             "fused": True, "nvls": True})
+    assert isinstance(grc, NvlsAllreduce)
+    x = torch.arange(8.0)
+    assert torch.equal(grc.step(x.clone(), "w"), x)
+    assert grc.buffer(1024) is None and grc.stats()["nvls_launches"] == 0
+    h, ctx = grc.send_step(x.clone(), "w")
+    assert torch.equal(grc.receive_step(h, ctx), x)
+    # the option is ignored for compressors that are not the identity
+    other = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                               "world_size": 1, "compress_ratio": 0.5, "fused": True, "nvls": True})
+    assert not isinstance(other, NvlsAllreduce)

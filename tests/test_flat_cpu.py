@@ -82,3 +82,25 @@ def test_fused_sgd_flat_state_dict_roundtrip():
     o2.load_state_dict(sd)
     for off, p in zip(f2.layout.offsets, f2.params):
         assert torch.equal(o2._flat_buf[off:off + p.numel()], o1._flat_buf[off:off + p.numel()])
+
+
+def test_flat_params_adopt_an_external_gradient_buffer():
+    """``grad_buffer`` (a tensor or a ``numel -> tensor`` callable, e.g. a symmetric multicast buffer) becomes
+    the storage of every ``.grad``; a buffer that is too small or of the wrong dtype is refused."""
+    import pytest
+    from grace_b200.parallel.flat import FlatParams
+
+    model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 3))
+    big = torch.full((4096,), 7.0)
+    fp = FlatParams(model.named_parameters(), grad_buffer=lambda n: big)
+    assert fp.flat_g.data_ptr() == big.data_ptr() and fp.flat_g.numel() == fp.layout.total
+    assert float(fp.flat_g.abs().sum()) == 0.0            # adopted storage starts from zero
+    model(torch.randn(2, 6)).sum().backward()
+    assert fp.check_views() and float(big[: fp.layout.total].abs().sum()) > 0
+    with pytest.raises(ValueError):
+        FlatParams(torch.nn.Linear(6, 5).named_parameters(), grad_buffer=torch.zeros(8))
+    with pytest.raises(ValueError):
+        FlatParams(torch.nn.Linear(6, 5).named_parameters(), grad_buffer=torch.zeros(4096, dtype=torch.float64))
+    # a callable may decline (no multicast on this machine): the ordinary buffer is used
+    fp2 = FlatParams(torch.nn.Linear(6, 5).named_parameters(), grad_buffer=lambda n: None)
+    assert fp2.flat_g.numel() == fp2.layout.total

@@ -38,7 +38,7 @@ def _body(rank, world, dev):
 
     res = {}
     grc = grace_from_params({"compressor": "none", "memory": "none", "communicator": "allreduce", "world_size": world,
-                             "fused": True, "nvls": True, "timeout_ms": 5000})
+                             "fused": True, "nvls": True, "nvls_min_world": 2, "timeout_ms": 5000})
     n = 1_000_000
     buf = grc.buffer(n)          # collective; returns None on every rank alike when there is no multicast
     if buf is None:
