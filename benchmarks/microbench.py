@@ -94,6 +94,9 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "library", "reference"])
+    ap.add_argument("--virtual-ranks", type=int, default=0,
+                    help="one GPU only: run W ranks of the fused exchange on this GPU, phase by phase (all ranks "
+                         "compress and publish, then all ranks exchange); reports the time of all W ranks divided by W")
     args = ap.parse_args()
 
     import torch
@@ -166,13 +169,24 @@ def main():
             else:
                 shape = (n,)
             try:
-                grc = build(case)
+                if args.virtual_ranks > 1:
+                    if world != 1 or args.impl != "ours" or case.startswith("dense_nvls"):
+                        raise RuntimeError("--virtual-ranks needs one process, --impl ours and a peer-load case")
+                    import grace_b200
+                    from grace_b200.communicator.fused import VirtualWorld
+
+                    vp = dict(CASES[case], world_size=args.virtual_ranks, fused=True)
+                    grc = VirtualWorld(args.virtual_ranks, lambda r: grace_b200.grace_from_params(dict(vp)), dev)
+                else:
+                    grc = build(case)
             except Exception as e:
                 if rank == 0:
                     print(json.dumps({"case": case, "impl": args.impl, "unavailable": str(e)[:120]}))
                 break
             gen = torch.Generator(device=dev).manual_seed(rank)
             base = torch.randn(shape, generator=gen, device=dev) * 1e-3
+            vranks = args.virtual_ranks if args.virtual_ranks > 1 else 0
+            vbase = [base.roll(1001 * r) for r in range(vranks)]   # a different gradient per virtual rank
             times = []
             resident = None
             if case.endswith("_inplace") and args.impl == "ours" and hasattr(grc, "buffer"):
@@ -180,12 +194,16 @@ def main():
             try:
                 for it in range(args.warmup + args.iters):
                     g = base.clone() if resident is None else resident.copy_(base)
+                    vg = [b.clone() for b in vbase]
                     flush.fill_(float(it))
                     dist.barrier()
                     torch.cuda.synchronize()
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                    out = grc.step(g, "w") if resident is None else grc.step_flat(g)
+                    if vranks:
+                        out = grc.step(vg, "w")
+                    else:
+                        out = grc.step(g, "w") if resident is None else grc.step_flat(g)
                     e1.record()
                     torch.cuda.synchronize()
                     if it >= args.warmup:
@@ -199,16 +217,19 @@ def main():
                 continue
             t = torch.tensor([sorted(times)[len(times) // 2]], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t)
-            roof, hbm, link = roofline_ms(case, n, world, bw)
+            ms = float(t) / (vranks or 1)
+            roof, hbm, link = roofline_ms(case, n, vranks or world, bw)
             row = {"case": case, "impl": args.impl, "size_m": size_m, "n_gpus": world, "ms": round(ms, 4),
                    "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / ms, 3) if args.impl == "ours" else None,
                    "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
                    "timing": "cuda events, median of %d, max over ranks, L2 flushed" % args.iters}
+            if vranks:
+                row["virtual_ranks"] = vranks
+                row["timing"] += "; %d ranks emulated on one GPU phase by phase, time of all ranks / %d" % (vranks, vranks)
             rows.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
-            del grc, base, out, g
+            del grc, base, out, g, vbase, vg
             torch.cuda.empty_cache()
     dist.destroy_process_group()
 
