@@ -79,6 +79,38 @@ def _body(rank, world, dev):
     got = grc.step(small, "s")
     res["small"] = bool(torch.allclose(got, torch.full_like(got, (world - 1) / 2.0)))
     res["launches"] = grc.stats()["nvls_launches"]
+    # 5. optimizer integration: gradients live in the symmetric buffer and are averaged in place
+    from grace_b200.optim import FusedSGD
+    from grace_b200.parallel import DistributedOptimizer
+    from grace_b200.parallel.flat import FlatParams
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 512), torch.nn.ReLU(), torch.nn.Linear(512, 256)).to(dev)
+    twin = torch.nn.Sequential(torch.nn.Linear(64, 512), torch.nn.ReLU(), torch.nn.Linear(512, 256)).to(dev)
+    twin.load_state_dict(model.state_dict())
+    grc.min_numel = 0
+    flat = FlatParams(model.named_parameters(), grad_buffer=grc.buffer)
+    res["grads_in_symmetric_buffer"] = grc._buf.contains(flat.flat_g)
+    opt = DistributedOptimizer(FusedSGD(model.parameters(), lr=0.1, momentum=0.9, flat=flat), grace=grc,
+                               named_parameters=model.named_parameters(), flat=flat)
+    ref_opt = torch.optim.SGD(twin.parameters(), lr=0.1, momentum=0.9)
+    before = grc.stats()["nvls_launches"]
+    for step in range(2):
+        g = torch.Generator().manual_seed(900 + 10 * step + rank)
+        x = torch.randn(32, 64, generator=g).to(dev)
+        opt.zero_grad()
+        model(x).square().mean().backward()
+        _guard(res, "optimizer", opt.step, None)
+        ref_opt.zero_grad()
+        twin(x).square().mean().backward()
+        for p in twin.parameters():
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        ref_opt.step()
+    _guard(res, "check", grc.check, None)
+    res["optimizer_launches"] = grc.stats()["nvls_launches"] - before
+    res["optimizer_err"] = max(((a - b).abs().max() / b.abs().max()).item()
+                               for a, b in zip(model.parameters(), twin.parameters()))
     return res
 
 
@@ -121,3 +153,4 @@ def test_multicast_allreduce_matches_library_allreduce():
         assert all(r["same_%d" % s] for s in range(4)), "ranks disagree"
         assert r["inplace_same_storage"] and r["exact"] and r["small"], r
         assert r["launches"] == 6, r
+        assert r["grads_in_symmetric_buffer"] and r["optimizer_launches"] == 2 and r["optimizer_err"] < 1e-5, r
