@@ -12,8 +12,10 @@ sparse values+indices all-gather.  Weak scaling: per-GPU batch is fixed.
 For N > 1 launch through ``python -m torch.distributed.run --nproc-per-node N``.
 Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over
 ranks) with inputs resident on the GPU; ``e2e`` repeats the measurement through
-the public API with a pinned-host -> device copy of every batch and a
-device -> host read of the loss every step.
+the public API with a pinned-host -> device copy of every batch (prefetched on
+a copy stream) and a device -> host copy of every step's loss into pinned
+memory, read on the host one step later so that the host keeps queueing work
+(the last one is read before the closing event); both arms use the same loop.
 """
 from __future__ import annotations
 
@@ -393,6 +395,12 @@ def main():
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         nxt = fetch(0)
+        # every step's loss is copied to pinned host memory and read there; the read of step i happens after
+        # step i + 1 has been queued, so the host never drains the GPU between steps (the last one is read
+        # before the closing event)
+        loss_pin = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        loss_host = float("nan")
         for i in range(args.steps):
             dev, ev = nxt
             torch.cuda.current_stream().wait_event(ev)
@@ -401,7 +409,13 @@ def main():
             loss = step(dev, amp)
             for t in dev:
                 t.record_stream(torch.cuda.current_stream())
-            loss_host = float(loss)  # device -> host read of the step's result
+            loss_pin[i & 1].copy_(loss.detach().float(), non_blocking=True)   # device -> host copy of the step's result
+            loss_ev[i & 1].record()
+            if i > 0:
+                loss_ev[(i - 1) & 1].synchronize()
+                loss_host = float(loss_pin[(i - 1) & 1])
+        loss_ev[(args.steps - 1) & 1].synchronize()
+        loss_host = float(loss_pin[(args.steps - 1) & 1])
         f1.record()
         barrier_sync()
         ms2 = torch.tensor([f0.elapsed_time(f1)], device=device)

@@ -41,7 +41,8 @@ class NvlsAllreduce(Communicator):
         # (measured at 2 ranks, 256 Mi floats: 2.79 ms in place against 2.14 ms; NCCL 2.26 ms)
         self.min_world = min_world
         self.inplace = True
-        self._buf = None
+        self._buf = None                 # staging buffer for tensors that live elsewhere (grown on demand)
+        self._resident = []              # buffers handed out by buffer(): their tensors are reduced in place
         self._unavailable = False
         self._channel = None
         self.launches = 0
@@ -54,39 +55,62 @@ class NvlsAllreduce(Communicator):
         return (tensor.is_cuda and not self._unavailable and self.world_size >= max(2, self.min_world)
                 and isinstance(self.compressor, NoneCompressor) and isinstance(self.memory, NoneMemory))
 
-    def _ensure(self, numel: int, device) -> bool:
-        """Make sure a multicast buffer of at least ``numel`` floats exists (collective on first use / growth)."""
+    def _setup(self, device) -> bool:
+        """Flags and status words on the symmetric heap (collective on first use)."""
         from ..ops.exchange import ExchangeChannel
-        from ..parallel.nvls import NvlsBuffer
         from ..parallel.symm import SymmetricHeap
 
         if self._unavailable:
             return False
         if self.device is None:
             self.device = device
-        if self._buf is None or self._buf.numel < numel:
-            cap = 1 << max(16, (int(numel) - 1).bit_length())
-            buf = NvlsBuffer.create(cap, self.group, self.device)
-            if buf is None:
-                self._unavailable = True
-                return False
-            self._buf = buf
         if self._channel is None:
             heap = SymmetricHeap.create(1 << 16, group=self.group, device=self.device)
             self._channel = ExchangeChannel(heap, 256, 1, self.timeout_ms, self.comm_sms)
         return True
 
-    def buffer(self, numel: int, device=None) -> Optional[torch.Tensor]:
-        """A view of ``numel`` floats inside the symmetric buffer (None when multicast is unavailable).
+    def _new_buffer(self, numel: int):
+        from ..parallel.nvls import NvlsBuffer
 
-        Gradients kept there are reduced in place.  Collective: every rank must call it with the same size.
-        """
+        buf = NvlsBuffer.create(max(int(numel), 1 << 16), self.group, self.device)
+        if buf is None:
+            self._unavailable = True
+        return buf
+
+    def _find(self, t: torch.Tensor):
+        for b in self._resident:
+            if b.contains(t):
+                return b
+        return None
+
+    def _ensure(self, t: torch.Tensor) -> bool:
+        """Make sure ``t`` can be reduced: it lives in a buffer handed out by ``buffer()``, or a staging buffer of
+        at least its size exists (collective on first use / growth; every rank sees the same sizes)."""
+        if not self._setup(t.device):
+            return False
+        if self._find(t) is not None:
+            return True
+        if self._buf is None or self._buf.numel < t.numel():
+            buf = self._new_buffer(1 << max(16, (t.numel() - 1).bit_length()))
+            if buf is None:
+                return False
+            self._buf = buf
+        return True
+
+    def buffer(self, numel: int, device=None) -> Optional[torch.Tensor]:
+        """A tensor of ``numel`` floats in symmetric memory with a multicast mapping of its own (None when
+        multicast is unavailable).  Gradients kept there are reduced in place.  Collective: every rank must
+        call it with the same size, in the same order."""
         if self.world_size < max(2, self.min_world) or not torch.cuda.is_available():
             return None
         device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        if not self._ensure(numel, device):
+        if not self._setup(device):
             return None
-        return self._buf.tensor[:numel]
+        buf = self._new_buffer(numel)
+        if buf is None:
+            return None
+        self._resident.append(buf)
+        return buf.tensor[:numel]
 
     # ------------------------------------------------------------------
     def _allreduce(self, flat: torch.Tensor, out: torch.Tensor):
@@ -94,13 +118,14 @@ class NvlsAllreduce(Communicator):
         from ..ops.exchange import _stream_ptr
 
         C = native()
-        ch, buf = self._channel, self._buf
+        ch = self._channel
         n = flat.numel()
         assert n % 4 == 0 and flat.dtype == torch.float32 and out.dtype == torch.float32
-        if buf.contains(flat):
-            symm_ptr, mc_ptr = flat.data_ptr(), buf.multicast_of(flat)
+        home = self._find(flat)
+        if home is not None:
+            symm_ptr, mc_ptr = flat.data_ptr(), home.multicast_of(flat)
         else:
-            symm_ptr, mc_ptr = buf.base_ptr, buf.multicast_ptr
+            symm_ptr, mc_ptr = self._buf.base_ptr, self._buf.multicast_ptr
         out_ptr = out.data_ptr()
         if out_ptr == flat.data_ptr() and symm_ptr == flat.data_ptr():
             out_ptr = symm_ptr                       # fully in place
@@ -118,7 +143,7 @@ class NvlsAllreduce(Communicator):
     def step_flat(self, flat: torch.Tensor, layout=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Average a flat fp32 buffer over the ranks (``layout`` is accepted for interface parity and ignored)."""
         if (not self._eligible(flat) or flat.dtype != torch.float32 or flat.numel() % 4 or flat.data_ptr() % 16
-                or not flat.is_contiguous() or not self._ensure(flat.numel(), flat.device)):
+                or not flat.is_contiguous() or not self._ensure(flat)):
             return self.fallback.step_flat(flat, layout, out) if hasattr(self.fallback, "step_flat") and layout is not None \
                 else self._library(flat, out)
         out = flat if out is None else out
@@ -136,7 +161,7 @@ class NvlsAllreduce(Communicator):
     def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:
         n = tensor.numel()
         if (not self._eligible(tensor) or n < self.min_numel or tensor.dtype != torch.float32 or n % 4
-                or not tensor.is_contiguous() or tensor.data_ptr() % 16 or not self._ensure(n, tensor.device)):
+                or not tensor.is_contiguous() or tensor.data_ptr() % 16 or not self._ensure(tensor)):
             return self.fallback.step(tensor, name)
         flat = tensor.detach().reshape(-1)
         out = flat if self.inplace else torch.empty_like(flat)
@@ -172,5 +197,5 @@ class NvlsAllreduce(Communicator):
     def stats(self):
         s = dict(self.fallback.stats()) if hasattr(self.fallback, "stats") else {}
         s["nvls_launches"] = self.launches
-        s["nvls"] = self._buf is not None
+        s["nvls"] = self._buf is not None or bool(self._resident)
         return s

@@ -90,7 +90,7 @@ def _body(rank, world, dev):
     twin.load_state_dict(model.state_dict())
     grc.min_numel = 0
     flat = FlatParams(model.named_parameters(), grad_buffer=grc.buffer)
-    res["grads_in_symmetric_buffer"] = grc._buf.contains(flat.flat_g)
+    res["grads_in_symmetric_buffer"] = grc._find(flat.flat_g) is not None
     opt = DistributedOptimizer(FusedSGD(model.parameters(), lr=0.1, momentum=0.9, flat=flat), grace=grc,
                                named_parameters=model.named_parameters(), flat=flat)
     ref_opt = torch.optim.SGD(twin.parameters(), lr=0.1, momentum=0.9)
