@@ -156,7 +156,7 @@ def build_ours_loop(cfg, device, world):
     params = dict(cfg["grace"])
     params.update(world_size=world, fused=True)
     grc = grace_b200.grace_from_params(params)
-    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
     named = list(model.named_parameters())
 
     def step(batch, amp):
@@ -194,11 +194,11 @@ def build_ours(cfg, device, world):
     fused_flat = getattr(grc, "_kind", None) in ("sparse", "quant", "powersgd")
     if fused_flat:
         flat = FlatParams(named, bucket_bytes=cfg.get("bucket_bytes"))
-        opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, flat=flat)
+        opt = FusedSGD(model.parameters(), lr=0.01, momentum=0.9, flat=flat)
         opt = DistributedOptimizer(opt, grace=grc, named_parameters=named, flat=flat, always_hook=True)
         launches = len(flat.buckets) + 1
     else:
-        opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9)
+        opt = FusedSGD(model.parameters(), lr=0.01, momentum=0.9)
         opt = DistributedOptimizer(opt, grace=grc, named_parameters=named, always_hook=True)
         launches = 1 + len(named)
 
@@ -265,7 +265,7 @@ def build_reference(cfg, device, world):
         model = getattr(torchvision.models, cfg["model"])(weights=None).to(device)
         if g["compressor"] != "powersgd":  # the reference's PowerSGD calls .view() on the gradient: needs NCHW weights
             model = model.to(memory_format=torch.channels_last)
-    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
 
     def step(batch, amp):
         opt.zero_grad()
