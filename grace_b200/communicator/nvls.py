@@ -142,10 +142,12 @@ class NvlsAllreduce(Communicator):
 
     def step_flat(self, flat: torch.Tensor, layout=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Average a flat fp32 buffer over the ranks (``layout`` is accepted for interface parity and ignored)."""
-        if (not self._eligible(flat) or flat.dtype != torch.float32 or flat.numel() % 4 or flat.data_ptr() % 16
-                or not flat.is_contiguous() or not self._ensure(flat)):
-            return self.fallback.step_flat(flat, layout, out) if hasattr(self.fallback, "step_flat") and layout is not None \
-                else self._library(flat, out)
+        usable = (self._eligible(flat) and flat.dtype == torch.float32 and flat.numel() % 4 == 0
+                  and flat.data_ptr() % 16 == 0 and flat.is_contiguous() and self._ensure(flat))
+        if not usable:
+            if layout is not None and hasattr(self.fallback, "step_flat"):
+                return self.fallback.step_flat(flat, layout, out)
+            return self._library(flat, out)
         out = flat if out is None else out
         self._allreduce(flat, out)
         return out
@@ -193,6 +195,20 @@ class NvlsAllreduce(Communicator):
             self._channel.check()
         if hasattr(self.fallback, "check"):
             self.fallback.check()
+
+    def reset(self):
+        """After a ``GraceCommError``: clear flags and sequence numbers (call on every rank, then barrier on the host)."""
+        if self._channel is not None:
+            self._channel.reset()
+        if hasattr(self.fallback, "reset"):
+            self.fallback.reset()
+
+    def state_dict(self):
+        return self.fallback.state_dict() if hasattr(self.fallback, "state_dict") else super().state_dict()
+
+    def load_state_dict(self, state):
+        if hasattr(self.fallback, "load_state_dict"):
+            self.fallback.load_state_dict(state)
 
     def stats(self):
         s = dict(self.fallback.stats()) if hasattr(self.fallback, "stats") else {}
