@@ -40,6 +40,13 @@ CASES = {
     "qsgd8": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127),
     "qsgd8_a2a": dict(compressor="qsgd", memory="residual", communicator="alltoall", quantum_num=127),
     "efsign": dict(compressor="efsignsgd", memory="efsignsgd", communicator="allgather", lr=0.1),
+    # *_push: same codec, encoded slots replicated to every GPU with multimem.st, decode from local memory
+    "qsgd8_push": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127, nvls=True,
+                       nvls_min_world=2),
+    "efsign_push": dict(compressor="efsignsgd", memory="efsignsgd", communicator="allgather", lr=0.1, nvls=True,
+                        nvls_min_world=2),
+    "natural_push": dict(compressor="natural", memory="residual", communicator="allgather", nvls=True,
+                         nvls_min_world=2),
     "natural": dict(compressor="natural", memory="residual", communicator="allgather"),
     # uncompressed mean: "dense" = one-shot peer loads + two-phase option, "dense_nvls" = NVSwitch multicast kernel
     "dense": dict(compressor="none", memory="none", communicator="alltoall"),
@@ -66,7 +73,7 @@ def roofline_ms(case, n, world, bw):
         per_elem = 20 if case == "topk1" else 28          # g,r read; r,out write; one re-read (+u read/write for DGC)
         hbm = per_elem * n
         link = (world - 1) * ratio * n * 8
-    elif case in ("qsgd8", "natural"):
+    elif case in ("qsgd8", "natural", "qsgd8_push", "natural_push"):
         hbm = (12 + 1 + world + 4) * n                       # g,r read, r write, code write, W code reads, out write
         link = (world - 1) * n * (1 + 4.0 / 128)
     elif case == "qsgd8_a2a":
@@ -77,7 +84,7 @@ def roofline_ms(case, n, world, bw):
         # two-phase peer loads: reduce-scatter + all-gather; multicast: all W copies of every slice leave through
         # the switch once (the requester's own copy included) plus the broadcast of this rank's slice
         link = (2.0 * (world - 1) / world if case == "dense" else 1.0 + 1.0 / world) * n * 4
-    elif case == "efsign":
+    elif case in ("efsign", "efsign_push"):
         hbm = (12 + 8 + 4) * n + (1 + world) * n / 8
         link = (world - 1) * n / 8
     else:  # powersgd on sqrt(n) x sqrt(n)
@@ -148,7 +155,7 @@ def main():
 
             comp = PowerSGDCompressor(rank=4, use_memory=True, world_size=world)
             return Allreduce(comp, PowerSGDMemory(comp.q_memory, 4), world)
-        if case == "natural":
+        if case.startswith("natural"):
             raise RuntimeError("reference natural compression needs cupy (not installed)")
         from grace_dl.dist.helper import grace_from_params
 

@@ -95,6 +95,15 @@ class _Plan:
             self.alltoall = owner.mode == "alltoall" and self.codec in (X.CODEC["qsgd"], X.CODEC["natural"],
                                                                         X.CODEC["fp16"], X.CODEC["fp32"])
             slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg, owner.world_size if self.alltoall else 0)
+            self.recv = None
+            if (owner.nvls and not self.alltoall and owner._virtual is None
+                    and owner.world_size >= max(2, owner.nvls_min_world)):
+                from ..parallel.nvls import NvlsBuffer
+
+                stride = (slot_bytes + 255) // 256 * 256
+                buf = NvlsBuffer.create(2 * owner.world_size * stride // 4, owner.group, device)   # collective
+                if buf is not None:
+                    self.recv = (buf, stride)
         heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 8192
         self.heap = owner._make_heap(layout.key(), heap_bytes)
         self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
@@ -110,9 +119,14 @@ class _Plan:
 
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
-                 group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None):
+                 group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None, nvls=False,
+                 nvls_min_world=4):
         super().__init__(compressor, memory, world_size)
         self.mode = mode
+        # push transport for the quantised codecs in all-gather mode: encoded slots are replicated into every
+        # GPU's receive area with multimem.st and decoded from local memory (opt-in; needs NVSwitch multicast)
+        self.nvls = bool(nvls)
+        self.nvls_min_world = int(nvls_min_world)
         self.seed = int(seed)
         self.timeout_ms = float(timeout_ms)
         self.comm_sms = comm_sms
@@ -246,6 +260,7 @@ class FusedExchange(Communicator):
                 first_step=plan.steps == 0, beta=beta, gamma=gamma, mom_beta=float(getattr(comp, "momentum", 0.0)),
                 lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
                 phases=phases | (X.PHASE_REDUCE if (plan.alltoall and phases == X.PHASE_ALL) else 0), seq=seq,
+                recv=plan.recv,
                 alltoall=plan.alltoall)
         return seq
 

@@ -109,8 +109,12 @@ PYBIND11_MODULE(_C, m) {
            float scale, unsigned long long seed, unsigned step, uintptr_t stats, uintptr_t barrier, uintptr_t status,
            int phases, int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
-           unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off) {
+           unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off,
+           uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride) {
           QuantArgs a{};
+          a.recv_local = ptr<char>(recv_local); a.recv_mc = ptr<char>(recv_mc); a.recv_stride = recv_stride;
+          if ((recv_local != 0) != (recv_mc != 0) || (recv_mc && (alltoall || recv_stride % 16 || recv_local % 16 || recv_mc % 16)))
+            throw std::invalid_argument("quant_exchange: bad push-transport arguments");
           a.alltoall = alltoall; a.ready2_off = ready2_off;
           a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
           a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.codec = codec; a.quantum = quantum;

@@ -119,6 +119,10 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   const int rank = a.peers.rank, world = a.peers.world;
   char* const my_heap = a.peers.heap[rank];
   char* const my_slot = my_heap + a.peers.slot_off;
+  // where rank p's payload is read from: its own slot over NVLink (pull), or the local receive area (push)
+  auto slot_of = [&](int p) -> const char* {
+    return a.recv_local ? a.recv_local + (size_t)p * a.recv_stride : a.peers.heap[p] + a.peers.slot_off;
+  };
   const size_t off_codes = kHeaderBytes + scalars_bytes(a.nseg);
   const size_t off_norms = off_codes + codes_bytes(T::bits, a.total);
 
@@ -362,6 +366,32 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
     }
   }
 
+  if ((a.phases & kPhasePublish) && a.recv_mc) {
+    // ---- push: replicate this rank's encoded slot into region `rank` of every GPU's receive area ----
+    // (the slot was completed by all CTAs before the grid barrier that ends the compress phase)
+    const size_t n16 = (region1_bytes(C, T::bits, a.total, a.nseg) + 15) / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(my_slot);
+    char* dst = a.recv_mc + (size_t)rank * a.recv_stride;
+    const size_t gtid = (size_t)blockIdx.x * kBlock + tid, gstride = (size_t)gridDim.x * kBlock;
+    constexpr int kAhead = 4;
+    if (!status.failed()) {
+      for (size_t i0 = gtid; i0 < n16; i0 += gstride * kAhead) {
+        uint4 v[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) if (i0 + u * gstride < n16) v[u] = ld_cg_u4(src + i0 + u * gstride);
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u)
+          if (i0 + u * gstride < n16)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + (i0 + u * gstride) * 16),
+                         "f"(__uint_as_float(v[u].x)), "f"(__uint_as_float(v[u].y)), "f"(__uint_as_float(v[u].z)),
+                         "f"(__uint_as_float(v[u].w))
+                         : "memory");
+      }
+    }
+    __threadfence_system();   // the multicast stores precede the flag raised after the barrier
+    bar.sync();
+  }
+
   if (a.phases & kPhasePublish) {
     if (blockIdx.x == 0) {
       __syncthreads();
@@ -592,7 +622,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
         if (T::stats) {
           __syncthreads();
           if (tid < world) {
-            const uint4 v = ld_cg_u4(a.peers.heap[tid] + a.peers.slot_off + kHeaderBytes + (size_t)s * 16);
+            const uint4 v = ld_cg_u4(slot_of(tid) + kHeaderBytes + (size_t)s * 16);
             s_peer[tid] = SegScalars{__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
           }
           __syncthreads();
@@ -624,7 +654,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                   for (int k = 0; k < kWordsPerGroup; ++k) w[pp][k] = 0u;
                   // lanes 8*round .. 8*round+7 own the groups of this round
                   if (p0 + pp < world && have && (lane >> 3) == round) {
-                    const char* src_blk = a.peers.heap[p0 + pp] + a.peers.slot_off + off_codes +
+                    const char* src_blk = slot_of(p0 + pp) + off_codes +
                                           (size_t)my_group * (kWordsPerGroup * 4);
                     const uint4 v0 = ld_cg_u4(src_blk);
                     w[pp][0] = v0.x; w[pp][1] = v0.y; w[pp][2] = v0.z; w[pp][3] = v0.w;
@@ -688,7 +718,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc16[q][j] = 0.f;
             for (int p = 0; p < world; ++p) {
-              const char* slot = a.peers.heap[p] + a.peers.slot_off;
+              const char* slot = slot_of(p);
               uint4 cw[kX];
               float dq[kX];
 #pragma unroll
@@ -743,7 +773,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
 #pragma unroll
             for (int j = 0; j < 4; ++j) { sum[q][j] = 0.f; votes[q][j] = 0; }
           for (int p = 0; p < world; ++p) {
-            const char* slot = a.peers.heap[p] + a.peers.slot_off;
+            const char* slot = slot_of(p);
             unsigned w0[kU], w1[kU];
             float dq[kU];
 #pragma unroll

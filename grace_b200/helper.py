@@ -14,9 +14,11 @@ codecs of ``grace_dl/tensorflow/helper.py`` (``adaq``, ``inceptionn``,
 ``seed``, ``timeout_ms``, ``comm_sms``
     forwarded to the fused exchange.
 ``nvls`` (bool, default False; needs ``fused``)
-    with the ``none`` compressor and no memory, average through the NVSwitch
-    multicast mapping (``communicator/nvls.py``) where it is available and the
-    job has at least ``nvls_min_world`` (default 4) ranks; the fused peer-load
+    use the NVSwitch multicast mapping where it is available and the job has
+    at least ``nvls_min_world`` (default 4) ranks: the ``none`` compressor with
+    no memory averages with ``multimem.ld_reduce`` (``communicator/nvls.py``);
+    the quantised codecs in all-gather mode push their encoded slots to every
+    GPU with ``multimem.st`` and decode from local memory.  The peer-load
     exchange stays the fallback.
 
 Unknown names raise ``NotImplementedError`` as in the reference.
@@ -104,6 +106,7 @@ def grace_from_params(params: Dict[str, Any]):
             comp, mem, _world(params), mode=mode,
             seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
             comm_sms=params.get("comm_sms"), group=params.get("group"),
+            nvls=params.get("nvls", False), nvls_min_world=params.get("nvls_min_world", 4),
         )
         if params.get("nvls", False) and comp_name == "none" and mem_name == "none":
             from .communicator.nvls import NvlsAllreduce

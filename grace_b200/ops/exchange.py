@@ -314,7 +314,9 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
               quantum: int = 0, deterministic: bool = False, first_step: bool = False, beta: float = 1.0,
               gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
               step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None,
-              alltoall: bool = False) -> int:
+              alltoall: bool = False, recv=None) -> int:
+    """``recv``: ``(NvlsBuffer, stride)`` of the push transport (two parities of ``world`` regions of ``stride``
+    bytes each), or None for the pull transport."""
     C = native()
     heap = channel.heap
     if seq is None:
@@ -326,12 +328,17 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
     for t in (g, acc, mom, out):
         if t is not None:
             assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    recv_local = recv_mc = recv_stride = 0
+    if recv is not None and phases == PHASE_ALL:
+        buf, recv_stride = recv
+        parity_off = (seq & 1) * heap.world * recv_stride
+        recv_local, recv_mc = buf.base_ptr + parity_off, buf.multicast_ptr + parity_off
     C.quant_exchange(
         _ptr(g), _ptr(acc), _ptr(mom), _ptr(out), segs_dev.data_ptr(), len(layout.names), layout.total, codec, quantum,
         int(deterministic), int(first_step), beta, gamma, mom_beta, lr, scale, seed & (2 ** 64 - 1), step & 0xFFFFFFFF,
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
-        grid, _stream_ptr(), int(alltoall), channel.ready2_off,
+        grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride,
     )
     channel.post_status()
     return seq

@@ -114,14 +114,50 @@ def _body(rank, world, dev):
     return res
 
 
-def _entry(rank, world, port, ret):
+def _push_body(rank, world, dev):
+    """Quantised codecs, all-gather mode: the push transport (slots replicated with multimem.st, decode from
+    local memory) must give the bits of the pull transport (peers' slots read over NVLink)."""
+    from grace_b200 import grace_from_params
+
+    res = {}
+    cases = [
+        ("qsgd", "residual", {"quantum_num": 64}),
+        ("natural", "residual", {}),
+        ("terngrad", "none", {}),
+        ("efsignsgd", "efsignsgd", {"lr": 0.1}),
+        ("signsgd", "none", {}),
+        ("onebit", "residual", {}),
+        ("u8bit", "none", {}),
+        ("fp16", "none", {}),
+    ]
+    n = 400_003
+    for comp, mem, extra in cases:
+        base = {"compressor": comp, "memory": mem, "communicator": "allgather", "world_size": world, "fused": True,
+                "timeout_ms": 5000, "seed": 11, **extra}
+        pull = grace_from_params(dict(base))
+        push = grace_from_params(dict(base, nvls=True, nvls_min_world=2))      # collective: allocates the receive area
+        same, pushed = True, False
+        for step in range(3):
+            g = torch.Generator().manual_seed(97 * step + rank)
+            x = (torch.randn(n, generator=g) * 1e-3).to(dev)
+            a = _guard(res, comp + " pull", lambda: pull.step(x.clone(), "w"), torch.zeros_like(x))
+            b = _guard(res, comp + " push", lambda: push.step(x.clone(), "w"), torch.ones_like(x))
+            _guard(res, comp + " check", lambda: (pull.check(), push.check()), None)
+            same = same and torch.equal(a, b)
+        plans = list(push._plans.values())
+        pushed = bool(plans) and all(getattr(p, "recv", None) is not None for p in plans)
+        res[comp] = (same, pushed)
+    return res
+
+
+def _entry(rank, world, port, ret, body=None):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        ret[rank] = _body(rank, world, dev)
+        ret[rank] = (body or _body)(rank, world, dev)
     except Exception:  # noqa: BLE001 - reported by the parent; the rank still leaves through the barrier
         ret[rank] = {"error": traceback.format_exc()}
     torch.cuda.synchronize()
@@ -154,3 +190,28 @@ def test_multicast_allreduce_matches_library_allreduce():
         assert r["inplace_same_storage"] and r["exact"] and r["small"], r
         assert r["launches"] == 6, r
         assert r["grads_in_symmetric_buffer"] and r["optimizer_launches"] == 2 and r["optimizer_err"] < 1e-5, r
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_push_transport_gives_the_bits_of_the_pull_transport():
+    world = min(torch.cuda.device_count(), 8)
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _port()
+        procs = [ctx.Process(target=_entry, args=(r, world, port, ret, _push_body)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(600)
+        for p in procs:
+            assert p.exitcode == 0, "rank exited with %s" % p.exitcode
+        res = dict(ret)
+    for rank in range(world):
+        r = res[rank]
+        assert "error" not in r, r.get("error")
+        if not any(pushed for _, pushed in r.values()):
+            pytest.skip("no NVSwitch multicast on this machine")
+        for comp, (same, pushed) in r.items():
+            assert pushed, "%s: the push transport was not used" % comp
+            assert same, "%s: push and pull transports disagree" % comp
