@@ -132,6 +132,9 @@ __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseStat
   __syncthreads();
 }
 
+// kTile selects the tile-ordered exchange (sender orders its list by output tile, receivers build dense
+// tiles); it is a separate instantiation so that the scatter-add variant keeps its code and registers.
+template <bool kTile>
 __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const SparseArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   const float* __restrict__ src = a.acc ? a.acc : a.g;
   const bool topk = a.mode == kSparseTopK;
   const bool randomk = a.mode == kSparseRandomK;
-  const bool dense_decode = a.tile_start != nullptr && !randomk;  // tile-ordered lists and decode
+  const bool dense_decode = kTile && !randomk;  // tile-ordered lists and decode
 
   if (a.phases & kPhaseCompress) {
     // Before overwriting the slot of parity (seq & 1): every peer must have
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     if (blockIdx.x == 0 && tid == 0) { my_hdr[0] = 0; my_hdr[1] = 0; }
-    if (dense_decode) {   // tile counters of the ordering step; many grid barriers lie between here and their use
+    if (kTile && dense_decode) {   // tile counters of the ordering step; many grid barriers lie between here and their use
       const long long nb1 = ((a.total + kTileElems - 1) >> kTileShift) + 1;
       for (long long b = (long long)blockIdx.x * kBlock + tid; b < nb1; b += (long long)gridDim.x * kBlock) a.tile_start[b] = 0;
     }
@@ -504,7 +507,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       }
       ok = bar.sync();
     }
-    if (dense_decode) {
+    if constexpr (kTile) if (dense_decode) {
       // ---- order the list by output tile (counting sort of this rank's own picks, all in local memory) and
       //      publish a directory of tile offsets: the receivers then build whole tiles without any sorting ----
       const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
@@ -658,21 +661,18 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       }
       return;
     }
-    if (dense_decode && a.out) {
+    if constexpr (kTile) if (dense_decode && a.out) {
       // ---- tile-ordered decode: every peer's list arrives sorted by 8192-element output tile with a
       //      directory of tile offsets, so each CTA builds whole output tiles in shared memory (source
       //      ranks in order 0..W-1) and writes them once, densely; nothing is scattered to global memory ----
-      // The CTA works as two independent halves of 256 threads (named barriers 1 and 2): each half builds one
-      // tile at a time in its own 32 KiB of the staging area, so a half that waits for its peers' ranges or
-      // drains its stores does not hold up the other.
-      constexpr int kR = 4;                          // pairs per thread and chunk (1024 per half and chunk)
-      constexpr int kHalf = kBlock / 2;
-      static_assert(kHalf % 32 == 0 && 2 * kMaxWorld <= kHalf, "a half is made of whole warps and covers the directory fetch");
+      constexpr int kR = 8;                          // pairs per thread and chunk
+      constexpr int kGroup = 2;                      // tiles per unit: stage.val and stage.idx hold one each
+      constexpr int kUnitElems = kGroup * kTileElems;
       __shared__ unsigned s_n[kMaxWorld];
-      __shared__ unsigned s_b[2][3][kMaxWorld][2];      // per half, tile (ring of 3) and peer: first and one-past-last entry
-      __shared__ unsigned s_pref[2][3][kMaxWorld + 1];  // running sum of the peers' range lengths
-      __shared__ int s_go;
+      __shared__ unsigned s_b[3][kMaxWorld][2];      // per unit (ring of 3) and peer: first and one-past-last entry
+      __shared__ unsigned s_pref[3][kMaxWorld + 1];  // running sum of the peers' range lengths
       const long long tiles = (a.total + kTileElems - 1) >> kTileShift;
+      const long long units = (tiles + kGroup - 1) / kGroup;
       const size_t sorted_off = kSlotHeaderBytes + (size_t)a.cap * 8, dir_off = sorted_off + (size_t)a.cap * 8;
       if (tid < world) {
         unsigned n = 0;
@@ -682,53 +682,49 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         s_n[tid] = n < a.cap ? n : a.cap;
       }
       __syncthreads();
-      if (tid == 0) s_go = !status.failed();         // one decision for the whole CTA: the loops below hold barriers
+      __shared__ int s_go;
+      if (tid == 0) s_go = !status.failed();         // one decision for the whole CTA: the loop below holds barriers
       __syncthreads();
       if (s_go) {
-        const int half = tid / kHalf, lt = tid - half * kHalf;
-        auto half_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "n"(kHalf) : "memory"); };
-        float* tile = half ? reinterpret_cast<float*>(sm.stage.idx) : sm.stage.val;
-        unsigned (*hb)[kMaxWorld][2] = s_b[half];
-        unsigned (*hp)[kMaxWorld + 1] = s_pref[half];
-        const long long stride = 2ll * gridDim.x;
-        auto fetch_bound = [&](long long t) {        // thread 2p+k of the half: entry k (0: first, 1: end) of peer p
-          const int p = lt >> 1;
-          long long tt = t + (lt & 1);
-          if (tt > tiles) tt = tiles;
-          const unsigned d = ld_cg_u32(a.peers.heap[p] + a.peers.slot_off + dir_off + (size_t)tt * 4);
+        float* tile = sm.stage.val;                  // val[8192] and idx[8192] are adjacent: 16384 floats
+        auto fetch_bound = [&](long long u) {        // thread 2p+k: entry k (0: first, 1: end) of peer p
+          const int p = tid >> 1;
+          long long t = u * kGroup + (tid & 1) * kGroup;
+          if (t > tiles) t = tiles;
+          const unsigned d = ld_cg_u32(a.peers.heap[p] + a.peers.slot_off + dir_off + (size_t)t * 4);
           return d < s_n[p] ? d : s_n[p];            // a directory can never point past the list
         };
-        auto prefix_of = [&](int ring) {             // first warp of the half: running sum of range lengths
-          if (lt < 32) {
+        auto prefix_of = [&](int ring) {             // warp 0: running sum of range lengths
+          if (tid < 32) {
             unsigned len = 0;
-            if (lt < world) {
-              const unsigned d0 = hb[ring][lt][0], d1 = hb[ring][lt][1];
+            if (tid < world) {
+              const unsigned d0 = s_b[ring][tid][0], d1 = s_b[ring][tid][1];
               len = d1 > d0 ? d1 - d0 : 0u;
             }
             unsigned incl = len;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
               const unsigned nb = __shfl_up_sync(0xffffffffu, incl, o);
-              if (lt >= o) incl += nb;
+              if (tid >= o) incl += nb;
             }
-            if (lt < world) hp[ring][lt + 1] = incl;
-            if (lt == 0) hp[ring][0] = 0;
+            if (tid < world) s_pref[ring][tid + 1] = incl;
+            if (tid == 0) s_pref[ring][0] = 0;
           }
         };
-        // pairs j0 + r * kHalf + lt of a tile's concatenated ranges (rank-major), fetched from the peers
+        // pairs j0 + r * kBlock + tid of a unit's concatenated ranges (rank-major), fetched from the peers
         auto load_chunk = [&](uint2 (&pr)[kR], int (&src)[kR], int ring, unsigned j0) {
-          const unsigned total_len = hp[ring][world];
+          const unsigned total_len = s_pref[ring][world];
 #pragma unroll
           for (int r = 0; r < kR; ++r) {
-            const unsigned j = j0 + r * kHalf + lt;
+            const unsigned j = j0 + r * kBlock + tid;
             src[r] = -1;
             pr[r] = make_uint2(0u, 0u);
             if (j < total_len) {
               int p = 0;                             // last p with pref[p] <= j (world <= 16: four halving steps)
 #pragma unroll
               for (int step = 8; step > 0; step >>= 1)
-                if (p + step < world && hp[ring][p + step] <= j) p += step;
-              const size_t e = (size_t)hb[ring][p][0] + (j - hp[ring][p]);
+                if (p + step < world && s_pref[ring][p + step] <= j) p += step;
+              const size_t e = (size_t)s_b[ring][p][0] + (j - s_pref[ring][p]);
               const char* pv = a.peers.heap[p] + a.peers.slot_off + sorted_off;
               pr[r].x = ld_cg_u32(pv + e * 4);
               pr[r].y = ld_cg_u32(pv + ((size_t)a.cap + e) * 4);
@@ -736,56 +732,56 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             }
           }
         };
-        long long t = 2ll * blockIdx.x + half;
-        if (lt < 2 * world) {
-          if (t < tiles) hb[0][lt >> 1][lt & 1] = fetch_bound(t);
-          if (t + stride < tiles) hb[1][lt >> 1][lt & 1] = fetch_bound(t + stride);
+        long long u = blockIdx.x;
+        if (tid < 2 * world) {
+          if (u < units) s_b[0][tid >> 1][tid & 1] = fetch_bound(u);
+          if (u + gridDim.x < units) s_b[1][tid >> 1][tid & 1] = fetch_bound(u + gridDim.x);
         }
-        half_sync();
-        if (t < tiles) prefix_of(0);
-        if (t + stride < tiles) prefix_of(1);
-        half_sync();
+        __syncthreads();
+        if (u < units) prefix_of(0);
+        if (u + gridDim.x < units) prefix_of(1);
+        __syncthreads();
         uint2 pr[kR], prn[kR];
         int src[kR], srcn[kR];
-        if (t < tiles) load_chunk(pr, src, 0, 0u);
+        if (u < units) load_chunk(pr, src, 0, 0u);
         int cur = 0;
-        for (; t < tiles; t += stride) {
+        for (; u < units; u += gridDim.x) {
           const int nxt = cur == 2 ? 0 : cur + 1, nn = nxt == 2 ? 0 : nxt + 1;
-          const bool more = t + stride < tiles, more2 = t + 2 * stride < tiles;
-          // the directory entries two tiles ahead and the first chunk of the next tile travel while this one is built
+          const bool more = u + gridDim.x < units, more2 = u + 2 * (long long)gridDim.x < units;
+          // the directory entries two units ahead and the first chunk of the next unit travel while this one is built
           unsigned nb = 0;
-          if (more2 && lt < 2 * world) nb = fetch_bound(t + 2 * stride);
+          if (more2 && tid < 2 * world) nb = fetch_bound(u + 2 * (long long)gridDim.x);
           if (more) load_chunk(prn, srcn, nxt, 0u);
-          for (int i = lt * 4; i < kTileElems; i += kHalf * 4)
+          for (int i = tid * 4; i < kUnitElems; i += kBlock * 4)
             *reinterpret_cast<float4*>(tile + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-          half_sync();
-          const unsigned total_len = hp[cur][world];
-          for (unsigned j0 = 0; j0 < total_len; j0 += kHalf * kR) {
+          __syncthreads();
+          const unsigned total_len = s_pref[cur][world];
+          for (unsigned j0 = 0; j0 < total_len; j0 += kBlock * kR) {
             if (j0 != 0) load_chunk(pr, src, cur, j0);
-            // ranks present in this chunk (uniform over the half)
-            const unsigned jlast = min(j0 + kHalf * kR, total_len) - 1;
+            // ranks present in this chunk (uniform over the CTA)
+            const unsigned jlast = min(j0 + kBlock * kR, total_len) - 1;
             int p_first = 0, p_last = 0;
 #pragma unroll
             for (int step = 8; step > 0; step >>= 1) {
-              if (p_first + step < world && hp[cur][p_first + step] <= j0) p_first += step;
-              if (p_last + step < world && hp[cur][p_last + step] <= jlast) p_last += step;
+              if (p_first + step < world && s_pref[cur][p_first + step] <= j0) p_first += step;
+              if (p_last + step < world && s_pref[cur][p_last + step] <= jlast) p_last += step;
             }
             for (int p = p_first; p <= p_last; ++p) {
 #pragma unroll
               for (int r = 0; r < kR; ++r)
                 if (src[r] == p) {
-                  if ((long long)(pr[r].y >> kTileShift) != t) {   // not an index of this tile: corrupt list
+                  if ((long long)(pr[r].y >> (kTileShift + 1)) != u) {   // not an index of this unit: corrupt list
                     status.fail(kBadArgument, p, (unsigned)a.peers.seq);
                   } else {   // product rounded first, as in the scatter-add decode
-                    float* slot = tile + (pr[r].y & (kTileElems - 1));
+                    float* slot = tile + (pr[r].y & (kUnitElems - 1));
                     *slot = __fadd_rn(*slot, __fmul_rn(__uint_as_float(pr[r].x), a.scale));
                   }
                 }
-              half_sync();
+              __syncthreads();
             }
           }
-          const long long base = t << kTileShift;
-          for (int i = lt * 4; i < kTileElems; i += kHalf * 4) {
+          const long long base = u * kUnitElems;
+          for (int i = tid * 4; i < kUnitElems; i += kBlock * 4) {
             const long long gi = base + i;
             if (gi + 4 <= a.total) {
               *reinterpret_cast<float4*>(a.out + gi) = *reinterpret_cast<const float4*>(tile + i);
@@ -793,12 +789,12 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
               for (int j = 0; j < 4; ++j) if (gi + j < a.total) a.out[gi + j] = tile[i + j];
             }
           }
-          if (more2 && lt < 2 * world) hb[nn][lt >> 1][lt & 1] = nb;
+          if (more2 && tid < 2 * world) s_b[nn][tid >> 1][tid & 1] = nb;
 #pragma unroll
           for (int r = 0; r < kR; ++r) { pr[r] = prn[r]; src[r] = srcn[r]; }
-          half_sync();
+          __syncthreads();
           if (more2) prefix_of(nn);
-          half_sync();
+          __syncthreads();
           cur = nxt;
         }
       }
@@ -867,11 +863,14 @@ size_t sparse_smem_bytes() { return sizeof(Smem); }
 int sparse_max_grid(int device, int sm_limit) {
   static bool attr_set[64] = {};
   if (device >= 0 && device < 64 && !attr_set[device]) {
-    cudaFuncSetAttribute(sparse_exchange_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+    cudaFuncSetAttribute(sparse_exchange_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+    cudaFuncSetAttribute(sparse_exchange_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
     attr_set[device] = true;
   }
-  int per_sm = 0, sms = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sparse_exchange_kernel, kBlock, sizeof(Smem));
+  int per_sm = 0, per_sm_tile = 0, sms = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sparse_exchange_kernel<false>, kBlock, sizeof(Smem));
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_tile, sparse_exchange_kernel<true>, kBlock, sizeof(Smem));
+  if (per_sm_tile < per_sm) per_sm = per_sm_tile;   // one grid size serves both variants
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
   if (per_sm > 2) per_sm = 2;
@@ -887,8 +886,8 @@ cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t s
   }
   SparseArgs copy = a;
   void* params[] = {&copy};
-  return cudaLaunchCooperativeKernel((const void*)sparse_exchange_kernel, dim3(grid), dim3(kBlock), params,
-                                     sizeof(Smem), stream);
+  const void* fn = a.tile_start ? (const void*)sparse_exchange_kernel<true> : (const void*)sparse_exchange_kernel<false>;
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kBlock), params, sizeof(Smem), stream);
 }
 
 }  // namespace grace
