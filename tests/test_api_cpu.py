@@ -265,3 +265,20 @@ def test_nvls_option_falls_back_cleanly_without_multicast():
     other = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
                                "world_size": 1, "compress_ratio": 0.5, "fused": True, "nvls": True})
     assert not isinstance(other, NvlsAllreduce)
+
+
+def test_native_module_loads_without_a_gpu_and_sizes_its_slots():
+    """The extension links no driver library, so its host-side helpers work on a machine without a GPU."""
+    from grace_b200.ops import native
+
+    C = native()
+    cap, total = 4096, 1 << 20
+    plain = C.sparse_slot_bytes(cap)
+    tiled = C.sparse_slot_bytes(cap, total)
+    tiles = total // 8192
+    assert plain == 128 + 8 * cap
+    # tile-ordered layout: a second (value, index) list and a directory of tiles + 1 offsets, 16-byte granular
+    assert tiled == plain + 8 * cap + (tiles + 1 + 3) // 4 * 16
+    q8 = C.quant_slot_bytes(0, total, 1)          # codec 0 = QSGD: 1 byte per element + one norm per 128
+    assert q8 >= 128 + total + total // 128 * 4 and q8 % 256 == 0
+    assert C.MAX_WORLD == 16
