@@ -233,3 +233,36 @@ def test_horovod_style_helpers():
     for r in (0, 1):
         gathered, wsum, lr = res[r]
         assert gathered == [0.0, 0.0, 1.0] and wsum == 0.0 and abs(lr - 0.1) < 1e-12
+
+
+def _nvls_fallback(rank, world):
+    """``nvls=True`` on CPU ranks: no multicast, so every call lands in the library path and still averages."""
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.nvls import NvlsAllreduce
+
+    out = {}
+    grc = grace_from_params({"compressor": "none", "memory": "none", "communicator": "allreduce", "world_size": world,
+                             "fused": True, "nvls": True, "nvls_min_world": 2})
+    out["type"] = isinstance(grc, NvlsAllreduce)
+    x = torch.full((1024,), float(rank + 1))
+    got = grc.step(x.clone(), "w")
+    out["step"] = bool(torch.allclose(got, torch.full_like(got, (world + 1) / 2.0)))
+    flat = torch.full((256,), float(rank))
+    res = grc.step_flat(flat)                     # no layout: library all-reduce, in place
+    out["flat"] = bool(torch.allclose(res, torch.full_like(res, (world - 1) / 2.0))) and res.data_ptr() == flat.data_ptr()
+    out["buffer"] = grc.buffer(1024) is None
+    out["launches"] = grc.stats()["nvls_launches"]
+    # quantised codec with the push option: CPU tensors use the library communicator, the option is inert
+    q = grace_from_params({"compressor": "fp16", "memory": "none", "communicator": "allgather", "world_size": world,
+                           "fused": True, "nvls": True, "nvls_min_world": 2})
+    got = q.step(torch.full((64,), float(rank + 1)), "h")
+    out["fp16"] = bool(torch.allclose(got, torch.full_like(got, (world + 1) / 2.0)))
+    return out
+
+
+def test_nvls_options_fall_back_on_cpu_ranks():
+    res = _run(_nvls_fallback, world=2)
+    for rank in range(2):
+        r = res[rank]
+        assert r["type"] and r["step"] and r["flat"] and r["buffer"] and r["fp16"], r
+        assert r["launches"] == 0
