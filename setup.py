@@ -1,0 +1,47 @@
+"""Packaging for grace_b200 (and the ``grace_dl`` import-path package).
+
+The native extension is built IN TREE by ``grace_b200/ops/build.py`` (plain nvcc, ``-gencode
+arch=compute_100a,code=sm_100a``), on first use or explicitly with ``python -m grace_b200.ops.build``;
+``python setup.py build_ext`` / ``pip install -e .`` call the same builder, so there is one build path.
+The reference ships a ten-line ``setup.py`` plus three per-extension ``setup.py`` files without an architecture
+list (``setup.py:1-10``, ``grace_dl/dist/compressor/*_cuda/setup.py``).
+"""
+from setuptools import Command, find_packages, setup
+from setuptools.command.build_py import build_py
+
+
+class BuildNative(Command):
+    description = "compile the sm_100a extension in tree (grace_b200/_C*.so)"
+    user_options = []
+
+    def initialize_options(self):
+        pass
+
+    def finalize_options(self):
+        pass
+
+    def run(self):
+        from grace_b200.ops.build import ensure_built
+
+        print("built", ensure_built())
+
+
+class BuildPyWithNative(build_py):
+    def run(self):
+        try:
+            self.run_command("build_native")
+        except Exception as e:  # nvcc missing: the extension is then built on first use on the GPU machine
+            print("native build skipped:", e)
+        super().run()
+
+
+setup(
+    name="grace_b200",
+    version="1.0",
+    description="Blackwell-native gradient compression framework with the GRACE API",
+    packages=find_packages(include=["grace_b200", "grace_b200.*", "grace_dl", "grace_dl.*"]),
+    package_data={"grace_b200": ["csrc/*", "*.so"]},
+    python_requires=">=3.10",
+    install_requires=["torch", "numpy"],
+    cmdclass={"build_native": BuildNative, "build_ext": BuildNative, "build_py": BuildPyWithNative},
+)

@@ -26,6 +26,17 @@ def test_reference_import_paths():
     out = grc.step(torch.randn(4, 5), "w")
     assert out.shape == (4, 5)
     assert g2 is grace_from_params
+    # the TensorFlow tree's module names resolve to the PyTorch implementations (TensorFlow itself is not used)
+    from grace_dl.tensorflow.communicator.allgather import Allgather as TfAllgather
+    from grace_dl.tensorflow.compressor.inceptionn import INCEPTIONNCompressor  # noqa: F401
+    from grace_dl.tensorflow.compressor.packing import decode_byte, encode_byte  # noqa: F401
+    from grace_dl.tensorflow.compressor.u8bit import U8bitCompressor
+    from grace_dl.tensorflow.helper import grace_from_params as g4
+    from grace_dl.tensorflow.memory.residual import ResidualMemory as TfResidual
+
+    assert TfAllgather is Allgather and g4 is grace_from_params
+    out = TfAllgather(U8bitCompressor(), TfResidual(), 1).step(torch.randn(300), "u")
+    assert out.shape == (300,)
 
 
 COMPRESSORS = ["dgc", "efsignsgd", "fp16", "natural", "natural_cuda", "none", "onebit", "powersgd", "qsgd",
