@@ -279,6 +279,14 @@ class FusedExchange(Communicator):
                                    "that could only time out" % dead)
         plan = self._plan(layout)
         out = flat if out is None else out
+        from ..utils import timeline
+
+        tl = timeline.active()
+        tok = None
+        if tl is not None:
+            tok = tl.begin(layout.names[0] if len(layout.names) == 1 else "%d tensors" % len(layout.names),
+                           "fused." + plan.kind, device=flat.is_cuda, numel=sum(layout.numels),
+                           compressor=type(self.compressor).__name__, payload_bytes=self._payload_bytes(plan))
         nvtx = self.nvtx and flat.is_cuda
         if nvtx:
             torch.cuda.nvtx.range_push("grace.exchange.%s" % plan.kind)
@@ -295,6 +303,8 @@ class FusedExchange(Communicator):
         self._stats["steps"] += 1
         if nvtx:
             torch.cuda.nvtx.range_pop()
+        if tok is not None:
+            tl.end(tok)
         return out
 
     def _payload_bytes(self, plan) -> int:

@@ -129,6 +129,10 @@ class NvlsAllreduce(Communicator):
         out_ptr = out.data_ptr()
         if out_ptr == flat.data_ptr() and symm_ptr == flat.data_ptr():
             out_ptr = symm_ptr                       # fully in place
+        from ..utils import timeline
+
+        tl = timeline.active()
+        tok = tl.begin("dense %d" % n, "nvls.allreduce", device=True, numel=n, staged=home is None) if tl else None
         seq = ch.next_seq()
         grid = self._grid = getattr(self, "_grid", None) or C.dense_max_grid(ch.heap.device.index, ch.sm_limit)
         grid = max(1, min(grid, -(-n // (4 * 512))))
@@ -139,6 +143,8 @@ class NvlsAllreduce(Communicator):
                           ch.ready_off, ch.ack_off, grid, _stream_ptr())
         ch.post_status()
         self.launches += 1
+        if tok is not None:
+            tl.end(tok)
 
     def step_flat(self, flat: torch.Tensor, layout=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Average a flat fp32 buffer over the ranks (``layout`` is accepted for interface parity and ignored)."""

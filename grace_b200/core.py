@@ -128,11 +128,19 @@ class Communicator(ABC):
         return self.wait_receive(handles, ctx)
 
     def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:
+        from .utils import timeline
+
+        tl = timeline.active()
+        tok = tl.begin(name, type(self).__name__, device=tensor.is_cuda, numel=tensor.numel(),
+                       compressor=type(self.compressor).__name__) if tl is not None else None
         tensor = self.memory.compensate(tensor, name)
         payload, ctx = self.compressor.compress(tensor, name)
         self.memory.update(tensor, name, self.compressor, payload, ctx)
         self._account(tensor, payload)
-        return self.send_receive(payload, name, ctx)
+        out = self.send_receive(payload, name, ctx)
+        if tok is not None:
+            tl.end(tok, payload_bytes=sum(t.numel() * t.element_size() for t in payload))
+        return out
 
     # -- split-phase style ------------------------------------------------
     def async_send(self, tensors, name):

@@ -13,7 +13,7 @@ codecs of ``grace_dl/tensorflow/helper.py`` (``adaq``, ``inceptionn``,
     to the memory).
 ``seed``, ``timeout_ms``, ``comm_sms``
     forwarded to the fused exchange.
-``nvls`` (bool, default False; needs ``fused``)
+``nvls`` / ``use_nvls`` (bool, default False; needs ``fused``)
     use the NVSwitch multicast mapping where it is available and the job has
     at least ``nvls_min_world`` (default 4) ranks: the ``none`` compressor with
     no memory averages with ``multimem.ld_reduce`` (``communicator/nvls.py``);
@@ -86,6 +86,10 @@ _COMMUNICATORS: Dict[str, Callable[..., Any]] = {
 }
 
 
+def _nvls(params) -> bool:
+    return bool(params.get("nvls", params.get("use_nvls", False)))
+
+
 def grace_from_params(params: Dict[str, Any]):
     comp_name = params.get("compressor", "none")
     mem_name = params.get("memory", "none")
@@ -106,9 +110,9 @@ def grace_from_params(params: Dict[str, Any]):
             comp, mem, _world(params), mode=mode,
             seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
             comm_sms=params.get("comm_sms"), group=params.get("group"),
-            nvls=params.get("nvls", False), nvls_min_world=params.get("nvls_min_world", 4),
+            nvls=_nvls(params), nvls_min_world=params.get("nvls_min_world", 4),
         )
-        if params.get("nvls", False) and comp_name == "none" and mem_name == "none":
+        if _nvls(params) and comp_name == "none" and mem_name == "none":
             from .communicator.nvls import NvlsAllreduce
 
             return NvlsAllreduce(comp, mem, _world(params), fallback=fused, group=params.get("group"),

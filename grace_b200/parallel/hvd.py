@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from .optimizer import Average, DistributedOptimizer, Sum  # noqa: F401
+from ..utils.timeline import start_timeline, stop_timeline  # noqa: F401  (same names as horovod.torch)
 
 _handles: Dict[int, Tuple[Any, torch.Tensor, Optional[float]]] = {}
 _next_handle = 0

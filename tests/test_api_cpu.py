@@ -293,3 +293,28 @@ def test_native_module_loads_without_a_gpu_and_sizes_its_slots():
     q8 = C.quant_slot_bytes(0, total, 1)          # codec 0 = QSGD: 1 byte per element + one norm per 128
     assert q8 >= 128 + total + total // 128 * 4 and q8 % 256 == 0
     assert C.MAX_WORLD == 16
+
+
+def test_timeline_records_every_exchange_as_chrome_trace(tmp_path):
+    import json
+
+    import grace_b200.parallel.hvd as hvd
+    from grace_b200 import grace_from_params
+    from grace_b200.utils import timeline
+
+    path = str(tmp_path / "trace.json")
+    assert timeline.active() is None and hvd.stop_timeline() is None
+    hvd.start_timeline(path)                      # same entry points as horovod.torch
+    grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                             "compress_ratio": 0.1, "world_size": 1})
+    for step in range(3):
+        grc.step(torch.randn(1000), "layer.weight")
+    timeline.active().instant("epoch", index=0)
+    assert hvd.stop_timeline() == path and timeline.active() is None
+    trace = json.load(open(path))
+    xs = [e for e in trace["traceEvents"] if e.get("ph") == "X"]
+    assert len(xs) == 3 and all(e["name"] == "layer.weight" and e["cat"] == "Allgather" for e in xs)
+    assert all(e["args"]["numel"] == 1000 and e["args"]["payload_bytes"] == 100 * 8 and e["dur"] >= 0 for e in xs)
+    assert xs[0]["ts"] <= xs[1]["ts"] <= xs[2]["ts"]
+    assert any(e.get("ph") == "i" and e["name"] == "epoch" for e in trace["traceEvents"])
+    grc.step(torch.randn(10), "untraced")          # no active timeline: nothing is recorded, nothing breaks

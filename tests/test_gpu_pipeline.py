@@ -68,3 +68,26 @@ def test_fast_pipeline_powersgd_runs_and_matches_loosely():
     params = {"compressor": "powersgd", "memory": "powersgd", "communicator": "allreduce", "compress_rank": 4}
     fast = _run("fast", params=params)
     assert torch.isfinite(fast).all()
+
+
+def test_timeline_device_track_for_fused_exchanges(tmp_path):
+    """CUDA tensors get a second, device-timed event per exchange (CUDA events resolved when the timeline stops)."""
+    import json
+
+    from grace_b200 import grace_from_params
+    from grace_b200.utils import timeline
+
+    path = str(tmp_path / "trace.json")
+    timeline.start_timeline(path, rank=0)
+    grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather", "quantum_num": 64,
+                             "world_size": 1, "fused": True})
+    x = torch.randn(1 << 20, device="cuda")
+    for _ in range(3):
+        grc.step(x.clone(), "w")
+    grc.check()
+    timeline.stop_timeline()
+    ev = [e for e in json.load(open(path))["traceEvents"] if e.get("ph") == "X"]
+    host = [e for e in ev if e["tid"] == 0]
+    dev = [e for e in ev if e["tid"] == 1]
+    assert len(host) == 3 and len(dev) == 3
+    assert all(e["cat"] == "fused.quant" and e["dur"] > 0 and e["args"]["numel"] == 1 << 20 for e in dev)
