@@ -5,7 +5,6 @@
 ``torch.nn.functional.scaled_dot_product_attention`` (a library kernel: the
 model is the workload here, the gradient exchange is the product).
 """
-import math
 
 import torch
 from torch import nn

@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from . import native
-from .exchange import (CODEC, PHASE_ALL, PHASE_COMPRESS, PHASE_EXCHANGE, PHASE_PUBLISH, ExchangeChannel, FlatLayout,
+from .exchange import (CODEC, PHASE_ALL, PHASE_COMPRESS, PHASE_EXCHANGE, ExchangeChannel, FlatLayout,
                        run_quant, segments_to_device, _stream_ptr)
 
 RANK_PAD = 16

@@ -12,7 +12,7 @@ Python and calls ``grc.step`` per tensor
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Optional, Sequence, Tuple
+from typing import Iterable, List, Optional, Tuple
 
 import torch
 
