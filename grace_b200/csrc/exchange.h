@@ -140,8 +140,8 @@ struct QuantArgs {
   int alltoall;          // 1: compressed reduce-scatter + compressed all-gather (QSGD, natural, fp16, fp32)
   unsigned long long ready2_off;  // flag pad of the second publication (alltoall mode)
   // Push transport (all-gather mode only; null = peers pull from each other's slots with remote loads):
-  // after encoding, the rank copies its slot with multimem.st into region `rank` of the receive area of
-  // EVERY GPU (the NVSwitch replicates the stores), and the decode pass reads local memory only.
+  // the encode pass stores its codes, norms and scalars with multimem.st into region `rank` of the receive
+  // area of EVERY GPU (the NVSwitch replicates the stores), and the decode pass reads local memory only.
   char* recv_local;               // this GPU's receive area of the current parity: world regions of recv_stride bytes
   char* recv_mc;                  // multicast address of the same area
   unsigned long long recv_stride;

@@ -104,7 +104,10 @@ __device__ __forceinline__ float natural_decode(unsigned code) {
   return __uint_as_float(bits | ((code & 0x80u) << 24));
 }
 
-template <int C>
+// kPush selects the push transport of the all-gather mode: every store of the encode pass goes through the
+// NVSwitch multicast mapping (multimem.st) into region `rank` of ALL GPUs' receive areas, and the decode pass
+// reads local memory.  It is a separate instantiation, so the pull variant keeps its code and registers.
+template <int C, bool kPush>
 __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantArgs a) {
   using T = CodecTraits<C>;
   __shared__ double red_d[kWarps][4];
@@ -121,7 +124,31 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   char* const my_slot = my_heap + a.peers.slot_off;
   // where rank p's payload is read from: its own slot over NVLink (pull), or the local receive area (push)
   auto slot_of = [&](int p) -> const char* {
-    return a.recv_local ? a.recv_local + (size_t)p * a.recv_stride : a.peers.heap[p] + a.peers.slot_off;
+    return kPush ? a.recv_local + (size_t)p * a.recv_stride : a.peers.heap[p] + a.peers.slot_off;
+  };
+  // stores of the encode pass: into the local slot (pull), or replicated by the switch into every GPU (push)
+  char* const put_base = kPush ? a.recv_mc + (size_t)rank * a.recv_stride : my_slot;
+  auto put_u32 = [&](size_t off, unsigned w) {
+    if (kPush) asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(put_base + off), "r"(w) : "memory");
+    else *reinterpret_cast<unsigned*>(put_base + off) = w;
+  };
+  auto put_f32 = [&](size_t off, float f) {
+    if (kPush) asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(put_base + off), "f"(f) : "memory");
+    else *reinterpret_cast<float*>(put_base + off) = f;
+  };
+  auto put_u2 = [&](size_t off, uint2 w) {
+    if (kPush) {
+      const unsigned long long q = ((unsigned long long)w.y << 32) | w.x;
+      asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(put_base + off), "l"(q) : "memory");
+    } else {
+      *reinterpret_cast<uint2*>(put_base + off) = w;
+    }
+  };
+  auto put_f4 = [&](size_t off, float4 v) {
+    if (kPush) asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(put_base + off), "f"(v.x),
+                            "f"(v.y), "f"(v.z), "f"(v.w)
+                            : "memory");
+    else *reinterpret_cast<float4*>(put_base + off) = v;
   };
   const size_t off_codes = kHeaderBytes + scalars_bytes(a.nseg);
   const size_t off_norms = off_codes + codes_bytes(T::bits, a.total);
@@ -203,7 +230,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
         if (T::stats) {
           sc = make_scalars<C>(a.stats[s], a.segs[s].numel);
           if (b0 == a.segs[s].offset && tid == 0)
-            *reinterpret_cast<float4*>(my_slot + kHeaderBytes + (size_t)s * 16) = make_float4(sc.s0, sc.s1, sc.s2, sc.s3);
+            put_f4(kHeaderBytes + (size_t)s * 16, make_float4(sc.s0, sc.s1, sc.s2, sc.s3));
         }
         // b0 is a multiple of 128: every warp step covers one whole code group
         for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
@@ -269,8 +296,8 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               word |= ((unsigned)code & 0xffu) << (8 * j);
               dv[j] = dq * (float)code;
             }
-            *reinterpret_cast<unsigned*>(my_slot + off_codes + (size_t)i) = word;
-            if (lane == 0) *reinterpret_cast<float*>(my_slot + off_norms + group * 4) = norm;
+            put_u32(off_codes + (size_t)i, word);
+            if (lane == 0) put_f32(off_norms + group * 4, norm);
           } else if (C == kCodecNatural) {
             unsigned word = 0;
 #pragma unroll
@@ -289,7 +316,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               word |= code << (8 * j);
               dv[j] = natural_decode(code);
             }
-            *reinterpret_cast<unsigned*>(my_slot + off_codes + (size_t)i) = word;
+            put_u32(off_codes + (size_t)i, word);
           } else if (C == kCodecU8bit) {
             const float s0 = sc.s0;
             const float safe = s0 > 0.f ? s0 : 1.f;
@@ -303,7 +330,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               word |= ((unsigned)code & 0xffu) << (8 * j);
               dv[j] = code ? s_edges[bin] * s0 * (float)sg : 0.f;  // bin 0 decodes to exactly 0
             }
-            *reinterpret_cast<unsigned*>(my_slot + off_codes + (size_t)i) = word;
+            put_u32(off_codes + (size_t)i, word);
           } else if (C == kCodecTernGrad) {
             const float s0 = sc.s0, c = sc.s1;
             unsigned nz[4], ng[4];
@@ -318,7 +345,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
             }
             if (lane < 8) {
               const unsigned w = lane < 4 ? nz[lane & 3] : ng[lane & 3];
-              *reinterpret_cast<unsigned*>(my_slot + off_codes + group * 32 + lane * 4) = w;
+              put_u32(off_codes + group * 32 + lane * 4, w);
             }
           } else if (C == kCodecSign || C == kCodecEFSign || C == kCodecOneBit) {
             unsigned bw[4];
@@ -331,18 +358,18 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               if (C == kCodecEFSign) dv[j] = bit ? sc.s0 : -sc.s0;
               if (C == kCodecOneBit) dv[j] = bit ? sc.s0 : sc.s1;
             }
-            if (lane < 4) *reinterpret_cast<unsigned*>(my_slot + off_codes + group * 16 + lane * 4) = bw[lane];
+            if (lane < 4) put_u32(off_codes + group * 16 + lane * 4, bw[lane]);
           } else if (C == kCodecFP16) {
             __half2 h01 = __floats2half2_rn(xv[0], xv[1]);
             __half2 h23 = __floats2half2_rn(xv[2], xv[3]);
             uint2 w;
             w.x = *reinterpret_cast<unsigned*>(&h01);
             w.y = *reinterpret_cast<unsigned*>(&h23);
-            *reinterpret_cast<uint2*>(my_slot + off_codes + (size_t)i * 2) = w;
+            put_u2(off_codes + (size_t)i * 2, w);
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
             dv[0] = f01.x; dv[1] = f01.y; dv[2] = f23.x; dv[3] = f23.y;
           } else if (C == kCodecFP32) {
-            *reinterpret_cast<float4*>(my_slot + off_codes + (size_t)i * 4) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+            put_f4(off_codes + (size_t)i * 4, make_float4(xv[0], xv[1], xv[2], xv[3]));
 #pragma unroll
             for (int j = 0; j < 4; ++j) dv[j] = xv[j];
           }
@@ -356,6 +383,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
         }
       });
     }
+    if (kPush) __threadfence_system();   // the multicast stores precede the flag raised after this barrier
     ok = bar.sync();
     if (T::stats && ok) {
       // leave the statistics scratch zeroed for the next launch
@@ -364,32 +392,6 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
         a.stats[s] = z;
       }
     }
-  }
-
-  if ((a.phases & kPhasePublish) && a.recv_mc) {
-    // ---- push: replicate this rank's encoded slot into region `rank` of every GPU's receive area ----
-    // (the slot was completed by all CTAs before the grid barrier that ends the compress phase)
-    const size_t n16 = (region1_bytes(C, T::bits, a.total, a.nseg) + 15) / 16;
-    const uint4* src = reinterpret_cast<const uint4*>(my_slot);
-    char* dst = a.recv_mc + (size_t)rank * a.recv_stride;
-    const size_t gtid = (size_t)blockIdx.x * kBlock + tid, gstride = (size_t)gridDim.x * kBlock;
-    constexpr int kAhead = 4;
-    if (!status.failed()) {
-      for (size_t i0 = gtid; i0 < n16; i0 += gstride * kAhead) {
-        uint4 v[kAhead];
-#pragma unroll
-        for (int u = 0; u < kAhead; ++u) if (i0 + u * gstride < n16) v[u] = ld_cg_u4(src + i0 + u * gstride);
-#pragma unroll
-        for (int u = 0; u < kAhead; ++u)
-          if (i0 + u * gstride < n16)
-            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + (i0 + u * gstride) * 16),
-                         "f"(__uint_as_float(v[u].x)), "f"(__uint_as_float(v[u].y)), "f"(__uint_as_float(v[u].z)),
-                         "f"(__uint_as_float(v[u].w))
-                         : "memory");
-      }
-    }
-    __threadfence_system();   // the multicast stores precede the flag raised after the barrier
-    bar.sync();
   }
 
   if (a.phases & kPhasePublish) {
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   }
 
   constexpr bool kTwoPhaseCodec = C == kCodecQSGD || C == kCodecNatural || C == kCodecFP16 || C == kCodecFP32;
-  if (kTwoPhaseCodec && a.alltoall) {
+  if (kTwoPhaseCodec && !kPush && a.alltoall) {
     // ---- two-phase mode: compressed reduce-scatter, re-encode, compressed all-gather ----
     // Rank j owns the contiguous chunk j of 128-element groups.  Region 2 of every
     // slot holds that rank's re-encoded chunk: codes, then (QSGD) one norm per group.
@@ -874,13 +876,17 @@ template <int C>
 cudaError_t launch_codec(const QuantArgs& a, int grid, cudaStream_t stream) {
   QuantArgs copy = a;
   void* params[] = {&copy};
-  return cudaLaunchCooperativeKernel((const void*)quant_exchange_kernel<C>, dim3(grid), dim3(kBlock), params, 0, stream);
+  const void* fn = a.recv_mc ? (const void*)quant_exchange_kernel<C, true> : (const void*)quant_exchange_kernel<C, false>;
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kBlock), params, 0, stream);
 }
 
 template <int C>
 int occupancy(int device, int sm_limit) {
   int per_sm = 0, sms = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_exchange_kernel<C>, kBlock, 0);
+  int per_sm_push = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_exchange_kernel<C, false>, kBlock, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_push, quant_exchange_kernel<C, true>, kBlock, 0);
+  if (per_sm_push < per_sm) per_sm = per_sm_push;   // one grid size serves both variants
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
   if (per_sm > 2) per_sm = 2;
