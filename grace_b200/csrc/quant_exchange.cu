@@ -297,7 +297,12 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               dv[j] = dq * (float)code;
             }
             put_u32(off_codes + (size_t)i, word);
-            if (lane == 0) put_f32(off_norms + group * 4, norm);
+            if (lane == 0) {
+              // one scalar per 128 elements: as single 4-byte multicast stores these cost more than all the codes,
+              // so in push mode they go to the local slot and are replicated in one vectorised sweep afterwards
+              if (kPush) *reinterpret_cast<float*>(my_slot + off_norms + group * 4) = norm;
+              else put_f32(off_norms + group * 4, norm);
+            }
           } else if (C == kCodecNatural) {
             unsigned word = 0;
 #pragma unroll
@@ -385,6 +390,20 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
     }
     if (kPush) __threadfence_system();   // the multicast stores precede the flag raised after this barrier
     ok = bar.sync();
+    if (kPush && C == kCodecQSGD) {
+      // replicate the norm array (total / 128 floats, complete after the barrier above), 16 bytes per store
+      const size_t n16 = ((size_t)(a.total / 128) * 4 + 15) / 16;
+      const uint4* nsrc = reinterpret_cast<const uint4*>(my_slot + off_norms);
+      const size_t gt = (size_t)blockIdx.x * kBlock + tid, gs = (size_t)gridDim.x * kBlock;
+      if (ok)
+        for (size_t k = gt; k < n16; k += gs) {
+          const uint4 v = ld_cg_u4(nsrc + k);
+          put_f4(off_norms + k * 16, make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z),
+                                                 __uint_as_float(v.w)));
+        }
+      __threadfence_system();
+      ok = bar.sync();
+    }
     if (T::stats && ok) {
       // leave the statistics scratch zeroed for the next launch
       for (int s = blockIdx.x * kBlock + tid; s < a.nseg; s += gridDim.x * kBlock) {
