@@ -253,6 +253,10 @@ TILE_DECODE_MAX_DENSITY = 0.5                                            # above
 def tile_decode_wanted(total: int, cap: int, world: int, mode: int) -> bool:
     if not TILE_DECODE_DEFAULT or mode == SPARSE_RANDOMK:
         return False
+    if mode == SPARSE_THRESHOLD and _TILE_ENV != "force":
+        # the capacity of a threshold exchange is a bound (max_ratio), not the number of entries that will travel:
+        # it says nothing about the density, and the ordered copy of the list would double an already large slot
+        return False
     return (total >= TILE_DECODE_MIN_ELEMS and world * cap >= TILE_DECODE_MIN_DENSITY * total
             and cap <= TILE_DECODE_MAX_DENSITY * total)
 

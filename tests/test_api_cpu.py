@@ -258,6 +258,7 @@ def test_tile_ordered_exchange_rule_is_a_pure_function_of_layout_capacity_and_wo
     assert not X.tile_decode_wanted(n, n // 1000, 8, X.SPARSE_TOPK)
     assert not X.tile_decode_wanted(1 << 20, 1 << 14, 8, X.SPARSE_TOPK)   # fits the L2 cache
     assert not X.tile_decode_wanted(n, k, 8, X.SPARSE_RANDOMK)   # random-k sends no indices at all
+    assert not X.tile_decode_wanted(n, n // 4, 8, X.SPARSE_THRESHOLD)   # capacity is a bound there, not a density
 
 
 def test_nvls_option_falls_back_cleanly_without_multicast():

@@ -353,6 +353,7 @@ def test_tile_bucketed_decode_threshold_and_segments(monkeypatch):
     import grace_b200.ops.exchange as X
     from grace_b200.ops.exchange import FlatLayout
 
+    monkeypatch.setattr(X, "_TILE_ENV", "force")        # threshold exchanges use the tile-ordered path only when forced
     monkeypatch.setattr(X, "TILE_DECODE_DEFAULT", True)
     monkeypatch.setattr(X, "TILE_DECODE_MIN_ELEMS", 0)
     monkeypatch.setattr(X, "TILE_DECODE_MIN_DENSITY", 0.0)
