@@ -149,3 +149,105 @@ def broadcast_optimizer_state(optimizer: torch.optim.Optimizer, root_rank: int =
     dist.broadcast_object_list(payload, src=root_rank)
     if rank() != root_rank:
         optimizer.load_state_dict(payload[0])
+
+
+# ---------------------------------------------------------------------------
+# Smaller pieces of the Horovod surface that training scripts use
+# (patch_files/horovod/torch/__init__.py:26-50, mpi_ops.py:846-861, compression.py)
+# ---------------------------------------------------------------------------
+def is_initialized() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+def local_size() -> int:
+    """Ranks on this node (torchrun's LOCAL_WORLD_SIZE; the whole job when it is not set)."""
+    return int(os.environ.get("LOCAL_WORLD_SIZE", size()))
+
+
+def cross_rank() -> int:
+    """Index of this node among the nodes of the job."""
+    return rank() // max(local_size(), 1)
+
+
+def cross_size() -> int:
+    return max(size() // max(local_size(), 1), 1)
+
+
+def barrier() -> None:
+    if size() > 1:
+        dist.barrier()
+
+
+def join() -> int:
+    """Horovod's ``join``: block until every rank has called it; returns the rank that arrived last.
+
+    Ranks publish their arrival time through an all-gather, so the answer is the same everywhere."""
+    if size() == 1:
+        return 0
+    import time
+
+    stamp = torch.tensor([time.time()], dtype=torch.float64)
+    if dist.get_backend() == "nccl":
+        stamp = stamp.cuda()
+    stamps = [torch.zeros_like(stamp) for _ in range(size())]
+    dist.all_gather(stamps, stamp)
+    return int(torch.stack([s.cpu() for s in stamps]).flatten().argmax())
+
+
+def broadcast_object(obj: Any, root_rank: int = 0, name: Optional[str] = None) -> Any:
+    if size() == 1:
+        return obj
+    box = [obj if rank() == root_rank else None]
+    dist.broadcast_object_list(box, src=root_rank)
+    return box[0]
+
+
+def allgather_object(obj: Any, name: Optional[str] = None) -> list:
+    if size() == 1:
+        return [obj]
+    out = [None] * size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def metric_average(value: float, name: Optional[str] = None) -> float:
+    """Average a Python number over the ranks (the reference's example averages its test metrics this way,
+    ``examples/torch/pytorch_mnist.py:139-171``)."""
+    t = torch.tensor([float(value)], dtype=torch.float64)
+    if is_initialized() and dist.get_backend() == "nccl":
+        t = t.cuda()
+    return float(allreduce(t, average=True, name=name).cpu())
+
+
+class _NoneCompressor:
+    """Horovod's wire-format "compression" (not GRACE's): identity."""
+
+    @staticmethod
+    def compress(tensor):
+        return tensor, None
+
+    @staticmethod
+    def decompress(tensor, ctx):
+        return tensor
+
+
+class _FP16Compressor:
+    """Cast floating tensors to fp16 for the wire, back to their dtype afterwards."""
+
+    @staticmethod
+    def compress(tensor):
+        if tensor.dtype.is_floating_point and tensor.dtype != torch.float16:
+            return tensor.to(torch.float16), tensor.dtype
+        return tensor, None
+
+    @staticmethod
+    def decompress(tensor, ctx):
+        return tensor.to(ctx) if ctx is not None else tensor
+
+
+class Compression:
+    """``hvd.Compression.none`` / ``hvd.Compression.fp16`` as accepted by ``DistributedOptimizer(compression=...)``;
+    only consulted for gradients that bypass ``grace`` (``num_groups > 0`` or ``op != Average``)."""
+
+    none = _NoneCompressor
+    fp16 = _FP16Compressor

@@ -150,11 +150,14 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         if self._grace is not None and self._num_groups == 0 and self.op == Average:
             return self._grace.send_step(tensor, name)
         work = None
+        wire_ctx = None
         if _world_size() > 1:
             if self.op == Average:
                 tensor.div_(_world_size())
+            if self._compression is not None:      # Horovod's wire-format compression (none / fp16)
+                tensor, wire_ctx = self._compression.compress(tensor)
             work = dist.all_reduce(tensor, async_op=True)
-        return ("plain", tensor, work), None
+        return ("plain", tensor, work), wire_ctx
 
     def _make_hook(self, p):
         def hook(*ignore):
@@ -211,6 +214,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 if work is not None:
                     work.wait()
                 output = tensor
+                if self._compression is not None and work is not None:
+                    output = self._compression.decompress(tensor, ctx)
             else:
                 output = self._grace.receive_step(handle, ctx)
             self._allreduce_delay[p] = self.backward_passes_per_step

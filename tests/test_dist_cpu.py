@@ -266,3 +266,36 @@ def test_nvls_options_fall_back_on_cpu_ranks():
         r = res[rank]
         assert r["type"] and r["step"] and r["flat"] and r["buffer"] and r["fp16"], r
         assert r["launches"] == 0
+
+
+def _hvd_surface(rank, world):
+    import grace_b200.parallel.hvd as hvd
+
+    out = {}
+    out["sizes"] = (hvd.size(), hvd.rank(), hvd.is_initialized(), hvd.local_size() >= 1, hvd.cross_size() >= 1)
+    out["join"] = hvd.join()
+    out["bobj"] = hvd.broadcast_object({"lr": 0.1 * (rank + 1)}, root_rank=1)["lr"]
+    out["gobj"] = hvd.allgather_object(rank * 10)
+    out["metric"] = hvd.metric_average(float(rank))
+    hvd.barrier()
+    # gradients that bypass grace (op=Sum) travel in fp16 when hvd.Compression.fp16 is given
+    torch.manual_seed(0)
+    model = torch.nn.Linear(8, 4)
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.0), named_parameters=model.named_parameters(),
+                                   compression=hvd.Compression.fp16, op=hvd.Sum)
+    x = torch.full((2, 8), float(rank + 1))
+    model(x).sum().backward()
+    opt.step()
+    g = model.weight.grad
+    out["fp16_wire"] = (g.dtype == torch.float32, bool(torch.allclose(g, torch.full_like(g, 2.0 * sum(range(1, world + 1))))))
+    return out
+
+
+def test_horovod_surface_helpers():
+    res = _run(_hvd_surface, world=2)
+    for rank in range(2):
+        r = res[rank]
+        assert r["sizes"] == (2, rank, True, True, True)
+        assert r["join"] in (0, 1) and r["join"] == res[0]["join"]
+        assert abs(r["bobj"] - 0.2) < 1e-12 and r["gobj"] == [0, 10] and abs(r["metric"] - 0.5) < 1e-12
+        assert r["fp16_wire"] == (True, True)
