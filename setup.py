@@ -40,6 +40,7 @@ setup(
     version="1.0",
     description="Blackwell-native gradient compression framework with the GRACE API",
     packages=find_packages(include=["grace_b200", "grace_b200.*", "grace_dl", "grace_dl.*"]),
+    py_modules=["rdxtopk", "cnat_cuda", "qsgd_cuda"],   # the reference's extension-module names
     package_data={"grace_b200": ["csrc/*", "*.so"]},
     python_requires=">=3.10",
     install_requires=["torch", "numpy"],
