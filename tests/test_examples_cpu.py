@@ -50,3 +50,8 @@ def test_distributed_optimizer_example_single_process():
 
 def test_ddp_hook_example_two_gloo_ranks():
     _run(_torchrun("examples/ddp_hook_example.py"))
+
+
+def test_native_ops_demo_checks_pass():
+    out = _run(["examples/native_ops_demo.py"])
+    assert "equals torch.topk: True" in out and "within one level: True" in out
