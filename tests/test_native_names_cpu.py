@@ -1,10 +1,15 @@
 """The reference's three extension modules keep their names and call signatures (``rdxtopk``, ``cnat_cuda``,
 ``qsgd_cuda``); on CPU tensors they run the torch implementations."""
+import os
+import sys
+
 import torch
 
-import cnat_cuda
-import qsgd_cuda
-import rdxtopk
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import cnat_cuda  # noqa: E402
+import qsgd_cuda  # noqa: E402
+import rdxtopk  # noqa: E402
 
 
 def test_rdxtopk_topk_signature_and_result():
