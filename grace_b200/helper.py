@@ -13,6 +13,9 @@ codecs of ``grace_dl/tensorflow/helper.py`` (``adaq``, ``inceptionn``,
     to the memory).
 ``seed``, ``timeout_ms``, ``comm_sms``
     forwarded to the fused exchange.
+``deterministic`` (natural compression, default False)
+    round to the nearest power of two instead of drawing (the reference's
+    ``cnat_cuda.compress_deterministic``, which its helper never reaches).
 ``nvls`` / ``use_nvls`` (bool, default False; needs ``fused``)
     use the NVSwitch multicast mapping where it is available and the job has
     at least ``nvls_min_world`` (default 4) ranks: the ``none`` compressor with
@@ -56,8 +59,8 @@ _COMPRESSORS: Dict[str, Callable[[Dict[str, Any]], Any]] = {
     "signum": lambda p: C.SignumCompressor(p.get("momentum", 0.9)),
     "efsignsgd": lambda p: C.EFSignSGDCompressor(p.get("lr", 0.1)),
     "onebit": lambda p: C.OneBitCompressor(),
-    "natural": lambda p: C.NaturalCompressor(),
-    "natural_cuda": lambda p: C.NaturalCompressor_CUDA(),
+    "natural": lambda p: C.NaturalCompressor(deterministic=bool(p.get("deterministic", False))),
+    "natural_cuda": lambda p: C.NaturalCompressor_CUDA(deterministic=bool(p.get("deterministic", False))),
     "u8bit": lambda p: C.U8bitCompressor(),
     "8bit": lambda p: C.U8bitCompressor(),
     "powersgd": lambda p: C.PowerSGDCompressor(
