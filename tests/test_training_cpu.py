@@ -52,3 +52,20 @@ def test_train_epoch_runs_the_manual_grace_loop_and_learns():
     assert out["steps"] == len(data) and last["loss"] < 0.5 * first["loss"]
     assert grc.stats()["steps"] == 6 * len(data) * 4          # four parameter tensors per step
     assert evaluate(model, data)["acc"] > 0.9
+
+
+def test_model_diagram_is_valid_dot_with_residual_joins():
+    from grace_b200.models import resnet9
+    from grace_b200.utils.diagram import model_to_dot
+
+    dot = model_to_dot(resnet9(), torch.zeros(1, 3, 32, 32), "resnet9")
+    assert dot.startswith("digraph resnet9 {") and dot.rstrip().endswith("}")
+    assert dot.count("{") == dot.count("}") == 1
+    assert '"input" -> ' in dot and '-> "output"' in dot
+    assert "Conv2d" in dot and "(1, 10)" in dot
+    # every edge endpoint is a declared node
+    import re
+
+    declared = set(re.findall(r'^  "([^"]+)" \[', dot, flags=re.M))
+    for src, dst in re.findall(r'^  "([^"]+)" -> "([^"]+)";', dot, flags=re.M):
+        assert src in declared and dst in declared
