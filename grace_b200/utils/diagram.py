@@ -15,42 +15,77 @@ import torch
 
 
 def model_to_dot(model: torch.nn.Module, example_input: torch.Tensor, name: str = "net") -> str:
+    from torch.overrides import TorchFunctionMode
+
     leaves = {m: n for n, m in model.named_modules() if len(list(m.children())) == 0}
     producer: Dict[int, str] = {id(example_input): "input"}
     nodes: List[Tuple[str, str]] = [("input", "input\\n%s" % (tuple(example_input.shape),))]
     edges: List[Tuple[str, str]] = []
-    hooks = []
+    keep = []            # intermediate tensors stay alive during the trace so that ids are never reused
+    depth = [0]          # > 0 while a leaf module runs: its internal torch calls are not part of the picture
+    joins = [0]
+
+    def tensors_in(obj):
+        if torch.is_tensor(obj):
+            yield obj
+        elif isinstance(obj, (list, tuple)):
+            for o in obj:
+                yield from tensors_in(o)
+        elif isinstance(obj, dict):
+            for o in obj.values():
+                yield from tensors_in(o)
+
+    class Trace(TorchFunctionMode):
+        def __torch_function__(self, func, types, args=(), kwargs=None):
+            out = func(*args, **(kwargs or {}))
+            if depth[0] == 0 and torch.is_tensor(out):
+                srcs = []
+                for t in tensors_in((args, kwargs or {})):
+                    s = producer.get(id(t))
+                    if s is not None and s not in srcs:
+                        srcs.append(s)
+                if len(srcs) == 1:                       # view / pooling / scaling between modules: transparent
+                    producer[id(out)] = srcs[0]
+                    keep.append(out)
+                elif len(srcs) > 1:                      # a join, e.g. the residual addition
+                    joins[0] += 1
+                    node = "%s_%d" % (getattr(func, "__name__", "op"), joins[0])
+                    nodes.append((node, "%s\\n%s" % (getattr(func, "__name__", "op"), tuple(out.shape))))
+                    for s in srcs:
+                        edges.append((s, node))
+                    producer[id(out)] = node
+                    keep.append(out)
+            return out
+
+    def pre_hook(mod, inputs):
+        depth[0] += 1
 
     def hook(mod, inputs, output):
+        depth[0] -= 1
         node = leaves[mod]
-        srcs = []
-        for t in inputs:
-            if torch.is_tensor(t):
-                srcs.append(producer.get(id(t), None))
         nparams = sum(p.numel() for p in mod.parameters(recurse=False))
         label = "%s\\n%s" % (node, type(mod).__name__)
         if nparams:
             label += "\\n%d params" % nparams
         if torch.is_tensor(output):
             label += "\\n%s" % (tuple(output.shape),)
-            producer[id(output)] = node
         nodes.append((node, label))
-        for s in srcs:
-            edges.append((s if s is not None else "(op)", node))
+        for t in tensors_in(inputs):
+            s = producer.get(id(t))
+            if s is not None:
+                edges.append((s, node))
+        for t in tensors_in(output):
+            producer[id(t)] = node
+            keep.append(t)
 
+    hooks = []
     for m in leaves:
+        hooks.append(m.register_forward_pre_hook(pre_hook))
         hooks.append(m.register_forward_hook(hook))
     was_training = model.training
     model.eval()
-    keep = []  # keep intermediate tensors alive so that ids stay unique during the trace
-
-    def keeper(mod, inputs, output):
-        keep.append(output)
-
-    for m in leaves:
-        hooks.append(m.register_forward_hook(keeper))
     try:
-        with torch.no_grad():
+        with torch.no_grad(), Trace():
             out = model(example_input)
     finally:
         for h in hooks:
@@ -63,9 +98,7 @@ def model_to_dot(model: torch.nn.Module, example_input: torch.Tensor, name: str 
             continue
         seen.add(node)
         lines.append('  "%s" [label="%s"];' % (node, label))
-    if any(s == "(op)" for s, _ in edges):
-        lines.append('  "(op)" [label="tensor op\\n(add / view / ...)", shape=ellipse];')
-    for s, d in edges:
+    for s, d in dict.fromkeys(edges):
         lines.append('  "%s" -> "%s";' % (s, d))
     if torch.is_tensor(out) and id(out) in producer:
         lines.append('  "output" [label="output\\n%s"];' % (tuple(out.shape),))
