@@ -3,8 +3,8 @@
 Reference: ``grace_dl/dist/compressor/dgc.py:6-50``: estimate the top-``ratio``
 magnitude threshold from a 1 % sample, then nudge it by x1.3 / x0.7 (at most ten
 rounds, one host sync each) until the selected count lies in
-``[0.7, 1.3] * ratio * N``.  ``mode='sampled'`` reproduces that procedure with
-on-device sampling; ``mode='exact'`` (default on CUDA) takes the exact k-th
+``[0.7, 1.3] * ratio * N``.  ``mode='sampled'`` reproduces that procedure draw for
+draw (same host-side uniform sample, hence the reference's selection for equal seeds); ``mode='exact'`` (default on CUDA) takes the exact k-th
 magnitude from the radix-select kernel, which always lands inside the accepted
 band and needs no host round trip.  ``ctx`` carries the selection mask that
 ``DgcMemory.update`` consumes.
@@ -24,7 +24,9 @@ class DgcCompressor(Compressor):
     def _sampled_threshold(self, flat):
         numel = flat.numel()
         n_sample = max(1, int(numel * 0.01))
-        sample_idx = torch.randint(numel, (n_sample,), device=flat.device)
+        # drawn exactly as the reference draws it (a float uniform on the host, truncated), so that equal seeds
+        # give equal samples; the clamp covers the float rounding of `numel` itself for very large tensors
+        sample_idx = torch.empty(n_sample).uniform_(0, numel).type(torch.long).clamp_(max=numel - 1).to(flat.device)
         k = max(1, int(numel * self.compress_ratio * 0.01))
         thr = torch.topk(flat[sample_idx].abs(), min(k, n_sample)).values.min()
         target = numel * self.compress_ratio

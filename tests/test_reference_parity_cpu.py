@@ -1,0 +1,85 @@
+"""Behavioural parity with the unmodified reference, on CPU: the reference package installed under
+``baseline/_ref`` runs in a subprocess (its own ``grace_dl``), this package runs here on the same inputs, and the
+aggregated gradients of three consecutive steps (so error-feedback state takes part) must agree; the stochastic
+codecs (QSGD, TernGrad, sampled DGC) draw from torch's global generator on both sides and are seeded alike.
+Not compared: 1-bit SGD (the reference's dist copy applies ``~`` to a uint8 mask and returns garbage) and natural
+compression (needs cupy there).  Skipped when the reference is not installed."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "grace_dl", "dist")),
+                                reason="reference not installed under baseline/_ref")
+
+
+def _port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.fixture(scope="module")
+def reference(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("ref") / "ref.pt")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "MASTER_PORT"):
+        env.pop(k, None)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "ref_oracle_runner.py"), REF, out, str(_port())],
+                         cwd="/", env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    return torch.load(out)
+
+
+@pytest.fixture(scope="module")
+def group():
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(_port())
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    yield
+    dist.destroy_process_group()
+
+
+def _ours(case):
+    from ref_oracle_runner import CASES, STEPS, inputs, pipeline
+
+    from grace_b200 import grace_from_params
+
+    grc = grace_from_params(dict(CASES[case], world_size=1))
+    res = [pipeline(grc, inputs(case, step).clone(), "layer.weight").clone() for step in range(STEPS)]
+    # the public entry point gives the same result as the spelled-out pipeline
+    again = grace_from_params(dict(CASES[case], world_size=1))
+    for step in range(STEPS):
+        torch.manual_seed(4242)                      # the seed the pipeline sets before its draws
+        torch.testing.assert_close(again.step(inputs(case, step).clone(), "layer.weight"), res[step], rtol=0, atol=0)
+    return res
+
+
+@pytest.mark.parametrize("case", ["topk", "threshold", "fp16", "none", "signsgd", "efsignsgd", "signum", "randomk", "qsgd",
+                                  "terngrad", "dgc", "dgc_momentum"])
+def test_three_steps_match_the_reference(case, reference, group):
+    ours = _ours(case)
+    for step, (a, b) in enumerate(zip(ours, reference[case])):
+        assert a.shape == b.shape and a.dtype == b.dtype, (case, step)
+        torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-7, msg=lambda m: "%s step %d: %s" % (case, step, m))
+
+
+def test_orthogonalize_matches_the_reference(reference):
+    from ref_oracle_runner import inputs
+
+    from grace_b200.compressor.powersgd import orthogonalize
+
+    m = inputs("orth", 0, (64, 4)).clone()
+    orthogonalize(m)
+    torch.testing.assert_close(m, reference["orthogonalize"][0], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(m.t() @ m, torch.eye(4), rtol=0, atol=1e-5)
