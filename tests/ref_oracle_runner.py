@@ -50,7 +50,55 @@ def pipeline(grc, x, name):
     return out / 1 if comp.average else out
 
 
+DIST_CASES = ["topk", "fp16", "none", "signsgd", "efsignsgd", "signum", "randomk", "qsgd", "terngrad"]
+
+
+def dist_inputs(case, step, rank, shape=(40, 25)):
+    import torch
+
+    g = torch.Generator().manual_seed(1000 * sum(case.encode()) + 10 * step + rank + 5)
+    return torch.randn(*shape, generator=g)
+
+
+def dist_steps(grace_from_params, rank, world):
+    """``grc.step`` through the real communicator (same-size payloads only: they run on gloo) on every rank."""
+    import torch
+
+    out = {}
+    for case in DIST_CASES:
+        grc = grace_from_params(dict(CASES[case], world_size=world))
+        res = []
+        for step in range(STEPS):
+            torch.manual_seed(77 + rank)
+            res.append(grc.step(dist_inputs(case, step, rank).clone(), "layer.weight").clone())
+        out[case] = res
+    return out
+
+
+def _dist_worker(rank, world, ref_root, out_path, port):
+    sys.path.insert(0, ref_root)
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from grace_dl.dist.helper import grace_from_params
+
+    out = dist_steps(grace_from_params, rank, world)
+    if rank == 0:
+        torch.save(out, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
+    if len(sys.argv) > 4 and int(sys.argv[4]) > 1:
+        import torch.multiprocessing as mp
+
+        world = int(sys.argv[4])
+        mp.spawn(_dist_worker, args=(world, sys.argv[1], sys.argv[2], int(sys.argv[3])), nprocs=world, join=True)
+        return
     ref_root, out_path = sys.argv[1], sys.argv[2]
     sys.path.insert(0, ref_root)
     import torch

@@ -83,3 +83,57 @@ def test_orthogonalize_matches_the_reference(reference):
     orthogonalize(m)
     torch.testing.assert_close(m, reference["orthogonalize"][0], rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(m.t() @ m, torch.eye(4), rtol=0, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# two ranks over gloo, through the real communicators (same-size payloads: the ones the reference can run on CPU)
+# ---------------------------------------------------------------------------------------------------------
+def _our_rank(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ref_oracle_runner import dist_steps
+
+        from grace_b200 import grace_from_params
+
+        out = dist_steps(grace_from_params, rank, world)
+        if rank == 0:
+            ret["out"] = out
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_match_the_reference_through_the_communicators(tmp_path):
+    import torch.multiprocessing as mp
+
+    from ref_oracle_runner import DIST_CASES, STEPS
+
+    out = str(tmp_path / "ref2.pt")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "MASTER_PORT"):
+        env.pop(k, None)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "ref_oracle_runner.py"), REF, out, str(_port()), "2"],
+                         cwd="/", env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
+    ref = torch.load(out)
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _port()
+        procs = [ctx.Process(target=_our_rank, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        for p in procs:
+            assert p.exitcode == 0
+        ours = ret["out"]
+    for case in DIST_CASES:
+        for step in range(STEPS):
+            torch.testing.assert_close(ours[case][step], ref[case][step], rtol=1e-6, atol=1e-7,
+                                       msg=lambda m, c=case, s=step: "%s step %d: %s" % (c, s, m))
