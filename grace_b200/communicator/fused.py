@@ -162,6 +162,8 @@ class FusedExchange(Communicator):
         elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor, C_.RandomKCompressor)):
             if isinstance(mem, M_.DgcMemory) and isinstance(comp, (C_.ThresholdCompressor, C_.RandomKCompressor)):
                 self._kind = None
+            elif isinstance(comp, C_.ThresholdCompressor) and getattr(comp, "strict", False):
+                self._kind = None   # the kernel implements ``|x| >= min(threshold, max)``; the strict rule stays in torch ops
             elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.DgcMemory)):
                 self._kind = "sparse"
         elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.EFSignSGDMemory)):

@@ -319,3 +319,20 @@ def test_timeline_records_every_exchange_as_chrome_trace(tmp_path):
     assert xs[0]["ts"] <= xs[1]["ts"] <= xs[2]["ts"]
     assert any(e.get("ph") == "i" and e["name"] == "epoch" for e in trace["traceEvents"])
     grc.step(torch.randn(10), "untraced")          # no active timeline: nothing is recorded, nothing breaks
+
+
+def test_threshold_flavours_of_the_two_import_paths():
+    """``grace_dl.dist``: ``|x| >= min(thr, max(x))``; ``grace_dl.torch`` (Horovod flavour): ``|x| > thr``."""
+    from grace_b200.communicator.fused import FusedExchange
+    from grace_b200.memory.none import NoneMemory
+    from grace_dl.dist.compressor.threshold import ThresholdCompressor as DistThreshold
+    from grace_dl.torch.compressor.threshold import ThresholdCompressor as TorchThreshold
+
+    x = torch.tensor([0.5, -1.0, 2.0, 1.0])
+    assert DistThreshold(1.0).compress(x, "a")[0][1].tolist() == [1, 2, 3]
+    assert TorchThreshold(1.0).compress(x, "a")[0][1].tolist() == [2]
+    assert DistThreshold(5.0).compress(x, "a")[0][1].tolist() == [2]      # capped at the largest element
+    assert TorchThreshold(5.0).compress(x, "a")[0][1].tolist() == []
+    # the fused kernel implements the dist rule only: the strict flavour is left to the library path
+    assert FusedExchange(DistThreshold(1.0), NoneMemory(), 1)._kind == "sparse"
+    assert FusedExchange(TorchThreshold(1.0), NoneMemory(), 1)._kind is None
