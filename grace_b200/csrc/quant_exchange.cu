@@ -15,6 +15,11 @@
 //       order 0..W-1 so that every rank computes bit-identical sums),
 //       dequantises, accumulates in fp32 or counts votes, and stores the
 //       aggregate.
+// Two more transports exist besides this pull: the two-phase mode (compressed
+// reduce-scatter, re-encode, compressed all-gather; `alltoall`), and the push
+// mode (kPush instantiation): every store of pass E is a multimem.st through the
+// NVSwitch multicast mapping into region `rank` of all GPUs' receive areas, and
+// pass X reads local memory only.
 //
 // Replaces, in the reference: grace_dl/dist/compressor/{qsgd,terngrad,natural,
 // signsgd,signum,efsignsgd,onebit,fp16}.py, qsgd_cuda/qsgd_cuda.cu (K4-K6 and

@@ -22,6 +22,14 @@
 //       dense output scaled by 1/W (a grid barrier separates the lists when
 //       W > 2 so that all replicas get bit-identical sums); then acknowledge
 //       so the slot can be reused.
+//   X'  tile-ordered variant (kTile instantiation, chosen by the host for large
+//       tensors whose ranks together deliver a few percent of the elements):
+//       before publishing, every rank orders its own picks by 8192-element
+//       output tile (counting sort in local memory) and appends a directory of
+//       tile offsets; a receiver then reads, for two tiles at a time, each
+//       peer's range of the ordered list, adds the ranks in order 0..W-1 in
+//       shared memory and writes the tiles once, densely: no global atomics,
+//       no zero-fill of the output in pass A, the same bits as X.
 // Threshold mode skips the select; random-k mode draws the positions from
 // Philox so that only values travel.
 //
