@@ -53,6 +53,50 @@ def _name_seed(seed: int, name: str) -> int:
     return ((seed & 0xFFFFFFFF) << 32) | (zlib.crc32(name.encode("utf8")) & 0xFFFFFFFF)
 
 
+class _Arena:
+    """The symmetric memory of one communicator: a few large heaps, carved up by the plans.
+
+    A heap costs one ``cudaMalloc``, one exchange of IPC handles among the ranks and ``W - 1`` mappings; a plan
+    only needs a range of it.  The first plan creates a heap of at least ``default_bytes``; a later plan that
+    does not fit makes the arena grow by another heap (again a collective step, so plans must be created in the
+    same order on every rank: ``FusedExchange.prepare`` does that up front, in name order)."""
+
+    def __init__(self, create, default_bytes: int):
+        self._create = create
+        self.default_bytes = int(default_bytes)
+        self.segments = []
+
+    def carve(self, nbytes: int):
+        if self.segments:
+            try:
+                return self.segments[-1].carve(nbytes)
+            except MemoryError:
+                pass
+        need = (int(nbytes) + 255) // 256 * 256 + 256
+        seg = self._create(max(self.default_bytes, need))
+        self.segments.append(seg)
+        return seg.carve(nbytes)
+
+    def close(self):
+        for seg in self.segments:
+            seg.close()
+        self.segments = []
+
+
+class _VirtualSegment:
+    """One arena heap of a ``VirtualWorld``: W heaps in this process, carved in lock step."""
+
+    def __init__(self, heaps):
+        self.heaps = heaps
+
+    def carve(self, nbytes: int):
+        return [h.carve(nbytes) for h in self.heaps]
+
+    def close(self):
+        for h in self.heaps:
+            h.close()
+
+
 class _Plan:
     """Everything one layout needs: heap, channel, segment table, arenas."""
 
@@ -120,9 +164,20 @@ class _Plan:
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
                  group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None, nvls=False,
-                 nvls_min_world=4):
+                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None):
+        """``comm_sms``: SMs an exchange may use when nothing else runs (None: all of them).  ``overlap_sms``: SMs
+        of an exchange that runs next to the backward pass (launched from a gradient hook: ``send_step``, the
+        bucketed ``DistributedOptimizer``, the DDP hook); the rest stays with backward.  ``arena_mb``: size of
+        the symmetric heaps the plans are carved from.  ``store``: a ``torch.distributed`` store through which the
+        ranks tell each other about a failed exchange (``agree`` / ``recover``)."""
         super().__init__(compressor, memory, world_size)
         self.mode = mode
+        self.overlap_sms = overlap_sms
+        self.arena_bytes = int(arena_mb * (1 << 20))
+        self._arena = None
+        self._side_stream = None
+        self.store = store
+        self._epoch = 0
         # push transport for the quantised codecs in all-gather mode: encoded slots are replicated into every
         # GPU's receive area with multimem.st and decoded from local memory (opt-in; needs NVSwitch multicast)
         self.nvls = bool(nvls)
@@ -188,11 +243,58 @@ class FusedExchange(Communicator):
 
     # ------------------------------------------------------------------
     def _make_heap(self, key, nbytes):
+        """A range of the communicator's arena (created, collectively, on first use)."""
         from ..parallel.symm import SymmetricHeap
 
         if self._virtual is not None:
             return self._virtual.heap_for(key, nbytes, self._rank)
-        return SymmetricHeap.create(nbytes, group=self.group, device=self.device)
+        if self._arena is None:
+            self._arena = _Arena(lambda n: SymmetricHeap.create(n, group=self.group, device=self.device),
+                                 self.arena_bytes)
+        return self._arena.carve(nbytes)
+
+    def prepare(self, named_tensors):
+        """Create the plans of single tensors now, in name order, so that no allocation and no host collective
+        is left for the first backward pass (where gradient hooks may fire in any order).  ``named_tensors``:
+        iterable of ``(name, tensor)``; tensors the fused path does not cover are skipped."""
+        from ..ops.exchange import FlatLayout
+
+        for name, t in sorted(((n, t) for n, t in named_tensors), key=lambda kv: kv[0]):
+            if not self.supported(t):
+                continue
+            if self.device is None:
+                self.device = t.device
+            lkey = (name, t.numel(), tuple(t.shape))
+            layout = self._single_layouts.get(lkey)
+            if layout is None:
+                layout = self._single_layouts[lkey] = FlatLayout.single(name, t.numel(), t.shape)
+            self._plan(layout)
+
+    def prepare_layouts(self, layouts, device):
+        """Same for whole buckets (``FlatParams.buckets``), in the order given."""
+        if self.device is None:
+            self.device = torch.device(device)
+        for layout in layouts:
+            self._plan(layout)
+
+    def _comm_stream(self):
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        return self._side_stream
+
+    def close(self):
+        """Tear down: wait for this rank's launches, meet the other ranks, unmap and free the arena.
+        Error-feedback state goes with the plans; take ``state_dict()`` first to keep it."""
+        if self.device is not None and torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if (self._virtual is None and self._arena is not None and dist.is_available() and dist.is_initialized()
+                and self.world_size > 1):
+            dist.barrier(group=self.group)
+        self._plans.clear()
+        self._single_layouts.clear()
+        if self._arena is not None:
+            self._arena.close()
+            self._arena = None
 
     def _plan(self, layout) -> _Plan:
         key = getattr(layout, "_key", None)
@@ -235,8 +337,11 @@ class FusedExchange(Communicator):
             return (0.0, 1.0) if first else (1.0, float(mem.learning_rate))
         return 0.0, 1.0
 
-    def _launch(self, plan: _Plan, g: torch.Tensor, out: torch.Tensor, phases: int, seq: Optional[int] = None) -> int:
+    def _launch(self, plan: _Plan, g: torch.Tensor, out: torch.Tensor, phases: int, seq: Optional[int] = None,
+                sm_limit: Optional[int] = None) -> int:
         from ..ops import exchange as X
+
+        grid = None if sm_limit is None else plan.channel.max_grid(plan.kind, sm_limit)
 
         comp = self.compressor
         scale = (1.0 / self.world_size) if comp.average else 1.0
@@ -254,7 +359,7 @@ class FusedExchange(Communicator):
                 beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
                 threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
                 phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps, clip=clip,
-                tile_decode=plan.tile)
+                tile_decode=plan.tile, grid=grid)
         else:
             seq = X.run_quant(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,
@@ -262,13 +367,14 @@ class FusedExchange(Communicator):
                 first_step=plan.steps == 0, beta=beta, gamma=gamma, mom_beta=float(getattr(comp, "momentum", 0.0)),
                 lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
                 phases=phases | (X.PHASE_REDUCE if (plan.alltoall and phases == X.PHASE_ALL) else 0), seq=seq,
-                recv=plan.recv,
-                alltoall=plan.alltoall)
+                recv=plan.recv, alltoall=plan.alltoall, grid=grid)
         return seq
 
     # ------------------------------------------------------------------
-    def step_flat(self, flat: torch.Tensor, layout, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Exchange a whole flat buffer of named gradients in one launch."""
+    def step_flat(self, flat: torch.Tensor, layout, out: Optional[torch.Tensor] = None,
+                  sm_limit: Optional[int] = None) -> torch.Tensor:
+        """Exchange a whole flat buffer of named gradients in one launch (on the current stream).
+        ``sm_limit`` caps the grid of this launch (an exchange that runs next to backward)."""
         from ..ops.exchange import PHASE_ALL
 
         if self.device is None:
@@ -297,10 +403,10 @@ class FusedExchange(Communicator):
         if plan.kind == "powersgd":
             if plan.matrices:
                 plan.channel.poll()
-                plan.launch(flat, out)
-            plan.launch_dense(flat, out)
+                plan.launch(flat, out, sm_limit=sm_limit)
+            plan.launch_dense(flat, out, sm_limit=sm_limit)
         else:
-            self._launch(plan, flat, out, PHASE_ALL)
+            self._launch(plan, flat, out, PHASE_ALL, sm_limit=sm_limit)
         plan.steps += 1
         self._stats["steps"] += 1
         if nvtx:
@@ -324,7 +430,7 @@ class FusedExchange(Communicator):
             flat = flat.float().contiguous().clone()
         return flat
 
-    def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:
+    def step(self, tensor: torch.Tensor, name: str, sm_limit: Optional[int] = None) -> torch.Tensor:
         if not self.supported(tensor):
             return self._fallback.step(tensor, name)
         from ..ops.exchange import FlatLayout
@@ -336,22 +442,31 @@ class FusedExchange(Communicator):
         layout = self._single_layouts.get(lkey)
         if layout is None:
             layout = self._single_layouts[lkey] = FlatLayout.single(name, flat.numel(), tensor.shape)
-        self.step_flat(flat, layout, out)
+        self.step_flat(flat, layout, out, sm_limit=sm_limit)
         return out.view(tensor.shape).to(tensor.dtype)
 
-    # split-phase: launch on the caller's current stream, hand back an event
+    # split-phase (the reference's Horovod flavour, grace_dl/torch/__init__.py:50-58): the exchange is launched
+    # from the gradient hook on a high-priority side stream with a capped grid, so it runs next to the rest of
+    # backward; receive_step makes the caller's stream wait for it
     def send_step(self, tensor: torch.Tensor, name: str):
         if not self.supported(tensor):
             return self._fallback.send_step(tensor, name)
-        out = self.step(tensor, name)
-        ev = torch.cuda.Event()
-        ev.record()
+        if self.device is None:
+            self.device = tensor.device
+        side = self._comm_stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            out = self.step(tensor, name, sm_limit=self.overlap_sms)
+            ev = torch.cuda.Event()
+            ev.record(side)
         return ("fused", out, ev), None
 
     def receive_step(self, handles, ctx) -> torch.Tensor:
         if isinstance(handles, tuple) and len(handles) == 3 and handles[0] == "fused":
             _, out, ev = handles
-            torch.cuda.current_stream().wait_event(ev)
+            cur = torch.cuda.current_stream()
+            cur.wait_event(ev)
+            out.record_stream(cur)
             return out
         return self._fallback.receive_step(handles, ctx)
 
@@ -370,6 +485,58 @@ class FusedExchange(Communicator):
                     plan.dense_channel.reset()
             else:
                 plan.channel.reset()
+
+    def agree(self, local_error: Optional[BaseException] = None, timeout_s: float = 30.0):
+        """Step-boundary vote through the store: every rank posts whether its exchanges failed and reads the
+        others' votes.  Returns the sorted list of ranks that reported a failure (empty: all healthy), the same
+        list on every rank, so that either all of them call ``recover()`` or none does.  Needs ``store``."""
+        if self.store is None:
+            raise RuntimeError("agree() needs a store (FusedExchange(..., store=...))")
+        board = self._error_board()
+        failed = local_error is not None
+        if not failed:
+            try:
+                self.check()
+            except RuntimeError as e:   # GraceCommError included
+                local_error, failed = e, True
+        return board.vote(self._epoch, failed, timeout_s=timeout_s,
+                          info=str(local_error)[:200] if failed else "")
+
+    def recover(self, timeout_s: float = 30.0):
+        """After a failed exchange, on every rank: (1) wait for this rank's kernels (their waits are bounded, so
+        this returns) - from then on this rank writes no flag of a peer any more; (2) meet the other ranks;
+        (3) clear flags, sequence numbers and scratch of every plan; (4) meet again, so that nobody launches
+        before every pad is clean.  The meetings go through the store when one is attached, else through
+        process-group barriers.  Error-feedback state, warm starts and step counters are kept; the next exchange
+        starts from sequence 1 on every rank."""
+        if self.device is not None and torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize(self.device)
+        real = self._virtual is None and self.world_size > 1
+
+        def meet(tag):
+            if not real:
+                return
+            if self.store is not None:
+                self._error_board().barrier(self._epoch, timeout_s=timeout_s, tag=tag)
+            elif dist.is_available() and dist.is_initialized():
+                dist.barrier(group=self.group)
+
+        meet("quiet")
+        self.reset()
+        meet("clean")
+        self._epoch += 1
+
+    def _error_board(self):
+        from ..utils.faults import ErrorBoard
+
+        if getattr(self, "_board", None) is None:
+            self._board = ErrorBoard(self.store, self._host_rank(), self.world_size)
+        return self._board
+
+    def _host_rank(self) -> int:
+        if self._rank is not None:
+            return int(self._rank)
+        return dist.get_rank(self.group) if dist.is_available() and dist.is_initialized() else 0
 
     def check(self):
         """Block until every launched exchange finished; raise on failure."""
@@ -467,6 +634,8 @@ class VirtualWorld:
         if self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
         self._heaps = {}
+        self._arena = None
+        self.arena_bytes = 64 << 20
         self.comms: List[FusedExchange] = []
         for r in range(world):
             c = make_comm(r)
@@ -476,10 +645,14 @@ class VirtualWorld:
             self.comms.append(c)
 
     def heap_for(self, key, nbytes, rank):
+        """Range ``key`` of the world's arena, as seen by virtual rank ``rank`` (carved once for all W ranks)."""
         from ..parallel.symm import SymmetricHeap
 
         if key not in self._heaps:
-            self._heaps[key] = SymmetricHeap.virtual(nbytes, self.world, self.device)
+            if self._arena is None:
+                self._arena = _Arena(lambda n: _VirtualSegment(SymmetricHeap.virtual(n, self.world, self.device)),
+                                     self.arena_bytes)
+            self._heaps[key] = self._arena.carve(nbytes)
         return self._heaps[key][rank]
 
     def step_flat(self, flats: Sequence[torch.Tensor], layout, outs: Optional[Sequence[torch.Tensor]] = None):

@@ -425,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   bool ok = true;
 
   if (part1) {
-    if (blockIdx.x == 0 && tid < world && tid != rank && a.peers.seq > 2) {
+    if (tid < world && tid != rank && a.peers.seq > 2) {   // every CTA: none may zero the slot before the peers are done with it
       const uint64_t* ack = reinterpret_cast<const uint64_t*>(a.peers.heap[rank] + a.peers.ack_off) + tid;
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }

@@ -44,6 +44,12 @@ constexpr int kWarps = kBlock / 32;
 constexpr int kIterElems = kBlock * 4;
 constexpr unsigned kHeaderBytes = 128;
 constexpr int kU = 4;  // groups per warp trip whose loads are issued up front
+// Staged decode (1-, 2- and 8-bit codes, 2..kStagePeers ranks): every warp owns a staging area in shared memory
+// that takes 512 bytes of codes from each rank (and four QSGD norms), so the loads from ALL ranks are in flight
+// together and no register has to hold them while the sums are formed.
+constexpr int kStagePeers = 8;
+constexpr int kStageWarpBytes = kStagePeers * (512 + 16);
+constexpr int kStageBytes = kWarps * kStageWarpBytes;
 
 template <int C> struct CodecTraits;
 template <> struct CodecTraits<kCodecQSGD>     { static constexpr bool stats = false; static constexpr int bits = 8; };
@@ -120,6 +126,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   __shared__ float red_m[kWarps];
   __shared__ float s_edges[128];
   __shared__ SegScalars s_peer[kMaxWorld];
+  extern __shared__ __align__(16) unsigned char s_dyn[];   // staging areas of the staged decode (kStageBytes, or nothing)
 
   const Status status{a.status};
   GridBarrier bar{a.barrier, 0u, a.peers.timeout_ns, status};
@@ -168,14 +175,17 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   }
 
   if (a.phases & kPhaseCompress) {
-    if (blockIdx.x == 0 && tid < world && tid != rank && a.peers.seq > 2) {
+    // The slot of this parity was last used by sequence seq-2: every CTA waits (on local memory) until all peers
+    // have acknowledged reading it, and only then may any of its threads store into the slot or push to the peers.
+    if (tid < world && tid != rank && a.peers.seq > 2) {
       const uint64_t* ack = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ack_off) + tid;
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
-    bool ok = true;
+    __syncthreads();
+    bool ok = !status.failed();
     if (T::stats) {
       // ---- pass S: compensate, store, per-segment statistics ----
-      if (lo < hi) {
+      if (ok && lo < hi) {
         for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
           double t_sum = 0, t_sq = 0, t_neg = 0, t_pos = 0;
           unsigned long long t_cnt = 0;
@@ -653,57 +663,107 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
           }
           __syncthreads();
         }
-        if ((T::bits == 1 || T::bits == 2) && world > 1) {
-          // Bit-packed codes, remote peers: lane l fetches the whole code block of group g0 + l with
-          // 16-byte loads (all loads of up to four peers in flight), then the blocks are handed round
-          // with shuffles so that every group is decoded and stored by the full warp (coalesced).
-          constexpr int kWordsPerGroup = T::bits * 4;     // 4 words (1 bit) or 8 words (2 bits)
-          constexpr int kPeerChunk = T::bits == 2 ? 2 : 4;   // peers whose loads are in flight together
-          for (long long g0 = (b0 >> 7) + 32ll * warp; (g0 << 7) < e0; g0 += 32ll * kWarps) {
-            const long long my_group = g0 + lane;
-            const bool have = (my_group << 7) < e0;
-            // this lane's 4 elements of each of the 32 groups would need 128 accumulators,
-            // so the groups are processed in four rounds of eight
-#pragma unroll 1
-            for (int round = 0; round < 4; ++round) {
-              float acc[8][4];
-              int votes[8][4];
+        if ((T::bits == 1 || T::bits == 2 || T::bits == 8) && world > 1 && world <= kStagePeers) {
+          // Staged decode.  Per trip a warp covers one block of 512 code bytes per rank: 512 elements of an
+          // 8-bit code, 16 groups of a 2-bit code, 32 groups of a 1-bit code.  Lane l fetches bytes
+          // [16 l, 16 l + 16) of the block from EVERY rank (one 512-byte request per rank and warp, all of them
+          // in flight together), parks them in the warp's staging area and the registers are free again; the
+          // sums are then formed rank by rank (0..W-1: identical bits on every GPU) from shared memory.
+          constexpr long long kBlockElems = 512ll * 8 / T::bits;
+          uint4* const st_codes = reinterpret_cast<uint4*>(s_dyn + warp * kStageWarpBytes);            // [rank][32]
+          float* const st_norms = reinterpret_cast<float*>(s_dyn + warp * kStageWarpBytes + kStagePeers * 512);  // [rank][4]
+          for (long long w0 = b0 + kBlockElems * warp; w0 < e0; w0 += kBlockElems * kWarps) {
+            // ---- fetch: all ranks, then park ----
+            {
+              // first element covered by this lane's 16 bytes
+              const long long le = w0 + (T::bits == 8 ? 16ll * lane : (T::bits == 2 ? 128ll * (lane >> 1) : 128ll * lane));
+              const size_t byte_off = T::bits == 8 ? (size_t)le : (size_t)(w0 >> 7) * (T::bits * 16) + 16u * lane;
+              const bool have = le < e0;
+              uint4 v[kStagePeers];
+              float nv[kStagePeers];
 #pragma unroll
-              for (int gi = 0; gi < 8; ++gi)
+              for (int p = 0; p < kStagePeers; ++p) {
+                v[p] = make_uint4(0u, 0u, 0u, 0u);
+                nv[p] = 0.f;
+                if (p < world) {
+                  const char* slot = slot_of(p);
+                  if (have) v[p] = ld_cg_u4(slot + off_codes + byte_off);
+                  if (C == kCodecQSGD && lane < 4 && w0 + 128ll * lane < e0)
+                    nv[p] = ld_cg_f32(slot + off_norms + (size_t)((w0 >> 7) + lane) * 4);
+                }
+              }
+              __syncwarp();   // the previous trip's readers are done with the staging area
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { acc[gi][j] = 0.f; votes[gi][j] = 0; }
-              for (int p0 = 0; p0 < world; p0 += kPeerChunk) {
-                unsigned w[kPeerChunk][kWordsPerGroup];
+              for (int p = 0; p < kStagePeers; ++p) {
+                if (p < world) {
+                  st_codes[p * 32 + lane] = v[p];
+                  if (C == kCodecQSGD && lane < 4) st_norms[p * 4 + lane] = nv[p];
+                }
+              }
+              __syncwarp();
+            }
+            if (T::bits == 8) {
+              float acc16[16];
 #pragma unroll
-                for (int pp = 0; pp < kPeerChunk; ++pp) {
+              for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
+              for (int p = 0; p < world; ++p) {
+                const uint4 cw = st_codes[p * 32 + lane];
+                const unsigned words[4] = {cw.x, cw.y, cw.z, cw.w};
+                float d = 0.f;
+                if (C == kCodecQSGD) d = st_norms[p * 4 + (lane >> 3)] / (float)a.quantum;
+                if (C == kCodecU8bit) d = s_peer[p].s0;
 #pragma unroll
-                  for (int k = 0; k < kWordsPerGroup; ++k) w[pp][k] = 0u;
-                  // lanes 8*round .. 8*round+7 own the groups of this round
-                  if (p0 + pp < world && have && (lane >> 3) == round) {
-                    const char* src_blk = slot_of(p0 + pp) + off_codes +
-                                          (size_t)my_group * (kWordsPerGroup * 4);
-                    const uint4 v0 = ld_cg_u4(src_blk);
-                    w[pp][0] = v0.x; w[pp][1] = v0.y; w[pp][2] = v0.z; w[pp][3] = v0.w;
-                    if (T::bits == 2) {
-                      const uint4 v1 = ld_cg_u4(src_blk + 16);
-                      w[pp][4] = v1.x; w[pp][5] = v1.y; w[pp][6] = v1.z; w[pp][7] = v1.w;
-                    }
+                for (int j = 0; j < 16; ++j) {
+                  const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                  if (C == kCodecQSGD) acc16[j] += d * (float)(int)(signed char)byte;
+                  if (C == kCodecNatural) acc16[j] += natural_decode(byte);
+                  if (C == kCodecU8bit) {
+                    const int code = (int)(signed char)byte;
+                    const int ab = code < 0 ? -code : code;
+                    const float sg = code > 0 ? 1.f : (code < 0 ? -1.f : 0.f);
+                    acc16[j] += s_edges[ab] * d * sg;
                   }
                 }
+              }
+              const long long i = w0 + 16ll * lane;
 #pragma unroll
-                for (int pp = 0; pp < kPeerChunk; ++pp) {
-                  if (p0 + pp >= world) break;
-                  const SegScalars sp = s_peer[p0 + pp];
+              for (int v4 = 0; v4 < 4; ++v4) {
+                const long long iv = i + 4 * v4;
+                if (iv >= e0) continue;
+                const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
+                const float ov[4] = {acc16[4 * v4] * a.scale, acc16[4 * v4 + 1] * a.scale,
+                                     acc16[4 * v4 + 2] * a.scale, acc16[4 * v4 + 3] * a.scale};
+                store4(a.out, iv, valid, ov);
+              }
+            } else {
+              // bit-packed codes: word j of a group holds, in bit l, the code bit of element 4 l + j
+              constexpr int kGroups = T::bits == 2 ? 16 : 32;   // groups per block
+              constexpr int kVec = T::bits == 2 ? 2 : 1;        // 16-byte vectors per group and rank
+#pragma unroll 1
+              for (int r0 = 0; r0 < kGroups; r0 += 8) {
+                if (w0 + 128ll * r0 >= e0) break;   // warp-uniform
+                float acc[8][4];
+                int votes[8][4];
+#pragma unroll
+                for (int gi = 0; gi < 8; ++gi)
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { acc[gi][j] = 0.f; votes[gi][j] = 0; }
+                for (int p = 0; p < world; ++p) {
+                  const SegScalars sp = s_peer[p];
 #pragma unroll
                   for (int gi = 0; gi < 8; ++gi) {
-                    const int owner = round * 8 + gi;
+                    const uint4 w = st_codes[p * 32 + (r0 + gi) * kVec];   // same address in every lane: broadcast
+                    const unsigned wj[4] = {w.x, w.y, w.z, w.w};
+                    unsigned nj[4] = {0u, 0u, 0u, 0u};
+                    if (T::bits == 2) {
+                      const uint4 n = st_codes[p * 32 + (r0 + gi) * kVec + 1];
+                      nj[0] = n.x; nj[1] = n.y; nj[2] = n.z; nj[3] = n.w;
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                      const unsigned b0w = __shfl_sync(0xffffffffu, w[pp][j], owner);
-                      const bool bit = (b0w >> lane) & 1u;
+                      const bool bit = (wj[j] >> lane) & 1u;
                       if (T::bits == 2) {
-                        const unsigned ngw = __shfl_sync(0xffffffffu, w[pp][4 + j], owner);
-                        if (bit) acc[gi][j] += ((ngw >> lane) & 1u) ? -sp.s0 : sp.s0;
+                        if (bit) acc[gi][j] += ((nj[j] >> lane) & 1u) ? -sp.s0 : sp.s0;
                       } else {
                         if (C == kCodecSign) votes[gi][j] += bit ? 1 : -1;
                         if (C == kCodecEFSign) acc[gi][j] += bit ? sp.s0 : -sp.s0;
@@ -712,80 +772,22 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                     }
                   }
                 }
-              }
 #pragma unroll
-              for (int gi = 0; gi < 8; ++gi) {
-                const long long gb = (g0 + round * 8 + gi) << 7;
-                if (gb >= e0) break;  // warp-uniform
-                const long long i = gb + 4 * lane;
-                int valid = 0;
-                if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
-                float ov[4];
+                for (int gi = 0; gi < 8; ++gi) {
+                  const long long gb = w0 + 128ll * (r0 + gi);
+                  if (gb >= e0) break;  // warp-uniform
+                  const long long i = gb + 4 * lane;
+                  int valid = 0;
+                  if (i < e0) valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
+                  float ov[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (C == kCodecSign) ov[j] = votes[gi][j] >= 0 ? 1.f : -1.f;
-                  else if (C == kCodecEFSign) ov[j] = acc[gi][j] / a.lr;
-                  else ov[j] = acc[gi][j] * a.scale;
-                }
-                if (valid) store4(a.out, i, valid, ov);
-              }
-            }
-          }
-        } else
-        if (T::bits == 8 && world > 1) {
-          // 8-bit codes, remote peers: one 16-byte load brings 16 codes, a warp covers 512 elements per load
-          // instruction (remote reads over NVLink need large requests in flight); kX such loads per
-          // peer are issued before the first one is consumed.
-          constexpr int kX = 2;
-          for (long long w0 = b0 + 512ll * warp; w0 < e0; w0 += 512ll * kWarps * kX) {
-            float acc16[kX][16];
-#pragma unroll
-            for (int q = 0; q < kX; ++q)
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc16[q][j] = 0.f;
-            for (int p = 0; p < world; ++p) {
-              const char* slot = slot_of(p);
-              uint4 cw[kX];
-              float dq[kX];
-#pragma unroll
-              for (int q = 0; q < kX; ++q) {
-                const long long i = w0 + 512ll * kWarps * q + 16 * lane;
-                cw[q] = make_uint4(0u, 0u, 0u, 0u);
-                dq[q] = 0.f;
-                if (i < e0) {
-                  cw[q] = ld_cg_u4(slot + off_codes + (size_t)i);
-                  if (C == kCodecQSGD) dq[q] = ld_cg_f32(slot + off_norms + (size_t)(i >> 7) * 4);
-                }
-              }
-#pragma unroll
-              for (int q = 0; q < kX; ++q) {
-                const unsigned words[4] = {cw[q].x, cw[q].y, cw[q].z, cw[q].w};
-                const float d = dq[q] / (float)a.quantum;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
-                  if (C == kCodecQSGD) acc16[q][j] += d * (float)(int)(signed char)byte;
-                  if (C == kCodecNatural) acc16[q][j] += natural_decode(byte);
-                  if (C == kCodecU8bit) {
-                    const int code = (int)(signed char)byte;
-                    const int ab = code < 0 ? -code : code;
-                    const float sg = code > 0 ? 1.f : (code < 0 ? -1.f : 0.f);
-                    acc16[q][j] += s_edges[ab] * s_peer[p].s0 * sg;
+                  for (int j = 0; j < 4; ++j) {
+                    if (C == kCodecSign) ov[j] = votes[gi][j] >= 0 ? 1.f : -1.f;
+                    else if (C == kCodecEFSign) ov[j] = acc[gi][j] / a.lr;
+                    else ov[j] = acc[gi][j] * a.scale;
                   }
+                  if (valid) store4(a.out, i, valid, ov);
                 }
-              }
-            }
-#pragma unroll
-            for (int q = 0; q < kX; ++q) {
-              const long long i = w0 + 512ll * kWarps * q + 16 * lane;
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const long long iv = i + 4 * v;
-                if (iv >= e0) continue;
-                const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
-                const float ov[4] = {acc16[q][4 * v] * a.scale, acc16[q][4 * v + 1] * a.scale,
-                                     acc16[q][4 * v + 2] * a.scale, acc16[q][4 * v + 3] * a.scale};
-                store4(a.out, iv, valid, ov);
               }
             }
           }
@@ -896,20 +898,39 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   }
 }
 
+// Dynamic shared memory of a launch: the staging areas, when the staged decode can run.
+template <int C>
+constexpr bool staged_codec() { return CodecTraits<C>::bits == 1 || CodecTraits<C>::bits == 2 || CodecTraits<C>::bits == 8; }
+
 template <int C>
 cudaError_t launch_codec(const QuantArgs& a, int grid, cudaStream_t stream) {
   QuantArgs copy = a;
   void* params[] = {&copy};
   const void* fn = a.recv_mc ? (const void*)quant_exchange_kernel<C, true> : (const void*)quant_exchange_kernel<C, false>;
-  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kBlock), params, 0, stream);
+  size_t smem = 0;
+  if (staged_codec<C>() && a.peers.world > 1 && a.peers.world <= kStagePeers && (a.phases & kPhaseExchange)) {
+    smem = kStageBytes;
+    static bool attr_set[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int v = a.recv_mc ? 1 : 0;
+    if (dev >= 0 && dev < 64 && !attr_set[dev][v]) {
+      cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+      if (err != cudaSuccess) return err;
+      attr_set[dev][v] = true;
+    }
+  }
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kBlock), params, smem, stream);
 }
 
 template <int C>
 int occupancy(int device, int sm_limit) {
   int per_sm = 0, sms = 0;
   int per_sm_push = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_exchange_kernel<C, false>, kBlock, 0);
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_push, quant_exchange_kernel<C, true>, kBlock, 0);
+  cudaFuncSetAttribute(quant_exchange_kernel<C, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  cudaFuncSetAttribute(quant_exchange_kernel<C, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_exchange_kernel<C, false>, kBlock, kStageBytes);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_push, quant_exchange_kernel<C, true>, kBlock, kStageBytes);
   if (per_sm_push < per_sm) per_sm = per_sm_push;   // one grid size serves both variants
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;

@@ -168,10 +168,12 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   if (a.phases & kPhaseCompress) {
     // Before overwriting the slot of parity (seq & 1): every peer must have
     // finished reading what sequence seq-2 put there.
-    if (blockIdx.x == 0 && tid < world && tid != rank && a.peers.seq > 2) {
+    // Every CTA waits (the acknowledgement words are local memory), so none of them can touch the slot early.
+    if (tid < world && tid != rank && a.peers.seq > 2) {
       const uint64_t* ack = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ack_off) + tid;
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
+    __syncthreads();
     if (blockIdx.x == 0 && tid == 0) { my_hdr[0] = 0; my_hdr[1] = 0; }
     if (kTile && dense_decode) {   // tile counters of the ordering step; many grid barriers lie between here and their use
       const long long nb1 = ((a.total + kTileElems - 1) >> kTileShift) + 1;

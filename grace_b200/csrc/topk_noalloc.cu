@@ -172,7 +172,7 @@ DeviceSetup g_setup[64] = {};
 extern "C" const char* grace_topk_noalloc_strerror(int code) {
   switch (code) {
     case GRACE_NOALLOC_OK: return "ok";
-    case GRACE_NOALLOC_BAD_ARGUMENT: return "bad argument: need non-null 16-byte aligned x, values, indices and 1 <= k <= n";
+    case GRACE_NOALLOC_BAD_ARGUMENT: return "bad argument: need non-null x (16-byte aligned), values and indices, and 1 <= k <= n";
     case GRACE_NOALLOC_TOO_LARGE: return "input too large: n exceeds 2^31 - 1 elements";
     case GRACE_NOALLOC_SETUP_FAILED: return "set-up failed: could not resolve the device work area or the launch geometry";
     case GRACE_NOALLOC_LAUNCH_FAILED: return "launch failed: the memset or the kernel launch was refused";
@@ -202,7 +202,10 @@ extern "C" int grace_topk_select_noalloc(const float* x, long long n, int k, flo
     s.ready = true;
   }
   // The work area still holds the previous call's state: clear all of it.
-  if (cudaMemsetAsync(s.scratch, 0, sizeof(Scratch), stream) != cudaSuccess) return GRACE_NOALLOC_LAUNCH_FAILED;
+  if (cudaMemsetAsync(s.scratch, 0, sizeof(Scratch), stream) != cudaSuccess) {
+    cudaGetLastError();
+    return GRACE_NOALLOC_LAUNCH_FAILED;
+  }
   long long need = (n + kIter - 1) / kIter;
   int grid = (int)(need < (long long)s.max_grid ? need : (long long)s.max_grid);
   if (grid < 1) grid = 1;
@@ -211,7 +214,24 @@ extern "C" int grace_topk_select_noalloc(const float* x, long long n, int k, flo
   unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;
   void* params[] = {&x, &n, &uk, &values, &indices, &sc, &timeout_ns};
   if (cudaLaunchCooperativeKernel((const void*)topk_noalloc_kernel, dim3(grid), dim3(kBlock), params, 0, stream) !=
-      cudaSuccess)
+      cudaSuccess) {
+    cudaGetLastError();   // the refusal is reported through the return code; do not leave it for the caller's next check
     return GRACE_NOALLOC_LAUNCH_FAILED;
+  }
+  return GRACE_NOALLOC_OK;
+}
+
+extern "C" int grace_topk_noalloc_status(unsigned out[4], void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int dev = 0;
+  if (!out || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_setup[dev].ready)
+    return GRACE_NOALLOC_SETUP_FAILED;
+  // the address resolved at set-up; the host-side name g_scratch would be the wrong thing to copy from
+  const Scratch* sc = g_setup[dev].scratch;
+  if (cudaMemcpyAsync(out, sc->status, 4 * sizeof(unsigned), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess) {
+    cudaGetLastError();
+    return GRACE_NOALLOC_LAUNCH_FAILED;
+  }
   return GRACE_NOALLOC_OK;
 }

@@ -40,9 +40,26 @@ extern "C" {
 // that area and produce garbage: serialise them.
 //
 // Returns 0 when the work was enqueued, a negative GRACE_NOALLOC_* code
-// otherwise.  `stream` is a cudaStream_t (0 = default stream).  Completion and
-// asynchronous errors are observed through the stream as usual.
+// otherwise.  `stream` is a cudaStream_t (0 = default stream).  Completion is
+// observed through the stream as usual.  One failure is NOT a CUDA error and
+// does not show on the stream: the kernel's grid-wide barriers give up after
+// ten seconds (a co-resident grid that never assembles); the kernel then
+// records the fact in the status words of the work area, skips the rest of its
+// work and returns, leaving values / indices unwritten.  Read those words with
+// grace_topk_noalloc_status() before trusting the outputs of a call whose
+// latency looked wrong, or after every call if you can afford the stream
+// synchronisation.
 int grace_topk_select_noalloc(const float* x, long long n, int k, float* values, int* indices, void* stream);
+
+// Copies the four status words of the work area of the CURRENT device to
+// out[0..4) (host memory) after everything queued on `stream` so far has
+// finished: out[0] = 0 when the last grace_topk_select_noalloc call on this
+// device ran to completion, 1 when a grid barrier timed out (out[1] = index of
+// that barrier).  The next grace_topk_select_noalloc call clears the words, so
+// ask before issuing it.  Allocates nothing; blocks the calling thread until
+// `stream` is idle.  Returns 0, or GRACE_NOALLOC_SETUP_FAILED when no call has
+// set up this device yet, or GRACE_NOALLOC_LAUNCH_FAILED when the copy failed.
+int grace_topk_noalloc_status(unsigned out[4], void* stream);
 
 // Human-readable text for a return code of the function above.
 const char* grace_topk_noalloc_strerror(int code);
@@ -52,7 +69,7 @@ const char* grace_topk_noalloc_strerror(int code);
 #endif
 
 #define GRACE_NOALLOC_OK 0
-#define GRACE_NOALLOC_BAD_ARGUMENT (-1)   /* null pointer, k < 1, k > n, misaligned x */
+#define GRACE_NOALLOC_BAD_ARGUMENT (-1)   /* null pointer, k < 1, k > n, x not 16-byte aligned */
 #define GRACE_NOALLOC_TOO_LARGE (-2)      /* n beyond kGraceTopkNoallocMaxElems */
 #define GRACE_NOALLOC_SETUP_FAILED (-3)   /* cudaGetSymbolAddress / occupancy query failed */
 #define GRACE_NOALLOC_LAUNCH_FAILED (-4)  /* memset or kernel launch was refused */

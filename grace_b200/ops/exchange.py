@@ -144,14 +144,16 @@ class ExchangeChannel:
         self.seq += 1
         return self.seq
 
-    def max_grid(self, kind: str) -> int:
-        """Largest co-resident grid of a kernel family on this device (cached)."""
-        g = self._grids.get(kind)
+    def max_grid(self, kind: str, sm_limit: Optional[int] = None) -> int:
+        """Largest co-resident grid of a kernel family on this device (cached).  ``sm_limit`` overrides the
+        channel's own limit for one launch (a capped grid leaves SMs to the backward pass it overlaps with)."""
+        limit = self.sm_limit if sm_limit is None else int(sm_limit)
+        g = self._grids.get((kind, limit))
         if g is None:
             C = native()
             fn = C.sparse_max_grid if kind == "sparse" else C.quant_max_grid
-            g = fn(self.heap.device.index, self.sm_limit)
-            self._grids[kind] = g
+            g = fn(self.heap.device.index, limit)
+            self._grids[(kind, limit)] = g
         return g
 
     def tile_scratch(self, total: int):
@@ -161,7 +163,7 @@ class ExchangeChannel:
             dev = self.device
             self._tile = (total, (torch.zeros(tiles + 1, dtype=torch.int32, device=dev),
                                   torch.empty(tiles, dtype=torch.int32, device=dev),
-                                  torch.empty(self.max_grid("sparse"), dtype=torch.int32, device=dev)))
+                                  torch.empty(self.max_grid("sparse", 0), dtype=torch.int32, device=dev)))
         return self._tile[1]
 
     def slot_view(self, seq: int, numel: int, dtype, byte_offset: int = 0, rank: Optional[int] = None):

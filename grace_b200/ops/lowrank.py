@@ -153,7 +153,8 @@ class LowRankPlan:
         self.maps = torch.from_numpy(host.copy()).to(self.device)
         self._maps_key = key
 
-    def launch(self, g: torch.Tensor, out: torch.Tensor, part: int = 0, seq: Optional[int] = None) -> int:
+    def launch(self, g: torch.Tensor, out: torch.Tensor, part: int = 0, seq: Optional[int] = None,
+               sm_limit: Optional[int] = None) -> int:
         """Run the low-rank exchange of all matrices (``part`` 0 = everything)."""
         C = native()
         assert g.dtype == torch.float32 and g.data_ptr() % 16 == 0
@@ -161,7 +162,7 @@ class LowRankPlan:
         ch = self.channel
         if seq is None:
             seq = ch.next_seq()
-        grid = C.lowrank_max_grid(ch.heap.device.index, ch.sm_limit)
+        grid = C.lowrank_max_grid(ch.heap.device.index, ch.sm_limit if sm_limit is None else int(sm_limit))
         heap = ch.heap
         C.powersgd_exchange(
             g.data_ptr(), self.acc.data_ptr() if self.acc is not None else 0, out.data_ptr(), self.mats.data_ptr(),
@@ -173,7 +174,8 @@ class LowRankPlan:
         ch.post_status()
         return seq
 
-    def launch_dense(self, g: torch.Tensor, out: torch.Tensor, phases: int = PHASE_ALL, seq: Optional[int] = None):
+    def launch_dense(self, g: torch.Tensor, out: torch.Tensor, phases: int = PHASE_ALL, seq: Optional[int] = None,
+                     sm_limit: Optional[int] = None):
         """Uncompressed mean of the non-matrix tensors (one-shot all-gather-sum)."""
         if not self.dense:
             return None
@@ -181,7 +183,8 @@ class LowRankPlan:
             self.dense_stage.index_copy_(0, self.dense_dst, g.index_select(0, self.dense_src))
         seq = run_quant(self.dense_channel, self.dense_layout, self.dense_segs, self.dense_stage, None, None,
                         self.dense_stage, codec=CODEC["fp32"], beta=0.0, gamma=1.0, scale=1.0 / self.world,
-                        phases=phases, seq=seq)
+                        phases=phases, seq=seq,
+                        grid=None if sm_limit is None else self.dense_channel.max_grid("quant", sm_limit))
         if phases & PHASE_EXCHANGE:
             out.index_copy_(0, self.dense_src, self.dense_stage.index_select(0, self.dense_dst))
         return seq

@@ -4,8 +4,9 @@
 GRACE instead of all-reducing it.  GRACE compresses per *named parameter* (k,
 norms and residuals are per tensor), so the hook builds, once per bucket index,
 a segment table from ``bucket.parameters()`` and runs the fused exchange kernel
-over the bucket on a side stream; the returned future resolves to the bucket
-buffer holding the aggregated gradients.  With a library communicator (or on
+over the bucket on a high-priority side stream with a capped grid; the returned
+future is tied to that stream (it completes on the device, nobody waits on the
+host) and resolves to the bucket buffer holding the aggregated gradients.  With a library communicator (or on
 CPU) the hook falls back to ``grc.step`` per parameter.  DDP re-partitions its
 buckets once, after the first iteration; error-feedback state collected during
 that first iteration belongs to the old partition and is not carried over.
@@ -58,13 +59,13 @@ class GraceDDPHook:
 
     def __call__(self, state, bucket):  # returns torch.futures.Future[torch.Tensor]
         buf = bucket.buffer()
-        fut: torch.futures.Future = torch.futures.Future()
         fused = hasattr(self.grc, "step_flat") and buf.is_cuda and buf.dtype == torch.float32 \
             and getattr(self.grc, "_kind", None) in ("sparse", "quant", "powersgd")
         if not fused:
             for p, g in zip(bucket.parameters(), bucket.gradients()):
                 name = self.names.get(id(p), "param")
                 g.copy_(self.grc.step(g, name).view_as(g))
+            fut: torch.futures.Future = torch.futures.Future()
             fut.set_result(buf)
             return fut
         info = self._layout_for(bucket)
@@ -73,24 +74,31 @@ class GraceDDPHook:
             self._stream = torch.cuda.Stream(priority=-1)
         side = self._stream
         side.wait_stream(torch.cuda.current_stream())
+        # A device-aware future: set_result() records an event on the stream that is current at that moment (the
+        # side stream), and whoever consumes the future (DDP, when it finalises backward) makes ITS stream wait
+        # for that event.  Neither the host nor the backward stream blocks here, so the exchange of this bucket
+        # runs next to the backward kernels of the layers still to come.
+        fut = torch.futures.Future(devices=[buf.device])
+        limit = getattr(self.grc, "overlap_sms", None)
         with torch.cuda.stream(side):
             if info["aligned"] and buf.numel() == layout.total:
-                self.grc.step_flat(buf, layout)
+                self.grc.step_flat(buf, layout, sm_limit=limit)
             else:
-                # DDP packs tensors back to back: stage into an aligned buffer
+                # DDP packs tensors back to back; the kernels want every tensor on a 128-element boundary:
+                # one multi-tensor copy into an aligned staging buffer and one back
                 stage = self._staging.get(info["key"])
                 if stage is None:
-                    stage = torch.zeros(layout.total, dtype=torch.float32, device=buf.device)
-                    self._staging[info["key"]] = stage
-                for g, off, n in zip(bucket.gradients(), layout.offsets, layout.numels):
-                    stage[off:off + n].copy_(g.reshape(-1))
-                self.grc.step_flat(stage, layout)
-                for g, off, n in zip(bucket.gradients(), layout.offsets, layout.numels):
-                    g.copy_(stage[off:off + n].view_as(g))
-            ev = torch.cuda.Event()
-            ev.record(side)
-        torch.cuda.current_stream().wait_event(ev)
-        fut.set_result(buf)
+                    flat = torch.zeros(layout.total, dtype=torch.float32, device=buf.device)
+                    views = [flat[off:off + n] for off, n in zip(layout.offsets, layout.numels)]
+                    stage = self._staging[info["key"]] = (flat, views)
+                flat, views = stage
+                # every gradient is a dense block of the bucket buffer (whatever its strides): address it there
+                grads = [buf[off:off + n] for off, n in zip(info["offsets"], info["numels"])]
+                torch._foreach_copy_(views, grads)
+                self.grc.step_flat(flat, layout, sm_limit=limit)
+                torch._foreach_copy_(grads, views)
+            buf.record_stream(side)
+            fut.set_result(buf)
         return fut
 
 

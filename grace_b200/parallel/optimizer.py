@@ -1,34 +1,41 @@
 """Horovod-style ``DistributedOptimizer`` without Horovod.
 
-Contract reproduced from the reference's patched
-``horovod/torch/optimizer.py:35-277,451-519``:
+What a user of the reference's patched ``horovod/torch/optimizer.py:35-277,
+451-519`` relies on, and gets here:
 
-* the returned object is an instance of a dynamically created subclass of the
-  user's optimizer class (``state_dict`` is the wrapped optimizer's own);
-* names default to ``allreduce.noname.<i>``; tuples, duplicate names and
-  unnamed parameters are rejected;
-* a hook on every parameter's gradient accumulation decrements a per-parameter
-  delay counter (``backward_passes_per_step``) and, at zero, launches
-  ``grace.send_step(p.grad, name)`` so the exchange overlaps with the rest of
-  backward;
-* ``synchronize()`` launches what never fired, then
-  ``p.grad.set_(grace.receive_step(handle, ctx))``;
-* ``step()`` synchronises unless inside ``skip_synchronize()`` and warns on a
-  redundant ``synchronize()``; ``zero_grad()`` refuses to run with exchanges in
-  flight; ``load_state_dict`` and ``set_backward_passes_per_step`` reset the
-  counters.
+* ``DistributedOptimizer(opt, grace=grc, named_parameters=...)`` returns an
+  object whose class is a subclass of ``type(opt)`` carrying its name
+  (``state_dict`` is the wrapped optimizer's own);
+* parameters without a name are called ``allreduce.noname.<i>``; a
+  ``named_parameters`` that is not a sequence of pairs, repeats a name or
+  leaves a parameter out is rejected with ``ValueError``;
+* when a gradient has been accumulated ``backward_passes_per_step`` times the
+  exchange of that gradient starts, inside backward
+  (``grace.send_step(p.grad, name)``), and ``synchronize()`` finishes it
+  (``p.grad.set_(grace.receive_step(handle, ctx))``), also starting the
+  exchanges whose hook never ran;
+* ``step()`` synchronises first unless called under ``skip_synchronize()``,
+  and warns when ``synchronize()`` had already been called without it;
+* ``zero_grad()`` between ``backward()`` and ``step()`` raises;
+  ``load_state_dict`` and ``set_backward_passes_per_step`` re-arm the counters;
+* ``num_groups > 0`` or ``op != Average`` take GRACE out of the path
+  (plain all-reduce); with ``num_groups`` the parameters are split into that
+  many groups and each group is reduced by ONE all-reduce of its flattened
+  gradients, started when the last gradient of the group is ready.
 
-B200 additions: with ``flat=FlatParams(...)`` and a ``FusedExchange`` the hooks
-work per *bucket*: when the last gradient of a bucket has been accumulated the
-whole bucket is exchanged by one fused kernel on a high-priority side stream,
-and ``synchronize()`` only makes the compute stream wait for those launches.
-``grace=None`` gives a plain averaged all-reduce.
+How it is built here: every parameter has a ledger entry (name, countdown,
+in-flight ticket); the entries point to an optional *bucket* (a range of a
+``FlatParams`` buffer exchanged by one fused kernel) or *group* (plain
+all-reduce of several tensors at once).  Bucket exchanges run on a
+high-priority side stream with a capped grid while backward continues;
+``synchronize()`` only makes the compute stream wait for their events.
 """
 from __future__ import annotations
 
 import os
 import warnings
 from contextlib import contextmanager
+from typing import Dict, List, Optional
 
 import torch
 from torch import distributed as dist
@@ -40,188 +47,271 @@ def _world_size() -> int:
     return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
 
 
-class _DistributedOptimizer(torch.optim.Optimizer):
-    def __init__(self, params, named_parameters, grace, compression=None, backward_passes_per_step=1, op=Average,
-                 gradient_predivide_factor=1.0, num_groups=0, flat=None, always_hook=False):
-        super(self.__class__, self).__init__(params)
+class _Entry:
+    """Ledger line of one parameter."""
+
+    __slots__ = ("param", "name", "countdown", "ticket", "ctx", "armed", "group")
+
+    def __init__(self, param, name, passes):
+        self.param, self.name = param, name
+        self.countdown = passes      # backward passes left before the exchange starts
+        self.ticket = None           # what send_step / the plain all-reduce handed back
+        self.ctx = None
+        self.armed = False           # a backward pass touched this parameter since the last synchronize
+        self.group = None
+
+
+class _Group:
+    """Parameters whose gradients travel in one plain all-reduce (``num_groups``)."""
+
+    def __init__(self, index: int, entries: List[_Entry]):
+        self.index, self.entries = index, entries
+        self.waiting = len(entries)
+        self.flat = None
+        self.work = None
+
+    def rearm(self):
+        self.waiting, self.flat, self.work = len(self.entries), None, None
+
+
+def _validated_names(param_groups, named_parameters) -> List[tuple]:
+    """(name, parameter) pairs for every parameter of the optimizer, or ValueError."""
+    params = [p for g in param_groups for p in g["params"]]
+    if named_parameters is None:
+        pairs = []
+        for g in param_groups:
+            pairs.extend(("allreduce.noname.%s" % i, p) for i, p in enumerate(g["params"]))
+        return pairs
+    pairs = list(named_parameters)
+    if not all(isinstance(kv, tuple) for kv in pairs):
+        raise ValueError("named_parameters should be a sequence of tuples (name, parameter), "
+                         "usually produced by model.named_parameters().")
+    repeated = _DistributedMixin.find_duplicates([k for k, _ in pairs])
+    if repeated:
+        raise ValueError("Parameter names in named_parameters must be unique. Found duplicates: %s"
+                         % ", ".join(sorted(repeated)))
+    covered = {id(p) for _, p in pairs}
+    missing = [str(id(p)) for p in params if id(p) not in covered]
+    if missing:
+        raise ValueError("named_parameters was specified, but one or more model parameters were not named. "
+                         "Python object ids: %s" % ", ".join(missing))
+    return pairs
+
+
+class _DistributedMixin:
+    """Methods mixed in front of the user's optimizer class (see ``DistributedOptimizer``)."""
+
+    # ---- set-up --------------------------------------------------------------
+    def _grace_setup(self, named_parameters, grace, compression, backward_passes_per_step, op,
+                     gradient_predivide_factor, num_groups, flat, always_hook):
         self._grace = grace
         self._compression = compression
-        if named_parameters is not None:
-            named_parameters = list(named_parameters)
-        else:
-            named_parameters = [("allreduce.noname.%s" % i, v)
-                                for group in self.param_groups for i, v in enumerate(group["params"])]
-        if any(not isinstance(p, tuple) for p in named_parameters):
-            raise ValueError("named_parameters should be a sequence of tuples (name, parameter), "
-                             "usually produced by model.named_parameters().")
-        dups = self.find_duplicates([k for k, _ in named_parameters])
-        if dups:
-            raise ValueError("Parameter names in named_parameters must be unique. Found duplicates: %s"
-                             % ", ".join(sorted(dups)))
-        all_ids = {id(v) for group in self.param_groups for v in group["params"]}
-        named_ids = {id(v) for _, v in named_parameters}
-        unnamed = all_ids - named_ids
-        if unnamed:
-            raise ValueError("named_parameters was specified, but one or more model parameters were not named. "
-                             "Python object ids: %s" % ", ".join(str(i) for i in unnamed))
-        ordered = sorted(named_parameters, key=lambda kv: kv[0])
-        self._parameter_names = {v: k for k, v in ordered}
         self.backward_passes_per_step = backward_passes_per_step
-        self._allreduce_delay = {v: backward_passes_per_step for _, v in ordered}
         self.op = op
         self.gradient_predivide_factor = gradient_predivide_factor
-        self._num_groups = num_groups
-        self._handles = {}
-        self._grad_accs = []
-        self._requires_update = set()
-        self._synchronized = False
-        self._should_synchronize = True
+        self._num_groups = int(num_groups)
         self._flat = flat
+        self._ledger: Dict[torch.nn.Parameter, _Entry] = {}
+        for name, p in sorted(_validated_names(self.param_groups, named_parameters), key=lambda kv: kv[0]):
+            self._ledger[p] = _Entry(p, name, backward_passes_per_step)
+        self._groups: List[_Group] = []
         self._bucket_events = {}
         self._side_stream = None
-        if _world_size() > 1 or always_hook or os.environ.get("GRACE_ELASTIC") == "1":
-            self._register_hooks()
-
-    # -- bookkeeping --------------------------------------------------------
-    @staticmethod
-    def find_duplicates(lst):
-        seen, dups = set(), set()
-        for el in lst:
-            if el in seen:
-                dups.add(el)
-            seen.add(el)
-        return dups
-
-    def load_state_dict(self, *args, **kwargs):
-        self._handles = {}
+        self._hook_handles = []
         self._synchronized = False
         self._should_synchronize = True
-        for p in self._allreduce_delay:
-            self._allreduce_delay[p] = self.backward_passes_per_step
-        super(self.__class__, self).load_state_dict(*args, **kwargs)
+        self._in_flight = False       # a backward pass ran since the last synchronize
+        if _world_size() > 1 or always_hook or os.environ.get("GRACE_ELASTIC") == "1":
+            self._install_hooks()
 
-    def set_backward_passes_per_step(self, passes):
-        self.backward_passes_per_step = passes
-        for p in self._allreduce_delay:
-            self._allreduce_delay[p] = passes
+    @property
+    def _parameter_names(self):
+        return {p: e.name for p, e in self._ledger.items()}
 
-    # -- hooks ----------------------------------------------------------------
-    def _register_hooks(self):
-        for group in self.param_groups:
-            for p in group["params"]:
-                if not p.requires_grad:
-                    continue
-                if p.grad is None:
-                    p.grad = torch.zeros_like(p)
-                self._requires_update.add(p)
-                if hasattr(p, "register_post_accumulate_grad_hook"):
-                    self._grad_accs.append(p.register_post_accumulate_grad_hook(self._make_hook(p)))
-                else:  # older torch: hook the AccumulateGrad node as Horovod does
-                    acc = p.expand_as(p).grad_fn.next_functions[0][0]
-                    acc.register_hook(self._make_hook(p))
-                    self._grad_accs.append(acc)
+    @staticmethod
+    def find_duplicates(lst):
+        counts: Dict[object, int] = {}
+        for item in lst:
+            counts[item] = counts.get(item, 0) + 1
+        return {item for item, c in counts.items() if c > 1}
+
+    def _uses_grace(self) -> bool:
+        return self._grace is not None and self._num_groups == 0 and self.op == Average
+
+    def _bucketed(self) -> bool:
+        return (self._uses_grace() and self._flat is not None and hasattr(self._grace, "step_flat")
+                and self._flat.flat_g.is_cuda)
+
+    def _trainable(self) -> List[torch.nn.Parameter]:
+        return [p for g in self.param_groups for p in g["params"] if p.requires_grad]
+
+    def _install_hooks(self):
+        trainable = self._trainable()
+        for p in trainable:
+            if p.grad is None:
+                p.grad = torch.zeros_like(p)
+            if hasattr(p, "register_post_accumulate_grad_hook"):
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._on_gradient))
+            else:   # older torch: the AccumulateGrad node itself
+                node = p.expand_as(p).grad_fn.next_functions[0][0]
+                node.register_hook(lambda *_, _p=p: self._on_gradient(_p))
+                self._hook_handles.append(node)
+        if self._num_groups > 0:
+            # the same split on every rank: by name, into num_groups runs of (nearly) equal length
+            ordered = sorted(trainable, key=lambda p: self._ledger[p].name)
+            n, g = len(ordered), max(1, min(self._num_groups, len(ordered)))
+            cuts = [round(i * n / g) for i in range(g + 1)]
+            for i in range(g):
+                entries = [self._ledger[p] for p in ordered[cuts[i]:cuts[i + 1]]]
+                if entries:
+                    grp = _Group(len(self._groups), entries)
+                    for e in entries:
+                        e.group = grp
+                    self._groups.append(grp)
         if self._bucketed():
             for b in self._flat.buckets:
                 b.pending = len(b.layout.names)
+            if hasattr(self._grace, "prepare_layouts"):
+                self._grace.prepare_layouts([b.layout for b in self._flat.buckets], self._flat.flat_g.device)
+        elif self._uses_grace() and hasattr(self._grace, "prepare"):
+            # plans (symmetric memory, flags) exist before the first backward pass fires any hook
+            self._grace.prepare([(self._ledger[p].name, p.grad) for p in trainable if p.grad is not None])
 
-    def _bucketed(self) -> bool:
-        return self._flat is not None and hasattr(self._grace, "step_flat") and self._flat.flat_g.is_cuda
+    # ---- re-arming -------------------------------------------------------------
+    def _rearm(self, entries=None):
+        for e in (self._ledger.values() if entries is None else entries):
+            e.countdown, e.ticket, e.ctx, e.armed = self.backward_passes_per_step, None, None, False
 
+    def load_state_dict(self, *args, **kwargs):
+        self._rearm()
+        for grp in self._groups:
+            grp.rearm()
+        self._in_flight = False
+        self._synchronized = False
+        self._should_synchronize = True
+        super().load_state_dict(*args, **kwargs)
+
+    def set_backward_passes_per_step(self, passes):
+        self.backward_passes_per_step = passes
+        for e in self._ledger.values():
+            e.countdown = passes
+
+    # ---- launches ----------------------------------------------------------------
     def _comm_stream(self):
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream(priority=-1)
         return self._side_stream
 
-    def _launch_bucket(self, bucket):
+    def _launch_bucket(self, bucket, overlapped: bool):
+        """One fused exchange for the whole bucket, on the side stream.  ``overlapped``: backward is still
+        running, so the kernel takes a capped share of the SMs (``grace.overlap_sms``)."""
         side = self._comm_stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             g = self._flat.grad_view(bucket)
             if self.gradient_predivide_factor != 1.0:
                 g.div_(self.gradient_predivide_factor)
-            self._grace.step_flat(g, bucket.layout)
+            limit = getattr(self._grace, "overlap_sms", None) if overlapped else None
+            if limit is not None:
+                self._grace.step_flat(g, bucket.layout, sm_limit=limit)
+            else:
+                self._grace.step_flat(g, bucket.layout)
             ev = torch.cuda.Event()
             ev.record(side)
         self._bucket_events[bucket.index] = ev
 
-    def _allreduce_grad_async(self, p):
-        name = self._parameter_names.get(p)
-        tensor = p.grad
-        if self._grace is not None and self._num_groups == 0 and self.op == Average:
-            return self._grace.send_step(tensor, name)
-        work = None
-        wire_ctx = None
+    def _plain_allreduce(self, tensor):
+        """(tensor on the wire, work, wire context) of an averaged / summed all-reduce without GRACE."""
+        work = wire_ctx = None
         if _world_size() > 1:
             if self.op == Average:
                 tensor.div_(_world_size())
             if self._compression is not None:      # Horovod's wire-format compression (none / fp16)
                 tensor, wire_ctx = self._compression.compress(tensor)
             work = dist.all_reduce(tensor, async_op=True)
-        return ("plain", tensor, work), wire_ctx
+        return tensor, work, wire_ctx
 
-    def _make_hook(self, p):
-        def hook(*ignore):
-            if p in self._handles and self._handles[p][0] is not None:
-                if self._allreduce_delay[p] <= 0:
-                    raise AssertionError(
-                        "Gradients were computed more than backward_passes_per_step times before call to step(). "
-                        "Increase backward_passes_per_step to accumulate gradients locally.")
-            assert not p.grad.requires_grad
-            assert self._allreduce_delay[p] > 0
-            handle, ctx = None, None
-            self._allreduce_delay[p] -= 1
-            if self._allreduce_delay[p] == 0:
-                if self._bucketed():
-                    bucket = self._flat.bucket_of[self._parameter_names[p]]
-                    bucket.pending -= 1
-                    handle = ("bucket", bucket.index)
-                    if bucket.pending == 0:
-                        self._launch_bucket(bucket)
-                else:
-                    handle, ctx = self._allreduce_grad_async(p)
-            self._handles[p] = (handle, ctx)
+    def _launch_entry(self, e: _Entry):
+        if self._uses_grace():
+            e.ticket, e.ctx = self._grace.send_step(e.param.grad, e.name)
+            return
+        if e.group is not None:
+            grp = e.group
+            grp.waiting -= 1
+            e.ticket = ("group", grp.index)
+            if grp.waiting == 0:
+                grp.flat = torch._utils._flatten_dense_tensors([x.param.grad for x in grp.entries])
+                grp.flat, grp.work, _ = self._plain_allreduce(grp.flat)
+            return
+        tensor, work, wire_ctx = self._plain_allreduce(e.param.grad)
+        e.ticket, e.ctx = ("plain", tensor, work), wire_ctx
 
-        return hook
-
-    # -- synchronisation --------------------------------------------------------
-    def synchronize(self):
-        missing = self._requires_update - set(self._handles.keys())
+    def _on_gradient(self, p):
+        e = self._ledger[p]
+        if e.ticket is not None and e.countdown <= 0:
+            raise AssertionError(
+                "Gradients were computed more than backward_passes_per_step times before call to step(). "
+                "Increase backward_passes_per_step to accumulate gradients locally.")
+        assert not p.grad.requires_grad
+        e.armed = True
+        self._in_flight = True
+        e.countdown -= 1
+        if e.countdown != 0:
+            return
         if self._bucketed():
-            for p in missing:
-                self._handles[p] = (("bucket", self._flat.bucket_of[self._parameter_names[p]].index), None)
+            bucket = self._flat.bucket_of[e.name]
+            bucket.pending -= 1
+            e.ticket = ("bucket", bucket.index)
+            if bucket.pending == 0:
+                self._launch_bucket(bucket, overlapped=True)
+        else:
+            self._launch_entry(e)
+
+    # ---- synchronisation ---------------------------------------------------------------
+    def synchronize(self):
+        entries = [self._ledger[p] for p in self._trainable() if p in self._ledger]
+        if self._bucketed():
             for b in self._flat.buckets:
                 if b.index not in self._bucket_events:
-                    self._launch_bucket(b)
+                    self._launch_bucket(b, overlapped=False)   # backward is over: nothing left to share the SMs with
             cur = torch.cuda.current_stream()
             for ev in self._bucket_events.values():
                 cur.wait_event(ev)
             self._bucket_events.clear()
             for b in self._flat.buckets:
                 b.pending = len(b.layout.names)
-            for p in self._handles:
-                self._allreduce_delay[p] = self.backward_passes_per_step
-            self._handles.clear()
-            self._synchronized = True
-            return
-        for p in missing:
-            self._handles[p] = self._allreduce_grad_async(p)
-        for p, (handle, ctx) in list(self._handles.items()):
-            if handle is None:
-                self._handles[p] = self._allreduce_grad_async(p)
-        for p, (handle, ctx) in self._handles.items():
-            if isinstance(handle, tuple) and len(handle) == 3 and handle[0] == "plain":
-                _, tensor, work = handle
-                if work is not None:
-                    work.wait()
-                output = tensor
-                if self._compression is not None and work is not None:
-                    output = self._compression.decompress(tensor, ctx)
-            else:
-                output = self._grace.receive_step(handle, ctx)
-            self._allreduce_delay[p] = self.backward_passes_per_step
-            if output.data_ptr() != p.grad.data_ptr():
-                p.grad.set_(output.to(p.grad.dtype).view(p.grad.shape))
-        self._handles.clear()
+        else:
+            for e in entries:
+                if e.ticket is None:     # hook never ran, or the countdown has not reached zero yet
+                    self._launch_entry(e)
+            for grp in self._groups:
+                if grp.work is not None:
+                    grp.work.wait()
+                if grp.flat is not None:
+                    flat = grp.flat
+                    if self._compression is not None and grp.work is not None:
+                        flat = self._compression.decompress(flat, None)
+                    grads = [x.param.grad for x in grp.entries]
+                    for g, piece in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                        g.copy_(piece)
+                grp.rearm()
+            for e in entries:
+                t = e.ticket
+                if isinstance(t, tuple) and t and t[0] == "group":
+                    continue
+                if isinstance(t, tuple) and len(t) == 3 and t[0] == "plain":
+                    _, tensor, work = t
+                    if work is not None:
+                        work.wait()
+                    output = tensor
+                    if self._compression is not None and work is not None:
+                        output = self._compression.decompress(tensor, e.ctx)
+                else:
+                    output = self._grace.receive_step(t, e.ctx)
+                if output.data_ptr() != e.param.grad.data_ptr():
+                    e.param.grad.set_(output.to(e.param.grad.dtype).view(e.param.grad.shape))
+        self._rearm(entries)
+        self._in_flight = False
         self._synchronized = True
 
     @contextmanager
@@ -240,40 +330,35 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                               "using optimizer.skip_synchronize() context if you use optimizer.synchronize() in your code.")
             self.synchronize()
         self._synchronized = False
-        return super(self.__class__, self).step(closure)
+        return super().step(closure)
 
     def zero_grad(self, *args, **kwargs):
-        if self._handles:
+        if self._in_flight:
             raise AssertionError("optimizer.zero_grad() was called after loss.backward() but before optimizer.step() "
                                  "or optimizer.synchronize(). This is prohibited as it can cause a race condition.")
-        if self._flat is not None or self._grad_accs:
+        if self._flat is not None or self._hook_handles:
             kwargs["set_to_none"] = False  # gradients are exchanged in place; keep their storage
             args = ()
-        return super(self.__class__, self).zero_grad(*args, **kwargs)
+        return super().zero_grad(*args, **kwargs)
 
 
 def DistributedOptimizer(optimizer, grace=None, named_parameters=None, compression=None, backward_passes_per_step=1,
                          op=Average, gradient_predivide_factor=1.0, num_groups=0, flat=None, always_hook=False):
     """Wrap ``optimizer`` so that gradients are exchanged through ``grace``.
 
-    Mirrors ``hvd.DistributedOptimizer(optimizer, grace=..., named_parameters=...)``
-    of the reference (``patch_files/horovod/torch/optimizer.py:451-519``).
-    ``num_groups > 0`` and ``op != Average`` bypass ``grace`` exactly as there.
+    Same call as ``hvd.DistributedOptimizer(optimizer, grace=..., named_parameters=...)`` of the reference
+    (``patch_files/horovod/torch/optimizer.py:451-519``).  The result shares the wrapped optimizer's parameter
+    groups, state and every attribute it had set up (flat buffers and momentum of ``FusedSGD``, ...).
+    ``flat=FlatParams(...)`` with a ``FusedExchange`` switches to bucket-wise exchanges.
     """
     if gradient_predivide_factor != 1.0 and op != Average:
         raise ValueError("gradient_predivide_factor not supported with op != Average")
-    cls = type(optimizer.__class__.__name__, (optimizer.__class__,), dict(_DistributedOptimizer.__dict__))
+    base = optimizer.__class__
+    cls = type(base.__name__, (_DistributedMixin, base), {})
+    obj = cls.__new__(cls)
+    obj.__dict__.update(optimizer.__dict__)
     if flat is None:
         flat = getattr(optimizer, "flat", None)
-    obj = cls.__new__(cls)
-    cls.__init__(obj, optimizer.param_groups, named_parameters, grace, compression, backward_passes_per_step, op,
-                 gradient_predivide_factor, num_groups, flat, always_hook)
-    # keep what the wrapped optimizer had already set up (per-parameter state, flat buffers and
-    # momentum of FusedSGD, ...): everything except what this wrapper itself owns
-    own = {"param_groups", "defaults", "_grace", "_compression", "_parameter_names", "backward_passes_per_step",
-           "_allreduce_delay", "op", "gradient_predivide_factor", "_num_groups", "_handles", "_grad_accs",
-           "_requires_update", "_synchronized", "_should_synchronize", "_flat", "_bucket_events", "_side_stream"}
-    for key, value in optimizer.__dict__.items():
-        if key not in own and not key.startswith("_optimizer_") and not key.startswith("_zero_grad_profile"):
-            obj.__dict__[key] = value
+    obj._grace_setup(named_parameters, grace, compression, backward_passes_per_step, op, gradient_predivide_factor,
+                     num_groups, flat, always_hook)
     return obj

@@ -138,6 +138,17 @@ class SymmetricHeap:
     def free_bytes(self) -> int:
         return self.nbytes - self._cursor
 
+    def carve(self, nbytes: int) -> "SymmetricHeap":
+        """Sub-heap of ``nbytes`` inside this heap: same mappings, own bump allocator, frees nothing.
+
+        Every rank must carve in the same order (the offset is part of the address every peer computes).
+        Raises ``MemoryError`` when the parent has no room left."""
+        nbytes = (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        off = self.alloc(nbytes)
+        child = SymmetricHeap(nbytes, self.rank, self.world, self.device, [b + off for b in self.bases], [], [])
+        child._parent = self          # keeps the mapping alive for as long as the child is in use
+        return child
+
     # -- teardown ---------------------------------------------------------
     @staticmethod
     def _release(owned, imported):

@@ -57,6 +57,40 @@ class HeartbeatMonitor:
         return dead
 
 
+class ErrorBoard:
+    """Agreement about failures through the process group's store (host side only, no collective).
+
+    A bounded wait that expires is seen by ONE rank; its peers may have finished the same exchange without a
+    complaint.  ``vote`` lets every rank learn, at a step boundary, whether any rank failed, so that all of them
+    recover together; ``barrier`` is the re-rendezvous after the reset.  Keys carry an epoch number, so the
+    records of an earlier recovery are never read again.  (The reference has only the 20 s process-group
+    timeout of ``examples/dist/CIFAR10-dawndist/core.py:225-226``.)"""
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "grace/error"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+        self._votes = 0   # votes are numbered: every rank calls vote() the same number of times
+
+    def _wait(self, keys, timeout_s: float):
+        from datetime import timedelta
+
+        self.store.wait(list(keys), timedelta(seconds=timeout_s))
+
+    def vote(self, epoch: int, failed: bool, timeout_s: float = 30.0, info: str = "") -> List[int]:
+        """Post this rank's verdict, wait for all others, return the ranks that failed (sorted)."""
+        self._votes += 1
+        base = "%s/%d/vote%d" % (self.prefix, epoch, self._votes)
+        self.store.set("%s/%d" % (base, self.rank), ("1" + info) if failed else "0")
+        keys = ["%s/%d" % (base, r) for r in range(self.world)]
+        self._wait(keys, timeout_s)
+        return [r for r, k in enumerate(keys) if self.store.get(k).decode()[:1] == "1"]
+
+    def barrier(self, epoch: int, timeout_s: float = 30.0, tag: str = "") -> None:
+        """Every rank sets its key and waits for all W keys of this epoch (and ``tag``)."""
+        base = "%s/%d/barrier%s" % (self.prefix, epoch, tag)
+        self.store.set("%s/%d" % (base, self.rank), "1")
+        self._wait(["%s/%d" % (base, r) for r in range(self.world)], timeout_s)
+
+
 @dataclass
 class FaultPlan:
     """``action:rankR:stepS`` from the ``GRACE_FAULT`` environment variable."""

@@ -299,3 +299,71 @@ def test_horovod_surface_helpers():
         assert r["join"] in (0, 1) and r["join"] == res[0]["join"]
         assert abs(r["bobj"] - 0.2) < 1e-12 and r["gobj"] == [0, 10] and abs(r["metric"] - 0.5) < 1e-12
         assert r["fp16_wire"] == (True, True)
+
+
+def _num_groups(rank, world):
+    """num_groups bypasses GRACE and reduces each group of parameters with ONE all-reduce."""
+    from grace_b200.parallel import DistributedOptimizer
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.ReLU(), torch.nn.Linear(5, 4), torch.nn.Linear(4, 2))
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)
+
+    class Boom:   # must never be touched when num_groups > 0
+        def send_step(self, *a):
+            raise AssertionError("GRACE used although num_groups > 0")
+
+    calls = []
+    real = dist.all_reduce
+
+    def counting(t, *a, **k):
+        calls.append(t.numel())
+        return real(t, *a, **k)
+
+    dist.all_reduce = counting
+    try:
+        d = DistributedOptimizer(opt, grace=Boom(), named_parameters=model.named_parameters(), num_groups=2)
+        g = torch.Generator().manual_seed(rank)
+        x = torch.randn(7, 6, generator=g)
+        model(x).sum().backward()
+        local = [p.grad.clone() for p in model.parameters()]
+        d.step()
+    finally:
+        dist.all_reduce = real
+    gathered = [None] * world
+    dist.all_gather_object(gathered, local)
+    mean = [sum(gs) / world for gs in zip(*gathered)]
+    for p, m in zip(model.parameters(), mean):
+        torch.testing.assert_close(p.grad, m)
+    return sorted(calls)
+
+
+def test_num_groups_reduces_group_wise():
+    res = _run(_num_groups, 2)
+    total = 6 * 5 + 5 + 5 * 4 + 4 + 4 * 2 + 2
+    assert len(res[0]) == 2 and sum(res[0]) == total   # two all-reduces cover all six tensors
+    assert res[0] == res[1]
+
+
+def _agree_and_recover(rank, world):
+    """A failure seen by one rank becomes known to all through the store; all recover, then exchange again."""
+    from grace_b200 import grace_from_params
+
+    store = dist.distributed_c10d._get_default_store()
+    grc = grace_from_params({"compressor": "fp16", "memory": "none", "communicator": "allgather",
+                             "world_size": world, "fused": True})
+    grc.store = store
+    x = torch.full((16,), float(rank + 1))
+    first = grc.step(x.clone(), "w")                     # CPU tensors: the library path carries the data
+    failed = grc.agree(RuntimeError("injected on the host") if rank == 1 else None, timeout_s=20)
+    assert failed == [1], failed
+    grc.recover(timeout_s=20)
+    assert grc.agree(None, timeout_s=20) == []           # a second vote in the new epoch: all healthy
+    again = grc.step(x.clone(), "w2")
+    return first.tolist(), again.tolist()
+
+
+def test_failed_rank_is_agreed_on_and_recovered():
+    res = _run(_agree_and_recover, 2)
+    assert res[0] == res[1]
+    assert res[0][1] == [1.5] * 16    # healthy exchange after the recovery: mean of 1 and 2

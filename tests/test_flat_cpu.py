@@ -1,4 +1,5 @@
 """Flat layouts, buckets and the flat SGD path on CPU tensors."""
+import pytest
 import torch
 
 from grace_b200.ops.exchange import ALIGN_ELEMS, FlatLayout
@@ -104,3 +105,31 @@ def test_flat_params_adopt_an_external_gradient_buffer():
     # a callable may decline (no multicast on this machine): the ordinary buffer is used
     fp2 = FlatParams(torch.nn.Linear(6, 5).named_parameters(), grad_buffer=lambda n: None)
     assert fp2.flat_g.numel() == fp2.layout.total
+
+
+def test_symmetric_heap_carving_shares_one_allocation():
+    """Plans take ranges of one arena heap: offsets are identical on every rank and nothing is allocated per plan."""
+    from grace_b200.communicator.fused import _Arena
+    from grace_b200.parallel.symm import SymmetricHeap
+
+    created = []
+
+    def create(nbytes):   # stands in for cudaMalloc + handle exchange: two "ranks" with fake base addresses
+        heap = SymmetricHeap(nbytes, 0, 2, torch.device("cpu"), [0x10000000, 0x20000000], [], [])
+        created.append(heap)
+        return heap
+
+    arena = _Arena(create, default_bytes=1 << 20)
+    subs = [arena.carve(1000 + 8 * i) for i in range(100)]
+    assert len(created) == 1                                   # 100 layouts, one heap
+    offs = [s.bases[0] - 0x10000000 for s in subs]
+    assert offs == sorted(offs) and len(set(offs)) == 100
+    assert all(s.bases[1] - 0x20000000 == o and o % 256 == 0 for s, o in zip(subs, offs))
+    a = subs[3].alloc(128)
+    b = subs[3].alloc(128)
+    assert a == 0 and b == 256
+    with pytest.raises(MemoryError):
+        subs[3].alloc(4096)
+    big = arena.carve(4 << 20)                                 # does not fit: the arena grows by one heap
+    assert len(created) == 2 and big.nbytes >= 4 << 20
+    arena.close()

@@ -28,7 +28,16 @@ def _lib():
     fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.grace_topk_noalloc_strerror.restype = ctypes.c_char_p
     lib.grace_topk_noalloc_strerror.argtypes = [ctypes.c_int]
+    lib.grace_topk_noalloc_status.restype = ctypes.c_int
+    lib.grace_topk_noalloc_status.argtypes = [ctypes.POINTER(ctypes.c_uint), ctypes.c_void_p]
     return lib
+
+
+def _status(lib):
+    words = (ctypes.c_uint * 4)()
+    rc = lib.grace_topk_noalloc_status(words, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.grace_topk_noalloc_strerror(rc)
+    return list(words)
 
 
 def _call(lib, x, k):
@@ -49,15 +58,44 @@ def test_no_alloc_topk_matches_regular_entry_point_twice():
     # two calls in a row share the static work area: different sizes and k on purpose
     for n, k in ((1_000_003, 10_000), (70_001, 700), (130, 130)):
         x = (torch.randn(n, generator=gen) * 1e-3).to(dev)
-        before = torch.cuda.memory_allocated()
         vals, idx = _call(lib, x, k)
         torch.cuda.synchronize()
+        assert _status(lib) == [0, 0, 0, 0]     # the kernel ran to completion: no barrier gave up
         ref_vals, ref_idx = topk_select(x, k)
         order, ref_order = idx.long().argsort(), ref_idx.long().argsort()
         assert torch.equal(idx.long()[order], ref_idx.long()[ref_order])
         assert torch.equal(vals[order], ref_vals[ref_order])
         assert torch.equal(vals, x[idx.long()])
-        del before
+
+
+def test_no_alloc_topk_allocates_nothing():
+    """With the outputs allocated beforehand, a call changes neither the device's free memory (cudaMalloc by
+    anyone in the process) nor the caching allocator's books (an allocation through torch)."""
+    lib = _lib()
+    x = torch.randn(300_000, device="cuda")
+    vals = torch.empty(3000, dtype=torch.float32, device="cuda")
+    idx = torch.empty(3000, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.grace_topk_select_noalloc(x.data_ptr(), x.numel(), 3000, vals.data_ptr(), idx.data_ptr(), stream)
+        assert rc == 0, lib.grace_topk_noalloc_strerror(rc)
+
+    call()                      # first call on the device: address look-up, kernel image load
+    _status(lib)                # and the first status read-back
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    stats0 = torch.cuda.memory_stats()
+    call()
+    call()
+    torch.cuda.synchronize()
+    assert _status(lib) == [0, 0, 0, 0]
+    stats1 = torch.cuda.memory_stats()
+    assert torch.cuda.mem_get_info()[0] == free0
+    for key in ("allocation.all.allocated", "segment.all.allocated", "allocated_bytes.all.current",
+                "reserved_bytes.all.current"):
+        assert stats1[key] == stats0[key], key
+    assert torch.equal(vals, x[idx.long()])
 
 
 def test_no_alloc_topk_rejects_bad_sizes():
@@ -70,3 +108,5 @@ def test_no_alloc_topk_rejects_bad_sizes():
     assert lib.grace_topk_select_noalloc(x.data_ptr(), 1024, 0, out_v.data_ptr(), out_i.data_ptr(), None) == -1
     assert lib.grace_topk_select_noalloc(x.data_ptr(), 4, 8, out_v.data_ptr(), out_i.data_ptr(), None) == -1
     assert lib.grace_topk_select_noalloc(None, 1024, 8, out_v.data_ptr(), out_i.data_ptr(), None) == -1
+    misaligned = lib.grace_topk_select_noalloc(x.data_ptr() + 4, 1000, 8, out_v.data_ptr(), out_i.data_ptr(), None)
+    assert misaligned == -1 and b"16-byte aligned" in lib.grace_topk_noalloc_strerror(misaligned)
