@@ -51,56 +51,17 @@ CONFIGS = {
 
 
 # ----------------------------------------------------------------------------- clocks
-class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+def _load_clock_sampler():
+    # the sampler lives in the package, but is loaded by file so that the reference arm imports nothing else of it
+    import importlib.util
 
-    def __init__(self, device_index: int):
-        self.device_index = device_index
-        self.proc = None
-        self.path = None
+    spec = importlib.util.spec_from_file_location("_grace_clocks", os.path.join(ROOT, "grace_b200", "utils", "clocks.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.ClockSampler
 
-    def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "200",
-                 "-i", str(self.device_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
 
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        try:
-            self.proc.terminate()
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
-        try:
-            rows = [r.strip().split(", ") for r in open(self.path).read().strip().splitlines() if r.strip()]
-            sm = [float(r[1]) for r in rows if len(r) >= 9]
-            reasons = set()
-            for r in rows:
-                if len(r) < 9:
-                    continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                    if val.strip().lower().startswith("active"):
-                        reasons.add(name)
-            if sm:
-                out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
-                       "samples": len(sm)}
-        except Exception:
-            pass
-        finally:
-            try:
-                os.unlink(self.path)
-            except Exception:
-                pass
-        return out
+ClockSampler = _load_clock_sampler()   # read-only nvidia-smi sampling during the timed region
 
 
 # ----------------------------------------------------------------------------- data

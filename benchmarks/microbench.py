@@ -100,6 +100,9 @@ def main():
     ap.add_argument("--cases", default=",".join(CASES))
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--min-iters", type=int, default=5,
+                    help="timed iterations for sizes of 16 Mi elements and more (keeps the clock sampler busy long "
+                         "enough to see the GPU under load)")
     ap.add_argument("--impl", default="ours", choices=["ours", "library", "reference"])
     ap.add_argument("--virtual-ranks", type=int, default=0,
                     help="one GPU only: run W ranks of the fused exchange on this GPU, phase by phase (all ranks "
@@ -119,6 +122,13 @@ def main():
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     bw, bw_src = hbm_gbs()
     flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    from grace_b200.utils.clocks import ClockSampler
+
+    import time
+
+    sampler = ClockSampler(local, period_ms=100)   # one sampler for the run; every line gets the samples of its window
+    if rank == 0:
+        sampler.start()
 
     if args.impl == "reference":
         for mod in [m for m in sys.modules if m.startswith("grace_dl")]:
@@ -198,8 +208,9 @@ def main():
             resident = None
             if case.endswith("_inplace") and args.impl == "ours" and hasattr(grc, "buffer"):
                 resident = grc.buffer(n)
+            t_case = time.time()
             try:
-                for it in range(args.warmup + args.iters):
+                for it in range(args.warmup + max(args.iters, args.min_iters if size_m >= 16 else args.iters)):
                     g = base.clone() if resident is None else resident.copy_(base)
                     vg = [b.clone() for b in vbase]
                     flush.fill_(float(it))
@@ -222,6 +233,7 @@ def main():
                     print(json.dumps({"case": case, "impl": args.impl, "size_m": size_m,
                                       "error": "%s: %s" % (type(e).__name__, str(e).splitlines()[0][:160])}))
                 continue
+            clocks = sampler.summary(t_case, time.time()) if rank == 0 else None
             t = torch.tensor([sorted(times)[len(times) // 2]], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t) / (vranks or 1)
@@ -229,7 +241,8 @@ def main():
             row = {"case": case, "impl": args.impl, "size_m": size_m, "n_gpus": world, "ms": round(ms, 4),
                    "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / ms, 3) if args.impl == "ours" else None,
                    "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
-                   "timing": "cuda events, median of %d, max over ranks, L2 flushed" % args.iters}
+                   "timing": "cuda events, median of %d, max over ranks, L2 flushed" % len(times),
+                   "clocks": clocks}
             if vranks:
                 row["virtual_ranks"] = vranks
                 row["timing"] += "; %d ranks emulated on one GPU phase by phase, time of all ranks / %d" % (vranks, vranks)
@@ -238,6 +251,8 @@ def main():
                 print(json.dumps(row), flush=True)
             del grc, base, out, g, vbase, vg
             torch.cuda.empty_cache()
+    if rank == 0:
+        sampler.stop()
     dist.destroy_process_group()
 
 
