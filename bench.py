@@ -111,7 +111,10 @@ def build_ours_loop(cfg, device, world):
     from grace_b200 import models
 
     torch.manual_seed(0)
-    model = getattr(models, cfg["model"])().to(device)
+    if cfg["model"] == "bert_large" and cfg.get("bert_impl", "hf") == "hf":
+        model = hf_bert_large().to(device)
+    else:
+        model = getattr(models, cfg["model"])().to(device)
     if cfg["model"] in ("resnet50", "resnet20"):
         model = model.to(memory_format=torch.channels_last)
     params = dict(cfg["grace"])
@@ -145,12 +148,18 @@ def build_ours(cfg, device, world):
     from grace_b200.parallel.flat import FlatParams
 
     torch.manual_seed(0)
-    model = getattr(models, cfg["model"])().to(device)
-    if cfg["model"] in ("resnet50", "vgg16", "resnet20"):
+    if cfg["model"] == "bert_large" and cfg.get("bert_impl", "hf") == "hf":
+        model = hf_bert_large().to(device)      # the same model class as the reference arm
+    else:
+        model = getattr(models, cfg["model"])().to(device)
+    if cfg["model"] in ("resnet50", "resnet20"):   # VGG-16 stays NCHW: the reference arm's PowerSGD needs it
         model = model.to(memory_format=torch.channels_last)
     named = list(model.named_parameters())
     params = dict(cfg["grace"])
     params.update(world_size=world, fused=True)
+    for key in ("overlap_sms", "comm_sms", "nvls", "nvls_min_world"):
+        if cfg.get(key) is not None:
+            params[key] = cfg[key]
     grc = grace_b200.grace_from_params(params)
     fused_flat = getattr(grc, "_kind", None) in ("sparse", "quant", "powersgd")
     if fused_flat:
@@ -171,6 +180,15 @@ def build_ours(cfg, device, world):
         return loss
 
     return step, launches, grc
+
+
+def hf_bert_large():
+    """BERT-large for pre-training (MLM + NSP heads) from the transformers package, random weights."""
+    from transformers import BertConfig, BertForPreTraining
+
+    return BertForPreTraining(BertConfig(vocab_size=30522, hidden_size=1024, num_hidden_layers=24,
+                                         num_attention_heads=16, intermediate_size=4096,
+                                         max_position_embeddings=512))
 
 
 def build_reference(cfg, device, world):
@@ -211,11 +229,7 @@ def build_reference(cfg, device, world):
 
     torch.manual_seed(0)
     if cfg["model"] == "bert_large":
-        from transformers import BertConfig, BertForPreTraining
-
-        model = BertForPreTraining(BertConfig(vocab_size=30522, hidden_size=1024, num_hidden_layers=24,
-                                              num_attention_heads=16, intermediate_size=4096,
-                                              max_position_embeddings=512)).to(device)
+        model = hf_bert_large().to(device)
     elif cfg["model"] == "resnet20":
         from grace_b200.models import resnet20  # torchvision has no CIFAR ResNet-20
 
@@ -257,7 +271,13 @@ def main():
                     help="ours: DistributedOptimizer over flat buckets (default) or the reference-style "
                          "per-parameter grc.step loop with torch.optim.SGD (drop-in usage)")
     ap.add_argument("--bucket-mb", type=float, default=None,
-                    help="exchange gradients in buckets of this size from backward hooks (overlap); default one bucket")
+                    help="exchange gradients in buckets of this size from backward hooks, next to the rest of backward "
+                         "(default: the config's own bucket size; 0 = one bucket after backward)")
+    ap.add_argument("--overlap-sms", type=int, default=None, help="SMs of an exchange that runs next to backward")
+    ap.add_argument("--nvls", action="store_true", help="push transport (multimem.st) for the quantised codecs")
+    ap.add_argument("--bert-impl", default="hf", choices=["hf", "own"],
+                    help="ours, bert_qsgd: transformers' BertForPreTraining as in the reference arm (default) or "
+                         "this package's own BERT")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -271,8 +291,15 @@ def main():
     cfg = dict(CONFIGS[args.config])
     if args.batch:
         cfg["batch"] = args.batch
-    if args.bucket_mb:
-        cfg["bucket_bytes"] = int(args.bucket_mb * (1 << 20))
+    if args.bucket_mb is not None:
+        cfg["bucket_bytes"] = int(args.bucket_mb * (1 << 20)) or None
+    elif cfg.get("bucket_mb"):
+        cfg["bucket_bytes"] = int(cfg["bucket_mb"] * (1 << 20))
+    cfg["bert_impl"] = args.bert_impl
+    if args.overlap_sms is not None:
+        cfg["overlap_sms"] = args.overlap_sms
+    if args.nvls:
+        cfg["nvls"], cfg["nvls_min_world"] = True, 2
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

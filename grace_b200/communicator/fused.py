@@ -148,9 +148,10 @@ class _Plan:
                 buf = NvlsBuffer.create(2 * owner.world_size * stride // 4, owner.group, device)   # collective
                 if buf is not None:
                     self.recv = (buf, stride)
-        heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 8192
+        self.clip = kind == "sparse" and bool(getattr(owner.memory, "gradient_clipping", False))
+        heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 8192 + (16 * nseg + 1024 if self.clip else 0)
         self.heap = owner._make_heap(layout.key(), heap_bytes)
-        self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms)
+        self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms, clip=self.clip)
         self.segs = X.segments_to_device(layout, self.ks, device)
         # the sparse kernel zeroes the output while it reads the gradient: when both alias (in-place
         # exchange) the accumulator is where later passes re-read the values, so it always exists there
@@ -217,8 +218,6 @@ class FusedExchange(Communicator):
         elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor, C_.ThresholdCompressor, C_.RandomKCompressor)):
             if isinstance(mem, M_.DgcMemory) and isinstance(comp, (C_.ThresholdCompressor, C_.RandomKCompressor)):
                 self._kind = None
-            elif isinstance(comp, C_.ThresholdCompressor) and getattr(comp, "strict", False):
-                self._kind = None   # the kernel implements ``|x| >= min(threshold, max)``; the strict rule stays in torch ops
             elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.DgcMemory)):
                 self._kind = "sparse"
         elif isinstance(mem, (M_.NoneMemory, M_.ResidualMemory, M_.EFSignSGDMemory)):
@@ -238,7 +237,7 @@ class FusedExchange(Communicator):
 
     def supported(self, tensor: torch.Tensor) -> bool:
         if self._kind == "powersgd":
-            return tensor.is_cuda and int(getattr(self.compressor, "rank", 1)) <= 8
+            return tensor.is_cuda and int(getattr(self.compressor, "rank", 1)) <= 16
         return self._kind in ("sparse", "quant") and tensor.is_cuda
 
     # ------------------------------------------------------------------
@@ -317,17 +316,6 @@ class FusedExchange(Communicator):
             self._plans[key] = plan
         return plan
 
-    def _clip_bounds(self, plan: _Plan, g: torch.Tensor) -> torch.Tensor:
-        """DGC gradient clipping: per tensor, ``sqrt(mean over ranks of sum(g^2))``
-        (``grace_dl/torch/memory/dgc.py:16-19``); the kernel clamps element-wise."""
-        views = list(plan.layout.slices(g).values())
-        sq = torch.stack(torch._foreach_norm(views)).pow(2)
-        if self._virtual is None and dist.is_available() and dist.is_initialized() and self.world_size > 1:
-            dist.all_reduce(sq, group=self.group)
-            sq = sq / self.world_size
-        plan.clip = sq.sqrt().float().contiguous()   # kept alive until the kernel has read it
-        return plan.clip
-
     def _memory_coeffs(self, plan: _Plan):
         mem = self.memory
         first = plan.steps == 0
@@ -347,9 +335,8 @@ class FusedExchange(Communicator):
         scale = (1.0 / self.world_size) if comp.average else 1.0
         beta, gamma = self._memory_coeffs(plan)
         plan.channel.poll()
-        clip = None
-        if plan.kind == "sparse" and getattr(self.memory, "gradient_clipping", False) and (phases & X.PHASE_COMPRESS):
-            clip = self._clip_bounds(plan, g)
+        if plan.kind == "sparse" and plan.clip and phases == X.PHASE_ALL:
+            phases |= X.PHASE_CLIP   # one launch: sums of squares, their exchange, clamp, compress, exchange
         if self._faults.action and (phases & X.PHASE_PUBLISH) and self._faults.hits(
                 "skip_publish", plan.heap.rank, plan.steps):
             phases &= ~X.PHASE_PUBLISH  # host-side fault injection: this rank "forgets" to publish
@@ -358,8 +345,8 @@ class FusedExchange(Communicator):
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.u, out, mode=plan.mode, cap=plan.cap,
                 beta=beta, gamma=gamma, momentum=float(getattr(self.memory, "momentum", 0.0)),
                 threshold=float(getattr(comp, "threshold", 0.0)), scale=scale, levels=3 if self.exact else 2,
-                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps, clip=clip,
-                tile_decode=plan.tile, grid=grid)
+                phases=phases, seq=seq, kprefix=plan.kprefix, seg_seed=plan.seg_seed, rk_step=plan.steps,
+                clip=plan.clip, strict=bool(getattr(comp, "strict", False)), tile_decode=plan.tile, grid=grid)
         else:
             seq = X.run_quant(
                 plan.channel, plan.layout, plan.segs, g, plan.acc, plan.mom, out, codec=plan.codec,
@@ -425,9 +412,15 @@ class FusedExchange(Communicator):
         return 4 * (plan.p_floats + plan.q_floats) * self.compressor.rank // 16 + dense
 
     def _prepare(self, tensor: torch.Tensor):
+        """The gradient as a flat, aligned buffer the kernels can read: fp32, bf16 and fp16 tensors are taken as
+        they are (the kernels convert on load); anything else is cast to fp32 first.  The low-rank kernel reads
+        fp32 only (its TMA tensor maps are typed)."""
         flat = tensor.detach().reshape(-1)
-        if flat.dtype != torch.float32 or not flat.is_contiguous() or flat.data_ptr() % 16 != 0:
-            flat = flat.float().contiguous().clone()
+        keep = (torch.float32,) if self._kind == "powersgd" else (torch.float32, torch.bfloat16, torch.float16)
+        if flat.dtype not in keep:
+            flat = flat.float()
+        if not flat.is_contiguous() or flat.data_ptr() % 16 != 0:
+            flat = flat.contiguous().clone()
         return flat
 
     def step(self, tensor: torch.Tensor, name: str, sm_limit: Optional[int] = None) -> torch.Tensor:
@@ -437,7 +430,10 @@ class FusedExchange(Communicator):
 
         flat = self._prepare(tensor)
         same = flat.data_ptr() == tensor.data_ptr()
-        out = flat if (self.inplace and same) else torch.empty_like(flat)
+        if self._kind == "sparse" and flat.dtype != torch.float32:
+            out = torch.empty(flat.shape, dtype=torch.float32, device=flat.device)   # the scatter-add needs fp32 words
+        else:
+            out = flat if (self.inplace and same) else torch.empty_like(flat)
         lkey = (name, flat.numel(), tuple(tensor.shape))
         layout = self._single_layouts.get(lkey)
         if layout is None:
@@ -673,9 +669,13 @@ class VirtualWorld:
             for p in plans:
                 p.steps += 1
             return outs
-        seqs = []
-        for c, p, g, o in zip(self.comms, plans, flats, outs):
-            seqs.append(c._launch(p, g, o, PHASE_COMPRESS | PHASE_PUBLISH))
+        seqs = [None] * len(plans)
+        if getattr(plans[0], "clip", False):   # every rank's sums of squares first: compress reads all of them
+            from ..ops.exchange import PHASE_CLIP
+
+            seqs = [c._launch(p, g, o, PHASE_CLIP) for c, p, g, o in zip(self.comms, plans, flats, outs)]
+        seqs = [c._launch(p, g, o, PHASE_COMPRESS | PHASE_PUBLISH, seq=s)
+                for c, p, g, o, s in zip(self.comms, plans, flats, outs, seqs)]
         if getattr(plans[0], "alltoall", False):
             from ..ops.exchange import PHASE_REDUCE
 

@@ -84,15 +84,18 @@ PYBIND11_MODULE(_C, m) {
            unsigned long long seq, unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps,
            unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
-           uintptr_t seg_seed, unsigned rk_step, uintptr_t clip, uintptr_t tile_start, uintptr_t tile_cur,
-           uintptr_t scan_tmp) {
+           uintptr_t seg_seed, unsigned rk_step, unsigned long long clip_off, unsigned long long clip_ready_off,
+           uintptr_t clip_sq, int strict, int g_dtype, uintptr_t tile_start, uintptr_t tile_cur, uintptr_t scan_tmp) {
           SparseArgs a{};
           a.tile_start = ptr<unsigned>(tile_start); a.tile_cur = ptr<unsigned>(tile_cur); a.scan_tmp = ptr<unsigned>(scan_tmp);
-          a.clip = ptr<const float>(clip);
+          a.clip_off = clip_off; a.clip_ready_off = clip_ready_off; a.clip_sq = ptr<double>(clip_sq); a.strict = strict;
+          if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");
+          a.g_dtype = g_dtype;
+          if ((clip_off != 0) != (clip_sq != 0)) throw std::invalid_argument("clipping needs both the heap area and the accumulators");
           a.kprefix = ptr<const int>(kprefix); a.seg_seed = ptr<const unsigned long long>(seg_seed); a.rk_step = rk_step;
           if (mode == kSparseRandomK && (!kprefix || !seg_seed)) throw std::invalid_argument("random-k needs kprefix and seeds");
           a.cand_val = ptr<float>(cand_val); a.cand_idx = ptr<int>(cand_idx); a.cand_cap = cand_val ? cand_cap : 0;
-          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.u = ptr<float>(u); a.out = ptr<float>(out);
+          a.g = ptr<const void>(g); a.acc = ptr<float>(acc); a.u = ptr<float>(u); a.out = ptr<float>(out);
           a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.mode = mode; a.levels = levels;
           a.beta = beta; a.gamma = gamma; a.momentum = momentum; a.threshold = threshold; a.scale = scale;
           a.hist = ptr<unsigned>(hist); a.state = ptr<SparseState>(state); a.barrier = ptr<unsigned>(barrier);
@@ -110,13 +113,15 @@ PYBIND11_MODULE(_C, m) {
            int phases, int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
            unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off,
-           uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride) {
+           uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride, int g_dtype) {
           QuantArgs a{};
+          if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");
+          a.g_dtype = g_dtype;
           a.recv_local = ptr<char>(recv_local); a.recv_mc = ptr<char>(recv_mc); a.recv_stride = recv_stride;
           if ((recv_local != 0) != (recv_mc != 0) || (recv_mc && (alltoall || recv_stride % 16 || recv_local % 16 || recv_mc % 16)))
             throw std::invalid_argument("quant_exchange: bad push-transport arguments");
           a.alltoall = alltoall; a.ready2_off = ready2_off;
-          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
+          a.g = ptr<const void>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<void>(out);
           a.segs = ptr<const Segment>(segs); a.nseg = nseg; a.total = total; a.codec = codec; a.quantum = quantum;
           a.deterministic = deterministic; a.first_step = first_step; a.beta = beta; a.gamma = gamma;
           a.mom_beta = mom_beta; a.lr = lr; a.scale = scale; a.seed = seed; a.step = step;
@@ -158,7 +163,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("powersgd_exchange",
         [](uintptr_t g, uintptr_t acc, uintptr_t out, uintptr_t mats, uintptr_t maps, int nmat, int rank_r,
            int has_memory, int divisor, int items_s1, int items_s2, int p_floats, int q_floats, uintptr_t p_mean,
-           uintptr_t q_mean, uintptr_t pt_orth, uintptr_t qt, uintptr_t gram, uintptr_t barrier, uintptr_t status,
+           uintptr_t q_mean, uintptr_t pt_orth, uintptr_t qt, uintptr_t gram, uintptr_t partial, uintptr_t counters,
+           uintptr_t barrier, uintptr_t status,
            unsigned long long ready2_off, int part, int rank, int world, unsigned long long seq,
            unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
            unsigned long long ack_off, unsigned long long slot_off, int grid, uintptr_t stream) {
@@ -168,10 +174,13 @@ PYBIND11_MODULE(_C, m) {
           a.rank = rank_r; a.has_memory = has_memory; a.divisor = divisor; a.items_s1 = items_s1; a.items_s2 = items_s2;
           a.p_floats = p_floats; a.q_floats = q_floats; a.p_mean = ptr<float>(p_mean); a.q_mean = ptr<float>(q_mean);
           a.pt_orth = ptr<float>(pt_orth); a.qt = ptr<float>(qt); a.gram = ptr<double>(gram);
+          a.partial = ptr<float>(partial); a.counters = ptr<unsigned>(counters);
+          if (!partial || !counters) throw std::invalid_argument("powersgd_exchange: split-K scratch missing");
           a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status); a.ready2_off = ready2_off;
           a.phases = kPhaseAll; a.part = part;
           a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
-          if (rank_r < 1 || rank_r > 8 || nmat < 1) throw std::invalid_argument("rank must be in [1,8], nmat >= 1");
+          if (rank_r < 1 || rank_r > 16 || nmat < 1) throw std::invalid_argument("rank must be in [1,16], nmat >= 1");
+          if (part < 0 || part > 3) throw std::invalid_argument("part: 0 (all) or 1..3");
           check(launch_powersgd(a, grid, reinterpret_cast<cudaStream_t>(stream)), "powersgd_exchange");
         });
 

@@ -42,6 +42,7 @@ enum Phase : int {
   kPhaseExchange = 4,  // wait for peers, pull, decode, aggregate, acknowledge
   kPhaseAll = 7,
   kPhaseReduce = 8,    // two-phase ("alltoall") mode only: reduce my chunk, re-encode, publish again
+  kPhaseClip = 16,     // sparse exchange with DGC gradient clipping: per-tensor sum of squares, published to the peers
 };
 
 // ---------------------------------------------------------------- sparse ----
@@ -55,7 +56,8 @@ struct SparseState {       // per segment, device scratch
 };
 
 struct SparseArgs {
-  const float* g;     // gradients, flat
+  const void* g;      // gradients, flat: fp32, bf16 or fp16 (g_dtype, a GradType of gradio.cuh)
+  int g_dtype;
   float* acc;         // accumulator / residual state (nullable: no memory)
   float* u;           // DGC momentum state (nullable)
   float* out;         // dense aggregated output; may alias g (nullable)
@@ -75,7 +77,11 @@ struct SparseArgs {
   const int* kprefix;               // nseg + 1 prefix sums of k (entry e belongs to the segment with kprefix[s] <= e)
   const unsigned long long* seg_seed;  // nseg seeds (derived from the tensor names, identical on every rank)
   unsigned rk_step;                 // per-plan step counter (part of the Philox counter)
-  const float* clip;                // nseg clamp bounds applied to g before compensation (DGC clipping), nullable
+  // DGC gradient clipping (0 = off): element-wise clamp of g to +-sqrt(mean over ranks of sum g^2) per tensor.
+  unsigned long long clip_off;      // heap offset of 2 (parities) x nseg doubles: this rank's sums, read by the peers
+  unsigned long long clip_ready_off;  // flag pad of their publication
+  double* clip_sq;                  // nseg local accumulators, zero on entry, left zero on exit
+  int strict;                       // threshold mode: |x| > threshold (no cap by max(x))
   // Tile-ordered exchange (nullable: then lists travel unordered and are scatter-added with red.global):
   // the sender orders its list by 8192-element output tile into a second pair of arrays in the slot,
   // followed by a directory of tile offsets; receivers build whole tiles in shared memory.  The slot
@@ -116,10 +122,11 @@ struct QuantSegStats {   // per segment, device scratch (double for stable sums)
 };
 
 struct QuantArgs {
-  const float* g;
-  float* acc;          // residual state (nullable)
-  float* mom;          // signum momentum state (nullable)
-  float* out;          // may alias g
+  const void* g;       // gradients: fp32, bf16 or fp16 (g_dtype, a GradType of gradio.cuh)
+  float* acc;          // residual state (nullable), always fp32
+  float* mom;          // signum momentum state (nullable), always fp32
+  void* out;           // aggregated gradients, same element type as g; may alias g
+  int g_dtype;
   const Segment* segs;
   int nseg;
   long long total;     // padded flat length, multiple of 128
@@ -183,6 +190,8 @@ struct LowRankMatrix {
   int qt_off;        // [16][m] block inside qt
   int item1_begin;   // first stage-1 work item (prefix sum over matrices)
   int item2_begin;   // first stage-2 work item
+  int splits1;       // K splits per 128-row block in stage 1 (work items of a block are consecutive)
+  int splits2;       // same for stage 2
 };
 
 enum LowRankMap : int { kMapG1 = 0, kMapA1 = 1, kMapM2 = 2, kMapQt = 3, kMapPt = 4, kMapsPerMatrix = 5 };
@@ -196,7 +205,7 @@ struct LowRankArgs {
   const LowRankMatrix* mats;
   const CUtensorMap_st* maps;  // nmat * kMapsPerMatrix tensor maps in device memory (64-byte aligned)
   int nmat;
-  int rank;                // actual rank r <= 8 (buffers are padded to 16 columns)
+  int rank;                // actual rank r <= 16 (buffers are padded to 16 columns)
   int has_memory;
   int divisor;             // world size (P and Q are averaged)
   int items_s1, items_s2;
@@ -206,6 +215,8 @@ struct LowRankArgs {
   float* pt_orth;          // sum_n 16*n
   float* qt;               // sum_m 16*m: Q^T, persistent across steps (warm start)
   double* gram;            // nmat * 256
+  float* partial;          // (items_s1 + items_s2) blocks of 128 x 16: split-K partial sums, one block per work item
+  unsigned* counters;      // items_s1 + items_s2: finished items per row block (indexed by the block's first item)
   unsigned* barrier;
   unsigned* status;
   unsigned long long ready2_off;  // second flag pad (Q); peers.ready_off is the first (P)

@@ -4,26 +4,38 @@
 // partial results over NVLink.
 //
 // For every matrix M (n x m, row-major slice of the flat gradient buffer) of a
-// launch, with rank r <= 8 padded to 16 columns:
+// launch, with rank r <= 16 padded to 16 columns:
 //   S1  M' = G + R (error feedback; added in shared memory on the swizzled
 //       tiles and written back by a TMA store), P = M' * Q: A = M' tile
 //       [128 x 32] K-major, B = Q^T tile [16 x 32] K-major, D in TMEM
-//       (128 lanes x 16 columns); split-K partial sums are added into this
-//       rank's P slot on the symmetric heap;
+//       (128 lanes x 16 columns, two accumulators used alternately);
 //   R1  publish; wait for every peer; P = mean over ranks of the W slots
 //       (identical order on every rank, so the results are bit-identical);
-//       Gram matrix P^T P accumulated on the way;
-//   O   orthogonalise P: Cholesky factor of the Gram matrix in fp64, P R^-1
-//       (what modified Gram-Schmidt computes in exact arithmetic), written
-//       transposed for the next stage;
-//   S2  Q = M'^T * P: TMA brings 32 rows x 128 columns of M' (four unswizzled
-//       boxes); the CTA transposes them in shared memory into a K-major
-//       128B-swizzled A tile [128 x 32] (the TF32 MMA returns zeros for an
-//       MN-major A operand on this part, so the transpose is done by hand),
-//       B = P^T tile [16 x 32] K-major, D [128 x 16] in TMEM;
+//   O   orthogonalise P: Gram matrix P^T P and its Cholesky factor in fp64,
+//       P R^-1 (what modified Gram-Schmidt computes in exact arithmetic),
+//       written transposed for the next stage;
+//   S2  Q = M'^T * P: TMA brings 32 rows x 128 columns of M' as four boxes of
+//       32 x 32 in the "128-byte rows, 32-byte swizzle atoms" layout, which IS
+//       the MN-major TF32 operand layout of the tensor core: the tile feeds
+//       the MMA as it lands (A = M'^T [128 x 32] MN-major, B = P^T tile
+//       [16 x 32] K-major); nothing is transposed by hand;
 //   R2  publish; wait; Q = mean over ranks; kept as next step's warm start;
 //   S3  out = P Q^T (rank-r outer products on CUDA cores), R = M' - out.
 //
+// The GEMM stages are warp specialised, with mbarriers between the roles and
+// no CTA-wide barrier inside the loops:
+//   warp 0     one thread issues the TMA loads of the operand ring;
+//   warp 1     one thread issues the MMAs and commits them to the ring's
+//              "empty" barriers and, at the end of a work item, to the
+//              accumulator's "full" barrier;
+//   warps 2-3  (S1 with error feedback) add the residual tile into the
+//              gradient tile in shared memory and hand it on;
+//   warps 4-7  epilogue: TMEM -> registers -> this item's partial result;
+//   warp 8     (S1 with error feedback) one thread writes M' back with TMA
+//              stores and frees the ring slot once the store has read it.
+// Split-K is deterministic: every work item (128 output rows x a K range)
+// writes its partial sums to its own block of a scratch buffer; the item that
+// completes a row block last adds the partials in split order into the slot.
 // Every mbarrier / flag / grid-barrier wait is bounded; TMA loads never use
 // cluster multicast and never read peer memory (peers are read with ld.cg).
 //
@@ -39,34 +51,41 @@ namespace grace {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kStages = 6;             // 6 x (16 + 16 + 2) KiB ring per CTA (one CTA per SM: the runtime reports one resident CTA for this kernel at any shared-memory size)
+constexpr int kThreads = 288;
 constexpr int kTileRows = 128;          // MMA M
-constexpr int kTileK = 32;              // fp32 elements per 128-byte swizzle row
+constexpr int kTileK = 32;              // fp32 elements per 128-byte row
 constexpr int kRankPad = 16;            // MMA N
 constexpr int kATileBytes = kTileRows * kTileK * 4;   // 16 KiB
 constexpr int kBTileBytes = kRankPad * kTileK * 4;    // 2 KiB
-constexpr int kKTilesPerItem = 16;      // split-K granularity: 512 columns (S1) / 512 rows (S2)
-constexpr unsigned kTmemCols = 32;
-constexpr int kProducerThread = 32;      // lane 0 of warp 1: TMA loads and stores
-constexpr int kMaxRank = 8;              // ranks 1..8 (buffers are padded to kRankPad columns)
-constexpr int kS3Trip = 16;             // rows whose loads are in flight together in stage 3
+constexpr int kStagesR = 6;             // ring depth with a residual tile per stage (34 KiB each)
+constexpr int kStagesNoR = 11;          // ring depth without (18 KiB each)
+constexpr int kRingBytes = kStagesR * (2 * kATileBytes + kBTileBytes);   // 204 KiB
+static_assert(kStagesNoR * (kATileBytes + kBTileBytes) <= kRingBytes, "ring too small");
+constexpr unsigned kTmemCols = 32;      // two accumulators of 16 columns
+constexpr int kMaxRank = 16;
+constexpr int kS3Trip = 8;              // rows of one trip of stage 3 (the next trip's loads are already in flight)
 constexpr int kS3Rows = 64;             // rows per stage-3 work item
+constexpr int kS3Cols = kThreads * 4;   // columns per stage-3 work item
+// warp roles of the GEMM stages
+constexpr int kProducerWarp = 0, kMmaWarp = 1, kAdderWarp0 = 2, kAdderWarps = 2, kEpilogueWarp0 = 4, kStoreWarp = 8;
 
 // instruction descriptor: D=f32, A=B=tf32, N=16, M=128 (bit layout: c_format
 // [4,6), a_format [7,10), b_format [10,13), a_major 15, b_major 16, N>>3
-// [17,23), M>>4 [24,29))
-constexpr uint32_t kIdescS1 = (1u << 4) | (2u << 7) | (2u << 10) | ((kRankPad >> 3) << 17) | ((kTileRows >> 4) << 24);
+// [17,23), M>>4 [24,29)); bit 15 set = A is MN-major (stage 2)
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRankPad >> 3) << 17) | ((kTileRows >> 4) << 24);
+constexpr uint32_t kIdescAmn = kIdesc | (1u << 15);
 
 struct __align__(1024) SmemLayout {
-  unsigned char a[kStages][kATileBytes];   // gradient tile, becomes the A operand
-  unsigned char r[kStages][kATileBytes];   // stage 1: residual tile; stage 2: unswizzled M' boxes before the transpose
-  unsigned char b[kStages][kBTileBytes];   // Q^T / P^T tile
-  unsigned long long full[kStages];
-  unsigned long long mma_done[kStages];
-  unsigned long long item_done;
+  unsigned char ring[kRingBytes];
+  unsigned long long full[kStagesNoR];     // TMA landed
+  unsigned long long ready[kStagesNoR];    // residual added (S1 with error feedback)
+  unsigned long long empty[kStagesNoR];    // MMAs retired (and the M' store has read the tile)
+  unsigned long long acc_full[2];          // an item's MMAs retired
+  unsigned long long acc_empty[2];         // the epilogue has read the accumulator
   unsigned tmem_base;
-  int bail;
+  int bars_valid;                          // the mbarriers above hold valid objects (a GEMM stage ran)
+  int epi_ok;                              // epilogue: the accumulator arrived in time
+  int last_flag;                           // epilogue: this CTA completed the row block
   double gram[kMaxRank][kMaxRank];
   double rinv[kMaxRank][kMaxRank];
   float prow[kS3Rows][kMaxRank];
@@ -77,8 +96,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_inval(void* bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
   unsigned ok;
@@ -89,7 +114,7 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait; returns false (and records the failure) when the limit expires.
+// Bounded wait; returns false (and records the failure) when the limit expires or another role already failed.
 __device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, uint64_t timeout_ns, const Status& status,
                                           unsigned detail) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -123,10 +148,12 @@ __device__ __forceinline__ void tma_wait_all0() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  // start>>4 [0,14) | LBO>>4 [16,30) | SBO>>4 [32,46) | version 1 [46,48) | SWIZZLE_128B (2) [61,64)
+// Shared-memory matrix descriptor: start>>4 [0,14) | LBO>>4 [16,30) | SBO>>4 [32,46) | version 1 [46,48) |
+// layout type [61,64): 2 = 128-byte swizzle of 16-byte chunks (K-major tiles), 1 = 128-byte rows swizzled in
+// 32-byte atoms (the one layout the tensor core accepts for an MN-major TF32 operand).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accum) {
   asm volatile(
@@ -141,10 +168,15 @@ __device__ __forceinline__ void umma_commit(void* bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 // Work item of a GEMM stage: (matrix, block of 128 output rows, K split).
 struct Item {
   int mat, blk, kt0, kt1;
+  int first;    // index of split 0 of this row block (the items of a block are consecutive)
+  int splits;
 };
 __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int idx, Item& it) {
   const int total = stage == 1 ? a.items_s1 : a.items_s2;
@@ -152,203 +184,231 @@ __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int
   int mat = 0;
   while (mat + 1 < a.nmat && (stage == 1 ? a.mats[mat + 1].item1_begin : a.mats[mat + 1].item2_begin) <= idx) ++mat;
   const LowRankMatrix& M = a.mats[mat];
-  const int local = idx - (stage == 1 ? M.item1_begin : M.item2_begin);
+  const int begin = stage == 1 ? M.item1_begin : M.item2_begin;
+  const int local = idx - begin;
   const int ktiles = ((stage == 1 ? M.m : M.n) + kTileK - 1) / kTileK;
-  const int splits = (ktiles + kKTilesPerItem - 1) / kKTilesPerItem;
+  const int splits = stage == 1 ? M.splits1 : M.splits2;
+  const int sp = local % splits;
   it.mat = mat;
   it.blk = local / splits;
-  it.kt0 = (local % splits) * kKTilesPerItem;
-  it.kt1 = min(it.kt0 + kKTilesPerItem, ktiles);
+  it.splits = splits;
+  it.first = begin + it.blk * splits;
+  it.kt0 = (int)((long long)sp * ktiles / splits);
+  it.kt1 = (int)((long long)(sp + 1) * ktiles / splits);
   return true;
 }
 
-// One GEMM stage over this CTA's items.  STAGE 1: P += M' Q.  STAGE 2: Q += M'^T P.
+// One GEMM stage over this CTA's items.  STAGE 1: P = M' Q.  STAGE 2: Q = M'^T P.
+// Every role walks the same sequence of (item, K tile) steps, which it derives from blockIdx by itself.
 template <int STAGE>
-__device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& status, float* __restrict__ dst_slot,
-                           unsigned& step_counter, unsigned& item_counter) {
+__device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& status, float* __restrict__ dst_slot) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool add_residual = STAGE == 1 && a.has_memory;
-  const uint32_t tmem_d = sm.tmem_base;
-  const unsigned tile_bytes = kATileBytes + kBTileBytes + (add_residual ? kATileBytes : 0);
-
-  // producer cursor (thread 0) and consumer cursor (all threads) walk the same sequence of (item, k-tile)
-  int p_item = blockIdx.x, c_item = blockIdx.x;
-  Item pit, cit;
-  bool p_valid = decode_item(a, STAGE, p_item, pit);
-  bool c_valid = decode_item(a, STAGE, c_item, cit);
-  int p_kt = p_valid ? pit.kt0 : 0, c_kt = c_valid ? cit.kt0 : 0;
-  unsigned p_step = step_counter, c_step = step_counter;
-
-  // Two single-thread roles run side by side after each CTA barrier: thread 0 issues the MMAs,
-  // thread kProducerThread issues the TMA store of M' and refills the ring.
-  auto produce = [&]() {  // producer thread only: issue the TMA loads of the next (item, k-tile)
-    if (!p_valid) return;
-    const unsigned slot = p_step % kStages;
-    if (p_step >= kStages) {
-      // the MMAs that read this slot kStages steps ago must have retired, and the
-      // TMA store that read its A tile must be done reading
-      if (!mbar_wait(&sm.mma_done[slot], ((p_step / kStages) - 1) & 1, a.peers.timeout_ns, status, 100 + slot)) {
-        p_valid = false;
-        return;
-      }
-      tma_wait_read1();  // all of this thread's stores except the newest one have read their tile
+  const bool has_r = STAGE == 1 && a.has_memory;
+  const unsigned nstages = has_r ? kStagesR : kStagesNoR;
+  const unsigned stage_bytes = (has_r ? 2 * kATileBytes : kATileBytes) + kBTileBytes;
+  const unsigned off_r = kATileBytes, off_b = has_r ? 2 * kATileBytes : kATileBytes;
+  const uint64_t tmo = a.peers.timeout_ns;
+  if (tid == 0) {
+    if (sm.bars_valid) {   // objects of the previous stage: all their phases are over (a CTA barrier lies behind us)
+      for (int s = 0; s < kStagesNoR; ++s) { mbar_inval(&sm.full[s]); mbar_inval(&sm.ready[s]); mbar_inval(&sm.empty[s]); }
+      for (int b = 0; b < 2; ++b) { mbar_inval(&sm.acc_full[b]); mbar_inval(&sm.acc_empty[b]); }
     }
-    const LowRankMatrix& M = a.mats[pit.mat];
-    const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)pit.mat * kMapsPerMatrix;
-    mbar_expect_tx(&sm.full[slot], tile_bytes);
-    if (STAGE == 1) {
-      tma_load_2d(sm.a[slot], maps + kMapG1, p_kt * kTileK, pit.blk * kTileRows, &sm.full[slot]);
-      if (add_residual) tma_load_2d(sm.r[slot], maps + kMapA1, p_kt * kTileK, pit.blk * kTileRows, &sm.full[slot]);
-      tma_load_2d(sm.b[slot], maps + kMapQt, p_kt * kTileK, 0, &sm.full[slot]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j)  // four unswizzled boxes of 32 columns x 32 rows of M'
-        tma_load_2d(sm.r[slot] + j * 4096, maps + kMapM2, pit.blk * kTileRows + j * 32, p_kt * kTileK, &sm.full[slot]);
-      tma_load_2d(sm.b[slot], maps + kMapPt, p_kt * kTileK, 0, &sm.full[slot]);
+    for (int s = 0; s < kStagesNoR; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.ready[s], kAdderWarps);
+      mbar_init(&sm.empty[s], has_r ? 2 : 1);
     }
-    (void)M;
-    ++p_step;
-    if (++p_kt >= pit.kt1) {
-      p_item += gridDim.x;
-      p_valid = decode_item(a, STAGE, p_item, pit);
-      p_kt = p_valid ? pit.kt0 : 0;
-    }
-  };
-
-  if (tid == kProducerThread) {
-    for (int i = 0; i < kStages - 1; ++i) produce();
+    for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 4); }
+    sm.bars_valid = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  __syncthreads();
 
-  long long t_wait = 0, t_work = 0, t_sync = 0, t_issue = 0, t_fence = 0, t_commit = 0;
-  const bool prof = (a.part & 0x100) && blockIdx.x == 0 && tid == 0;
-  while (c_valid) {
-    const unsigned slot = c_step % kStages;
-    long long t0 = prof ? clock64() : 0;
-    bool ok = mbar_wait(&sm.full[slot], (c_step / kStages) & 1, a.peers.timeout_ns, status, 200 + slot);
-    if (prof) { const long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; }
-    if (add_residual && ok) {
-      float4* pa = reinterpret_cast<float4*>(sm.a[slot]);
-      const float4* pr = reinterpret_cast<const float4*>(sm.r[slot]);
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      unsigned step = 0;
+      Item it;
+      bool ok = true;
+      for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
+        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)it.mat * kMapsPerMatrix;
+        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+          const unsigned slot = step % nstages;
+          if (step >= nstages) ok = mbar_wait(&sm.empty[slot], ((step / nstages) - 1) & 1, tmo, status, 100 + slot);
+          if (!ok) break;
+          unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
+          mbar_expect_tx(&sm.full[slot], stage_bytes);
+          if (STAGE == 1) {
+            tma_load_2d(base, maps + kMapG1, kt * kTileK, it.blk * kTileRows, &sm.full[slot]);
+            if (has_r) tma_load_2d(base + off_r, maps + kMapA1, kt * kTileK, it.blk * kTileRows, &sm.full[slot]);
+            tma_load_2d(base + off_b, maps + kMapQt, kt * kTileK, 0, &sm.full[slot]);
+          } else {
 #pragma unroll
-      for (int i = 0; i < kATileBytes / 16 / kThreads; ++i) {
-        float4 x = pa[tid + i * kThreads];
-        const float4 y = pr[tid + i * kThreads];
-        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-        pa[tid + i * kThreads] = x;
-      }
-      fence_async_smem();  // generic-proxy writes -> visible to the TMA store and the MMA
-    }
-    if (STAGE == 2 && ok) {
-      // transpose: staging[j][k][mi] (k = row of M', 32 per tile; m = 32*j + mi) -> A[m][k], K-major with the
-      // 128-byte swizzle (16-byte chunk index XOR row % 8).  One 4 x 4 block per thread.
-      // Thread -> block mapping chosen so that both sides are free of bank conflicts: the eight
-      // lanes of a quarter warp read eight different 16-byte chunks of the staging rows, and their
-      // swizzled destination chunks (kq ^ row % 8) are eight different values as well.
-      const int l8 = tid & 7, rest = tid >> 3;
-      const int mq = (rest & 3) * 8 + l8;             // m / 4
-      const int kq = (l8 >> 1) ^ (rest >> 2);         // k / 4
-      const int j = mq >> 3, mi4 = (mq & 7) * 4;
-      const unsigned char* st = sm.r[slot] + j * 4096 + mi4 * 4;
-      float4 rowv[4];
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) rowv[kk] = *reinterpret_cast<const float4*>(st + (kq * 4 + kk) * 128);
-      const float t[4][4] = {{rowv[0].x, rowv[1].x, rowv[2].x, rowv[3].x}, {rowv[0].y, rowv[1].y, rowv[2].y, rowv[3].y},
-                             {rowv[0].z, rowv[1].z, rowv[2].z, rowv[3].z}, {rowv[0].w, rowv[1].w, rowv[2].w, rowv[3].w}};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int mrow = mq * 4 + e;
-        *reinterpret_cast<float4*>(sm.a[slot] + mrow * 128 + ((kq ^ (mrow & 7)) << 4)) =
-            make_float4(t[e][0], t[e][1], t[e][2], t[e][3]);
-      }
-      fence_async_smem();
-    }
-    if (!ok) sm.bail = 1;
-    if (prof) { const long long t1 = clock64(); t_work += t1 - t0; t0 = t1; }
-    __syncthreads();
-    if (prof) { const long long t1 = clock64(); t_sync += t1 - t0; t0 = t1; }
-    if (sm.bail) break;
-    const bool last_kt = (c_kt + 1 >= cit.kt1);
-    if (tid == kProducerThread) {
-      if (add_residual) {  // M' goes back to the accumulator buffer
-        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)cit.mat * kMapsPerMatrix;
-        tma_store_2d(maps + kMapA1, c_kt * kTileK, cit.blk * kTileRows, sm.a[slot]);
-        tma_commit();
-      }
-      // refill the slot used one step ago: its MMAs were issued a whole iteration earlier, so the
-      // wait inside produce() rarely stalls
-      produce();
-    }
-    if (tid == 0) {
-      tc_fence_after();
-      if (prof) { const long long t1 = clock64(); t_fence += t1 - t0; t0 = t1; }
-      const uint32_t a_addr = smem_u32(sm.a[slot]), b_addr = smem_u32(sm.b[slot]);
-#pragma unroll
-      for (int kk = 0; kk < kTileK / 8; ++kk) {
-        const uint64_t adesc = smem_desc(a_addr + kk * 32, 16, 1024);   // K-major: 32 B per K step of 8
-        const uint64_t bdesc = smem_desc(b_addr + kk * 32, 16, 1024);
-        umma_tf32(tmem_d, adesc, bdesc, kIdescS1, !(c_kt == cit.kt0 && kk == 0));
-      }
-      if (prof) { const long long t1 = clock64(); t_issue += t1 - t0; t0 = t1; }
-      umma_commit(&sm.mma_done[slot]);
-      if (last_kt) umma_commit(&sm.item_done);
-      if (prof) { const long long t1 = clock64(); t_commit += t1 - t0; t0 = t1; }
-    }
-    ++c_step;
-    if (last_kt) {
-      // ---- epilogue: TMEM -> registers -> red.add into this rank's slot ----
-      ok = mbar_wait(&sm.item_done, item_counter & 1, a.peers.timeout_ns, status, 300);
-      ++item_counter;
-      if (!ok) sm.bail = 1;
-      __syncthreads();
-      if (sm.bail) break;
-      tc_fence_after();
-      if (warp < 4) {
-        uint32_t v[16];
-        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-            : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const LowRankMatrix& M = a.mats[cit.mat];
-        const int row = cit.blk * kTileRows + warp * 32 + lane;
-        const int rows = STAGE == 1 ? M.n : M.m;
-        if (row < rows) {
-          float* dst = dst_slot + (STAGE == 1 ? M.p_off : M.q_off) + (size_t)row * kRankPad;
-#pragma unroll
-          for (int c = 0; c < kRankPad; ++c)
-            if (c < a.rank) atomicAdd(dst + c, __uint_as_float(v[c]));
+            for (int j = 0; j < 4; ++j)  // four boxes of 32 columns x 32 rows of M': the MN-major operand layout
+              tma_load_2d(base + j * 4096, maps + kMapM2, it.blk * kTileRows + j * 32, kt * kTileK, &sm.full[slot]);
+            tma_load_2d(base + off_b, maps + kMapPt, kt * kTileK, 0, &sm.full[slot]);
+          }
         }
       }
-      tc_fence_before();
-      __syncthreads();  // TMEM reads done before the next item's first MMA overwrites the accumulator
-      c_item += gridDim.x;
-      c_valid = decode_item(a, STAGE, c_item, cit);
-      c_kt = c_valid ? cit.kt0 : 0;
-      if (prof) { const long long t1 = clock64(); t_commit += t1 - t0; t0 = t1; }
-    } else {
-      ++c_kt;
+      if (!ok || status.failed()) {
+        // a consumer gave up: every load already issued must still land before the shared memory is let go
+        for (unsigned s = step > nstages ? step - nstages : 0; s < step; ++s)
+          mbar_wait(&sm.full[s % nstages], (s / nstages) & 1, tmo, status, 400);
+      }
     }
-  }
-  if (prof) {
-    unsigned* w = a.status + 8 + (STAGE - 1) * 8;
-    w[0] = (unsigned)(t_wait >> 4); w[1] = (unsigned)(t_work >> 4); w[2] = (unsigned)(t_sync >> 4);
-    w[3] = (unsigned)(t_issue >> 4); w[4] = (unsigned)(t_fence >> 4); w[5] = (unsigned)(t_commit >> 4); w[6] = c_step;
-  }
-  // drain: every issued load must land and every store must finish before smem is reused
-  if (tid == kProducerThread) {
-    tma_wait_all0();
-    while (c_step < p_step && !sm.bail) {  // loads issued ahead of a bail-out
-      mbar_wait(&sm.full[c_step % kStages], (c_step / kStages) & 1, a.peers.timeout_ns, status, 400);
-      ++c_step;
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      unsigned step = 0, item = 0;
+      Item it;
+      bool ok = true;
+      for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x, ++item) {
+        const unsigned buf = item & 1, use = item >> 1;
+        if (use >= 1) ok = mbar_wait(&sm.acc_empty[buf], (use - 1) & 1, tmo, status, 300 + buf);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = sm.tmem_base + buf * kRankPad;
+        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+          const unsigned slot = step % nstages;
+          ok = mbar_wait(has_r ? &sm.ready[slot] : &sm.full[slot], (step / nstages) & 1, tmo, status, 200 + slot);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sm.ring + (size_t)slot * stage_bytes), b_addr = a_addr + off_b;
+#pragma unroll
+          for (int kk = 0; kk < kTileK / 8; ++kk) {
+            const uint64_t bdesc = smem_desc(b_addr + kk * 32, 16, 1024, 2);      // K-major: 32 B per K step of 8
+            const uint64_t adesc = STAGE == 1
+                                       ? smem_desc(a_addr + kk * 32, 16, 1024, 2)
+                                       // MN-major: a K step is 8 rows of 128 B (two atoms of 4 rows, 512 B apart);
+                                       // the next 32 of the 128 M-columns sit one box (4096 B) further on
+                                       : smem_desc(a_addr + kk * 1024, 4096, 512, 1);
+            umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdesc : kIdescAmn, !(kt == it.kt0 && kk == 0));
+          }
+          umma_commit(&sm.empty[slot]);
+        }
+        if (!ok) break;
+        umma_commit(&sm.acc_full[buf]);
+      }
+    }
+  } else if (warp >= kAdderWarp0 && warp < kAdderWarp0 + kAdderWarps) {
+    if (has_r) {
+      const int at = tid - kAdderWarp0 * 32;                  // 0 .. 63
+      constexpr int kAdders = kAdderWarps * 32;
+      unsigned step = 0;
+      Item it;
+      bool ok = true;
+      for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
+        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+          const unsigned slot = step % nstages;
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], (step / nstages) & 1, tmo, status, 500 + slot));
+          if (!ok) break;
+          unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
+          float4* pa = reinterpret_cast<float4*>(base);
+          const float4* pr = reinterpret_cast<const float4*>(base + off_r);
+#pragma unroll 4
+          for (int i = at; i < kATileBytes / 16; i += kAdders) {
+            float4 x = pa[i];
+            const float4 y = pr[i];
+            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+            pa[i] = x;
+          }
+          fence_async_smem();  // generic-proxy writes -> visible to the MMA and to the TMA store
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.ready[slot]);
+        }
+      }
+    }
+  } else if (warp == kStoreWarp) {
+    if (has_r && lane == 0) {
+      // M' goes back to the accumulator buffer; a ring slot is free once its store has READ the tile
+      unsigned step = 0;
+      Item it;
+      bool ok = true;
+      int prev_slot = -1;
+      for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
+        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)it.mat * kMapsPerMatrix;
+        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+          const unsigned slot = step % nstages;
+          ok = mbar_wait(&sm.ready[slot], (step / nstages) & 1, tmo, status, 600 + slot);
+          if (!ok) break;
+          tma_store_2d(maps + kMapA1, kt * kTileK, it.blk * kTileRows, sm.ring + (size_t)slot * stage_bytes);
+          tma_commit();
+          tma_wait_read1();   // every store but the newest has read its tile
+          if (prev_slot >= 0) mbar_arrive(&sm.empty[prev_slot]);
+          prev_slot = (int)slot;
+        }
+      }
+      tma_wait_read0();
+      if (prev_slot >= 0) mbar_arrive(&sm.empty[prev_slot]);
+      tma_wait_all0();
+    }
+  } else {
+    // ---- epilogue warps: TMEM -> registers -> partial block; the last item of a row block adds the partials ----
+    const int ew = warp - kEpilogueWarp0;                     // TMEM lane quarter of this warp (warp % 4)
+    const int erow = ew * 32 + lane;                          // row of the 128-row block held by this thread
+    const int rpad4 = (a.rank + 3) / 4;                       // float4 per row that carry data
+    const size_t item_base = STAGE == 1 ? 0 : (size_t)a.items_s1;
+    unsigned item = 0;
+    Item it;
+    for (int idx = blockIdx.x; decode_item(a, STAGE, idx, it); idx += gridDim.x, ++item) {
+      const unsigned buf = item & 1, use = item >> 1;
+      if (erow == 0) sm.epi_ok = mbar_wait(&sm.acc_full[buf], use & 1, tmo, status, 700 + buf) ? 1 : 0;
+      named_bar_sync(1, 128);
+      if (!sm.epi_ok) break;                                  // one decision for all four warps
+      tc_fence_after();
+      uint32_t v[16];
+      const uint32_t taddr = sm.tmem_base + buf * kRankPad + ((uint32_t)(ew * 32) << 16);
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+          : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);         // the MMA thread may start the item after next
+      float4* part = reinterpret_cast<float4*>(a.partial + (item_base + idx) * (size_t)(kTileRows * kRankPad)) + erow * 4;
+      for (int c4 = 0; c4 < rpad4; ++c4)
+        part[c4] = make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]), __uint_as_float(v[4 * c4 + 2]),
+                               __uint_as_float(v[4 * c4 + 3]));
+      // fixed-order reduction: whoever completes the row block last adds its partials, split 0 first
+      __threadfence();
+      named_bar_sync(1, 128);
+      if (erow == 0) {
+        const unsigned done = atomicAdd(a.counters + item_base + it.first, 1u);
+        sm.last_flag = done + 1 == (unsigned)it.splits;
+      }
+      named_bar_sync(1, 128);
+      if (sm.last_flag) {
+        __threadfence();
+        const LowRankMatrix& M = a.mats[it.mat];
+        const int row = it.blk * kTileRows + erow;
+        const int rows = STAGE == 1 ? M.n : M.m;
+        if (row < rows) {
+          float4 sum[4];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < it.splits; ++sp) {
+            const float4* src = reinterpret_cast<const float4*>(
+                                    a.partial + (item_base + it.first + sp) * (size_t)(kTileRows * kRankPad)) + erow * 4;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              if (c4 < rpad4) {
+                const float4 t = __ldcg(src + c4);
+                sum[c4].x += t.x; sum[c4].y += t.y; sum[c4].z += t.z; sum[c4].w += t.w;
+              }
+            }
+          }
+          float4* dst = reinterpret_cast<float4*>(dst_slot + (STAGE == 1 ? M.p_off : M.q_off) + (size_t)row * kRankPad);
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) if (c4 < rpad4) dst[c4] = sum[c4];
+        }
+      }
+      named_bar_sync(1, 128);   // last_flag and epi_ok are rewritten by the next item
     }
   }
   __syncthreads();
-  step_counter = c_step;  // uniform: every thread consumed the same steps
 }
 
-// Mean over ranks of a [rows x 16] region; optional Gram matrix per matrix.
+// Mean over ranks of a [rows x 16] region.
 __device__ void reduce_region(const LowRankArgs& a, size_t region_off, float* __restrict__ dst, size_t floats) {
   const int world = a.peers.world;
   const float inv = 1.f / (float)a.divisor;
@@ -384,6 +444,81 @@ __device__ bool publish_and_wait(const LowRankArgs& a, const Status& status, uns
   return s_ok != 0;
 }
 
+// S3 for one matrix: out = P Q^T, residual = M' - out.  Item = kS3Rows rows x kS3Cols columns; a thread owns four
+// columns and walks the rows in trips of kS3Trip with the loads of the next trip already in flight.
+template <int RH>   // RH = ceil(rank / 8): how many groups of eight rank columns take part
+__device__ void stage3_matrix(const LowRankArgs& a, SmemLayout& sm, const LowRankMatrix& M) {
+  const int tid = threadIdx.x;
+  const float* __restrict__ src = a.has_memory ? a.acc : a.g;
+  const int row_blocks = (M.n + kS3Rows - 1) / kS3Rows, col_blocks = (M.m + kS3Cols - 1) / kS3Cols;
+  for (int item = blockIdx.x; item < row_blocks * col_blocks; item += gridDim.x) {
+    const int rb = item / col_blocks, cb = item % col_blocks;
+    __syncthreads();
+    for (int i = tid; i < kS3Rows * kMaxRank; i += kThreads) {
+      const int rr = i / kMaxRank, c = i % kMaxRank, row = rb * kS3Rows + rr;
+      sm.prow[rr][c] = (row < M.n && c < a.rank) ? a.pt_orth[M.pt_off + (size_t)c * M.n + row] : 0.f;
+    }
+    __syncthreads();
+    const int col = cb * kS3Cols + tid * 4;
+    if (col >= M.m) continue;
+    const int valid = min(4, M.m - col);
+    float q[4][8 * RH];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+#pragma unroll
+      for (int h = 0; h < 2 * RH; ++h) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < valid && 4 * h < a.rank)   // columns >= rank of q_mean are zero
+          t = reinterpret_cast<const float4*>(a.q_mean + M.q_off + (size_t)(col + e) * kRankPad)[h];
+        q[e][4 * h] = t.x; q[e][4 * h + 1] = t.y; q[e][4 * h + 2] = t.z; q[e][4 * h + 3] = t.w;
+      }
+    }
+    const int rows = min(kS3Rows, M.n - rb * kS3Rows);
+    const bool vec = valid == 4 && (M.m & 3) == 0;
+    const size_t base0 = (size_t)M.g_off + (size_t)(rb * kS3Rows) * M.m + col;
+    auto fetch = [&](float4 (&mv)[kS3Trip], int r0) {
+#pragma unroll
+      for (int u = 0; u < kS3Trip; ++u) {
+        mv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r0 + u < rows && a.has_memory && vec)
+          mv[u] = *reinterpret_cast<const float4*>(src + base0 + (size_t)(r0 + u) * M.m);
+      }
+    };
+    float4 cur[kS3Trip], nxt[kS3Trip];
+    fetch(cur, 0);
+    for (int r0 = 0; r0 < rows; r0 += kS3Trip) {
+      fetch(nxt, r0 + kS3Trip);   // rows past the item read nothing
+#pragma unroll
+      for (int u = 0; u < kS3Trip; ++u) {
+        const int rr = r0 + u;
+        if (rr >= rows) break;
+        const size_t base = base0 + (size_t)rr * M.m;
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 8 * RH; ++c) {
+          const float p = sm.prow[rr][c];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] += p * q[e][c];
+        }
+        if (vec) {
+          if (a.has_memory)
+            *reinterpret_cast<float4*>(a.acc + base) =
+                make_float4(cur[u].x - o[0], cur[u].y - o[1], cur[u].z - o[2], cur[u].w - o[3]);
+          *reinterpret_cast<float4*>(a.out + base) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+          for (int e = 0; e < valid; ++e) {
+            const float m1 = src[base + e];
+            if (a.has_memory) a.acc[base + e] = m1 - o[e];
+            a.out[base + e] = o[e];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kS3Trip; ++u) cur[u] = nxt[u];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -395,14 +530,8 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   float* const slot_p = my_slot;                 // [p_floats]
   float* const slot_q = my_slot + a.p_floats;    // [q_floats]
 
-  // ---- set-up: barriers, TMEM ----
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.mma_done[s], 1); }
-    mbar_init(&sm.item_done, 1);
-    sm.bail = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
+  // ---- set-up: TMEM (the mbarriers are initialised by each GEMM stage) ----
+  if (tid == 0) sm.bars_valid = 0;
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                  "r"(kTmemCols) : "memory");
@@ -411,18 +540,16 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  unsigned steps = 0, items = 0;
 
-  // Phase groups (bit mask in a.phases, same meaning as the other exchanges):
-  //   compress: S1 ... exchange happens twice inside; a single launch runs
-  //   everything, the split launches of the one-GPU emulation run
-  //   [S1 | publish P] [reduce P, O, S2 | publish Q] [reduce Q, S3] as three
-  //   launches selected by a.part (0 = all, 1..3 = that part only).
-  const int part = a.part & 0xff;   // bit 8 of a.part asks CTA 0 to record per-phase cycle counts in status[8..]: wait, smem work, barrier, MMA issue, fence, commit + epilogue, steps (units of 16 cycles)
+  // A single launch runs everything; the split launches of the one-GPU emulation run
+  //   [S1 | publish P] [reduce P, O, S2 | publish Q] [reduce Q, S3]
+  // as three launches selected by a.part (0 = all, 1..3 = that part only).
+  const int part = a.part;
   const bool part1 = part == 0 || part == 1;
   const bool part2 = part == 0 || part == 2;
   const bool part3 = part == 0 || part == 3;
   bool ok = true;
+  const size_t gthreads = (size_t)gridDim.x * kThreads, gtid = (size_t)blockIdx.x * kThreads + tid;
 
   if (part1) {
     if (tid < world && tid != rank && a.peers.seq > 2) {   // every CTA: none may zero the slot before the peers are done with it
@@ -430,14 +557,15 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     __syncthreads();
-    // zero this rank's partial-sum slot (P and Q regions)
+    // zero this rank's slot (P and Q regions: rows of a last, partial block are never written otherwise),
+    // the Gram accumulators and the completion counters of both GEMM stages
     const size_t nfl = (size_t)a.p_floats + a.q_floats;
-    for (size_t i = ((size_t)blockIdx.x * kThreads + tid) * 4; i < nfl; i += (size_t)gridDim.x * kThreads * 4)
+    for (size_t i = gtid * 4; i < nfl; i += gthreads * 4)
       *reinterpret_cast<float4*>(my_slot + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (blockIdx.x == 0)
-      for (int i = tid; i < a.nmat * kRankPad * kRankPad; i += kThreads) a.gram[i] = 0.0;
+    for (size_t i = gtid; i < (size_t)a.nmat * kRankPad * kRankPad; i += gthreads) a.gram[i] = 0.0;
+    for (size_t i = gtid; i < (size_t)a.items_s1 + a.items_s2; i += gthreads) a.counters[i] = 0u;
     ok = bar.sync();
-    if (ok) gemm_stage<1>(a, sm, status, slot_p, steps, items);
+    if (ok) gemm_stage<1>(a, sm, status, slot_p);
     fence_async_all();
     ok = bar.sync();
   }
@@ -448,10 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   }
 
   if (part2) {
-    if (ok) {
-      // P = mean over ranks; Gram matrices
-      reduce_region(a, 0, a.p_mean, a.p_floats);
-    }
+    if (ok) reduce_region(a, 0, a.p_mean, a.p_floats);   // P = mean over ranks
     ok = bar.sync() && ok;
     if (ok) {
       // Gram: one thread per row, shared-memory fp64 accumulation per matrix
@@ -461,13 +586,13 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         __syncthreads();
         for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
           const float* pr = a.p_mean + M.p_off + (size_t)row * kRankPad;
-          float v[8];
+          float v[kMaxRank];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) v[c] = c < a.rank ? pr[c] : 0.f;
+          for (int c = 0; c < kMaxRank; ++c) v[c] = c < a.rank ? pr[c] : 0.f;
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
+          for (int c = 0; c < kMaxRank; ++c)
 #pragma unroll
-            for (int d = c; d < 8; ++d)
+            for (int d = c; d < kMaxRank; ++d)
               if (d < a.rank) atomicAdd(&sm.gram[c][d], (double)v[c] * (double)v[d]);
         }
         __syncthreads();
@@ -486,11 +611,11 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         const LowRankMatrix& M = a.mats[mat];
         if (tid == 0) {
           const int r = a.rank;
-          double R[8][8] = {};
+          double (&R)[kMaxRank][kMaxRank] = sm.gram;   // the factor overwrites the (finished) Gram scratch
           const double* G = a.gram + (size_t)mat * 256;
           for (int j = 0; j < r; ++j) {
             for (int i = 0; i <= j; ++i) {
-              double s = G[i * kRankPad + j];
+              double s = __ldcg(G + i * kRankPad + j);
               for (int k = 0; k < i; ++k) s -= R[k][i] * R[k][j];
               if (i == j) R[i][j] = s > 0.0 ? sqrt(s) : 0.0;
               else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;
@@ -510,9 +635,9 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         __syncthreads();
         for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
           const float* pr = a.p_mean + M.p_off + (size_t)row * kRankPad;
-          float v[8];
+          float v[kMaxRank];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) v[c] = c < a.rank ? pr[c] : 0.f;
+          for (int c = 0; c < kMaxRank; ++c) v[c] = c < a.rank ? pr[c] : 0.f;
           for (int c = 0; c < a.rank; ++c) {
             double s = 0.0;
             for (int k = 0; k <= c; ++k) s += (double)v[k] * sm.rinv[k][c];
@@ -521,10 +646,12 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         }
         __syncthreads();
       }
+      if (part != 0)   // split launch: the counters of this stage were zeroed by an earlier launch's part 1; do it again
+        for (size_t i = gtid; i < (size_t)a.items_s2; i += gthreads) a.counters[a.items_s1 + i] = 0u;
     }
     fence_async_all();  // pt_orth is read by TMA next
     ok = bar.sync() && ok;
-    if (ok) gemm_stage<2>(a, sm, status, slot_q, steps, items);
+    if (ok) gemm_stage<2>(a, sm, status, slot_q);
     ok = bar.sync() && ok;
   }
 
@@ -549,81 +676,14 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
           for (int c = 0; c < a.rank; ++c) a.qt[M.qt_off + (size_t)c * M.m + j] = qr[c];
         }
       }
-      // S3: out = P Q^T, residual = M' - out.  Item = kS3Rows rows x 1024 columns.
       for (int mat = 0; mat < a.nmat; ++mat) {
-        const LowRankMatrix& M = a.mats[mat];
-        const float* __restrict__ src = a.has_memory ? a.acc : a.g;
-        const int row_blocks = (M.n + kS3Rows - 1) / kS3Rows, col_blocks = (M.m + 1023) / 1024;
-        for (int item = blockIdx.x; item < row_blocks * col_blocks; item += gridDim.x) {
-          const int rb = item / col_blocks, cb = item % col_blocks;
-          __syncthreads();
-          for (int i = tid; i < kS3Rows * kMaxRank; i += kThreads) {
-            const int rr = i / kMaxRank, c = i % kMaxRank, row = rb * kS3Rows + rr;
-            sm.prow[rr][c] = (row < M.n && c < a.rank) ? a.pt_orth[M.pt_off + (size_t)c * M.n + row] : 0.f;
-          }
-          __syncthreads();
-          const int col = cb * 1024 + tid * 4;
-          if (col < M.m) {
-            const int valid = min(4, M.m - col);
-            float q[4][8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
-              if (e < valid) {   // columns >= rank of q_mean are zero
-                const float4* qp = reinterpret_cast<const float4*>(a.q_mean + M.q_off + (size_t)(col + e) * kRankPad);
-                lo4 = qp[0];
-                if (a.rank > 4) hi4 = qp[1];
-              }
-              q[e][0] = lo4.x; q[e][1] = lo4.y; q[e][2] = lo4.z; q[e][3] = lo4.w;
-              q[e][4] = hi4.x; q[e][5] = hi4.y; q[e][6] = hi4.z; q[e][7] = hi4.w;
-            }
-            const int rows = min(kS3Rows, M.n - rb * kS3Rows);
-            const bool vec = valid == 4 && (M.m & 3) == 0;
-            for (int r0 = 0; r0 < rows; r0 += kS3Trip) {
-              // kS3Trip rows per trip: issue the loads of M' first, then compute and store
-              float4 mv[kS3Trip];
-#pragma unroll
-              for (int u = 0; u < kS3Trip; ++u) {
-                mv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r0 + u < rows && a.has_memory && vec)
-                  mv[u] = *reinterpret_cast<const float4*>(src + (size_t)M.g_off + (size_t)(rb * kS3Rows + r0 + u) * M.m + col);
-              }
-#pragma unroll
-              for (int u = 0; u < kS3Trip; ++u) {
-                const int rr = r0 + u;
-                if (rr >= rows) break;
-                const size_t base = (size_t)M.g_off + (size_t)(rb * kS3Rows + rr) * M.m + col;
-                float o[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float s = 0.f;
-#pragma unroll
-                  for (int c = 0; c < 8; ++c) s += sm.prow[rr][c] * q[e][c];
-                  o[e] = s;
-                }
-                if (vec) {
-                  if (a.has_memory)
-                    *reinterpret_cast<float4*>(a.acc + base) =
-                        make_float4(mv[u].x - o[0], mv[u].y - o[1], mv[u].z - o[2], mv[u].w - o[3]);
-                  *reinterpret_cast<float4*>(a.out + base) = make_float4(o[0], o[1], o[2], o[3]);
-                } else {
-                  for (int e = 0; e < valid; ++e) {
-                    const float m1 = src[base + e];
-                    if (a.has_memory) a.acc[base + e] = m1 - o[e];
-                    a.out[base + e] = o[e];
-                  }
-                }
-              }
-            }
-          }
-        }
+        if (a.rank <= 8) stage3_matrix<1>(a, sm, a.mats[mat]);
+        else stage3_matrix<2>(a, sm, a.mats[mat]);
       }
     }
   }
 
   // ---- teardown ----
-  __syncthreads();
-  if (tid == kProducerThread) tma_wait_all0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
@@ -671,7 +731,8 @@ cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream)
 // Host: encode the five tensor maps of one matrix.
 //   G1 : gradient, box 32 x 128 (stage-1 A operand)
 //   A1 : accumulator, box 32 x 128 (residual load, M' store)
-//   M2 : M' (accumulator, or gradient without memory), box 32 x 32, not swizzled (transposed by the CTA in stage 2)
+//   M2 : M' (accumulator, or gradient without memory), box 32 x 32, 128-byte rows swizzled in 32-byte atoms: the
+//        MN-major TF32 operand layout of stage 2
 //   Qt : Q^T [16][m], box 32 x 16;  Pt : P^T [16][n], box 32 x 16
 int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m) {
   CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(maps_out);
@@ -690,19 +751,19 @@ int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float*
   }
   EncodeFn cuTensorMapEncodeTiled_rt = encode_fn;
   auto enc = [cuTensorMapEncodeTiled_rt](CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                uint32_t box_outer, bool swizzle = true) -> CUresult {
+                uint32_t box_outer, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) -> CUresult {
     cuuint64_t dims[2] = {inner, outer};
     cuuint64_t strides[1] = {inner * 4};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     return cuTensorMapEncodeTiled_rt(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
-                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
   CUresult r;
   if ((r = enc(maps + kMapG1, g, m, n, 32, 128)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapA1, acc ? acc : g, m, n, 32, 128)) != CUDA_SUCCESS) return (int)r;
-  if ((r = enc(maps + kMapM2, acc ? acc : g, m, n, 32, 32, false)) != CUDA_SUCCESS) return (int)r;
+  if ((r = enc(maps + kMapM2, acc ? acc : g, m, n, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapQt, qt, m, kRankPad, 32, 16)) != CUDA_SUCCESS) return (int)r;
   if ((r = enc(maps + kMapPt, pt, n, kRankPad, 32, 16)) != CUDA_SUCCESS) return (int)r;
   return 0;

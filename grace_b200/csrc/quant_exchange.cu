@@ -32,6 +32,7 @@
 #include "exchange.h"
 #include "philox.cuh"
 #include "segments.cuh"
+#include "gradio.cuh"
 
 namespace grace {
 
@@ -193,7 +194,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
           for (long long i = b0 + 4ll * tid; i < e0; i += kIterElems) {
             const int valid = (e0 - i) >= 4 ? 4 : (int)(e0 - i);
             float gv[4], rv[4] = {0.f, 0.f, 0.f, 0.f}, av[4];
-            load4(a.g, i, valid, gv);
+            load4g(a.g, a.g_dtype, i, valid, gv);
             if (a.acc && a.beta != 0.f) load4(a.acc, i, valid, rv);
 #pragma unroll
             for (int j = 0; j < 4; ++j) av[j] = a.beta * rv[j] + a.gamma * gv[j];
@@ -239,7 +240,8 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
 
     // ---- pass E: encode into the send slot, write the residual ----
     if (ok && lo < hi) {
-      const float* __restrict__ src = (T::stats && a.acc) ? a.acc : a.g;
+      const void* __restrict__ src = (T::stats && a.acc) ? (const void*)a.acc : a.g;
+      const int src_dtype = (T::stats && a.acc) ? (int)kGradF32 : a.g_dtype;
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         SegScalars sc{0.f, 0.f, 0.f, 0.f};
         if (T::stats) {
@@ -259,9 +261,9 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
             float gv[4] = {0.f, 0.f, 0.f, 0.f}, rv[4] = {0.f, 0.f, 0.f, 0.f};
             if (pvalid[q]) {
               if (T::stats) {
-                load4(src, pi, pvalid[q], gv);
+                load4g(src, src_dtype, pi, pvalid[q], gv);
               } else {
-                load4(a.g, pi, pvalid[q], gv);
+                load4g(a.g, a.g_dtype, pi, pvalid[q], gv);
                 if (a.acc && a.beta != 0.f) load4(a.acc, pi, pvalid[q], rv);
               }
             }
@@ -629,7 +631,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                 const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w4[q].y));
                 ov[0] = f01.x * a.scale; ov[1] = f01.y * a.scale; ov[2] = f23.x * a.scale; ov[3] = f23.y * a.scale;
               }
-              if (valid) store4(a.out, i, valid, ov);
+              if (valid) store4g(a.out, a.g_dtype, i, valid, ov);
             }
           }
         });
@@ -733,7 +735,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                 const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
                 const float ov[4] = {acc16[4 * v4] * a.scale, acc16[4 * v4 + 1] * a.scale,
                                      acc16[4 * v4 + 2] * a.scale, acc16[4 * v4 + 3] * a.scale};
-                store4(a.out, iv, valid, ov);
+                store4g(a.out, a.g_dtype, iv, valid, ov);
               }
             } else {
               // bit-packed codes: word j of a group holds, in bit l, the code bit of element 4 l + j
@@ -786,7 +788,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                     else if (C == kCodecEFSign) ov[j] = acc[gi][j] / a.lr;
                     else ov[j] = acc[gi][j] * a.scale;
                   }
-                  if (valid) store4(a.out, i, valid, ov);
+                  if (valid) store4g(a.out, a.g_dtype, i, valid, ov);
                 }
               }
             }
@@ -885,7 +887,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               else if (C == kCodecEFSign) ov[j] = sum[q][j] / a.lr;
               else ov[j] = sum[q][j] * a.scale;
             }
-            if (valid) store4(a.out, i, valid, ov);
+            if (valid) store4g(a.out, a.g_dtype, i, valid, ov);
           }
         }
       });

@@ -42,6 +42,7 @@
 #include "exchange.h"
 #include "philox.cuh"
 #include "segments.cuh"
+#include "gradio.cuh"
 
 namespace grace {
 
@@ -160,20 +161,84 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
   chunk = (chunk + kIterElems - 1) / kIterElems * kIterElems;
   const long long lo = (long long)blockIdx.x * chunk;
   const long long hi = lo + chunk < a.total ? lo + chunk : a.total;
-  const float* __restrict__ src = a.acc ? a.acc : a.g;
+  const void* __restrict__ src = a.acc ? (const void*)a.acc : a.g;   // what the passes after A re-read
+  const int src_dtype = a.acc ? (int)kGradF32 : a.g_dtype;
   const bool topk = a.mode == kSparseTopK;
   const bool randomk = a.mode == kSparseRandomK;
   const bool dense_decode = kTile && !randomk;  // tile-ordered lists and decode
 
-  if (a.phases & kPhaseCompress) {
-    // Before overwriting the slot of parity (seq & 1): every peer must have
-    // finished reading what sequence seq-2 put there.
-    // Every CTA waits (the acknowledgement words are local memory), so none of them can touch the slot early.
+  if (a.phases & (kPhaseCompress | kPhaseClip)) {
+    // Before overwriting anything of parity (seq & 1) in this rank's heap (send slot, clipping sums): every peer
+    // must have finished reading what sequence seq-2 put there.  Every CTA waits (the acknowledgement words are
+    // local memory), so none of them can touch the slot early.
     if (tid < world && tid != rank && a.peers.seq > 2) {
       const uint64_t* ack = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ack_off) + tid;
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     __syncthreads();
+  }
+
+  // ---- phase C (DGC gradient clipping): per tensor sum of g^2 on this rank, published to the peers; the clamp
+  //      bound sqrt(mean over ranks of the sums) is then formed by every rank from the W published values, in rank
+  //      order.  Replaces torch.sum(g*g) + all_reduce of grace_dl/torch/memory/dgc.py:16-19. ----
+  double* const my_clip = reinterpret_cast<double*>(my_heap + a.clip_off) + (size_t)(a.peers.seq & 1) * a.nseg;
+  if (a.phases & kPhaseClip) {
+    __shared__ double s_sq[kBlock / 32];
+    bool okc = !status.failed();
+    if (okc && lo < hi) {
+      for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+        double part = 0.0;
+        for (long long base = b0 + 4ll * tid; base < e0; base += (long long)kUnroll * kIterElems) {
+          float gv[kUnroll][4];
+#pragma unroll
+          for (int q = 0; q < kUnroll; ++q) {
+            const long long i = base + (long long)q * kIterElems;
+            const int valid = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) gv[q][j] = 0.f;
+            if (valid) load4g(a.g, a.g_dtype, i, valid, gv[q]);
+          }
+          float l = 0.f;
+#pragma unroll
+          for (int q = 0; q < kUnroll; ++q)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) l += gv[q][j] * gv[q][j];
+          part += (double)l;
+        }
+        part = warp_sum(part);
+        if ((tid & 31) == 0) s_sq[tid >> 5] = part;
+        __syncthreads();
+        if (tid == 0) {
+          double tot = 0.0;
+          for (int w = 0; w < kBlock / 32; ++w) tot += s_sq[w];
+          atomicAdd(&a.clip_sq[s], tot);
+        }
+        __syncthreads();
+      });
+    }
+    okc = bar.sync();
+    if (okc)
+      for (int s = blockIdx.x * kBlock + tid; s < a.nseg; s += gridDim.x * kBlock) {
+        my_clip[s] = __ldcg(&a.clip_sq[s]);
+        a.clip_sq[s] = 0.0;   // left zero for the next launch
+      }
+    okc = bar.sync();
+    if (blockIdx.x == 0 && tid < world && okc) {
+      __threadfence_system();
+      uint64_t* flag = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.clip_ready_off) + rank;
+      st_release_sys(flag, a.peers.seq);
+    }
+  }
+
+  if (a.phases & kPhaseCompress) {
+    __shared__ float s_bound;
+    if (a.clip_off) {   // the peers' sums must have arrived before the first clamp
+      if (tid < world) {
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.clip_ready_off) + tid;
+        wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid);
+      }
+      __syncthreads();
+    }
     if (blockIdx.x == 0 && tid == 0) { my_hdr[0] = 0; my_hdr[1] = 0; }
     if (kTile && dense_decode) {   // tile counters of the ordering step; many grid barriers lie between here and their use
       const long long nb1 = ((a.total + kTileElems - 1) >> kTileShift) + 1;
@@ -187,7 +252,22 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         float tmax = -INFINITY;
         const bool read_acc = a.u || (a.acc && a.beta != 0.f);
-        const float clip = a.clip ? a.clip[s] : INFINITY;   // element-wise clamp of the incoming gradient
+        float clip = INFINITY;   // element-wise clamp of the incoming gradient
+        if (a.clip_off) {
+          __syncthreads();
+          if (tid == 0) {
+            double tot = 0.0;
+            for (int p = 0; p < world; ++p) {   // rank order: the same bound, bit for bit, on every GPU
+              const char* pc = a.peers.heap[p] + a.clip_off + ((size_t)(a.peers.seq & 1) * a.nseg + s) * 8;
+              unsigned long long raw;
+              asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(raw) : "l"(pc));
+              tot += __longlong_as_double((long long)raw);
+            }
+            s_bound = (float)sqrt(tot / (double)world);
+          }
+          __syncthreads();
+          clip = s_bound;
+        }
         auto trip_a = [&](auto full_tag, long long base) {
           constexpr bool kFull = decltype(full_tag)::value;   // all kUnroll vectors fully inside the range
           // issue every load of the trip before the first dependent instruction
@@ -200,7 +280,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
 #pragma unroll
             for (int j = 0; j < 4; ++j) { rv[q][j] = 0.f; uv[q][j] = 0.f; gv[q][j] = 0.f; }
             if (valid[q]) {
-              load4(a.g, i, valid[q], gv[q]);
+              load4g(a.g, a.g_dtype, i, valid[q], gv[q]);
               if (read_acc) load4(a.acc, i, valid[q], rv[q]);
               if (a.u) load4(a.u, i, valid[q], uv[q]);
             }
@@ -210,7 +290,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             if (!valid[q]) continue;
             const long long i = base + (long long)q * kIterElems;
             float av[4];
-            if (a.clip) {
+            if (a.clip_off) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) gv[q][j] = fminf(fmaxf(gv[q][j], -clip), clip);
             }
@@ -290,7 +370,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
                 for (int q = 0; q < kUnroll; ++q) {
                   const long long i = base + (long long)q * kIterElems;
                   valid[q] = i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0;
-                  if (valid[q]) load4(src, i, valid[q], av[q]);
+                  if (valid[q]) load4g(src, src_dtype, i, valid[q], av[q]);
                 }
 #pragma unroll
                 for (int q = 0; q < kUnroll; ++q) {
@@ -377,7 +457,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         const Philox4 r4 = philox_group((uint64_t)(j >> 2), a.rk_step, 7u, a.seg_seed[sgm]);
         const unsigned word = (j & 3) == 0 ? r4.x : ((j & 3) == 1 ? r4.y : ((j & 3) == 2 ? r4.z : r4.w));
         const long long idx = a.segs[sgm].offset + (long long)(word % (unsigned)a.segs[sgm].numel);
-        my_vals[e] = src[idx];
+        my_vals[e] = load1g(src, src_dtype, idx);
         my_idx[e] = (int)idx;
       }
       ok = bar.sync();
@@ -390,7 +470,8 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         const unsigned pivot = a.state[s].prefix;
         const unsigned need = a.state[s].need;
         float thr = a.threshold;
-        if (!topk) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));
+        if (!topk && !a.strict) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));   // dist flavour: capped by max(x)
+        const bool strict = a.strict != 0;                                                  // Horovod flavour: |x| > threshold
         auto trip_b = [&](auto full_tag, long long base) {
           constexpr bool kFull = decltype(full_tag)::value;
           int valid[kUnroll];
@@ -401,7 +482,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             valid[q] = kFull ? 4 : (i < e0 ? ((e0 - i) >= 4 ? 4 : (int)(e0 - i)) : 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) avs[q][j] = 0.f;
-            if (valid[q]) load4(src, i, valid[q], avs[q]);
+            if (valid[q]) load4g(src, src_dtype, i, valid[q], avs[q]);
           }
 #pragma unroll
           for (int q = 0; q < kUnroll; ++q) {
@@ -420,7 +501,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
                 kp = (__float_as_uint(av[j]) & 0x7fffffffu) >> key_shift;
                 hit = kp >= pivot;
               } else {
-                hit = fabsf(av[j]) >= thr;
+                hit = strict ? fabsf(av[j]) > thr : fabsf(av[j]) >= thr;
               }
               if (hit) {
                 bool sel = true;
@@ -894,6 +975,7 @@ cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t s
     err = cudaMemsetAsync(a.state, 0, sizeof(SparseState) * (size_t)(a.nseg + 1), stream);
     if (err != cudaSuccess) return err;
   }
+  if ((a.phases & kPhaseClip) && (!a.clip_off || !a.clip_sq)) return cudaErrorInvalidValue;
   SparseArgs copy = a;
   void* params[] = {&copy};
   const void* fn = a.tile_start ? (const void*)sparse_exchange_kernel<true> : (const void*)sparse_exchange_kernel<false>;

@@ -23,6 +23,8 @@ from ..parallel.symm import SymmetricHeap
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
 PHASE_REDUCE = 8  # two-phase (alltoall) mode: reduce my chunk, re-encode, publish again
+PHASE_CLIP = 16   # sparse exchange with DGC gradient clipping: per-tensor sums of squares, published before compress
+GRAD_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 SPARSE_TOPK, SPARSE_THRESHOLD, SPARSE_RANDOMK = 0, 1, 2
 CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8}
 
@@ -101,7 +103,7 @@ class ExchangeChannel:
     """Flags + two send slots on the symmetric heap, and local scratch."""
 
     def __init__(self, heap: SymmetricHeap, slot_bytes: int, nseg: int, timeout_ms: float = 10000.0,
-                 sm_limit: Optional[int] = None):
+                 sm_limit: Optional[int] = None, clip: bool = False):
         C = native()
         self.heap = heap
         self.device = heap.device
@@ -124,6 +126,13 @@ class ExchangeChannel:
             for off in self.guard_off:
                 heap.view(off, GUARD_BYTES, torch.uint8).fill_(GUARD_PATTERN)
         self.ready2_off = heap.alloc(C.MAX_WORLD * 8) if heap.free_bytes >= C.MAX_WORLD * 8 + 256 else 0
+        # DGC gradient clipping: every rank publishes its per-tensor sums of squares (two parities) + a flag pad
+        self.clip_off = self.clip_ready_off = 0
+        self.clip_sq = None
+        if clip:
+            self.clip_ready_off = heap.alloc(C.MAX_WORLD * 8)
+            self.clip_off = heap.alloc(2 * max(1, nseg) * 8)
+            self.clip_sq = torch.zeros(max(1, nseg), dtype=torch.float64, device=heap.device)
         self.seq = 0
         self._grids = {}
         self._events = [None, None]
@@ -217,6 +226,9 @@ class ExchangeChannel:
         self.heap.view(self.flags_off, 2 * C.MAX_WORLD, torch.int64).zero_()
         if self.ready2_off:
             self.heap.view(self.ready2_off, C.MAX_WORLD, torch.int64).zero_()
+        if self.clip_ready_off:
+            self.heap.view(self.clip_ready_off, C.MAX_WORLD, torch.int64).zero_()
+            self.clip_sq.zero_()
         self.status.zero_()
         self.hist.zero_()
         self.sparse_state.zero_()
@@ -280,7 +292,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
                scale: float = 1.0, levels: int = 3, phases: int = PHASE_ALL, seq: Optional[int] = None,
                grid: Optional[int] = None, kprefix: Optional[torch.Tensor] = None,
                seg_seed: Optional[torch.Tensor] = None, rk_step: int = 0,
-               clip: Optional[torch.Tensor] = None, tile_decode: bool = False) -> int:
+               clip: bool = False, strict: bool = False, tile_decode: bool = False) -> int:
     """``tile_decode``: the slot was sized with ``sparse_slot_bytes(cap, total)`` and every rank orders its list
     by output tile (see ``tile_decode_wanted``)."""
     C = native()
@@ -292,9 +304,13 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
     td = channel.tile_scratch(layout.total) if (tile_decode and mode != SPARSE_RANDOMK) else None
     need = -(-layout.total // 2048)
     grid = max(1, min(grid, max(need, 1)))
-    for t in (g, acc, u, out):
+    for t in (acc, u, out):
         if t is not None:
             assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    assert g.is_cuda and g.dtype in GRAD_DTYPE and g.data_ptr() % (16 if g.dtype == torch.float32 else 8) == 0, \
+        "gradients: fp32 (16-byte aligned), bf16 or fp16 (8-byte aligned) on the GPU"
+    if clip and not channel.clip_off:
+        raise ValueError("this channel was built without a clipping area (ExchangeChannel(..., clip=True))")
     cand_cap = 0
     if mode == SPARSE_TOPK and levels == 3 and (phases & PHASE_COMPRESS):
         if channel.cand is None:
@@ -308,7 +324,9 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
         _stream_ptr(), channel.cand.data_ptr() if cand_cap else 0,
         (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
-        _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF, _ptr(clip),
+        _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF,
+        channel.clip_off if clip else 0, channel.clip_ready_off if clip else 0,
+        channel.clip_sq.data_ptr() if clip else 0, int(strict), GRAD_DTYPE[g.dtype],
         td[0].data_ptr() if td else 0, td[1].data_ptr() if td else 0, td[2].data_ptr() if td else 0,
     )
     channel.post_status()
@@ -331,9 +349,13 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         grid = channel.max_grid("quant")
     need = -(-layout.total // 2048)
     grid = max(1, min(grid, max(need, 1)))
-    for t in (g, acc, mom, out):
+    for t in (acc, mom):
         if t is not None:
             assert t.dtype == torch.float32 and t.is_cuda and t.data_ptr() % 16 == 0, "fp32, cuda, 16-byte aligned"
+    assert g.is_cuda and g.dtype in GRAD_DTYPE and g.data_ptr() % (16 if g.dtype == torch.float32 else 8) == 0, \
+        "gradients: fp32 (16-byte aligned), bf16 or fp16 (8-byte aligned) on the GPU"
+    assert out is None or (out.dtype == g.dtype and out.data_ptr() % (16 if g.dtype == torch.float32 else 8) == 0), \
+        "the output has the gradient's element type"
     recv_local = recv_mc = recv_stride = 0
     if recv is not None and phases == PHASE_ALL:
         buf, recv_stride = recv
@@ -344,7 +366,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         int(deterministic), int(first_step), beta, gamma, mom_beta, lr, scale, seed & (2 ** 64 - 1), step & 0xFFFFFFFF,
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
-        grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride,
+        grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
     )
     channel.post_status()
     return seq

@@ -22,9 +22,10 @@ from .exchange import (CODEC, PHASE_ALL, PHASE_COMPRESS, PHASE_EXCHANGE, Exchang
                        run_quant, segments_to_device, _stream_ptr)
 
 RANK_PAD = 16
-K_TILES_PER_ITEM = 16
 TILE_K = 32
 TILE_ROWS = 128
+MIN_K_TILES_PER_ITEM = 8      # a work item streams at least 8 x 16 KiB of the matrix (unless the matrix is smaller)
+MAX_RANK = 16
 
 
 def eligible(shape: Sequence[int]) -> bool:
@@ -37,10 +38,20 @@ def eligible(shape: Sequence[int]) -> bool:
     return n % 4 == 0 and m % 4 == 0 and n >= 16 and m >= 16
 
 
-def _items(n_out: int, n_k: int) -> int:
+def choose_splits(n_out: int, n_k: int, grid: int) -> int:
+    """K splits per 128-row block of one GEMM stage: the work items (blocks x splits) should fill whole waves of
+    ``grid`` persistent CTAs, and an item should not be shorter than ``MIN_K_TILES_PER_ITEM`` K tiles."""
     blocks = -(-n_out // TILE_ROWS)
     ktiles = -(-n_k // TILE_K)
-    return blocks * (-(-ktiles // K_TILES_PER_ITEM))
+    max_splits = max(1, ktiles // MIN_K_TILES_PER_ITEM)
+    best, best_score = 1, -1.0
+    for splits in range(1, max_splits + 1):
+        items = blocks * splits
+        waves = -(-items // grid)
+        score = items / (waves * grid) - 1e-4 * splits     # fill of the last wave; ties go to fewer splits
+        if waves * (-(-ktiles // splits)) > 0 and score > best_score + 1e-9:
+            best, best_score = splits, score
+    return best
 
 
 def orthogonal_init(m: int, r: int, seed: int, device) -> torch.Tensor:
@@ -63,8 +74,8 @@ class LowRankPlan:
         self.device = device
         self.has_memory = has_memory
         self.steps = 0
-        if not 1 <= self.rank <= 8:
-            raise ValueError("the fused PowerSGD path supports ranks 1..8")
+        if not 1 <= self.rank <= MAX_RANK:
+            raise ValueError("the fused PowerSGD path supports ranks 1..%d" % MAX_RANK)
         self.matrices: List[Tuple[str, int, int, int]] = []   # name, offset, n, m
         self.others: List[int] = []                           # indices of densely exchanged tensors
         for i, (name, off, numel, shape) in enumerate(zip(layout.names, layout.offsets, layout.numels, shapes)):
@@ -77,14 +88,21 @@ class LowRankPlan:
         p_off = q_off = pt_off = qt_off = 0
         i1 = i2 = 0
         rows = []
+        grid = 148
+        try:
+            if torch.device(device).type == "cuda":
+                grid = max(1, C.lowrank_max_grid(torch.device(device).index or 0, sm_limit or 0))
+        except Exception:
+            pass
         for name, off, n, m in self.matrices:
-            rows.append(struct.pack("<qiiiiiiii", off, n, m, p_off, q_off, pt_off, qt_off, i1, i2) + b"\0" * 0)
+            s1, s2 = choose_splits(n, m, grid), choose_splits(m, n, grid)
+            rows.append(struct.pack("<qiiiiiiiiii", off, n, m, p_off, q_off, pt_off, qt_off, i1, i2, s1, s2))
             p_off += n * RANK_PAD
             q_off += m * RANK_PAD
             pt_off += n * RANK_PAD
             qt_off += m * RANK_PAD
-            i1 += _items(n, m)
-            i2 += _items(m, n)
+            i1 += -(-n // TILE_ROWS) * s1
+            i2 += -(-m // TILE_ROWS) * s2
         self.p_floats, self.q_floats = p_off, q_off
         self.items_s1, self.items_s2 = i1, i2
         nmat = len(self.matrices)
@@ -97,6 +115,10 @@ class LowRankPlan:
             self.pt_orth = torch.zeros(self.p_floats, dtype=torch.float32, device=device)
             self.qt = torch.zeros(self.q_floats, dtype=torch.float32, device=device)
             self.gram = torch.zeros(nmat * 256, dtype=torch.float64, device=device)
+            # split-K scratch: one 128 x 16 block of partial sums per work item, and the per-block completion counters
+            self.partial = torch.empty((self.items_s1 + self.items_s2) * TILE_ROWS * RANK_PAD, dtype=torch.float32,
+                                       device=device)
+            self.counters = torch.zeros(self.items_s1 + self.items_s2, dtype=torch.int32, device=device)
             qt_off = 0
             for name, off, n, m in self.matrices:
                 r = min(n, m, self.rank)
@@ -168,8 +190,8 @@ class LowRankPlan:
             g.data_ptr(), self.acc.data_ptr() if self.acc is not None else 0, out.data_ptr(), self.mats.data_ptr(),
             self.maps.data_ptr(), len(self.matrices), self.rank, int(self.has_memory), self.world, self.items_s1,
             self.items_s2, self.p_floats, self.q_floats, self.p_mean.data_ptr(), self.q_mean.data_ptr(),
-            self.pt_orth.data_ptr(), self.qt.data_ptr(), self.gram.data_ptr(), ch.barrier.data_ptr(),
-            ch.status.data_ptr(), self.ready2_off, part, heap.rank, heap.world, seq, ch.timeout_ns, heap.bases,
+            self.pt_orth.data_ptr(), self.qt.data_ptr(), self.gram.data_ptr(), self.partial.data_ptr(),
+            self.counters.data_ptr(), ch.barrier.data_ptr(), ch.status.data_ptr(), self.ready2_off, part, heap.rank, heap.world, seq, ch.timeout_ns, heap.bases,
             ch.ready_off, ch.ack_off, ch.slot_off[seq & 1], grid, _stream_ptr())
         ch.post_status()
         return seq

@@ -16,6 +16,12 @@ def pytest_collection_modifyitems(config, items):
     import torch
 
     if torch.cuda.is_available():
+        # a GPU test that waits on something that never comes (a lost rendezvous, a rank that died) must not
+        # take the whole run with it: every device-side wait is bounded, this bounds the host side
+        if config.pluginmanager.hasplugin("timeout"):
+            for item in items:
+                if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                    item.add_marker(pytest.mark.timeout(480))
         return
     skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:

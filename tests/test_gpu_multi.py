@@ -15,20 +15,23 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+def _token():
+    """Rendezvous file of one multi-process test (see tests/_rendezvous.py)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import new_token
+
+    return new_token()
 
 
 def _entry(rank, world, port, ret):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import init_group
+
+    init_group("nccl", rank, world, port, dev)
     try:
         ret[rank] = _body(rank, world, dev)
     finally:
@@ -100,7 +103,7 @@ def test_fused_exchange_matches_library_over_real_gpus():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = _port()
+        port = _token()
         procs = [ctx.Process(target=_entry, args=(r, world, port, ret)) for r in range(world)]
         for p in procs:
             p.start()
@@ -125,10 +128,13 @@ def test_fused_exchange_matches_library_over_real_gpus():
 
 def _timeout_entry(rank, world, port, ret):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import init_group
+
+    init_group("nccl", rank, world, port, dev)
     try:
         from grace_b200 import grace_from_params
         from grace_b200.ops.exchange import GraceCommError
@@ -165,7 +171,7 @@ def test_peer_that_stops_launching_is_reported_as_timeout():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = _port()
+        port = _token()
         procs = [ctx.Process(target=_timeout_entry, args=(r, 2, port, ret)) for r in range(2)]
         for p in procs:
             p.start()
@@ -181,10 +187,13 @@ def test_peer_that_stops_launching_is_reported_as_timeout():
 
 def _ddp_entry(rank, world, port, ret):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import init_group
+
+    init_group("nccl", rank, world, port, dev)
     try:
         from torch.nn.parallel import DistributedDataParallel as DDP
 
@@ -225,7 +234,7 @@ def test_ddp_comm_hook_with_fused_exchange():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = _port()
+        port = _token()
         procs = [ctx.Process(target=_ddp_entry, args=(r, world, port, ret)) for r in range(world)]
         for p in procs:
             p.start()

@@ -15,12 +15,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+def _token():
+    """Rendezvous file of one multi-process test (see tests/_rendezvous.py)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import new_token
+
+    return new_token()
 
 
 def _guard(res, label, fn, default):
@@ -152,10 +152,12 @@ def _push_body(rank, world, dev):
 
 def _entry(rank, world, port, ret, body=None):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import init_group
+
+    init_group("nccl", rank, world, port, dev)
     try:
         ret[rank] = (body or _body)(rank, world, dev)
     except Exception:  # noqa: BLE001 - reported by the parent; the rank still leaves through the barrier
@@ -171,7 +173,7 @@ def test_multicast_allreduce_matches_library_allreduce():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = _port()
+        port = _token()
         procs = [ctx.Process(target=_entry, args=(r, world, port, ret)) for r in range(world)]
         for p in procs:
             p.start()
@@ -198,7 +200,7 @@ def test_push_transport_gives_the_bits_of_the_pull_transport():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = _port()
+        port = _token()
         procs = [ctx.Process(target=_entry, args=(r, world, port, ret, _push_body)) for r in range(world)]
         for p in procs:
             p.start()
