@@ -173,7 +173,7 @@ PYBIND11_MODULE(_C, m) {
           a.mats = ptr<const LowRankMatrix>(mats); a.maps = ptr<const CUtensorMap_st>(maps); a.nmat = nmat;
           a.rank = rank_r; a.has_memory = has_memory; a.divisor = divisor; a.items_s1 = items_s1; a.items_s2 = items_s2;
           a.p_floats = p_floats; a.q_floats = q_floats; a.p_mean = ptr<float>(p_mean); a.q_mean = ptr<float>(q_mean);
-          a.pt_orth = ptr<float>(pt_orth); a.qt = ptr<float>(qt); a.gram = ptr<double>(gram);
+          a.pt_orth = ptr<float>(pt_orth); a.qt = ptr<float>(qt); a.gram_part = ptr<double>(gram);
           a.partial = ptr<float>(partial); a.counters = ptr<unsigned>(counters);
           if (!partial || !counters) throw std::invalid_argument("powersgd_exchange: split-K scratch missing");
           a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status); a.ready2_off = ready2_off;

@@ -214,7 +214,7 @@ struct LowRankArgs {
   float* q_mean;           // [q_floats]
   float* pt_orth;          // sum_n 16*n
   float* qt;               // sum_m 16*m: Q^T, persistent across steps (warm start)
-  double* gram;            // nmat * 256
+  double* gram_part;       // grid * nmat * 256: one partial Gram matrix per CTA and matrix (added in CTA order)
   float* partial;          // (items_s1 + items_s2) blocks of 128 x 16: split-K partial sums, one block per work item
   unsigned* counters;      // items_s1 + items_s2: finished items per row block (indexed by the block's first item)
   unsigned* barrier;

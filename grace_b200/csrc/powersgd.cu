@@ -562,7 +562,6 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
     const size_t nfl = (size_t)a.p_floats + a.q_floats;
     for (size_t i = gtid * 4; i < nfl; i += gthreads * 4)
       *reinterpret_cast<float4*>(my_slot + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (size_t i = gtid; i < (size_t)a.nmat * kRankPad * kRankPad; i += gthreads) a.gram[i] = 0.0;
     for (size_t i = gtid; i < (size_t)a.items_s1 + a.items_s2; i += gthreads) a.counters[i] = 0u;
     ok = bar.sync();
     if (ok) gemm_stage<1>(a, sm, status, slot_p);
@@ -579,27 +578,43 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
     if (ok) reduce_region(a, 0, a.p_mean, a.p_floats);   // P = mean over ranks
     ok = bar.sync() && ok;
     if (ok) {
-      // Gram: one thread per row, shared-memory fp64 accumulation per matrix
+      // Gram matrices P^T P in fp64, added in a fixed order at every level (lanes by shuffles, warps in warp order,
+      // CTAs in CTA order) so that two runs give the same bits: a thread takes one row, a warp adds its rows'
+      // products with shuffles, the CTA adds its warps and stores one partial matrix per CTA.
+      double* const wpart = reinterpret_cast<double*>(sm.ring);           // [warp][256], the ring is idle here
+      const int lane = tid & 31;
       for (int mat = 0; mat < a.nmat; ++mat) {
         const LowRankMatrix& M = a.mats[mat];
-        for (int i = tid; i < kMaxRank * kMaxRank; i += kThreads) (&sm.gram[0][0])[i] = 0.0;
-        __syncthreads();
-        for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
-          const float* pr = a.p_mean + M.p_off + (size_t)row * kRankPad;
-          float v[kMaxRank];
+        float v[kMaxRank];
 #pragma unroll
-          for (int c = 0; c < kMaxRank; ++c) v[c] = c < a.rank ? pr[c] : 0.f;
+        for (int c = 0; c < kMaxRank; ++c) v[c] = 0.f;
+        double acc_cd[kMaxRank] = {};   // row c of the upper triangle, one c at a time (keeps the register count low)
+        const int row0 = blockIdx.x * kThreads + tid;
+        for (int c = 0; c < a.rank; ++c) {
 #pragma unroll
-          for (int c = 0; c < kMaxRank; ++c)
+          for (int d = 0; d < kMaxRank; ++d) acc_cd[d] = 0.0;
+          for (int row = row0; row < M.n; row += gridDim.x * kThreads) {
+            const float* pr = a.p_mean + M.p_off + (size_t)row * kRankPad;
 #pragma unroll
-            for (int d = c; d < kMaxRank; ++d)
-              if (d < a.rank) atomicAdd(&sm.gram[c][d], (double)v[c] * (double)v[d]);
+            for (int d = 0; d < kMaxRank; ++d) v[d] = d < a.rank ? pr[d] : 0.f;
+            const double vc = (double)pr[c];
+#pragma unroll
+            for (int d = 0; d < kMaxRank; ++d) acc_cd[d] += vc * (double)v[d];
+          }
+#pragma unroll
+          for (int d = 0; d < kMaxRank; ++d) {
+            if (d < c || d >= a.rank) continue;   // uniform over the CTA
+            const double t = warp_sum(acc_cd[d]);
+            if (lane == 0) wpart[warp * 256 + c * kRankPad + d] = t;
+          }
         }
         __syncthreads();
-        if (tid < kMaxRank * kMaxRank) {
-          const int c = tid / kMaxRank, d = tid % kMaxRank;
-          if (c <= d && d < a.rank && sm.gram[c][d] != 0.0)
-            atomicAdd(&a.gram[(size_t)mat * 256 + c * kRankPad + d], sm.gram[c][d]);
+        if (tid < kRankPad * kRankPad) {
+          const int c = tid / kRankPad, d = tid % kRankPad;
+          double t = 0.0;
+          if (c <= d && d < a.rank)
+            for (int w = 0; w < kThreads / 32; ++w) t += wpart[w * 256 + tid];
+          a.gram_part[((size_t)blockIdx.x * a.nmat + mat) * 256 + tid] = t;
         }
         __syncthreads();
       }
@@ -609,13 +624,18 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       // O: P_orth = P R^-1 with R^T R = Gram (upper Cholesky), written transposed [16][n]
       for (int mat = 0; mat < a.nmat; ++mat) {
         const LowRankMatrix& M = a.mats[mat];
+        if (tid < kRankPad * kRankPad) {   // the CTAs' partial matrices, in CTA order
+          double t = 0.0;
+          for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(a.gram_part + ((size_t)b * a.nmat + mat) * 256 + tid);
+          (&sm.gram[0][0])[tid] = t;
+        }
+        __syncthreads();
         if (tid == 0) {
           const int r = a.rank;
-          double (&R)[kMaxRank][kMaxRank] = sm.gram;   // the factor overwrites the (finished) Gram scratch
-          const double* G = a.gram + (size_t)mat * 256;
+          double (*R)[kMaxRank] = reinterpret_cast<double (*)[kMaxRank]>(sm.ring);   // scratch: the ring is idle here
           for (int j = 0; j < r; ++j) {
             for (int i = 0; i <= j; ++i) {
-              double s = __ldcg(G + i * kRankPad + j);
+              double s = sm.gram[i][j];
               for (int k = 0; k < i; ++k) s -= R[k][i] * R[k][j];
               if (i == j) R[i][j] = s > 0.0 ? sqrt(s) : 0.0;
               else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;

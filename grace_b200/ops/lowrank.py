@@ -114,7 +114,7 @@ class LowRankPlan:
             self.q_mean = torch.zeros(self.q_floats, dtype=torch.float32, device=device)
             self.pt_orth = torch.zeros(self.p_floats, dtype=torch.float32, device=device)
             self.qt = torch.zeros(self.q_floats, dtype=torch.float32, device=device)
-            self.gram = torch.zeros(nmat * 256, dtype=torch.float64, device=device)
+            self.gram = torch.zeros(max(grid, 160) * nmat * 256, dtype=torch.float64, device=device)   # per-CTA partials
             # split-K scratch: one 128 x 16 block of partial sums per work item, and the per-block completion counters
             self.partial = torch.empty((self.items_s1 + self.items_s2) * TILE_ROWS * RANK_PAD, dtype=torch.float32,
                                        device=device)

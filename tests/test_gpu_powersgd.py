@@ -112,3 +112,39 @@ def test_warm_start_converges_on_a_low_rank_matrix():
         err.append(((out - m).norm() / m.norm()).item())
     vw.check()
     assert err[-1] < 3e-3 and err[-1] <= err[0] + 1e-6, err
+
+
+@pytest.mark.parametrize("r", [12, 16])
+def test_ranks_above_eight(r):
+    W, n, m = 2, 640, 1152
+    vw = _world(W, r, memory="none")
+    gen = torch.Generator().manual_seed(r)
+    base = torch.randn(n, 20, generator=gen) @ torch.randn(20, m, generator=gen)
+    mats = [(base + 0.1 * torch.randn(n, m, generator=gen)).to(_dev()) for _ in range(W)]
+    outs = vw.step([x.clone() for x in mats], "w")
+    vw.check()
+    from grace_b200.ops.lowrank import orthogonal_init
+    import zlib
+
+    q0 = orthogonal_init(m, r, vw.comms[0].seed ^ zlib.crc32(b"w"), _dev())
+    ref, _, _ = _reference(mats, q0, W)
+    assert ((outs[0] - ref).norm() / ref.norm()).item() < 5e-3
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_split_k_is_deterministic_run_to_run():
+    """Two independent runs on the same data give the same bits: the K splits of a row block are added in split
+    order, never in the order in which CTAs happen to finish."""
+    gen = torch.Generator().manual_seed(11)
+    m = torch.randn(1024, 8192, generator=gen).to(_dev())       # 8 row blocks x several K splits each
+    results = []
+    for _ in range(3):
+        vw = _world(1, 4)
+        first = vw.step([m.clone()], "w")[0].clone()
+        second = vw.step([m.clone()], "w")[0].clone()            # residual and warm start take part
+        vw.check()
+        plan = next(iter(vw.comms[0]._plans.values()))
+        results.append((first, second, plan.acc.clone(), plan.q_memory()["w"].clone()))
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert torch.equal(a, b)
