@@ -121,6 +121,8 @@ class _DistributedMixin:
         self._synchronized = False
         self._should_synchronize = True
         self._in_flight = False       # a backward pass ran since the last synchronize
+        self.trace_overlap = False    # True: keep (bucket, start event, end event, launched from a hook) per exchange
+        self.overlap_log = []         # ... of the current step, with timing events (see tests/test_gpu_pipeline.py)
         if _world_size() > 1 or always_hook or os.environ.get("GRACE_ELASTIC") == "1":
             self._install_hooks()
 
@@ -208,6 +210,9 @@ class _DistributedMixin:
         side = self._comm_stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            if self.trace_overlap:
+                start = torch.cuda.Event(enable_timing=True)
+                start.record(side)
             g = self._flat.grad_view(bucket)
             if self.gradient_predivide_factor != 1.0:
                 g.div_(self.gradient_predivide_factor)
@@ -216,8 +221,10 @@ class _DistributedMixin:
                 self._grace.step_flat(g, bucket.layout, sm_limit=limit)
             else:
                 self._grace.step_flat(g, bucket.layout)
-            ev = torch.cuda.Event()
+            ev = torch.cuda.Event(enable_timing=self.trace_overlap)
             ev.record(side)
+            if self.trace_overlap:
+                self.overlap_log.append((bucket.index, start, ev, overlapped))
         self._bucket_events[bucket.index] = ev
 
     def _plain_allreduce(self, tensor):
@@ -313,6 +320,8 @@ class _DistributedMixin:
         self._rearm(entries)
         self._in_flight = False
         self._synchronized = True
+        if self.trace_overlap:
+            self.last_overlap_log, self.overlap_log = self.overlap_log, []
 
     @contextmanager
     def skip_synchronize(self):

@@ -50,6 +50,9 @@ def test_dgc_clipping_inside_the_kernel(W):
     for step in range(3):
         flats = []
         grads = [[_rand(n, seed=1000 * step + 10 * r + i, scale=1.0) for i, n in enumerate(numels)] for r in range(W)]
+        for r in range(W):      # a few outliers that the clamp really cuts (N(0,1) alone never reaches the bound)
+            for i, n in enumerate(numels):
+                grads[r][i][torch.arange(3, device=_dev()) * (n // 3) + r] *= 3.0 * n ** 0.5
         for r in range(W):
             f = torch.zeros(layout.total, device=_dev())
             for g, off, n in zip(grads[r], layout.offsets, numels):
@@ -71,8 +74,9 @@ def test_dgc_clipping_inside_the_kernel(W):
                 v[r][i] = v[r][i] * keep
                 expect += sel
             expect /= W
+            assert any(float(g[i].abs().max()) > float(bound) for g in grads), "the clamp must bind somewhere"
             for r in range(W):
-                torch.testing.assert_close(outs[r][off:off + n], expect, rtol=1e-5, atol=1e-7)
+                torch.testing.assert_close(outs[r][off:off + n], expect, rtol=1e-5, atol=2e-6 * float(expect.abs().max()))
 
 
 def test_strict_threshold_rule_in_the_kernel():
@@ -115,9 +119,20 @@ def test_sixteen_bit_gradients_are_read_by_the_kernels(dtype, codec):
         out32 = b.step(g16.float(), "w")
         a.check(); b.check()
         assert out16.dtype == dtype and out16.shape == g16.shape
-        torch.testing.assert_close(out16, out32.to(dtype), rtol=0, atol=0)
+        if codec == "topk":
+            # 16-bit data is full of equal magnitudes and ties at the k-th place are broken arbitrarily: the same
+            # magnitudes must come out, not necessarily at the same places
+            ref = out32.to(dtype)
+            assert int((out16 != 0).sum()) == int((ref != 0).sum()) == max(1, int(n * 0.01))
+            assert torch.equal(out16.abs().sort().values, ref.abs().sort().values)
+            nz = out16 != 0
+            assert torch.equal(out16[nz].float(), (g16.float() + (0 if step == 0 else prev_res))[nz].to(dtype).float())
+        else:
+            torch.testing.assert_close(out16, out32.to(dtype), rtol=0, atol=0)
+        if codec == "topk":
+            prev_res = next(iter(a._plans.values())).acc[:n].clone()
     pa = next(iter(a._plans.values())); pb = next(iter(b._plans.values()))
-    if pa.acc is not None:
+    if pa.acc is not None and codec != "topk":
         torch.testing.assert_close(pa.acc, pb.acc, rtol=0, atol=0)       # residuals stay fp32 and identical
 
 
@@ -157,7 +172,7 @@ def test_staged_decode_matches_single_rank_decodes(codec, extra):
         expect = torch.where(votes >= 0, torch.ones_like(votes), -torch.ones_like(votes))
         assert torch.equal(outs[0], expect)
     elif codec == "efsignsgd":
-        torch.testing.assert_close(outs[0], sum(singles), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(outs[0], sum(singles), rtol=1e-5, atol=2e-5)   # sums of +-mean/lr ~ 8 that cancel
     else:
         torch.testing.assert_close(outs[0], sum(singles) / W, rtol=1e-5, atol=1e-7)
     for r in range(1, W):

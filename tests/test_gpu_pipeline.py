@@ -91,3 +91,44 @@ def test_timeline_device_track_for_fused_exchanges(tmp_path):
     dev = [e for e in ev if e["tid"] == 1]
     assert len(host) == 3 and len(dev) == 3
     assert all(e["cat"] == "fused.quant" and e["dur"] > 0 and e["args"]["numel"] == 1 << 20 for e in dev)
+
+
+def test_bucket_exchanges_start_before_backward_ends():
+    """Default behaviour of the bucketed optimizer: the exchange of a bucket is launched from the gradient hook of
+    its last parameter, on a side stream, and is on the device before the backward pass has finished; only the
+    bucket of the first layers is exchanged after backward.  Timed with CUDA events (device clock)."""
+    from grace_b200 import grace_from_params
+    from grace_b200.optim import FusedSGD
+    from grace_b200.parallel import DistributedOptimizer
+    from grace_b200.parallel.flat import FlatParams
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    width, depth = 4096, 8
+    model = torch.nn.Sequential(*[torch.nn.Linear(width, width) for _ in range(depth)]).to(dev)
+    named = list(model.named_parameters())
+    flat = FlatParams(named, bucket_bytes=2 * (width * width + width) * 4)     # two layers per bucket
+    assert len(flat.buckets) == depth // 2
+    grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather", "quantum_num": 64,
+                             "world_size": 1, "fused": True, "overlap_sms": 16})
+    opt = FusedSGD(model.parameters(), lr=0.01, momentum=0.9, flat=flat)
+    opt = DistributedOptimizer(opt, grace=grc, named_parameters=named, flat=flat, always_hook=True)
+    opt.trace_overlap = True
+    x = torch.randn(8192, width, device=dev)
+    for _ in range(3):
+        opt.zero_grad()
+        loss = model(x).square().mean()
+        loss.backward()
+        bwd_end = torch.cuda.Event(enable_timing=True)
+        bwd_end.record()
+        opt.step()
+    torch.cuda.synchronize()
+    grc.check()
+    log = opt.last_overlap_log
+    assert len(log) == depth // 2
+    from_hooks = [e for e in log if e[3]]
+    assert len(from_hooks) == depth // 2                        # every bucket was launched by a hook
+    early = [e for e in from_hooks if e[1].elapsed_time(bwd_end) > 0]      # started before backward ended
+    done_early = [e for e in from_hooks if e[2].elapsed_time(bwd_end) > 0]  # ... and finished before it ended
+    assert len(early) >= depth // 2 - 1, [e[1].elapsed_time(bwd_end) for e in log]
+    assert len(done_early) >= 1
