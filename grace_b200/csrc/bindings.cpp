@@ -184,6 +184,35 @@ PYBIND11_MODULE(_C, m) {
           check(launch_powersgd(a, grid, reinterpret_cast<cudaStream_t>(stream)), "powersgd_exchange");
         });
 
+  // ---- stand-alone error-feedback kernels (library path) ----
+  m.def("residual_compensate", [](uintptr_t g, int g_dtype, uintptr_t r, uintptr_t out, long long n, float beta, float gamma,
+                                  uintptr_t stream) {
+    check(launch_residual_compensate(ptr<const void>(g), g_dtype, ptr<const float>(r), ptr<float>(out), n, beta, gamma,
+                                     reinterpret_cast<cudaStream_t>(stream)), "residual_compensate");
+  });
+  m.def("residual_update", [](uintptr_t acc, uintptr_t dec, uintptr_t r, long long n, uintptr_t stream) {
+    check(launch_residual_update(ptr<const float>(acc), ptr<const float>(dec), ptr<float>(r), n,
+                                 reinterpret_cast<cudaStream_t>(stream)), "residual_update");
+  });
+  m.def("zero_at", [](uintptr_t a, uintptr_t b, uintptr_t idx, int idx64, long long k, long long n, uintptr_t stream) {
+    check(launch_zero_at(ptr<float>(a), ptr<float>(b), ptr<const void>(idx), idx64, k, n,
+                         reinterpret_cast<cudaStream_t>(stream)), "zero_at");
+  });
+  m.def("dgc_compensate", [](uintptr_t g, int g_dtype, uintptr_t u, uintptr_t v, long long n, float momentum, float bound,
+                             int first, uintptr_t stream) {
+    check(launch_dgc_compensate(ptr<const void>(g), g_dtype, ptr<float>(u), ptr<float>(v), n, momentum, bound, first,
+                                reinterpret_cast<cudaStream_t>(stream)), "dgc_compensate");
+  });
+  m.def("dgc_mask", [](uintptr_t u, uintptr_t v, uintptr_t mask, long long n, uintptr_t stream) {
+    check(launch_dgc_mask(ptr<float>(u), ptr<float>(v), ptr<const unsigned char>(mask), n,
+                          reinterpret_cast<cudaStream_t>(stream)), "dgc_mask");
+  });
+  m.def("sum_squares_scratch_doubles", &sum_squares_scratch_doubles);
+  m.def("sum_squares", [](uintptr_t g, int g_dtype, long long n, uintptr_t scratch, uintptr_t stream) {
+    check(launch_sum_squares(ptr<const void>(g), g_dtype, n, ptr<double>(scratch), reinterpret_cast<cudaStream_t>(stream)),
+          "sum_squares");
+  });
+
   // ---- fused SGD ----
   m.def("fused_sgd", [](uintptr_t p, uintptr_t g, uintptr_t buf, long long numel, float lr, float momentum,
                         float dampening, float weight_decay, int nesterov, int first_step, int zero_grad,

@@ -231,6 +231,18 @@ int lowrank_occupancy(int dynamic_smem_bytes);
 cudaError_t launch_powersgd(const LowRankArgs& a, int grid, cudaStream_t stream);
 int lowrank_encode_maps(void* maps_out, const float* g, float* acc, const float* qt, const float* pt, int n, int m);
 
+// ---------------------------------------------------------------- memory ----
+// Stand-alone error-feedback kernels of the library path (memory.cu).  g_dtype is a GradType of gradio.cuh.
+cudaError_t launch_residual_compensate(const void* g, int g_dtype, const float* r, float* out, long long n, float beta,
+                                       float gamma, cudaStream_t stream);   // r nullable: out = gamma * g
+cudaError_t launch_residual_update(const float* acc, const float* dec, float* r, long long n, cudaStream_t stream);
+cudaError_t launch_zero_at(float* a, float* b, const void* idx, int idx64, long long k, long long n, cudaStream_t stream);
+cudaError_t launch_dgc_compensate(const void* g, int g_dtype, float* u, float* v, long long n, float momentum, float bound,
+                                  int first, cudaStream_t stream);
+cudaError_t launch_dgc_mask(float* u, float* v, const unsigned char* mask, long long n, cudaStream_t stream);
+int sum_squares_scratch_doubles();
+cudaError_t launch_sum_squares(const void* g, int g_dtype, long long n, double* scratch, cudaStream_t stream);   // result in scratch[0]
+
 // ------------------------------------------------------------------- sgd ----
 struct SgdTensor {
   float* p;

@@ -26,14 +26,40 @@ class DgcMemory(Memory):
         self.gradients = {}
         self.residuals = {}
 
-    def _clip(self, tensor):
-        sq = torch.sum(tensor * tensor)
+    def _bound(self, tensor):
+        """``sqrt(mean over ranks of sum g^2)`` as a 0-d tensor (one kernel on CUDA, ``csrc/memory.cu``)."""
+        sq = None
+        if tensor.is_cuda:
+            from ..ops import memory as K
+
+            sq = K.sum_squares(tensor)
+            if sq is not None:
+                sq = sq.to(torch.float32)
+        if sq is None:
+            sq = torch.sum(tensor * tensor)
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(sq)
-        bound = torch.sqrt(sq / self.world_size)
+        return torch.sqrt(sq / self.world_size)
+
+    def _clip(self, tensor):
+        bound = self._bound(tensor)
         return torch.maximum(torch.minimum(tensor, bound), -bound)
 
     def compensate(self, tensor, name):
+        if tensor.is_cuda and tensor.dtype == torch.float32:
+            # momentum correction (and the clamp) as one kernel over g, u and v
+            from ..ops import memory as K
+
+            first = name not in self.residuals
+            if first:
+                self.residuals[name] = torch.empty_like(tensor)
+                self.gradients[name] = torch.empty_like(tensor)
+            u, v = self.residuals[name], self.gradients[name]
+            bound = float(self._bound(tensor)) if self.gradient_clipping else float("inf")
+            if u.shape == tensor.shape and K.dgc_compensate(tensor, u, v, self.momentum, bound, first):
+                return v
+            if first:
+                del self.residuals[name], self.gradients[name]
         if self.gradient_clipping:
             tensor = self._clip(tensor)
         if name in self.residuals:
@@ -48,6 +74,12 @@ class DgcMemory(Memory):
 
     def update(self, tensor, name, compressor, tensor_compressed, ctx):
         shape, mask, _ = ctx
+        u, v = self.residuals[name], self.gradients[name]
+        if u.is_cuda and mask.is_cuda and u.data_ptr() != v.data_ptr():
+            from ..ops import memory as K
+
+            if K.dgc_mask(u, v, mask.reshape(-1)):
+                return
         keep = ~mask.view(shape)
         self.residuals[name] = self.residuals[name] * keep
         self.gradients[name] = self.gradients[name] * keep
