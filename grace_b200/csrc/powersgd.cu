@@ -63,7 +63,7 @@ constexpr int kRingBytes = kStagesR * (2 * kATileBytes + kBTileBytes);   // 204 
 static_assert(kStagesNoR * (kATileBytes + kBTileBytes) <= kRingBytes, "ring too small");
 constexpr unsigned kTmemCols = 32;      // two accumulators of 16 columns
 constexpr int kMaxRank = 16;
-constexpr int kS3Trip = 8;              // rows of one trip of stage 3 (the next trip's loads are already in flight)
+constexpr int kS3Trip = 12;             // rows of one trip of stage 3 (the next trip's loads are already in flight)
 constexpr int kS3Rows = 64;             // rows per stage-3 work item
 constexpr int kS3Cols = kThreads * 4;   // columns per stage-3 work item
 // warp roles of the GEMM stages
@@ -408,6 +408,71 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
   __syncthreads();
 }
 
+// Upper Cholesky factor R of sm.gram (R^T R = Gram) and its inverse into sm.rinv, by one thread.  RMAX bounds the
+// loops at compile time so that, for small ranks, R lives in registers.  A non-positive pivot (a rank-deficient P)
+// zeroes its row and column: the corresponding direction is dropped, as a projection onto nothing.
+template <int RMAX>
+__device__ void cholesky_inverse(SmemLayout& sm, int r) {
+  double R[RMAX][RMAX];
+#pragma unroll
+  for (int j = 0; j < RMAX; ++j) {
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) {
+      R[i][j] = 0.0;
+      if (i <= j && j < r) {
+        double s = sm.gram[i][j];
+#pragma unroll
+        for (int k = 0; k < RMAX; ++k) if (k < i) s -= R[k][i] * R[k][j];
+        if (i == j) R[i][j] = s > 0.0 ? sqrt(s) : 0.0;
+        else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;
+      }
+    }
+  }
+  // invert the upper-triangular R by back substitution
+  double inv[RMAX][RMAX];
+#pragma unroll
+  for (int j = 0; j < RMAX; ++j) {
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) inv[i][j] = 0.0;
+    if (j < r && R[j][j] > 0.0) inv[j][j] = 1.0 / R[j][j];
+#pragma unroll
+    for (int i = RMAX - 1; i >= 0; --i) {
+      if (i < j && j < r) {
+        double s = 0.0;
+#pragma unroll
+        for (int k = 0; k < RMAX; ++k) if (k > i && k <= j) s += R[i][k] * inv[k][j];
+        inv[i][j] = R[i][i] > 0.0 ? -s / R[i][i] : 0.0;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RMAX; ++i)
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) sm.rinv[i][j] = inv[i][j];
+}
+
+// Same for ranks above 4, with the factor in shared memory (the operand ring is idle at that point).
+__device__ void cholesky_inverse_large(SmemLayout& sm, int r) {
+  double (*R)[kMaxRank] = reinterpret_cast<double (*)[kMaxRank]>(sm.ring);
+  for (int j = 0; j < r; ++j) {
+    for (int i = 0; i <= j; ++i) {
+      double s = sm.gram[i][j];
+      for (int k = 0; k < i; ++k) s -= R[k][i] * R[k][j];
+      if (i == j) R[i][j] = s > 0.0 ? sqrt(s) : 0.0;
+      else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;
+    }
+  }
+  for (int j = 0; j < r; ++j) {
+    for (int i = 0; i < r; ++i) sm.rinv[i][j] = 0.0;
+    if (R[j][j] > 0.0) sm.rinv[j][j] = 1.0 / R[j][j];
+    for (int i = j - 1; i >= 0; --i) {
+      double s = 0.0;
+      for (int k = i + 1; k <= j; ++k) s += R[i][k] * sm.rinv[k][j];
+      sm.rinv[i][j] = R[i][i] > 0.0 ? -s / R[i][i] : 0.0;
+    }
+  }
+}
+
 // Mean over ranks of a [rows x 16] region.
 __device__ void reduce_region(const LowRankArgs& a, size_t region_off, float* __restrict__ dst, size_t floats) {
   const int world = a.peers.world;
@@ -446,7 +511,7 @@ __device__ bool publish_and_wait(const LowRankArgs& a, const Status& status, uns
 
 // S3 for one matrix: out = P Q^T, residual = M' - out.  Item = kS3Rows rows x kS3Cols columns; a thread owns four
 // columns and walks the rows in trips of kS3Trip with the loads of the next trip already in flight.
-template <int RH>   // RH = ceil(rank / 8): how many groups of eight rank columns take part
+template <int R4>   // R4 = ceil(rank / 4): how many groups of four rank columns take part
 __device__ void stage3_matrix(const LowRankArgs& a, SmemLayout& sm, const LowRankMatrix& M) {
   const int tid = threadIdx.x;
   const float* __restrict__ src = a.has_memory ? a.acc : a.g;
@@ -462,11 +527,11 @@ __device__ void stage3_matrix(const LowRankArgs& a, SmemLayout& sm, const LowRan
     const int col = cb * kS3Cols + tid * 4;
     if (col >= M.m) continue;
     const int valid = min(4, M.m - col);
-    float q[4][8 * RH];
+    float q[4][4 * R4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
 #pragma unroll
-      for (int h = 0; h < 2 * RH; ++h) {
+      for (int h = 0; h < R4; ++h) {
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e < valid && 4 * h < a.rank)   // columns >= rank of q_mean are zero
           t = reinterpret_cast<const float4*>(a.q_mean + M.q_off + (size_t)(col + e) * kRankPad)[h];
@@ -495,7 +560,7 @@ __device__ void stage3_matrix(const LowRankArgs& a, SmemLayout& sm, const LowRan
         const size_t base = base0 + (size_t)rr * M.m;
         float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 8 * RH; ++c) {
+        for (int c = 0; c < 4 * R4; ++c) {
           const float p = sm.prow[rr][c];
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] += p * q[e][c];
@@ -624,33 +689,26 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       // O: P_orth = P R^-1 with R^T R = Gram (upper Cholesky), written transposed [16][n]
       for (int mat = 0; mat < a.nmat; ++mat) {
         const LowRankMatrix& M = a.mats[mat];
-        if (tid < kRankPad * kRankPad) {   // the CTAs' partial matrices, in CTA order
-          double t = 0.0;
-          for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(a.gram_part + ((size_t)b * a.nmat + mat) * 256 + tid);
-          (&sm.gram[0][0])[tid] = t;
+        {
+          // the CTAs' partial matrices: one warp per entry of the upper triangle; a lane adds the partials of CTAs
+          // lane, lane + 32, ... (in that order), the lanes are combined by the shuffle tree: a fixed order
+          const int lane = tid & 31;
+          const int entries = a.rank * (a.rank + 1) / 2;
+          for (int e = warp; e < entries; e += kThreads / 32) {
+            int c = 0, rem = e;
+            while (rem >= a.rank - c) { rem -= a.rank - c; ++c; }
+            const int d = c + rem;
+            double t = 0.0;
+            for (unsigned b = lane; b < gridDim.x; b += 32)
+              t += __ldcg(a.gram_part + ((size_t)b * a.nmat + mat) * 256 + c * kRankPad + d);
+            t = warp_sum(t);
+            if (lane == 0) sm.gram[c][d] = t;
+          }
         }
         __syncthreads();
         if (tid == 0) {
-          const int r = a.rank;
-          double (*R)[kMaxRank] = reinterpret_cast<double (*)[kMaxRank]>(sm.ring);   // scratch: the ring is idle here
-          for (int j = 0; j < r; ++j) {
-            for (int i = 0; i <= j; ++i) {
-              double s = sm.gram[i][j];
-              for (int k = 0; k < i; ++k) s -= R[k][i] * R[k][j];
-              if (i == j) R[i][j] = s > 0.0 ? sqrt(s) : 0.0;
-              else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;
-            }
-          }
-          // invert the upper-triangular R by back substitution
-          for (int j = 0; j < r; ++j) {
-            for (int i = 0; i < r; ++i) sm.rinv[i][j] = 0.0;
-            if (R[j][j] > 0.0) sm.rinv[j][j] = 1.0 / R[j][j];
-            for (int i = j - 1; i >= 0; --i) {
-              double s = 0.0;
-              for (int k = i + 1; k <= j; ++k) s += R[i][k] * sm.rinv[k][j];
-              sm.rinv[i][j] = R[i][i] > 0.0 ? -s / R[i][i] : 0.0;
-            }
-          }
+          if (a.rank <= 4) cholesky_inverse<4>(sm, a.rank);
+          else cholesky_inverse_large(sm, a.rank);
         }
         __syncthreads();
         for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
@@ -697,8 +755,10 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         }
       }
       for (int mat = 0; mat < a.nmat; ++mat) {
-        if (a.rank <= 8) stage3_matrix<1>(a, sm, a.mats[mat]);
-        else stage3_matrix<2>(a, sm, a.mats[mat]);
+        if (a.rank <= 4) stage3_matrix<1>(a, sm, a.mats[mat]);
+        else if (a.rank <= 8) stage3_matrix<2>(a, sm, a.mats[mat]);
+        else if (a.rank <= 12) stage3_matrix<3>(a, sm, a.mats[mat]);
+        else stage3_matrix<4>(a, sm, a.mats[mat]);
       }
     }
   }

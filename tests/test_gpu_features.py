@@ -50,9 +50,8 @@ def test_dgc_clipping_inside_the_kernel(W):
     for step in range(3):
         flats = []
         grads = [[_rand(n, seed=1000 * step + 10 * r + i, scale=1.0) for i, n in enumerate(numels)] for r in range(W)]
-        for r in range(W):      # a few outliers that the clamp really cuts (N(0,1) alone never reaches the bound)
-            for i, n in enumerate(numels):
-                grads[r][i][torch.arange(3, device=_dev()) * (n // 3) + r] *= 3.0 * n ** 0.5
+        for i, n in enumerate(numels):   # one rank with a much larger norm: its outliers exceed the RMS-over-ranks bound
+            grads[0][i][torch.arange(3, device=_dev()) * (n // 3)] *= 1000.0
         for r in range(W):
             f = torch.zeros(layout.total, device=_dev())
             for g, off, n in zip(grads[r], layout.offsets, numels):
@@ -74,7 +73,8 @@ def test_dgc_clipping_inside_the_kernel(W):
                 v[r][i] = v[r][i] * keep
                 expect += sel
             expect /= W
-            assert any(float(g[i].abs().max()) > float(bound) for g in grads), "the clamp must bind somewhere"
+            if W > 1:
+                assert any(float(g[i].abs().max()) > float(bound) for g in grads), "the clamp must bind somewhere"
             for r in range(W):
                 torch.testing.assert_close(outs[r][off:off + n], expect, rtol=1e-5, atol=2e-6 * float(expect.abs().max()))
 
@@ -120,17 +120,18 @@ def test_sixteen_bit_gradients_are_read_by_the_kernels(dtype, codec):
         a.check(); b.check()
         assert out16.dtype == dtype and out16.shape == g16.shape
         if codec == "topk":
-            # 16-bit data is full of equal magnitudes and ties at the k-th place are broken arbitrarily: the same
-            # magnitudes must come out, not necessarily at the same places
-            ref = out32.to(dtype)
-            assert int((out16 != 0).sum()) == int((ref != 0).sum()) == max(1, int(n * 0.01))
-            assert torch.equal(out16.abs().sort().values, ref.abs().sort().values)
+            # 16-bit data is full of equal magnitudes and ties at the k-th place are broken arbitrarily, so the two
+            # runs may pick different places: check the selection against the accumulator it was made from
+            k = max(1, int(n * 0.01))
+            acc = g16.float() + (0 if step == 0 else prev_res)
             nz = out16 != 0
-            assert torch.equal(out16[nz].float(), (g16.float() + (0 if step == 0 else prev_res))[nz].to(dtype).float())
+            assert int(nz.sum()) == k
+            assert torch.equal(out16[nz].float(), acc[nz].to(dtype).float())
+            assert float(acc[nz].abs().min()) >= float(acc[~nz].abs().max())      # a true top-k of the accumulator
+            prev_res = next(iter(a._plans.values())).acc[:n].clone()
+            assert torch.equal(prev_res, torch.where(nz, torch.zeros_like(acc), acc))
         else:
             torch.testing.assert_close(out16, out32.to(dtype), rtol=0, atol=0)
-        if codec == "topk":
-            prev_res = next(iter(a._plans.values())).acc[:n].clone()
     pa = next(iter(a._plans.values())); pb = next(iter(b._plans.values()))
     if pa.acc is not None and codec != "topk":
         torch.testing.assert_close(pa.acc, pb.acc, rtol=0, atol=0)       # residuals stay fp32 and identical

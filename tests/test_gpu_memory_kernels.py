@@ -79,7 +79,7 @@ def test_memory_classes_on_cuda_match_cpu(case):
             res = a.memory.residuals["w"].cpu()
             assert res.shape == x.shape and torch.isfinite(res).all()
             continue
-        torch.testing.assert_close(outs[0], outs[1], rtol=1e-6, atol=1e-7)
+        torch.testing.assert_close(outs[0], outs[1], rtol=1e-5, atol=1e-6)     # means are summed in another order
         for field in a.memory._state_fields:
             torch.testing.assert_close(getattr(a.memory, field)["w"].cpu(), getattr(b.memory, field)["w"],
-                                       rtol=1e-6, atol=1e-7)
+                                       rtol=1e-5, atol=1e-6)
