@@ -5,10 +5,12 @@
 //
 // For every matrix M (n x m, row-major slice of the flat gradient buffer) of a
 // launch, with rank r <= 16 padded to 16 columns:
-//   S1  M' = G + R (error feedback; added in shared memory on the swizzled
-//       tiles and written back by a TMA store), P = M' * Q: A = M' tile
-//       [128 x 32] K-major, B = Q^T tile [16 x 32] K-major, D in TMEM
-//       (128 lanes x 16 columns, two accumulators used alternately);
+//   S1  P = M' * Q with M' = G + R (error feedback): the gradient tile and the
+//       residual tile [128 x 32, K-major] are both A operands of MMAs into the
+//       same accumulator (P = G Q + R Q; B = Q^T tile [16 x 32] K-major, D in
+//       TMEM: 128 lanes x 16 columns, two accumulators used alternately), while
+//       other warps add the two tiles from shared memory and write M' to the
+//       residual buffer for the later stages;
 //   R1  publish; wait for every peer; P = mean over ranks of the W slots
 //       (identical order on every rank, so the results are bit-identical);
 //   O   orthogonalise P: Gram matrix P^T P and its Cholesky factor in fp64,
@@ -28,11 +30,12 @@
 //   warp 1     one thread issues the MMAs and commits them to the ring's
 //              "empty" barriers and, at the end of a work item, to the
 //              accumulator's "full" barrier;
-//   warps 2-3  (S1 with error feedback) add the residual tile into the
-//              gradient tile in shared memory and hand it on;
-//   warps 4-7  epilogue: TMEM -> registers -> this item's partial result;
-//   warp 8     (S1 with error feedback) one thread writes M' back with TMA
-//              stores and frees the ring slot once the store has read it.
+//   warps 2, 3, 8  (S1 with error feedback) read the gradient and the residual
+//              tile from shared memory, add them and store M' to global
+//              memory (16 bytes per thread and access);
+//   warps 4-7  epilogue: TMEM -> registers -> this item's partial result.
+// A ring slot is free again when its MMAs have retired and the adder warps
+// have read it.
 // Split-K is deterministic: every work item (128 output rows x a K range)
 // writes its partial sums to its own block of a scratch buffer; the item that
 // completes a row block last adds the partials in split order into the slot.
@@ -67,7 +70,8 @@ constexpr int kS3Trip = 12;             // rows of one trip of stage 3 (the next
 constexpr int kS3Rows = 64;             // rows per stage-3 work item
 constexpr int kS3Cols = kThreads * 4;   // columns per stage-3 work item
 // warp roles of the GEMM stages
-constexpr int kProducerWarp = 0, kMmaWarp = 1, kAdderWarp0 = 2, kAdderWarps = 2, kEpilogueWarp0 = 4, kStoreWarp = 8;
+constexpr int kProducerWarp = 0, kMmaWarp = 1, kEpilogueWarp0 = 4;
+constexpr int kAdderWarps = 3;          // warps 2, 3 and 8
 
 // instruction descriptor: D=f32, A=B=tf32, N=16, M=128 (bit layout: c_format
 // [4,6), a_format [7,10), b_format [10,13), a_major 15, b_major 16, N>>3
@@ -78,8 +82,7 @@ constexpr uint32_t kIdescAmn = kIdesc | (1u << 15);
 struct __align__(1024) SmemLayout {
   unsigned char ring[kRingBytes];
   unsigned long long full[kStagesNoR];     // TMA landed
-  unsigned long long ready[kStagesNoR];    // residual added (S1 with error feedback)
-  unsigned long long empty[kStagesNoR];    // MMAs retired (and the M' store has read the tile)
+  unsigned long long empty[kStagesNoR];    // MMAs retired (and, in S1 with error feedback, the adder warps have read the tiles)
   unsigned long long acc_full[2];          // an item's MMAs retired
   unsigned long long acc_empty[2];         // the epilogue has read the accumulator
   unsigned tmem_base;
@@ -137,15 +140,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src)) : "memory");
-}
-__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void tma_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: start>>4 [0,14) | LBO>>4 [16,30) | SBO>>4 [32,46) | version 1 [46,48) |
@@ -172,10 +166,18 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Work item of a GEMM stage: (matrix, block of 128 output rows, K split).
+// Work item of a GEMM stage: (matrix, block of 128 output rows, K split).  Which K tiles a split takes, and how the
+// items are numbered, is chosen so that CTAs running side by side read NEIGHBOURING pieces of the same matrix rows at
+// about the same time (a tile row is only 128 bytes in stage 1 and 512 bytes in stage 2: taken alone they would
+// open a DRAM page for very little):
+//   stage 1  items of a row block are consecutive (split fastest) and split s takes the K tiles s, s + S, s + 2S, ...
+//            so the S CTAs of a block walk the rows together, 128 bytes apart;
+//   stage 2  blocks are fastest (item = split * blocks + block) and a split takes a contiguous K range, so
+//            consecutive CTAs read adjacent 512-byte pieces of the same rows.
 struct Item {
-  int mat, blk, kt0, kt1;
-  int first;    // index of split 0 of this row block (the items of a block are consecutive)
+  int mat, blk;
+  int kt0, kt_step, kt_count;   // K tiles kt0, kt0 + kt_step, ... (kt_count of them)
+  int first, stride;            // split s of this row block is item first + s * stride
   int splits;
 };
 __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int idx, Item& it) {
@@ -188,13 +190,26 @@ __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int
   const int local = idx - begin;
   const int ktiles = ((stage == 1 ? M.m : M.n) + kTileK - 1) / kTileK;
   const int splits = stage == 1 ? M.splits1 : M.splits2;
-  const int sp = local % splits;
   it.mat = mat;
-  it.blk = local / splits;
   it.splits = splits;
-  it.first = begin + it.blk * splits;
-  it.kt0 = (int)((long long)sp * ktiles / splits);
-  it.kt1 = (int)((long long)(sp + 1) * ktiles / splits);
+  if (stage == 1) {
+    const int sp = local % splits;
+    it.blk = local / splits;
+    it.first = begin + it.blk * splits;
+    it.stride = 1;
+    it.kt0 = sp;
+    it.kt_step = splits;
+    it.kt_count = (ktiles - sp + splits - 1) / splits;
+  } else {
+    const int blocks = (M.m + kTileRows - 1) / kTileRows;
+    const int sp = local / blocks;
+    it.blk = local % blocks;
+    it.first = begin + it.blk;
+    it.stride = blocks;
+    it.kt0 = (int)((long long)sp * ktiles / splits);
+    it.kt_step = 1;
+    it.kt_count = (int)((long long)(sp + 1) * ktiles / splits) - it.kt0;
+  }
   return true;
 }
 
@@ -210,13 +225,12 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
   const uint64_t tmo = a.peers.timeout_ns;
   if (tid == 0) {
     if (sm.bars_valid) {   // objects of the previous stage: all their phases are over (a CTA barrier lies behind us)
-      for (int s = 0; s < kStagesNoR; ++s) { mbar_inval(&sm.full[s]); mbar_inval(&sm.ready[s]); mbar_inval(&sm.empty[s]); }
+      for (int s = 0; s < kStagesNoR; ++s) { mbar_inval(&sm.full[s]); mbar_inval(&sm.empty[s]); }
       for (int b = 0; b < 2; ++b) { mbar_inval(&sm.acc_full[b]); mbar_inval(&sm.acc_empty[b]); }
     }
     for (int s = 0; s < kStagesNoR; ++s) {
       mbar_init(&sm.full[s], 1);
-      mbar_init(&sm.ready[s], kAdderWarps);
-      mbar_init(&sm.empty[s], has_r ? 2 : 1);
+      mbar_init(&sm.empty[s], has_r ? 1 + kAdderWarps : 1);
     }
     for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 4); }
     sm.bars_valid = 1;
@@ -231,7 +245,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       bool ok = true;
       for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
         const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)it.mat * kMapsPerMatrix;
-        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+        for (int kj = 0, kt = it.kt0; kj < it.kt_count; ++kj, kt += it.kt_step, ++step) {
           const unsigned slot = step % nstages;
           if (step >= nstages) ok = mbar_wait(&sm.empty[slot], ((step / nstages) - 1) & 1, tmo, status, 100 + slot);
           if (!ok) break;
@@ -266,9 +280,9 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = sm.tmem_base + buf * kRankPad;
-        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+        for (int kj = 0, kt = it.kt0; kj < it.kt_count; ++kj, kt += it.kt_step, ++step) {
           const unsigned slot = step % nstages;
-          ok = mbar_wait(has_r ? &sm.ready[slot] : &sm.full[slot], (step / nstages) & 1, tmo, status, 200 + slot);
+          ok = mbar_wait(&sm.full[slot], (step / nstages) & 1, tmo, status, 200 + slot);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.ring + (size_t)slot * stage_bytes), b_addr = a_addr + off_b;
@@ -280,7 +294,13 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
                                        // MN-major: a K step is 8 rows of 128 B (two atoms of 4 rows, 512 B apart);
                                        // the next 32 of the 128 M-columns sit one box (4096 B) further on
                                        : smem_desc(a_addr + kk * 1024, 4096, 512, 1);
-            umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdesc : kIdescAmn, !(kt == it.kt0 && kk == 0));
+            umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdesc : kIdescAmn, !(kj == 0 && kk == 0));
+          }
+          if (has_r) {   // the residual tile into the same accumulator: P = G Q + R Q
+#pragma unroll
+            for (int kk = 0; kk < kTileK / 8; ++kk)
+              umma_tf32(tmem_d, smem_desc(a_addr + off_r + kk * 32, 16, 1024, 2), smem_desc(b_addr + kk * 32, 16, 1024, 2),
+                        kIdesc, true);
           }
           umma_commit(&sm.empty[slot]);
         }
@@ -288,57 +308,39 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
         umma_commit(&sm.acc_full[buf]);
       }
     }
-  } else if (warp >= kAdderWarp0 && warp < kAdderWarp0 + kAdderWarps) {
+  } else if (warp == 2 || warp == 3 || warp == 8) {
     if (has_r) {
-      const int at = tid - kAdderWarp0 * 32;                  // 0 .. 63
+      // M' = G + R for the later stages: both tiles are read from shared memory (they hold the same 128-byte
+      // swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)), added, and stored straight to global memory
+      const int at = (warp == 8 ? 64 : (warp - 2) * 32) + lane;   // 0 .. 95
       constexpr int kAdders = kAdderWarps * 32;
       unsigned step = 0;
       Item it;
       bool ok = true;
       for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
-        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
+        const LowRankMatrix& M = a.mats[it.mat];
+        float* const dst = a.acc + M.g_off;
+        for (int kj = 0, kt = it.kt0; kj < it.kt_count; ++kj, kt += it.kt_step, ++step) {
           const unsigned slot = step % nstages;
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], (step / nstages) & 1, tmo, status, 500 + slot));
           if (!ok) break;
-          unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
-          float4* pa = reinterpret_cast<float4*>(base);
+          const unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
+          const float4* pa = reinterpret_cast<const float4*>(base);
           const float4* pr = reinterpret_cast<const float4*>(base + off_r);
 #pragma unroll 4
           for (int i = at; i < kATileBytes / 16; i += kAdders) {
             float4 x = pa[i];
             const float4 y = pr[i];
             x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-            pa[i] = x;
+            const int row = i >> 3, grow = it.blk * kTileRows + row;
+            const int gcol = kt * kTileK + (((i & 7) ^ (row & 7)) << 2);
+            if (grow < M.n && gcol < M.m)   // m is a multiple of 4: the four columns are inside together
+              *reinterpret_cast<float4*>(dst + (size_t)grow * M.m + gcol) = x;
           }
-          fence_async_smem();  // generic-proxy writes -> visible to the MMA and to the TMA store
           __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.ready[slot]);
+          if (lane == 0) mbar_arrive(&sm.empty[slot]);
         }
       }
-    }
-  } else if (warp == kStoreWarp) {
-    if (has_r && lane == 0) {
-      // M' goes back to the accumulator buffer; a ring slot is free once its store has READ the tile
-      unsigned step = 0;
-      Item it;
-      bool ok = true;
-      int prev_slot = -1;
-      for (int idx = blockIdx.x; ok && decode_item(a, STAGE, idx, it); idx += gridDim.x) {
-        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(a.maps) + (size_t)it.mat * kMapsPerMatrix;
-        for (int kt = it.kt0; kt < it.kt1; ++kt, ++step) {
-          const unsigned slot = step % nstages;
-          ok = mbar_wait(&sm.ready[slot], (step / nstages) & 1, tmo, status, 600 + slot);
-          if (!ok) break;
-          tma_store_2d(maps + kMapA1, kt * kTileK, it.blk * kTileRows, sm.ring + (size_t)slot * stage_bytes);
-          tma_commit();
-          tma_wait_read1();   // every store but the newest has read its tile
-          if (prev_slot >= 0) mbar_arrive(&sm.empty[prev_slot]);
-          prev_slot = (int)slot;
-        }
-      }
-      tma_wait_read0();
-      if (prev_slot >= 0) mbar_arrive(&sm.empty[prev_slot]);
-      tma_wait_all0();
     }
   } else {
     // ---- epilogue warps: TMEM -> registers -> partial block; the last item of a row block adds the partials ----
@@ -388,7 +390,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
           for (int c4 = 0; c4 < 4; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int sp = 0; sp < it.splits; ++sp) {
             const float4* src = reinterpret_cast<const float4*>(
-                                    a.partial + (item_base + it.first + sp) * (size_t)(kTileRows * kRankPad)) + erow * 4;
+                                    a.partial + (item_base + it.first + (size_t)sp * it.stride) * (size_t)(kTileRows * kRankPad)) + erow * 4;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
               if (c4 < rpad4) {
