@@ -163,7 +163,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("powersgd_exchange",
         [](uintptr_t g, uintptr_t acc, uintptr_t out, uintptr_t mats, uintptr_t maps, int nmat, int rank_r,
            int has_memory, int divisor, int items_s1, int items_s2, int p_floats, int q_floats, uintptr_t p_mean,
-           uintptr_t q_mean, uintptr_t pt_orth, uintptr_t qt, uintptr_t gram, uintptr_t partial, uintptr_t counters,
+           uintptr_t q_mean, uintptr_t pt_orth, uintptr_t qt, uintptr_t gram, uintptr_t partial,
            uintptr_t barrier, uintptr_t status,
            unsigned long long ready2_off, int part, int rank, int world, unsigned long long seq,
            unsigned long long timeout_ns, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
@@ -174,8 +174,8 @@ PYBIND11_MODULE(_C, m) {
           a.rank = rank_r; a.has_memory = has_memory; a.divisor = divisor; a.items_s1 = items_s1; a.items_s2 = items_s2;
           a.p_floats = p_floats; a.q_floats = q_floats; a.p_mean = ptr<float>(p_mean); a.q_mean = ptr<float>(q_mean);
           a.pt_orth = ptr<float>(pt_orth); a.qt = ptr<float>(qt); a.gram_part = ptr<double>(gram);
-          a.partial = ptr<float>(partial); a.counters = ptr<unsigned>(counters);
-          if (!partial || !counters) throw std::invalid_argument("powersgd_exchange: split-K scratch missing");
+          a.partial = ptr<float>(partial);
+          if (!partial) throw std::invalid_argument("powersgd_exchange: split-K scratch missing");
           a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status); a.ready2_off = ready2_off;
           a.phases = kPhaseAll; a.part = part;
           a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);

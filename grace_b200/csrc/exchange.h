@@ -216,7 +216,6 @@ struct LowRankArgs {
   float* qt;               // sum_m 16*m: Q^T, persistent across steps (warm start)
   double* gram_part;       // grid * nmat * 256: one partial Gram matrix per CTA and matrix (added in CTA order)
   float* partial;          // (items_s1 + items_s2) blocks of 128 x 16: split-K partial sums, one block per work item
-  unsigned* counters;      // items_s1 + items_s2: finished items per row block (indexed by the block's first item)
   unsigned* barrier;
   unsigned* status;
   unsigned long long ready2_off;  // second flag pad (Q); peers.ready_off is the first (P)

@@ -37,8 +37,10 @@
 // A ring slot is free again when its MMAs have retired and the adder warps
 // have read it.
 // Split-K is deterministic: every work item (128 output rows x a K range)
-// writes its partial sums to its own block of a scratch buffer; the item that
-// completes a row block last adds the partials in split order into the slot.
+// writes its partial sums to its own block of a scratch buffer; after the
+// stage (and a grid barrier) the partials of a row block are added in split
+// order into the slot.  The epilogue itself is a TMEM read and one store per
+// row, so that many short items do not hold up the MMA thread.
 // Every mbarrier / flag / grid-barrier wait is bounded; TMA loads never use
 // cluster multicast and never read peer memory (peers are read with ld.cg).
 //
@@ -60,10 +62,16 @@ constexpr int kTileK = 32;              // fp32 elements per 128-byte row
 constexpr int kRankPad = 16;            // MMA N
 constexpr int kATileBytes = kTileRows * kTileK * 4;   // 16 KiB
 constexpr int kBTileBytes = kRankPad * kTileK * 4;    // 2 KiB
-constexpr int kStagesR = 6;             // ring depth with a residual tile per stage (34 KiB each)
-constexpr int kStagesNoR = 11;          // ring depth without (18 KiB each)
-constexpr int kRingBytes = kStagesR * (2 * kATileBytes + kBTileBytes);   // 204 KiB
+// A DRAM page should be visited for more than one 128-byte tile row: a ring step of stage 1 therefore carries
+// kS1Tiles K tiles side by side (256 contiguous bytes of every matrix row); a step of stage 2 has its four boxes of
+// 32 columns side by side already (512 bytes).
+constexpr int kS1Tiles = 2;
+constexpr int kStagesR = 3;             // stage 1 with a residual tile: 3 steps of 2 x (16 + 16 + 2) KiB
+constexpr int kStagesS1 = 5;            // stage 1 without: 5 steps of 2 x (16 + 2) KiB
+constexpr int kStagesNoR = 11;          // stage 2: 11 steps of 16 + 2 KiB
+constexpr int kRingBytes = kStagesR * kS1Tiles * (2 * kATileBytes + kBTileBytes);   // 204 KiB
 static_assert(kStagesNoR * (kATileBytes + kBTileBytes) <= kRingBytes, "ring too small");
+static_assert(kStagesS1 * kS1Tiles * (kATileBytes + kBTileBytes) <= kRingBytes, "ring too small");
 constexpr unsigned kTmemCols = 32;      // two accumulators of 16 columns
 constexpr int kMaxRank = 16;
 constexpr int kS3Trip = 12;             // rows of one trip of stage 3 (the next trip's loads are already in flight)
@@ -88,7 +96,6 @@ struct __align__(1024) SmemLayout {
   unsigned tmem_base;
   int bars_valid;                          // the mbarriers above hold valid objects (a GEMM stage ran)
   int epi_ok;                              // epilogue: the accumulator arrived in time
-  int last_flag;                           // epilogue: this CTA completed the row block
   double gram[kMaxRank][kMaxRank];
   double rinv[kMaxRank][kMaxRank];
   float prow[kS3Rows][kMaxRank];
@@ -188,7 +195,7 @@ __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int
   const LowRankMatrix& M = a.mats[mat];
   const int begin = stage == 1 ? M.item1_begin : M.item2_begin;
   const int local = idx - begin;
-  const int ktiles = ((stage == 1 ? M.m : M.n) + kTileK - 1) / kTileK;
+  const int ktiles = stage == 1 ? (M.m + kS1Tiles * kTileK - 1) / (kS1Tiles * kTileK) : (M.n + kTileK - 1) / kTileK;   // ring steps
   const int splits = stage == 1 ? M.splits1 : M.splits2;
   it.mat = mat;
   it.splits = splits;
@@ -216,12 +223,14 @@ __device__ __forceinline__ bool decode_item(const LowRankArgs& a, int stage, int
 // One GEMM stage over this CTA's items.  STAGE 1: P = M' Q.  STAGE 2: Q = M'^T P.
 // Every role walks the same sequence of (item, K tile) steps, which it derives from blockIdx by itself.
 template <int STAGE>
-__device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& status, float* __restrict__ dst_slot) {
+__device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& status) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool has_r = STAGE == 1 && a.has_memory;
-  const unsigned nstages = has_r ? kStagesR : kStagesNoR;
-  const unsigned stage_bytes = (has_r ? 2 * kATileBytes : kATileBytes) + kBTileBytes;
-  const unsigned off_r = kATileBytes, off_b = has_r ? 2 * kATileBytes : kATileBytes;
+  constexpr int T = STAGE == 1 ? kS1Tiles : 1;                    // K tiles per ring step
+  const unsigned nstages = STAGE == 2 ? kStagesNoR : (has_r ? kStagesR : kStagesS1);
+  // a step holds T gradient tiles, then (S1 with error feedback) T residual tiles, then T B tiles
+  const unsigned off_r = T * kATileBytes, off_b = (has_r ? 2 : 1) * T * kATileBytes;
+  const unsigned stage_bytes = off_b + T * kBTileBytes;
   const uint64_t tmo = a.peers.timeout_ns;
   if (tid == 0) {
     if (sm.bars_valid) {   // objects of the previous stage: all their phases are over (a CTA barrier lies behind us)
@@ -252,9 +261,13 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
           unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
           mbar_expect_tx(&sm.full[slot], stage_bytes);
           if (STAGE == 1) {
-            tma_load_2d(base, maps + kMapG1, kt * kTileK, it.blk * kTileRows, &sm.full[slot]);
-            if (has_r) tma_load_2d(base + off_r, maps + kMapA1, kt * kTileK, it.blk * kTileRows, &sm.full[slot]);
-            tma_load_2d(base + off_b, maps + kMapQt, kt * kTileK, 0, &sm.full[slot]);
+#pragma unroll
+            for (int t = 0; t < T; ++t) {   // a tile past the last column is filled with zeros by the TMA unit
+              const int x = (kt * T + t) * kTileK;
+              tma_load_2d(base + t * kATileBytes, maps + kMapG1, x, it.blk * kTileRows, &sm.full[slot]);
+              if (has_r) tma_load_2d(base + off_r + t * kATileBytes, maps + kMapA1, x, it.blk * kTileRows, &sm.full[slot]);
+              tma_load_2d(base + off_b + t * kBTileBytes, maps + kMapQt, x, 0, &sm.full[slot]);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j)  // four boxes of 32 columns x 32 rows of M': the MN-major operand layout
@@ -287,20 +300,23 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.ring + (size_t)slot * stage_bytes), b_addr = a_addr + off_b;
 #pragma unroll
-          for (int kk = 0; kk < kTileK / 8; ++kk) {
-            const uint64_t bdesc = smem_desc(b_addr + kk * 32, 16, 1024, 2);      // K-major: 32 B per K step of 8
-            const uint64_t adesc = STAGE == 1
-                                       ? smem_desc(a_addr + kk * 32, 16, 1024, 2)
-                                       // MN-major: a K step is 8 rows of 128 B (two atoms of 4 rows, 512 B apart);
-                                       // the next 32 of the 128 M-columns sit one box (4096 B) further on
-                                       : smem_desc(a_addr + kk * 1024, 4096, 512, 1);
-            umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdesc : kIdescAmn, !(kj == 0 && kk == 0));
-          }
-          if (has_r) {   // the residual tile into the same accumulator: P = G Q + R Q
+          for (int t = 0; t < T; ++t) {
 #pragma unroll
-            for (int kk = 0; kk < kTileK / 8; ++kk)
-              umma_tf32(tmem_d, smem_desc(a_addr + off_r + kk * 32, 16, 1024, 2), smem_desc(b_addr + kk * 32, 16, 1024, 2),
-                        kIdesc, true);
+            for (int kk = 0; kk < kTileK / 8; ++kk) {
+              const uint64_t bdesc = smem_desc(b_addr + t * kBTileBytes + kk * 32, 16, 1024, 2);   // K-major: 32 B per K step of 8
+              const uint64_t adesc = STAGE == 1
+                                         ? smem_desc(a_addr + t * kATileBytes + kk * 32, 16, 1024, 2)
+                                         // MN-major: a K step is 8 rows of 128 B (two atoms of 4 rows, 512 B apart);
+                                         // the next 32 of the 128 M-columns sit one box (4096 B) further on
+                                         : smem_desc(a_addr + kk * 1024, 4096, 512, 1);
+              umma_tf32(tmem_d, adesc, bdesc, STAGE == 1 ? kIdesc : kIdescAmn, !(kj == 0 && t == 0 && kk == 0));
+            }
+            if (has_r) {   // the residual tile into the same accumulator: P = G Q + R Q
+#pragma unroll
+              for (int kk = 0; kk < kTileK / 8; ++kk)
+                umma_tf32(tmem_d, smem_desc(a_addr + off_r + t * kATileBytes + kk * 32, 16, 1024, 2),
+                          smem_desc(b_addr + t * kBTileBytes + kk * 32, 16, 1024, 2), kIdesc, true);
+            }
           }
           umma_commit(&sm.empty[slot]);
         }
@@ -325,17 +341,20 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], (step / nstages) & 1, tmo, status, 500 + slot));
           if (!ok) break;
           const unsigned char* base = sm.ring + (size_t)slot * stage_bytes;
-          const float4* pa = reinterpret_cast<const float4*>(base);
-          const float4* pr = reinterpret_cast<const float4*>(base + off_r);
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const float4* pa = reinterpret_cast<const float4*>(base + t * kATileBytes);
+            const float4* pr = reinterpret_cast<const float4*>(base + off_r + t * kATileBytes);
 #pragma unroll 4
-          for (int i = at; i < kATileBytes / 16; i += kAdders) {
-            float4 x = pa[i];
-            const float4 y = pr[i];
-            x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-            const int row = i >> 3, grow = it.blk * kTileRows + row;
-            const int gcol = kt * kTileK + (((i & 7) ^ (row & 7)) << 2);
-            if (grow < M.n && gcol < M.m)   // m is a multiple of 4: the four columns are inside together
-              *reinterpret_cast<float4*>(dst + (size_t)grow * M.m + gcol) = x;
+            for (int i = at; i < kATileBytes / 16; i += kAdders) {
+              float4 x = pa[i];
+              const float4 y = pr[i];
+              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+              const int row = i >> 3, grow = it.blk * kTileRows + row;
+              const int gcol = (kt * T + t) * kTileK + (((i & 7) ^ (row & 7)) << 2);
+              if (grow < M.n && gcol < M.m)   // m is a multiple of 4: the four columns are inside together
+                *reinterpret_cast<float4*>(dst + (size_t)grow * M.m + gcol) = x;
+            }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm.empty[slot]);
@@ -343,7 +362,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       }
     }
   } else {
-    // ---- epilogue warps: TMEM -> registers -> partial block; the last item of a row block adds the partials ----
+    // ---- epilogue warps: TMEM -> registers -> this item's block of partial sums ----
     const int ew = warp - kEpilogueWarp0;                     // TMEM lane quarter of this warp (warp % 4)
     const int erow = ew * 32 + lane;                          // row of the 128-row block held by this thread
     const int rpad4 = (a.rank + 3) / 4;                       // float4 per row that carry data
@@ -371,40 +390,7 @@ __device__ void gemm_stage(const LowRankArgs& a, SmemLayout& sm, const Status& s
       for (int c4 = 0; c4 < rpad4; ++c4)
         part[c4] = make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]), __uint_as_float(v[4 * c4 + 2]),
                                __uint_as_float(v[4 * c4 + 3]));
-      // fixed-order reduction: whoever completes the row block last adds its partials, split 0 first
-      __threadfence();
-      named_bar_sync(1, 128);
-      if (erow == 0) {
-        const unsigned done = atomicAdd(a.counters + item_base + it.first, 1u);
-        sm.last_flag = done + 1 == (unsigned)it.splits;
-      }
-      named_bar_sync(1, 128);
-      if (sm.last_flag) {
-        __threadfence();
-        const LowRankMatrix& M = a.mats[it.mat];
-        const int row = it.blk * kTileRows + erow;
-        const int rows = STAGE == 1 ? M.n : M.m;
-        if (row < rows) {
-          float4 sum[4];
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int sp = 0; sp < it.splits; ++sp) {
-            const float4* src = reinterpret_cast<const float4*>(
-                                    a.partial + (item_base + it.first + (size_t)sp * it.stride) * (size_t)(kTileRows * kRankPad)) + erow * 4;
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              if (c4 < rpad4) {
-                const float4 t = __ldcg(src + c4);
-                sum[c4].x += t.x; sum[c4].y += t.y; sum[c4].z += t.z; sum[c4].w += t.w;
-              }
-            }
-          }
-          float4* dst = reinterpret_cast<float4*>(dst_slot + (STAGE == 1 ? M.p_off : M.q_off) + (size_t)row * kRankPad);
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) if (c4 < rpad4) dst[c4] = sum[c4];
-        }
-      }
-      named_bar_sync(1, 128);   // last_flag and epi_ok are rewritten by the next item
+      named_bar_sync(1, 128);   // epi_ok is rewritten by the next item
     }
   }
   __syncthreads();
@@ -471,6 +457,43 @@ __device__ void cholesky_inverse_large(SmemLayout& sm, int r) {
       double s = 0.0;
       for (int k = i + 1; k <= j; ++k) s += R[i][k] * sm.rinv[k][j];
       sm.rinv[i][j] = R[i][i] > 0.0 ? -s / R[i][i] : 0.0;
+    }
+  }
+}
+
+// Split-K reduction after a GEMM stage: row by row, the partial sums of the K splits are added in split order (the
+// same order on every run and every rank) and stored to this rank's slot.  One thread per output row.
+template <int STAGE>
+__device__ void reduce_partials(const LowRankArgs& a, float* __restrict__ dst_slot) {
+  const int rpad4 = (a.rank + 3) / 4;
+  const size_t item_base = STAGE == 1 ? 0 : (size_t)a.items_s1;
+  for (int mat = 0; mat < a.nmat; ++mat) {
+    const LowRankMatrix& M = a.mats[mat];
+    const int rows = STAGE == 1 ? M.n : M.m;
+    const int splits = STAGE == 1 ? M.splits1 : M.splits2;
+    const int blocks = (rows + kTileRows - 1) / kTileRows;
+    const int begin = STAGE == 1 ? M.item1_begin : M.item2_begin;
+    for (int row = blockIdx.x * kThreads + threadIdx.x; row < rows; row += gridDim.x * kThreads) {
+      const int blk = row / kTileRows, erow = row % kTileRows;
+      // numbering of decode_item: stage 1 split fastest, stage 2 block fastest
+      const size_t first = item_base + begin + (STAGE == 1 ? (size_t)blk * splits : (size_t)blk);
+      const size_t stride = STAGE == 1 ? 1 : (size_t)blocks;
+      float4 sum[4];
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp = 0; sp < splits; ++sp) {
+        const float4* src = reinterpret_cast<const float4*>(a.partial + (first + sp * stride) * (size_t)(kTileRows * kRankPad)) + erow * 4;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          if (c4 < rpad4) {
+            const float4 t = __ldcg(src + c4);
+            sum[c4].x += t.x; sum[c4].y += t.y; sum[c4].z += t.z; sum[c4].w += t.w;
+          }
+        }
+      }
+      float4* dst = reinterpret_cast<float4*>(dst_slot + (STAGE == 1 ? M.p_off : M.q_off) + (size_t)row * kRankPad);
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) if (c4 < rpad4) dst[c4] = sum[c4];
     }
   }
 }
@@ -624,16 +647,16 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     __syncthreads();
-    // zero this rank's slot (P and Q regions: rows of a last, partial block are never written otherwise),
-    // the Gram accumulators and the completion counters of both GEMM stages
+    // zero this rank's slot (P and Q regions: padded columns are never written otherwise)
     const size_t nfl = (size_t)a.p_floats + a.q_floats;
     for (size_t i = gtid * 4; i < nfl; i += gthreads * 4)
       *reinterpret_cast<float4*>(my_slot + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (size_t i = gtid; i < (size_t)a.items_s1 + a.items_s2; i += gthreads) a.counters[i] = 0u;
     ok = bar.sync();
-    if (ok) gemm_stage<1>(a, sm, status, slot_p);
+    if (ok) gemm_stage<1>(a, sm, status);
     fence_async_all();
     ok = bar.sync();
+    if (ok) reduce_partials<1>(a, slot_p);
+    ok = bar.sync() && ok;
   }
 
   if (part1 || part2) {
@@ -726,12 +749,12 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
         }
         __syncthreads();
       }
-      if (part != 0)   // split launch: the counters of this stage were zeroed by an earlier launch's part 1; do it again
-        for (size_t i = gtid; i < (size_t)a.items_s2; i += gthreads) a.counters[a.items_s1 + i] = 0u;
     }
     fence_async_all();  // pt_orth is read by TMA next
     ok = bar.sync() && ok;
-    if (ok) gemm_stage<2>(a, sm, status, slot_q);
+    if (ok) gemm_stage<2>(a, sm, status);
+    ok = bar.sync() && ok;
+    if (ok) reduce_partials<2>(a, slot_q);
     ok = bar.sync() && ok;
   }
 

@@ -24,7 +24,8 @@ from .exchange import (CODEC, PHASE_ALL, PHASE_COMPRESS, PHASE_EXCHANGE, Exchang
 RANK_PAD = 16
 TILE_K = 32
 TILE_ROWS = 128
-MIN_K_TILES_PER_ITEM = 8      # a work item streams at least 8 x 16 KiB of the matrix (unless the matrix is smaller)
+S1_TILES = 2                  # K tiles per ring step of stage 1 (kS1Tiles of the kernel)
+MIN_STEPS_PER_ITEM = 8        # a work item runs at least this many ring steps (unless the matrix is smaller)
 MAX_RANK = 16
 
 
@@ -38,12 +39,12 @@ def eligible(shape: Sequence[int]) -> bool:
     return n % 4 == 0 and m % 4 == 0 and n >= 16 and m >= 16
 
 
-def choose_splits(n_out: int, n_k: int, grid: int) -> int:
+def choose_splits(n_out: int, n_k: int, grid: int, tiles_per_step: int = 1) -> int:
     """K splits per 128-row block of one GEMM stage: the work items (blocks x splits) should fill whole waves of
-    ``grid`` persistent CTAs, and an item should not be shorter than ``MIN_K_TILES_PER_ITEM`` K tiles."""
+    ``grid`` persistent CTAs, and an item should not be shorter than ``MIN_STEPS_PER_ITEM`` ring steps."""
     blocks = -(-n_out // TILE_ROWS)
-    ktiles = -(-n_k // TILE_K)
-    max_splits = max(1, ktiles // MIN_K_TILES_PER_ITEM)
+    ktiles = -(-n_k // (TILE_K * tiles_per_step))      # ring steps along K
+    max_splits = max(1, ktiles // MIN_STEPS_PER_ITEM)
     best, best_score = 1, -1.0
     for splits in range(1, max_splits + 1):
         items = blocks * splits
@@ -95,7 +96,7 @@ class LowRankPlan:
         except Exception:
             pass
         for name, off, n, m in self.matrices:
-            s1, s2 = choose_splits(n, m, grid), choose_splits(m, n, grid)
+            s1, s2 = choose_splits(n, m, grid, S1_TILES), choose_splits(m, n, grid)
             rows.append(struct.pack("<qiiiiiiiiii", off, n, m, p_off, q_off, pt_off, qt_off, i1, i2, s1, s2))
             p_off += n * RANK_PAD
             q_off += m * RANK_PAD
@@ -115,10 +116,9 @@ class LowRankPlan:
             self.pt_orth = torch.zeros(self.p_floats, dtype=torch.float32, device=device)
             self.qt = torch.zeros(self.q_floats, dtype=torch.float32, device=device)
             self.gram = torch.zeros(max(grid, 160) * nmat * 256, dtype=torch.float64, device=device)   # per-CTA partials
-            # split-K scratch: one 128 x 16 block of partial sums per work item, and the per-block completion counters
+            # split-K scratch: one 128 x 16 block of partial sums per work item
             self.partial = torch.empty((self.items_s1 + self.items_s2) * TILE_ROWS * RANK_PAD, dtype=torch.float32,
                                        device=device)
-            self.counters = torch.zeros(self.items_s1 + self.items_s2, dtype=torch.int32, device=device)
             qt_off = 0
             for name, off, n, m in self.matrices:
                 r = min(n, m, self.rank)
@@ -191,7 +191,7 @@ class LowRankPlan:
             self.maps.data_ptr(), len(self.matrices), self.rank, int(self.has_memory), self.world, self.items_s1,
             self.items_s2, self.p_floats, self.q_floats, self.p_mean.data_ptr(), self.q_mean.data_ptr(),
             self.pt_orth.data_ptr(), self.qt.data_ptr(), self.gram.data_ptr(), self.partial.data_ptr(),
-            self.counters.data_ptr(), ch.barrier.data_ptr(), ch.status.data_ptr(), self.ready2_off, part, heap.rank, heap.world, seq, ch.timeout_ns, heap.bases,
+            ch.barrier.data_ptr(), ch.status.data_ptr(), self.ready2_off, part, heap.rank, heap.world, seq, ch.timeout_ns, heap.bases,
             ch.ready_off, ch.ack_off, ch.slot_off[seq & 1], grid, _stream_ptr())
         ch.post_status()
         return seq
