@@ -7,8 +7,10 @@ process and the training step is then timed under several settings of
     bucket size (MiB of fp32 gradients per fused exchange; 0 = one exchange after backward),
     overlap_sms (SMs an exchange may use while backward is still running),
     transport   (pull = peers' slots are read over NVLink, push = multimem.st through the switch),
+    launches    (default: an overlapped exchange is split into a full-width compress launch and an exchange launch
+                 on ``overlap_sms`` SMs; ``:whole`` keeps it one launch on ``overlap_sms`` SMs),
 
-given as ``--settings 0:0:pull,64:32:pull,64:32:push``.  Every setting gets
+given as ``--settings 0:0:pull,64:32:pull,64:32:push:whole``.  Every setting gets
 its own communicator, flat buffers and optimizer; device-timed with CUDA events
 around ``--steps`` steps after ``--warmup`` steps, max over ranks; the batch
 (and the activations it produces) is larger than L2, so nothing stays cached
@@ -73,8 +75,10 @@ def main():
         sampler.start()
 
     for setting in args.settings.split(","):
-        bucket_mb, sms, transport = setting.split(":")
-        params = dict(cfg["grace"], world_size=world, fused=True)
+        fields = setting.split(":")
+        bucket_mb, sms, transport = fields[:3]
+        whole = len(fields) > 3 and fields[3] == "whole"
+        params = dict(cfg["grace"], world_size=world, fused=True, split_overlap=not whole)
         if int(sms) > 0:
             params["overlap_sms"] = int(sms)
         if transport == "push":
@@ -92,6 +96,7 @@ def main():
             return loss
 
         row = {"config": args.config, "bucket_mb": float(bucket_mb), "overlap_sms": int(sms), "transport": transport,
+               "launches_per_exchange": 1 if (whole or float(bucket_mb) == 0) else 2,
                "n_gpus": world, "buckets": len(flat.buckets)}
         try:
             for i in range(args.warmup):

@@ -165,15 +165,18 @@ class _Plan:
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
                  group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None, nvls=False,
-                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None):
+                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None, split_overlap=True):
         """``comm_sms``: SMs an exchange may use when nothing else runs (None: all of them).  ``overlap_sms``: SMs
         of an exchange that runs next to the backward pass (launched from a gradient hook: ``send_step``, the
-        bucketed ``DistributedOptimizer``, the DDP hook); the rest stays with backward.  ``arena_mb``: size of
+        bucketed ``DistributedOptimizer``, the DDP hook); the rest stays with backward.  With ``split_overlap`` such an
+        exchange is two launches: compress + publish at full width (short, HBM bound), then pull + decode on
+        ``overlap_sms`` SMs (long at 8 GPUs, NVLink bound).  ``arena_mb``: size of
         the symmetric heaps the plans are carved from.  ``store``: a ``torch.distributed`` store through which the
         ranks tell each other about a failed exchange (``agree`` / ``recover``)."""
         super().__init__(compressor, memory, world_size)
         self.mode = mode
         self.overlap_sms = overlap_sms
+        self.split_overlap = bool(split_overlap)
         self.arena_bytes = int(arena_mb * (1 << 20))
         self._arena = None
         self._side_stream = None
@@ -392,6 +395,15 @@ class FusedExchange(Communicator):
                 plan.channel.poll()
                 plan.launch(flat, out, sm_limit=sm_limit)
             plan.launch_dense(flat, out, sm_limit=sm_limit)
+        elif sm_limit is not None and self.split_overlap:
+            # next to backward: the compress half is HBM bound and short, so it runs at full width; the exchange half
+            # mostly waits for NVLink, so it keeps to a few SMs and leaves the rest to the backward kernels
+            from ..ops.exchange import PHASE_CLIP, PHASE_COMPRESS, PHASE_EXCHANGE, PHASE_PUBLISH, PHASE_REDUCE
+
+            first = PHASE_COMPRESS | PHASE_PUBLISH | (PHASE_CLIP if getattr(plan, "clip", False) else 0)
+            second = PHASE_EXCHANGE | (PHASE_REDUCE if getattr(plan, "alltoall", False) else 0)
+            seq = self._launch(plan, flat, out, first)
+            self._launch(plan, flat, out, second, seq=seq, sm_limit=sm_limit)
         else:
             self._launch(plan, flat, out, PHASE_ALL, sm_limit=sm_limit)
         plan.steps += 1

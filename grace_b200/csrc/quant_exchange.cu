@@ -461,6 +461,100 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
       __syncthreads();
       const long long g_begin = chunk_groups * rank;
       const long long g_end = g_begin + chunk_groups < groups_total ? g_begin + chunk_groups : groups_total;
+      if (s_ready2 && T::bits == 8 && world <= kStagePeers) {
+        // 8-bit codes: a warp trip covers 512 elements (four groups); lane l fetches its 16 code bytes from EVERY
+        // rank (one 512-byte request per rank and warp, all in flight together) and parks them in the warp's staging
+        // area; the sum is formed rank by rank, re-encoded with the chunk's own random stream and written as one
+        // 16-byte store per lane.
+        uint4* const st_codes = reinterpret_cast<uint4*>(s_dyn + warp * kStageWarpBytes);
+        float* const st_norms = reinterpret_cast<float*>(s_dyn + warp * kStageWarpBytes + kStagePeers * 512);
+        const long long e_begin = g_begin << 7, e_end = g_end << 7;
+        for (long long w0 = e_begin + 512ll * ((long long)blockIdx.x * kWarps + warp); w0 < e_end;
+             w0 += 512ll * gridDim.x * kWarps) {
+          const long long i = w0 + 16ll * lane;     // this lane's 16 elements (inside one group)
+          const bool have = i < e_end;
+          {
+            uint4 v[kStagePeers];
+            float nv[kStagePeers];
+#pragma unroll
+            for (int p = 0; p < kStagePeers; ++p) {
+              v[p] = make_uint4(0u, 0u, 0u, 0u);
+              nv[p] = 0.f;
+              if (p < world) {
+                const char* slot = a.peers.heap[p] + a.peers.slot_off;
+                if (have) v[p] = ld_cg_u4(slot + off_codes + (size_t)i);
+                if (C == kCodecQSGD && lane < 4 && w0 + 128ll * lane < e_end)
+                  nv[p] = ld_cg_f32(slot + off_norms + (size_t)((w0 >> 7) + lane) * 4);
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int p = 0; p < kStagePeers; ++p) {
+              if (p < world) {
+                st_codes[p * 32 + lane] = v[p];
+                if (C == kCodecQSGD && lane < 4) st_norms[p * 4 + lane] = nv[p];
+              }
+            }
+            __syncwarp();
+          }
+          float xs[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xs[j] = 0.f;
+          for (int p = 0; p < world; ++p) {
+            const uint4 cw = st_codes[p * 32 + lane];
+            const unsigned words[4] = {cw.x, cw.y, cw.z, cw.w};
+            const float d = C == kCodecQSGD ? st_norms[p * 4 + (lane >> 3)] / (float)a.quantum : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+              if (C == kCodecQSGD) xs[j] += d * (float)(int)(signed char)byte;
+              else xs[j] += natural_decode(byte);
+            }
+          }
+          // re-encode the reduced values (a second lossy step, with its own random stream: counter = element / 4)
+          unsigned out_words[4] = {0u, 0u, 0u, 0u};
+          float sq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sq += xs[j] * xs[j];
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);     // the eight lanes of a group
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          const float norm = sqrtf(sq);
+          const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            Philox4 rnd{0u, 0u, 0u, 0u};
+            if (C == kCodecQSGD || !a.deterministic) rnd = philox_group((uint64_t)((i >> 2) + q4), a.step, 1u, a.seed);
+            const unsigned rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float x = xs[4 * q4 + j];
+              unsigned code;
+              if (C == kCodecQSGD) {
+                const float lf = qn * fabsf(x);
+                const float fl = floorf(lf);
+                const float level = fminf(fl + ((u01(rw[j]) < lf - fl) ? 1.f : 0.f), 127.f);
+                code = (unsigned)(x < 0.f ? -(int)level : (int)level) & 0xffu;
+              } else {
+                const unsigned bits = __float_as_uint(x);
+                const unsigned biased = (bits >> 23) & 0xffu;
+                const unsigned mant = bits & 0x7fffffu;
+                const bool up = a.deterministic ? mant > 0x400000u : u01(rw[j]) < (float)mant * 1.1920928955078125e-07f;
+                int c7 = (int)biased + (up ? 1 : 0) - 17;
+                c7 = c7 < 0 ? 0 : (c7 > 127 ? 127 : c7);
+                if (biased == 0) c7 = 0;
+                code = (unsigned)c7 | ((bits >> 24) & 0x80u);
+              }
+              out_words[q4] |= code << (8 * j);
+            }
+          }
+          if (have) {
+            const size_t li = (size_t)(i - e_begin);      // element index inside my chunk
+            *reinterpret_cast<uint4*>(my_slot + off2_codes + li) = make_uint4(out_words[0], out_words[1], out_words[2], out_words[3]);
+            if (C == kCodecQSGD && (lane & 7) == 0) *reinterpret_cast<float*>(my_slot + off2_norms + (li >> 7) * 4) = norm;
+          }
+        }
+      } else
       if (s_ready2) {
         const long long wstride = (long long)gridDim.x * kWarps;
         for (long long grp0 = g_begin + (long long)blockIdx.x * kWarps + warp; grp0 < g_end; grp0 += wstride * kU) {
@@ -582,6 +676,50 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
         if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid)) s_ready2 = 0;
       }
       __syncthreads();
+      if (s_ready2 && lo < hi && T::bits == 8) {
+        // 8-bit codes: every lane fetches 16 codes (and its group's norm) from the rank that owns the group; two
+        // such 512-byte requests per warp are in flight before the first is decoded
+        constexpr int kX = 2;
+        for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
+          for (long long w0 = b0 + 512ll * warp; w0 < e0; w0 += 512ll * kWarps * kX) {
+            uint4 cw[kX];
+            float dq[kX];
+#pragma unroll
+            for (int q = 0; q < kX; ++q) {
+              const long long i = w0 + 512ll * kWarps * q + 16 * lane;
+              cw[q] = make_uint4(0u, 0u, 0u, 0u);
+              dq[q] = 0.f;
+              if (i < e0) {
+                const long long grp = i >> 7;
+                const int owner = (int)(grp / chunk_groups);
+                const long long lg = grp - (long long)owner * chunk_groups;
+                const char* slot = a.peers.heap[owner] + a.peers.slot_off;
+                cw[q] = ld_cg_u4(slot + off2_codes + (size_t)(lg << 7) + (size_t)(i & 127));
+                if (C == kCodecQSGD) dq[q] = ld_cg_f32(slot + off2_norms + (size_t)lg * 4);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < kX; ++q) {
+              const long long i = w0 + 512ll * kWarps * q + 16 * lane;
+              const unsigned words[4] = {cw[q].x, cw[q].y, cw[q].z, cw[q].w};
+              const float d = dq[q] / (float)a.quantum;
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                const long long iv = i + 4 * v4;
+                if (iv >= e0) continue;
+                const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
+                float ov[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const unsigned byte = (words[v4] >> (8 * j)) & 0xffu;
+                  ov[j] = (C == kCodecQSGD ? d * (float)(int)(signed char)byte : natural_decode(byte)) * a.scale;
+                }
+                store4g(a.out, a.g_dtype, iv, valid, ov);
+              }
+            }
+          }
+        });
+      } else
       if (s_ready2 && lo < hi) {
         for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
           for (long long gb0 = b0 + 128ll * warp; gb0 < e0; gb0 += 128ll * kWarps * kU) {
@@ -910,7 +1048,7 @@ cudaError_t launch_codec(const QuantArgs& a, int grid, cudaStream_t stream) {
   void* params[] = {&copy};
   const void* fn = a.recv_mc ? (const void*)quant_exchange_kernel<C, true> : (const void*)quant_exchange_kernel<C, false>;
   size_t smem = 0;
-  if (staged_codec<C>() && a.peers.world > 1 && a.peers.world <= kStagePeers && (a.phases & kPhaseExchange)) {
+  if (staged_codec<C>() && a.peers.world > 1 && a.peers.world <= kStagePeers && (a.phases & (kPhaseExchange | kPhaseReduce))) {
     smem = kStageBytes;
     static bool attr_set[64][2] = {};
     int dev = 0;
