@@ -104,6 +104,9 @@ def main():
                     help="timed iterations for sizes of 16 Mi elements and more (keeps the clock sampler busy long "
                          "enough to see the GPU under load)")
     ap.add_argument("--impl", default="ours", choices=["ours", "library", "reference"])
+    ap.add_argument("--timeout-ms", type=float, default=3000.0,
+                    help="limit of every device-side wait of the fused exchanges; a case that runs into it is "
+                         "reported as an error after its first failing iteration")
     ap.add_argument("--virtual-ranks", type=int, default=0,
                     help="one GPU only: run W ranks of the fused exchange on this GPU, phase by phase (all ranks "
                          "compress and publish, then all ranks exchange); reports the time of all W ranks divided by W")
@@ -142,6 +145,7 @@ def main():
             import grace_b200
 
             p["fused"] = True
+            p["timeout_ms"] = args.timeout_ms
             return grace_b200.grace_from_params(p)
         if args.impl == "library":
             import grace_b200
@@ -224,6 +228,8 @@ def main():
                         out = grc.step(g, "w") if resident is None else grc.step_flat(g)
                     e1.record()
                     torch.cuda.synchronize()
+                    if it == 0 and hasattr(grc, "check"):
+                        grc.check()          # a transport that does not work here fails once, not in every iteration
                     if it >= args.warmup:
                         times.append(e0.elapsed_time(e1))
                 if hasattr(grc, "check"):

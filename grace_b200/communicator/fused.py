@@ -16,10 +16,11 @@ compressor          memory                                 kernel
 ==================  =====================================  ==================
 TopK, DGC           none / residual / dgc                  sparse (radix select)
 Threshold           none / residual                        sparse (threshold)
-QSGD (bucket 128,   none / residual                        quantised
-q < 128), TernGrad,
-natural, 8-bit,
-fp16, none
+QSGD (any bucket    none / residual                        quantised
+that is a multiple
+of 4, q < 32768),
+TernGrad, natural,
+8-bit, fp16, none
 signSGD, signum     none / residual                        quantised, vote
 EF-signSGD          efsignsgd                              quantised
 1-bit               none / residual                        quantised
@@ -138,9 +139,19 @@ class _Plan:
             self.codec = owner._codec
             self.alltoall = owner.mode == "alltoall" and self.codec in (X.CODEC["qsgd"], X.CODEC["natural"],
                                                                         X.CODEC["fp16"], X.CODEC["fp32"])
-            slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg, owner.world_size if self.alltoall else 0)
+            self.qsgd_bucket = self.qsgd_nbuckets = 0
+            if self.codec == X.CODEC["qsgdx"]:
+                # Segment.k carries the index of each tensor's first bucket
+                self.qsgd_bucket = int(comp.bucket_size)
+                self.ks, first = [], 0
+                for n in layout.numels:
+                    self.ks.append(first)
+                    first += -(-n // self.qsgd_bucket)
+                self.qsgd_nbuckets = first
+            slot_bytes = Cn.quant_slot_bytes(self.codec, layout.total, nseg, owner.world_size if self.alltoall else 0,
+                                             self.qsgd_nbuckets)
             self.recv = None
-            if (owner.nvls and not self.alltoall and owner._virtual is None
+            if (owner.nvls and not self.alltoall and owner._virtual is None and self.codec != X.CODEC["qsgdx"]
                     and owner.world_size >= max(2, owner.nvls_min_world)):
                 from ..parallel.nvls import NvlsBuffer
 
@@ -236,7 +247,11 @@ class FusedExchange(Communicator):
                     self._kind = "quant"
                     break
             if isinstance(comp, C_.QSGDCompressor) and (comp.bucket_size != 128 or comp.quantum_num >= 128):
-                self._kind = None
+                # the general form: int16 codes, one norm per bucket of each tensor (all-gather mode, pull transport)
+                if comp.bucket_size >= 4 and comp.bucket_size % 4 == 0 and comp.quantum_num < 32768:
+                    self._codec = CODEC["qsgdx"]
+                else:
+                    self._kind = None
 
     def supported(self, tensor: torch.Tensor) -> bool:
         if self._kind == "powersgd":
@@ -357,7 +372,8 @@ class FusedExchange(Communicator):
                 first_step=plan.steps == 0, beta=beta, gamma=gamma, mom_beta=float(getattr(comp, "momentum", 0.0)),
                 lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
                 phases=phases | (X.PHASE_REDUCE if (plan.alltoall and phases == X.PHASE_ALL) else 0), seq=seq,
-                recv=plan.recv, alltoall=plan.alltoall, grid=grid)
+                recv=plan.recv, alltoall=plan.alltoall, grid=grid, qsgd_bucket=plan.qsgd_bucket,
+                qsgd_nbuckets=plan.qsgd_nbuckets)
         return seq
 
     # ------------------------------------------------------------------

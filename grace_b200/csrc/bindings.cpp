@@ -67,7 +67,8 @@ PYBIND11_MODULE(_C, m) {
   // ---- sizes / occupancy ----
   m.def("sparse_slot_bytes", &sparse_slot_bytes, pybind11::arg("cap"), pybind11::arg("tiled_total") = 0);
   m.def("sparse_max_grid", &sparse_max_grid);
-  m.def("quant_slot_bytes", &quant_slot_bytes, py::arg("codec"), py::arg("total"), py::arg("nseg"), py::arg("alltoall_world") = 0);
+  m.def("quant_slot_bytes", &quant_slot_bytes, py::arg("codec"), py::arg("total"), py::arg("nseg"), py::arg("alltoall_world") = 0,
+        py::arg("nbuckets") = 0);
   m.def("quant_max_grid", &quant_max_grid);
   m.def("sgd_table_chunk", &sgd_table_chunk);
   m.attr("SEGMENT_BYTES") = sizeof(Segment);
@@ -113,8 +114,10 @@ PYBIND11_MODULE(_C, m) {
            int phases, int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
            unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off,
-           uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride, int g_dtype) {
+           uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride, int g_dtype, int qsgd_bucket,
+           long long qsgd_nbuckets) {
           QuantArgs a{};
+          a.qsgd_bucket = qsgd_bucket; a.qsgd_nbuckets = qsgd_nbuckets;
           if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");
           a.g_dtype = g_dtype;
           a.recv_local = ptr<char>(recv_local); a.recv_mc = ptr<char>(recv_mc); a.recv_stride = recv_stride;

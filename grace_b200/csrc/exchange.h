@@ -112,6 +112,7 @@ enum Codec : int {
   kCodecOneBit = 6,    // 1 bit + two means per segment
   kCodecFP16 = 7,      // half cast, sum
   kCodecFP32 = 8,      // no compression: one-shot all-gather-sum (small dense tensors)
+  kCodecQSGDX = 9,     // QSGD, any bucket size that is a multiple of 4, up to 32767 levels: int16 codes + fp32 norm per bucket
 };
 
 struct QuantSegStats {   // per segment, device scratch (double for stable sums)
@@ -132,6 +133,8 @@ struct QuantArgs {
   long long total;     // padded flat length, multiple of 128
   int codec;
   int quantum;         // QSGD levels
+  int qsgd_bucket;     // kCodecQSGDX: elements per bucket (Segment::k = index of the tensor's first bucket)
+  long long qsgd_nbuckets;  // kCodecQSGDX: buckets of all tensors together
   int deterministic;   // natural: round at 0.5 instead of drawing
   int first_step;      // signum: momentum not yet initialised
   float beta, gamma;   // acc = beta*residual + gamma*g
@@ -156,7 +159,7 @@ struct QuantArgs {
 };
 
 // alltoall_world > 0 adds the second region (one re-encoded chunk per rank) used by the two-phase mode.
-size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world = 0);
+size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world = 0, long long nbuckets = 0);
 int quant_max_grid(int device, int sm_limit);
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
 

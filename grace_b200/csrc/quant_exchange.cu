@@ -62,13 +62,17 @@ template <> struct CodecTraits<kCodecEFSign>   { static constexpr bool stats = t
 template <> struct CodecTraits<kCodecOneBit>   { static constexpr bool stats = true;  static constexpr int bits = 1; };
 template <> struct CodecTraits<kCodecFP16>     { static constexpr bool stats = false; static constexpr int bits = 16; };
 template <> struct CodecTraits<kCodecFP32>     { static constexpr bool stats = false; static constexpr int bits = 32; };
+// QSGD with any bucket size (a multiple of 4) and up to 32767 levels: int16 codes, one norm per bucket of each tensor.
+// A pass of its own computes the bucket norms before the encode pass; decode goes through the generic path.
+template <> struct CodecTraits<kCodecQSGDX>    { static constexpr bool stats = false; static constexpr int bits = 16; };
 
 __host__ __device__ inline size_t scalars_bytes(int nseg) { return ((size_t)nseg * 16 + 127) / 128 * 128; }
 __host__ __device__ inline size_t codes_bytes(int bits, long long total) { return (size_t)total * bits / 8; }
 
-__host__ __device__ inline size_t region1_bytes(int codec, int bits, long long total, int nseg) {
+__host__ __device__ inline size_t region1_bytes(int codec, int bits, long long total, int nseg, long long nbuckets = 0) {
   size_t b = kHeaderBytes + scalars_bytes(nseg) + codes_bytes(bits, total);
   if (codec == kCodecQSGD) b += (size_t)(total / 128) * 4;
+  if (codec == kCodecQSGDX) b += (size_t)((nbuckets + 3) / 4 * 4) * 4;
   return (b + 255) / 256 * 256;
 }
 
@@ -238,6 +242,39 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
       ok = bar.sync();
     }
 
+    if (C == kCodecQSGDX && ok) {
+      // ---- pass N (general QSGD): one warp per bucket of `qsgd_bucket` consecutive elements of a tensor (the last
+      //      bucket of a tensor may be shorter): L2 norm of the compensated values, in a fixed order ----
+      const long long nb = a.qsgd_nbuckets;
+      const long long gw = (long long)blockIdx.x * kWarps + warp, nw = (long long)gridDim.x * kWarps;
+      for (long long b = gw; b < nb; b += nw) {
+        int lo_s = 0, hi_s = a.nseg;            // segment whose first bucket (Segment::k) is the last one <= b
+        while (lo_s + 1 < hi_s) {
+          const int mid = (lo_s + hi_s) >> 1;
+          if ((long long)a.segs[mid].k <= b) lo_s = mid; else hi_s = mid;
+        }
+        const Segment sg = a.segs[lo_s];
+        const long long e_begin = sg.offset + (b - sg.k) * a.qsgd_bucket;
+        long long e_end = e_begin + a.qsgd_bucket;
+        if (e_end > sg.offset + sg.numel) e_end = sg.offset + sg.numel;
+        float sq = 0.f;
+        for (long long i = e_begin + 4ll * lane; i < e_end; i += 128) {
+          const int valid = (e_end - i) >= 4 ? 4 : (int)(e_end - i);
+          float gv[4], rv[4] = {0.f, 0.f, 0.f, 0.f};
+          load4g(a.g, a.g_dtype, i, valid, gv);
+          if (a.acc && a.beta != 0.f) load4(a.acc, i, valid, rv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x = a.beta * rv[j] + a.gamma * gv[j];
+            sq += x * x;
+          }
+        }
+        sq = warp_sum(sq);
+        if (lane == 0) *reinterpret_cast<float*>(my_slot + off_norms + (size_t)b * 4) = sqrtf(sq);
+      }
+      ok = bar.sync();
+    }
+
     // ---- pass E: encode into the send slot, write the residual ----
     if (ok && lo < hi) {
       const void* __restrict__ src = (T::stats && a.acc) ? (const void*)a.acc : a.g;
@@ -292,7 +329,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
           float dv[4] = {0.f, 0.f, 0.f, 0.f};  // decode(code) for the residual
           const size_t group = (size_t)(gb >> 7);
           Philox4 rnd{0u, 0u, 0u, 0u};
-          if (C == kCodecQSGD || C == kCodecTernGrad || (C == kCodecNatural && !a.deterministic))
+          if (C == kCodecQSGD || C == kCodecQSGDX || C == kCodecTernGrad || (C == kCodecNatural && !a.deterministic))
             rnd = philox_group((uint64_t)(i >> 2), a.step, 0u, a.seed);
           const unsigned rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 
@@ -320,6 +357,26 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               if (kPush) *reinterpret_cast<float*>(my_slot + off_norms + group * 4) = norm;
               else put_f32(off_norms + group * 4, norm);
             }
+          } else if (C == kCodecQSGDX) {
+            // the lane's four elements lie in one bucket (bucket sizes are multiples of 4)
+            const long long bucket = a.segs[s].k + (i - a.segs[s].offset) / a.qsgd_bucket;
+            const float norm = valid ? __ldcg(reinterpret_cast<const float*>(my_slot + off_norms) + bucket) : 0.f;
+            const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f;
+            const float dq = norm / (float)a.quantum;
+            int codes[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lf = qn * fabsf(xv[j]);
+              const float fl = floorf(lf);
+              float level = fl + ((u01(rw[j]) < lf - fl) ? 1.f : 0.f);
+              level = fminf(level, 32767.f);
+              codes[j] = xv[j] < 0.f ? -(int)level : (int)level;
+              dv[j] = dq * (float)codes[j];
+            }
+            uint2 w;
+            w.x = ((unsigned)codes[0] & 0xffffu) | ((unsigned)codes[1] << 16);
+            w.y = ((unsigned)codes[2] & 0xffffu) | ((unsigned)codes[3] << 16);
+            put_u2(off_codes + (size_t)i * 2, w);
           } else if (C == kCodecNatural) {
             unsigned word = 0;
 #pragma unroll
@@ -961,6 +1018,8 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
               } else if (T::bits == 16) {
                 const char* ptr16 = slot + off_codes + (size_t)i * 2;
                 asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(w0[q]), "=r"(w1[q]) : "l"(ptr16));
+                if (C == kCodecQSGDX && i < e0)
+                  dq[q] = ld_cg_f32(slot + off_norms + (size_t)(a.segs[s].k + (i - a.segs[s].offset) / a.qsgd_bucket) * 4);
               }
             }
 #pragma unroll
@@ -1004,6 +1063,10 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                 const uint4 w = ld_cg_u4(slot + off_codes + (size_t)i * 4);
                 sum[q][0] += __uint_as_float(w.x); sum[q][1] += __uint_as_float(w.y);
                 sum[q][2] += __uint_as_float(w.z); sum[q][3] += __uint_as_float(w.w);
+              } else if (C == kCodecQSGDX) {
+                const float d = dq[q] / (float)a.quantum;
+                sum[q][0] += d * (float)(short)(w0[q] & 0xffffu); sum[q][1] += d * (float)(short)(w0[q] >> 16);
+                sum[q][2] += d * (float)(short)(w1[q] & 0xffffu); sum[q][3] += d * (float)(short)(w1[q] >> 16);
               } else {  // fp16
                 const float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&w0[q]));
                 const float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&w1[q]));
@@ -1095,16 +1158,17 @@ void build_u8_edges(float* e) {
 
 }  // namespace
 
-size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world) {
+size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world, long long nbuckets) {
   int bits = 8;
   switch (codec) {
+    case kCodecQSGDX: bits = 16; break;
     case kCodecTernGrad: bits = 2; break;
     case kCodecSign: case kCodecEFSign: case kCodecOneBit: bits = 1; break;
     case kCodecFP16: bits = 16; break;
     case kCodecFP32: bits = 32; break;
     default: bits = 8;
   }
-  size_t bytes = region1_bytes(codec, bits, total, nseg);
+  size_t bytes = region1_bytes(codec, bits, total, nseg, nbuckets);
   if (alltoall_world > 0) {
     const long long groups = total / 128;
     const long long chunk_groups = (groups + alltoall_world - 1) / alltoall_world;
@@ -1138,6 +1202,9 @@ cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t str
     case kCodecOneBit: return launch_codec<kCodecOneBit>(a, grid, stream);
     case kCodecFP16: return launch_codec<kCodecFP16>(a, grid, stream);
     case kCodecFP32: return launch_codec<kCodecFP32>(a, grid, stream);
+    case kCodecQSGDX:
+      if (a.qsgd_bucket < 4 || a.qsgd_bucket % 4 || a.qsgd_nbuckets < 1 || a.alltoall || a.recv_mc) return cudaErrorInvalidValue;
+      return launch_codec<kCodecQSGDX>(a, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

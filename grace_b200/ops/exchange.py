@@ -26,7 +26,8 @@ PHASE_REDUCE = 8  # two-phase (alltoall) mode: reduce my chunk, re-encode, publi
 PHASE_CLIP = 16   # sparse exchange with DGC gradient clipping: per-tensor sums of squares, published before compress
 GRAD_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 SPARSE_TOPK, SPARSE_THRESHOLD, SPARSE_RANDOMK = 0, 1, 2
-CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8}
+CODEC = {"qsgd": 0, "terngrad": 1, "natural": 2, "u8bit": 3, "sign": 4, "efsign": 5, "onebit": 6, "fp16": 7, "fp32": 8,
+         "qsgdx": 9}   # QSGD with any bucket size (multiple of 4) and up to 32767 levels: int16 codes
 
 STATUS_TEXT = {
     0: "ok", 1: "timeout at a grid barrier", 2: "timeout waiting for a peer's data",
@@ -338,7 +339,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
               quantum: int = 0, deterministic: bool = False, first_step: bool = False, beta: float = 1.0,
               gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
               step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None,
-              alltoall: bool = False, recv=None) -> int:
+              alltoall: bool = False, recv=None, qsgd_bucket: int = 0, qsgd_nbuckets: int = 0) -> int:
     """``recv``: ``(NvlsBuffer, stride)`` of the push transport (two parities of ``world`` regions of ``stride``
     bytes each), or None for the pull transport."""
     C = native()
@@ -367,6 +368,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
         grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
+        int(qsgd_bucket), int(qsgd_nbuckets),
     )
     channel.post_status()
     return seq

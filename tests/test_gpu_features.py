@@ -178,3 +178,46 @@ def test_staged_decode_matches_single_rank_decodes(codec, extra):
         torch.testing.assert_close(outs[0], sum(singles) / W, rtol=1e-5, atol=1e-7)
     for r in range(1, W):
         assert torch.equal(outs[0], outs[r])
+
+
+@pytest.mark.parametrize("bucket,q", [(32, 64), (64, 127), (256, 64), (512, 300), (100, 1000), (128, 255)])
+@pytest.mark.parametrize("W", [1, 2])
+def test_general_qsgd_buckets_and_levels(bucket, q, W):
+    """QSGD with any bucket size that is a multiple of 4 and more than 127 levels stays on the fused path: per bucket
+    of each tensor, codes are integers in [-q, q], the decoded value is norm / q * code, its error is below one level,
+    and the residual holds exactly what was not transmitted."""
+    from grace_b200.ops.exchange import FlatLayout
+
+    names, numels = ["a", "b"], [5000, 777]
+    layout = FlatLayout(names, numels)
+    vw = _world(W, {"compressor": "qsgd", "memory": "residual", "communicator": "allgather", "quantum_num": q,
+                    "bucket_size": bucket, "seed": 11})
+    assert vw.comms[0]._kind == "quant"
+    flats, grads = [], []
+    for r in range(W):
+        gs = [_rand(n, seed=31 * r + i, scale=1.0) for i, n in enumerate(numels)]
+        f = torch.zeros(layout.total, device=_dev())
+        for g, off, n in zip(gs, layout.offsets, numels):
+            f[off:off + n] = g
+        flats.append(f)
+        grads.append(gs)
+    outs = vw.step_flat([f.clone() for f in flats], layout, [torch.empty_like(f) for f in flats])
+    vw.check()
+    for i, (off, n) in enumerate(zip(layout.offsets, numels)):
+        expect = torch.zeros(n, device=_dev())
+        for r in range(W):
+            g = grads[r][i]
+            res = next(iter(vw.comms[r]._plans.values())).acc[off:off + n]
+            dec = g - res                                   # what rank r transmitted (error-feedback identity)
+            pad = (-n) % bucket
+            gb = torch.nn.functional.pad(g, (0, pad)).view(-1, bucket)
+            db = torch.nn.functional.pad(dec, (0, pad)).view(-1, bucket)
+            norms = gb.norm(dim=1, keepdim=True)
+            codes = db * q / norms.clamp_min(1e-30)
+            assert float((codes - codes.round()).abs().max()) < 2e-3           # integer levels
+            assert float(codes.abs().max()) <= q + 1e-3
+            assert float(((db - gb).abs() * q / norms.clamp_min(1e-30)).max()) < 1.0 + 1e-3   # within one level
+            expect += dec
+        torch.testing.assert_close(outs[0][off:off + n], expect / W, rtol=1e-5, atol=1e-6)
+    for r in range(1, W):
+        assert torch.equal(outs[0], outs[r])
