@@ -25,19 +25,28 @@ void check(cudaError_t err, const char* what) {
 
 PeerTable make_peers(int rank, int world, unsigned long long seq, unsigned long long timeout_ns,
                      const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
-                     unsigned long long slot_off) {
+                     unsigned long long slot_off, unsigned long long slot_bytes = ~0ull) {
   if (world < 1 || world > kMaxWorldH || (int)heaps.size() != world || rank < 0 || rank >= world)
     throw std::invalid_argument("bad rank/world/heap table");
   PeerTable t{};
   t.rank = rank; t.world = world; t.seq = seq; t.timeout_ns = timeout_ns;
   for (int i = 0; i < world; ++i) t.heap[i] = reinterpret_cast<char*>(heaps[i]);
-  t.ready_off = ready_off; t.ack_off = ack_off; t.slot_off = slot_off;
+  t.ready_off = ready_off; t.ack_off = ack_off; t.slot_off = slot_off; t.slot_bytes = slot_bytes;
   return t;
 }
 
 }  // namespace
 
-PYBIND11_MODULE(_C, m) {
+#ifndef GRACE_MODULE_NAME
+#define GRACE_MODULE_NAME _C
+#endif
+
+PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
+#ifdef GRACE_CHECKED
+  m.attr("CHECKED") = true;
+#else
+  m.attr("CHECKED") = false;
+#endif
   m.doc() = "grace_b200 native kernels and runtime (sm_100a)";
 
   // ---- symmetric heap ----
@@ -86,7 +95,8 @@ PYBIND11_MODULE(_C, m) {
            unsigned long long ready_off, unsigned long long ack_off, unsigned long long slot_off, int grid,
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
            uintptr_t seg_seed, unsigned rk_step, unsigned long long clip_off, unsigned long long clip_ready_off,
-           uintptr_t clip_sq, int strict, int g_dtype, uintptr_t tile_start, uintptr_t tile_cur, uintptr_t scan_tmp) {
+           uintptr_t clip_sq, int strict, int g_dtype, uintptr_t tile_start, uintptr_t tile_cur, uintptr_t scan_tmp,
+           unsigned long long slot_bytes) {
           SparseArgs a{};
           a.tile_start = ptr<unsigned>(tile_start); a.tile_cur = ptr<unsigned>(tile_cur); a.scan_tmp = ptr<unsigned>(scan_tmp);
           a.clip_off = clip_off; a.clip_ready_off = clip_ready_off; a.clip_sq = ptr<double>(clip_sq); a.strict = strict;
@@ -101,7 +111,7 @@ PYBIND11_MODULE(_C, m) {
           a.beta = beta; a.gamma = gamma; a.momentum = momentum; a.threshold = threshold; a.scale = scale;
           a.hist = ptr<unsigned>(hist); a.state = ptr<SparseState>(state); a.barrier = ptr<unsigned>(barrier);
           a.status = ptr<unsigned>(status); a.cap = cap; a.phases = phases;
-          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off, slot_bytes);
           if (total % 128 != 0 || cap % 16 != 0) throw std::invalid_argument("total %128 / cap %16");
           check(launch_sparse_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "sparse_exchange");
         });
@@ -115,7 +125,7 @@ PYBIND11_MODULE(_C, m) {
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
            unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off,
            uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride, int g_dtype, int qsgd_bucket,
-           long long qsgd_nbuckets) {
+           long long qsgd_nbuckets, unsigned long long slot_bytes) {
           QuantArgs a{};
           a.qsgd_bucket = qsgd_bucket; a.qsgd_nbuckets = qsgd_nbuckets;
           if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");
@@ -130,7 +140,7 @@ PYBIND11_MODULE(_C, m) {
           a.mom_beta = mom_beta; a.lr = lr; a.scale = scale; a.seed = seed; a.step = step;
           a.stats = ptr<QuantSegStats>(stats); a.barrier = ptr<unsigned>(barrier); a.status = ptr<unsigned>(status);
           a.phases = phases;
-          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off);
+          a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off, slot_bytes);
           if (total % 128 != 0) throw std::invalid_argument("total must be a multiple of 128");
           check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
         });

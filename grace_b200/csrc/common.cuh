@@ -24,10 +24,16 @@ enum StatusCode : unsigned {
   kSlotOverflow = 4,
   kBadArgument = 5,
   kTimeoutMbarrier = 6,
+  kCheckFailed = 7,   // checked build (-DGRACE_CHECKED): an index or offset was out of range; the access was skipped
 };
 
+// Kernel identifiers recorded with a failed check.
+enum KernelId : unsigned { kKernelSparse = 1, kKernelQuant = 2, kKernelLowRank = 3, kKernelDense = 4, kKernelSgd = 5 };
+
 // Status block layout (unsigned words): [0] code (first error wins), [1] detail
-// (peer rank or barrier index), [2] sequence number, [3] dropped-element count.
+// (peer rank or barrier index; source line of a failed check), [2] sequence number,
+// [3] dropped-element count, [4] kernel id and [5], [6] the offending index of a
+// failed check (checked build only).
 struct Status {
   unsigned* words;
   __device__ __forceinline__ bool failed() const {
@@ -40,7 +46,29 @@ struct Status {
       __threadfence_system();
     }
   }
+  __device__ __forceinline__ void fail_check(unsigned kernel, unsigned line, unsigned long long index) const {
+    if (atomicCAS(words, kOk, kCheckFailed) == kOk) {
+      words[1] = line;
+      words[4] = kernel;
+      words[5] = (unsigned)index;
+      words[6] = (unsigned)(index >> 32);
+      __threadfence_system();
+    }
+  }
 };
+
+// Checked build: GRACE_IN_RANGE(status, kernel, index, limit) is true when index < limit; otherwise it records
+// (kernel, source line, index) in the status block and is false, and the caller skips the access - nothing traps,
+// the kernel runs to its end and the host raises at its next poll.  Stands in for a memory checker on the small
+// shapes of the test-suite.  In the normal build the macro is the constant `true` and costs nothing.
+#ifdef GRACE_CHECKED
+#define GRACE_IN_RANGE(status, kernel, index, limit)                                                       \
+  ((unsigned long long)(index) < (unsigned long long)(limit)                                               \
+       ? true                                                                                              \
+       : ((status).fail_check((kernel), __LINE__, (unsigned long long)(index)), false))
+#else
+#define GRACE_IN_RANGE(status, kernel, index, limit) true
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

@@ -34,6 +34,7 @@ struct PeerTable {
   unsigned long long ready_off;
   unsigned long long ack_off;
   unsigned long long slot_off;
+  unsigned long long slot_bytes;   // size of one send slot (bounds of the checked build)
 };
 
 enum Phase : int {

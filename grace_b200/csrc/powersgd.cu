@@ -493,7 +493,7 @@ __device__ void reduce_partials(const LowRankArgs& a, float* __restrict__ dst_sl
       }
       float4* dst = reinterpret_cast<float4*>(dst_slot + (STAGE == 1 ? M.p_off : M.q_off) + (size_t)row * kRankPad);
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) if (c4 < rpad4) dst[c4] = sum[c4];
+      for (int c4 = 0; c4 < 4; ++c4) dst[c4] = sum[c4];   // the padded columns are written too (zeros)
     }
   }
 }
@@ -639,7 +639,6 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   const bool part2 = part == 0 || part == 2;
   const bool part3 = part == 0 || part == 3;
   bool ok = true;
-  const size_t gthreads = (size_t)gridDim.x * kThreads, gtid = (size_t)blockIdx.x * kThreads + tid;
 
   if (part1) {
     if (tid < world && tid != rank && a.peers.seq > 2) {   // every CTA: none may zero the slot before the peers are done with it
@@ -647,11 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
       wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
     }
     __syncthreads();
-    // zero this rank's slot (P and Q regions: padded columns are never written otherwise)
-    const size_t nfl = (size_t)a.p_floats + a.q_floats;
-    for (size_t i = gtid * 4; i < nfl; i += gthreads * 4)
-      *reinterpret_cast<float4*>(my_slot + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-    ok = bar.sync();
+    ok = !status.failed();   // (the slot is written only by reduce_partials below, whole rows at a time)
     if (ok) gemm_stage<1>(a, sm, status);
     fence_async_all();
     ok = bar.sync();
@@ -665,8 +660,33 @@ __global__ void __launch_bounds__(kThreads, 1) powersgd_kernel(const LowRankArgs
   }
 
   if (part2) {
-    if (ok) reduce_region(a, 0, a.p_mean, a.p_floats);   // P = mean over ranks
-    ok = bar.sync() && ok;
+    if (ok) {
+      // P = mean over ranks, one thread per row: the Gram pass below reads only the rows its own thread wrote
+      // (same row -> thread mapping), so no grid barrier separates the two
+      const float inv = 1.f / (float)a.divisor;
+      for (int mat = 0; mat < a.nmat; ++mat) {
+        const LowRankMatrix& M = a.mats[mat];
+        for (int row = blockIdx.x * kThreads + tid; row < M.n; row += gridDim.x * kThreads) {
+          const size_t off = ((size_t)M.p_off + (size_t)row * kRankPad) * 4;
+          float4 sum[4];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int p = 0; p < world; ++p) {
+            const char* src = a.peers.heap[p] + a.peers.slot_off + off;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const uint4 v = ld_cg_u4(src + 16 * c4);
+              sum[c4].x += __uint_as_float(v.x); sum[c4].y += __uint_as_float(v.y);
+              sum[c4].z += __uint_as_float(v.z); sum[c4].w += __uint_as_float(v.w);
+            }
+          }
+          float4* dst = reinterpret_cast<float4*>(a.p_mean + M.p_off + (size_t)row * kRankPad);
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            dst[c4] = make_float4(sum[c4].x * inv, sum[c4].y * inv, sum[c4].z * inv, sum[c4].w * inv);
+        }
+      }
+    }
     if (ok) {
       // Gram matrices P^T P in fp64, added in a fixed order at every level (lanes by shuffles, warps in warp order,
       // CTAs in CTA order) so that two runs give the same bits: a thread takes one row, a warp adds its rows'

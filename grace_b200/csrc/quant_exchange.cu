@@ -146,14 +146,17 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   // stores of the encode pass: into the local slot (pull), or replicated by the switch into every GPU (push)
   char* const put_base = kPush ? a.recv_mc + (size_t)rank * a.recv_stride : my_slot;
   auto put_u32 = [&](size_t off, unsigned w) {
+    if (!GRACE_IN_RANGE(status, kKernelQuant, off + 3, a.peers.slot_bytes)) return;
     if (kPush) asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(put_base + off), "r"(w) : "memory");
     else *reinterpret_cast<unsigned*>(put_base + off) = w;
   };
   auto put_f32 = [&](size_t off, float f) {
+    if (!GRACE_IN_RANGE(status, kKernelQuant, off + 3, a.peers.slot_bytes)) return;
     if (kPush) asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(put_base + off), "f"(f) : "memory");
     else *reinterpret_cast<float*>(put_base + off) = f;
   };
   auto put_u2 = [&](size_t off, uint2 w) {
+    if (!GRACE_IN_RANGE(status, kKernelQuant, off + 7, a.peers.slot_bytes)) return;
     if (kPush) {
       const unsigned long long q = ((unsigned long long)w.y << 32) | w.x;
       asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(put_base + off), "l"(q) : "memory");
@@ -162,6 +165,7 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
     }
   };
   auto put_f4 = [&](size_t off, float4 v) {
+    if (!GRACE_IN_RANGE(status, kKernelQuant, off + 15, a.peers.slot_bytes)) return;
     if (kPush) asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(put_base + off), "f"(v.x),
                             "f"(v.y), "f"(v.z), "f"(v.w)
                             : "memory");
@@ -884,7 +888,8 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
                 nv[p] = 0.f;
                 if (p < world) {
                   const char* slot = slot_of(p);
-                  if (have) v[p] = ld_cg_u4(slot + off_codes + byte_off);
+                  if (have && GRACE_IN_RANGE(status, kKernelQuant, off_codes + byte_off + 15, a.peers.slot_bytes))
+                    v[p] = ld_cg_u4(slot + off_codes + byte_off);
                   if (C == kCodecQSGD && lane < 4 && w0 + 128ll * lane < e0)
                     nv[p] = ld_cg_f32(slot + off_norms + (size_t)((w0 >> 7) + lane) * 4);
                 }

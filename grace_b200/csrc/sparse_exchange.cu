@@ -519,8 +519,10 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
                   const unsigned pos = atomicAdd(&sm.wcnt[warp], 1u);
                   w_val[pos] = av[j];
                   w_idx[pos] = (int)(i + j);
-                  if (a.acc) a.acc[i + j] = 0.f;
-                  if (a.u) a.u[i + j] = 0.f;
+                  if (GRACE_IN_RANGE(status, kKernelSparse, i + j, a.total)) {
+                    if (a.acc) a.acc[i + j] = 0.f;
+                    if (a.u) a.u[i + j] = 0.f;
+                  }
                 }
               }
             }
@@ -697,8 +699,10 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           base = __shfl_sync(0xffffffffu, base, leader);   // every lane takes part; only members of `mask` use it
           if (use) {
             const unsigned pos = base + __popc(mask & ((1u << lane_id) - 1u));
-            s_vals[pos] = __uint_as_float(val);
-            s_idx[pos] = (int)idx;
+            if (GRACE_IN_RANGE(status, kKernelSparse, pos, a.cap)) {
+              s_vals[pos] = __uint_as_float(val);
+              s_idx[pos] = (int)idx;
+            }
           }
         });
       }

@@ -20,10 +20,14 @@ def native():
             if _mod is None:
                 import torch  # noqa: F401  (loads libcudart before the extension)
 
+                import os
+
                 from . import build as _build
 
-                _build.ensure_built()
-                _mod = importlib.import_module("grace_b200._C")
+                # GRACE_CHECKED=1: the variant compiled with index / offset checks (see ops/build.py)
+                checked = os.environ.get("GRACE_CHECKED", "") not in ("", "0")
+                _build.ensure_built(checked)
+                _mod = importlib.import_module("grace_b200._C_checked" if checked else "grace_b200._C")
     return _mod
 
 

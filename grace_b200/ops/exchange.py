@@ -33,6 +33,7 @@ STATUS_TEXT = {
     0: "ok", 1: "timeout at a grid barrier", 2: "timeout waiting for a peer's data",
     3: "timeout waiting for a peer's acknowledgement", 4: "send slot overflow", 5: "bad argument / corrupt index",
     6: "timeout on an mbarrier",
+    7: "a bounds check of the checked build failed (detail = source line; the access was skipped)",
 }
 ALIGN_ELEMS = 128
 GUARD_BYTES = 256
@@ -218,7 +219,12 @@ class ExchangeChannel:
         code = int(self.status_host[0])
         if code != 0:
             detail, seq = int(self.status_host[1]), int(self.status_host[2])
-            raise GraceCommError(code, detail, seq, self.heap.rank)
+            err = GraceCommError(code, detail, seq, self.heap.rank)
+            if code == 7:   # checked build: which kernel and which index
+                err.kernel = int(self.status_host[4])
+                err.index = int(self.status_host[5]) | (int(self.status_host[6]) << 32)
+                err.args = (err.args[0] + " [kernel %d, index %d]" % (err.kernel, err.index),)
+            raise err
 
     def reset(self):
         """Clear flags and status after an error (call on every rank, then barrier)."""
@@ -329,6 +335,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         channel.clip_off if clip else 0, channel.clip_ready_off if clip else 0,
         channel.clip_sq.data_ptr() if clip else 0, int(strict), GRAD_DTYPE[g.dtype],
         td[0].data_ptr() if td else 0, td[1].data_ptr() if td else 0, td[2].data_ptr() if td else 0,
+        channel.slot_bytes,
     )
     channel.post_status()
     return seq
@@ -339,7 +346,8 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
               quantum: int = 0, deterministic: bool = False, first_step: bool = False, beta: float = 1.0,
               gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
               step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None,
-              alltoall: bool = False, recv=None, qsgd_bucket: int = 0, qsgd_nbuckets: int = 0) -> int:
+              alltoall: bool = False, recv=None, qsgd_bucket: int = 0, qsgd_nbuckets: int = 0,
+              slot_bytes: Optional[int] = None) -> int:
     """``recv``: ``(NvlsBuffer, stride)`` of the push transport (two parities of ``world`` regions of ``stride``
     bytes each), or None for the pull transport."""
     C = native()
@@ -368,7 +376,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
         grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
-        int(qsgd_bucket), int(qsgd_nbuckets),
+        int(qsgd_bucket), int(qsgd_nbuckets), channel.slot_bytes if slot_bytes is None else int(slot_bytes),
     )
     channel.post_status()
     return seq

@@ -346,15 +346,15 @@ def test_bindings_reject_inconsistent_arguments_before_any_launch():
     heaps = [4096]
     with pytest.raises(ValueError):     # push transport needs both addresses of the receive area
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 16, 0, 256, 0, 0, 0)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 16, 0, 256, 0, 0, 0, 4096)
     with pytest.raises(ValueError):     # total must be a multiple of 128
         C.quant_exchange(16, 0, 0, 16, 16, 1, 100, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096)
     with pytest.raises(ValueError):     # rank outside the world
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 3, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096)
     with pytest.raises(ValueError):     # gradient element type: 0 fp32, 1 bf16, 2 fp16
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 5, 0, 0)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 5, 0, 0, 4096)
     with pytest.raises(ValueError):     # dense all-reduce: 16-byte aligned pointers only
         C.dense_allreduce(8, 16, 16, 16, 128, 1.0, 16, 16, 0, 0, 1, 1, 10 ** 9, heaps, 0, 128, 1, 0)
