@@ -104,6 +104,9 @@ def main():
                     help="timed iterations for sizes of 16 Mi elements and more (keeps the clock sampler busy long "
                          "enough to see the GPU under load)")
     ap.add_argument("--impl", default="ours", choices=["ours", "library", "reference"])
+    ap.add_argument("--min-seconds", type=float, default=0.8,
+                    help="keep iterating a case until it has run this long (the clock sampler needs to see the GPU "
+                         "under load); 0 = the iteration counts only")
     ap.add_argument("--timeout-ms", type=float, default=3000.0,
                     help="limit of every device-side wait of the fused exchanges; a case that runs into it is "
                          "reported as an error after its first failing iteration")
@@ -214,7 +217,16 @@ def main():
                 resident = grc.buffer(n)
             t_case = time.time()
             try:
-                for it in range(args.warmup + max(args.iters, args.min_iters if size_m >= 16 else args.iters)):
+                n_iters = args.warmup + max(args.iters, args.min_iters if size_m >= 16 else args.iters)
+                it = -1
+                while True:
+                    it += 1
+                    if it >= n_iters:
+                        # every rank must take the same decision: rank 0's clock decides
+                        more = torch.tensor([1.0 if time.time() - t_case < args.min_seconds else 0.0], device=dev)
+                        dist.broadcast(more, 0)
+                        if float(more) == 0.0 or it >= 400:
+                            break
                     g = base.clone() if resident is None else resident.copy_(base)
                     vg = [b.clone() for b in vbase]
                     flush.fill_(float(it))

@@ -30,7 +30,10 @@ def main():
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--rank", type=int, default=4)
-    ap.add_argument("--iters", type=int, default=7)
+    ap.add_argument("--iters", type=int, default=7, help="timed iterations at least")
+    ap.add_argument("--min-seconds", type=float, default=1.2,
+                    help="keep iterating until the timed loop has run this long (so that the 100 ms clock sampler "
+                         "sees the GPU under load); 0 = exactly --iters")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-memory", action="store_true", help="no error feedback (stage 1 reads G only)")
     ap.add_argument("--whole", action="store_true")
@@ -63,7 +66,11 @@ def main():
     sampler = ClockSampler(0, period_ms=100).start()
     t_start = time.time()
     times = {1: [], 2: [], 3: [], 0: []}
-    for it in range(args.warmup + args.iters):
+    it = -1
+    while True:
+        it += 1
+        if it >= args.warmup + args.iters and time.time() - t_start >= args.min_seconds:
+            break
         seq = None
         for part in (1, 2, 3):
             flush.fill_(float(it))
@@ -98,7 +105,7 @@ def main():
                      "achieved_gbs": round(gbs, 1), "fraction_of_copy_bandwidth": round(gbs / bw, 3)})
     print(json.dumps({"shape": [n, m], "rank": args.rank, "error_feedback": not args.no_memory, "parts": rows,
                       "hbm_gbs": bw, "hbm_source": bw_src, "clocks": clocks,
-                      "timing": "cuda events per launch, median of %d, L2 flushed before every launch" % args.iters}))
+                      "timing": "cuda events per launch, median of %d, L2 flushed before every launch" % len(times[1])}))
 
 
 if __name__ == "__main__":

@@ -245,3 +245,63 @@ def test_ddp_comm_hook_with_fused_exchange():
         res = dict(ret)
     for r in range(world):
         assert res[r] < 5e-3, res  # two separate cuDNN backward passes agree to ~1e-3 of the largest entry
+
+
+def _recover_entry(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from _rendezvous import init_group
+
+    init_group("nccl", rank, world, port, dev)
+    try:
+        from grace_b200 import grace_from_params
+
+        store = dist.distributed_c10d._get_default_store()
+        grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather",
+                                 "quantum_num": 64, "world_size": world, "fused": True, "timeout_ms": 300,
+                                 "store": store})
+        gen = torch.Generator().manual_seed(rank)
+        x = (torch.randn(200_000, generator=gen) * 1e-3).to(dev)
+        grc.step(x.clone(), "w")
+        grc.check()
+        assert grc.agree(timeout_s=60) == []               # a healthy step: nobody votes "failed"
+        residual_before = next(iter(grc._plans.values())).acc.clone()
+        # rank 1 sits this step out (between steps, with nothing of its own in flight): rank 0's wait for its
+        # payload expires after 300 ms and is reported; rank 1 itself saw nothing wrong
+        if rank == 0:
+            grc.step(x.clone(), "w")
+        failed = grc.agree(timeout_s=60)                    # every rank learns that rank 0 failed
+        grc.recover(timeout_s=60)
+        if rank == 1:                                       # rank 1's error feedback did not move while it sat out
+            assert torch.equal(next(iter(grc._plans.values())).acc, residual_before)
+        # after the recovery: a healthy exchange again, identical on both ranks
+        out = grc.step(x.clone(), "w")
+        grc.check()
+        assert grc.agree(timeout_s=60) == []
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        ret[rank] = (failed, bool(torch.equal(gathered[0], gathered[1])), bool(torch.isfinite(out).all()),
+                     float(out.abs().max()) > 0)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_failure_is_agreed_on_and_a_healthy_exchange_follows_the_recovery():
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _token()
+        procs = [ctx.Process(target=_recover_entry, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        for p in procs:
+            assert p.exitcode == 0, "rank exited with %s" % p.exitcode
+        res = dict(ret)
+    assert res[0] == ([0], True, True, True)
+    assert res[1] == ([0], True, True, True)
