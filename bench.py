@@ -421,6 +421,9 @@ def main():
             "data": "synthetic N(0,1) inputs, uniform labels, random-init weights", "impl": args.impl, "api": args.api,
             "config": {"model": cfg["model"], "global_batch": cfg["batch"] * world,
                        "seq_len": cfg.get("seq"), "parallelism": "dp%d" % world, "compression": cfg["grace"],
+                       "bucket_mb": (cfg["bucket_bytes"] / (1 << 20)) if cfg.get("bucket_bytes") else None,
+                       "exchange": "buckets launched from gradient hooks next to backward" if cfg.get("bucket_bytes")
+                                   else "one fused exchange after backward",
                        "l2": "inputs and activations exceed L2 (batch %.0f MB)" % (
                            sum(t.numel() * t.element_size() for t in batches[0]) / 1e6)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,
