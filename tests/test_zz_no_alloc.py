@@ -69,8 +69,11 @@ def test_no_alloc_topk_matches_regular_entry_point_twice():
 
 
 def test_no_alloc_topk_allocates_nothing():
-    """With the outputs allocated beforehand, a call changes neither the device's free memory (cudaMalloc by
-    anyone in the process) nor the caching allocator's books (an allocation through torch)."""
+    """With the outputs allocated beforehand, a call takes nothing from the device's free memory (cudaMalloc by
+    anyone in the process) and does not change the caching allocator's books (an allocation through torch).  Free
+    memory may grow meanwhile (heaps of earlier tests whose last reference dies late), it must not shrink."""
+    import gc
+
     lib = _lib()
     x = torch.randn(300_000, device="cuda")
     vals = torch.empty(3000, dtype=torch.float32, device="cuda")
@@ -83,6 +86,7 @@ def test_no_alloc_topk_allocates_nothing():
 
     call()                      # first call on the device: address look-up, kernel image load
     _status(lib)                # and the first status read-back
+    gc.collect()
     torch.cuda.synchronize()
     free0 = torch.cuda.mem_get_info()[0]
     stats0 = torch.cuda.memory_stats()
@@ -91,7 +95,7 @@ def test_no_alloc_topk_allocates_nothing():
     torch.cuda.synchronize()
     assert _status(lib) == [0, 0, 0, 0]
     stats1 = torch.cuda.memory_stats()
-    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.cuda.mem_get_info()[0] >= free0
     for key in ("allocation.all.allocated", "segment.all.allocated", "allocated_bytes.all.current",
                 "reserved_bytes.all.current"):
         assert stats1[key] == stats0[key], key
