@@ -256,6 +256,9 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t) / (vranks or 1)
             roof, hbm, link = roofline_ms(case, n, vranks or world, bw)
+            if vranks:                       # emulated ranks share one GPU: nothing crosses a link, HBM is the bound
+                link = 0
+                roof = hbm / (bw * 1e9) * 1e3
             row = {"case": case, "impl": args.impl, "size_m": size_m, "n_gpus": world, "ms": round(ms, 4),
                    "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / ms, 3) if args.impl == "ours" else None,
                    "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
