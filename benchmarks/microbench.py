@@ -264,6 +264,9 @@ def main():
                    "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
                    "timing": "cuda events, median of %d, max over ranks, L2 flushed" % len(times),
                    "clocks": clocks}
+            if len(times) >= 10:   # error feedback changes the value distribution over the iterations of a case
+                row["ms_first5"] = round(sorted(times[:5])[2] / (vranks or 1), 4)
+                row["ms_last5"] = round(sorted(times[-5:])[2] / (vranks or 1), 4)
             if vranks:
                 row["virtual_ranks"] = vranks
                 row["timing"] += "; %d ranks emulated on one GPU phase by phase, time of all ranks / %d" % (vranks, vranks)
