@@ -96,8 +96,9 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
            uintptr_t stream, uintptr_t cand_val, uintptr_t cand_idx, unsigned cand_cap, uintptr_t kprefix,
            uintptr_t seg_seed, unsigned rk_step, unsigned long long clip_off, unsigned long long clip_ready_off,
            uintptr_t clip_sq, int strict, int g_dtype, uintptr_t tile_start, uintptr_t tile_cur, uintptr_t scan_tmp,
-           unsigned long long slot_bytes) {
+           unsigned long long slot_bytes, int fine_hint) {
           SparseArgs a{};
+          a.fine_hint = fine_hint;
           a.tile_start = ptr<unsigned>(tile_start); a.tile_cur = ptr<unsigned>(tile_cur); a.scan_tmp = ptr<unsigned>(scan_tmp);
           a.clip_off = clip_off; a.clip_ready_off = clip_ready_off; a.clip_sq = ptr<double>(clip_sq); a.strict = strict;
           if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");

@@ -54,6 +54,8 @@ struct SparseState {       // per segment, device scratch
   unsigned need;           // how many elements to take from the pivot bin
   unsigned tie_taken;      // claimed so far among keys equal to the pivot
   unsigned max_bits;       // ordered-int encoding of max(acc) (threshold mode)
+  unsigned pivot_count;    // keys in the pivot bin of the last level done on the histograms
+  unsigned fine;           // 1: the first pass already resolved 24 key bits for this segment (hinted histogram)
 };
 
 struct SparseArgs {
@@ -70,6 +72,8 @@ struct SparseArgs {
   float beta, gamma, momentum, threshold;
   float scale;        // factor applied while aggregating (1/W when averaging)
   unsigned* hist;     // nseg * 4096, zero on entry, left zero on exit
+  int fine_hint;      // 1: hist is followed by nseg * 4096 words of second-level histograms (zero between launches)
+                      //    and nseg hint words (the previous launch's first-level pivot bin, 0xffffffff = none)
   SparseState* state; // nseg + 1 (the extra entry holds the candidate counters), zeroed by the launcher
   float* cand_val;    // candidate list of the fast select path (nullable)
   int* cand_idx;

@@ -86,22 +86,23 @@ struct Smem {
   unsigned scan[kBlock / 32 + 1];
 };
 
-__device__ __forceinline__ void flush_hist(Smem& sm, unsigned* __restrict__ ghist) {
+__device__ __forceinline__ void flush_hist(unsigned* __restrict__ shist, unsigned* __restrict__ ghist) {
   __syncthreads();
   for (int b = threadIdx.x; b < kBins; b += kBlock) {
-    const unsigned c = sm.hist[b];
+    const unsigned c = shist[b];
     if (c) {
       atomicAdd(ghist + b, c);
-      sm.hist[b] = 0;
+      shist[b] = 0;
     }
   }
   __syncthreads();
 }
+__device__ __forceinline__ void flush_hist(Smem& sm, unsigned* __restrict__ ghist) { flush_hist(sm.hist, ghist); }
 
 // Suffix-scan one segment's histogram and pick the bin holding the `need`-th
 // largest key.  All threads of the CTA take part; the histogram is left zero.
 __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseState* __restrict__ st, unsigned need,
-                              int bits, unsigned* cand_total = nullptr) {
+                              int bits) {
   constexpr int kPer = kBins / kBlock;  // 8 bins per thread
   const int t = threadIdx.x;
   unsigned c[kPer];
@@ -133,7 +134,7 @@ __device__ void pivot_segment(Smem& sm, unsigned* __restrict__ ghist, SparseStat
         st->prefix = (st->prefix << bits) | (unsigned)(t * kPer + j);
         st->need = need - cum;
         st->tie_taken = 0;
-        if (cand_total) atomicAdd(cand_total, c[j]);
+        st->pivot_count = c[j];
       }
       cum += c[j];
     }
@@ -244,7 +245,18 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       const long long nb1 = ((a.total + kTileElems - 1) >> kTileShift) + 1;
       for (long long b = (long long)blockIdx.x * kBlock + tid; b < nb1; b += (long long)gridDim.x * kBlock) a.tile_start[b] = 0;
     }
-    for (int b = tid; b < kBins; b += kBlock) sm.hist[b] = 0;
+    // Hinted second-level histogram: under error feedback the selection threshold moves little from step to step
+    // while the accumulated values pile up just below it, so the first-level pivot bin holds a few percent of all
+    // elements.  Keys that fall into the bin that was the pivot in the previous launch are therefore also counted by
+    // their next 12 bits in this pass; when the pivot bin is the same again, 24 key bits are resolved before the
+    // compaction pass and the candidate list shrinks by three orders of magnitude.  A wrong hint costs nothing but the
+    // extra counting (the selection never depends on it).  The staging area of the candidates is free in this pass.
+    static_assert(sizeof(float) * kCandStage >= sizeof(unsigned) * kBins, "second histogram does not fit");
+    unsigned* const s_hist2 = reinterpret_cast<unsigned*>(sm.cand_val);
+    const bool hinted = a.fine_hint && topk;
+    auto g_hist2 = [&](int s) { return a.hist + ((size_t)a.nseg + s) * kBins; };   // second-level histogram of a segment
+    auto g_hint = [&](int s) { return a.hist + 2 * (size_t)a.nseg * kBins + s; };   // its hint word
+    for (int b = tid; b < kBins; b += kBlock) { sm.hist[b] = 0; s_hist2[b] = 0; }
     __syncthreads();
 
     // ---- phase A: compensate, store accumulator, zero output, histogram ----
@@ -252,6 +264,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         float tmax = -INFINITY;
         const bool read_acc = a.u || (a.acc && a.beta != 0.f);
+        const unsigned hint = hinted ? *g_hint(s) : 0xffffffffu;
         float clip = INFINITY;   // element-wise clamp of the incoming gradient
         if (a.clip_off) {
           __syncthreads();
@@ -307,7 +320,11 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
             if (topk) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (kFull || j < valid[q]) atomicAdd(&sm.hist[(__float_as_uint(av[j]) & 0x7fffffffu) >> 19], 1u);
+                if (kFull || j < valid[q]) {
+                  const unsigned key = __float_as_uint(av[j]) & 0x7fffffffu;
+                  atomicAdd(&sm.hist[key >> 19], 1u);
+                  if ((key >> 19) == hint) atomicAdd(&s_hist2[(key >> 7) & 0xfffu], 1u);
+                }
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j) if (kFull || j < valid[q]) tmax = fmaxf(tmax, av[j]);
@@ -322,6 +339,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         }
         if (topk) {
           flush_hist(sm, a.hist + (size_t)s * kBins);
+          if (hint != 0xffffffffu) flush_hist(s_hist2, g_hist2(s));
         } else if (!randomk) {
           tmax = warp_max(tmax);
           if ((tid & 31) == 0 && tmax > -INFINITY) atomicMax(&a.state[s].max_bits, ordered_bits(tmax));
@@ -344,9 +362,25 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
         const int bits = level == 2 ? 7 : 12;
         if (ok) {
           for (int s = blockIdx.x; s < a.nseg; s += gridDim.x) {
+            if (level == 1 && a.state[s].fine) continue;   // its second level came with the first pass
             const unsigned need = level == 0 ? (unsigned)a.segs[s].k : a.state[s].need;
-            pivot_segment(sm, a.hist + (size_t)s * kBins, &a.state[s], need, bits,
-                          level == 0 ? &extra->prefix : nullptr);
+            pivot_segment(sm, a.hist + (size_t)s * kBins, &a.state[s], need, bits);
+            if (level == 0) {
+              if (hinted) {
+                const unsigned hint = *g_hint(s), p0 = a.state[s].prefix;
+                if (hint == p0) {
+                  pivot_segment(sm, g_hist2(s), &a.state[s], a.state[s].need, 12);
+                } else if (hint != 0xffffffffu) {
+                  for (int b = tid; b < kBins; b += kBlock) g_hist2(s)[b] = 0;   // leave it zero
+                }
+                if (tid == 0) {
+                  *g_hint(s) = p0;
+                  a.state[s].fine = hint == p0 ? 1u : 0u;
+                }
+                __syncthreads();
+              }
+              if (tid == 0) atomicAdd(&extra->prefix, a.state[s].pivot_count);   // candidates of this segment
+            }
           }
         }
         ok = bar.sync();
@@ -363,6 +397,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           if (ok && lo < hi) {
             for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
               const unsigned prefix = a.state[s].prefix;
+              if (level == 0 && a.state[s].fine) return;   // 24 bits are known already
               for (long long base = b0 + 4ll * tid; base < e0; base += (long long)kUnroll * kIterElems) {
                 int valid[kUnroll];
                 float av[kUnroll][4];
@@ -394,7 +429,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
     // Every warp stages its picks in its own slice of shared memory and flushes it by itself
     // (one global atomic per flush, coalesced copies): the streaming loop has no CTA barrier.
     __syncthreads();
-    const int key_shift = topk ? (fast ? 19 : (a.levels == 3 ? 0 : (a.levels == 2 ? 7 : 19))) : 0;
+    const int key_shift_all = topk ? (fast ? 19 : (a.levels == 3 ? 0 : (a.levels == 2 ? 7 : 19))) : 0;
     const int lane = tid & 31, warp = tid >> 5;
     const unsigned lane_lt = (1u << lane) - 1u;
     float* const w_val = sm.stage.val + warp * kWarpStage;
@@ -469,6 +504,8 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
       for_each_segment_range(a.segs, a.nseg, lo, hi, [&](int s, long long b0, long long e0) {
         const unsigned pivot = a.state[s].prefix;
         const unsigned need = a.state[s].need;
+        // a hinted segment enters the candidate pass with 24 resolved key bits instead of 12
+        const int key_shift = (topk && fast && a.state[s].fine) ? 7 : key_shift_all;
         float thr = a.threshold;
         if (!topk && !a.strict) thr = fminf(thr, from_ordered_bits(a.state[s].max_bits));   // dist flavour: capped by max(x)
         const bool strict = a.strict != 0;                                                  // Horovod flavour: |x| > threshold
@@ -555,14 +592,19 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
           for (unsigned e = gtid; e < ncand; e += gstride) {
             const unsigned key = __float_as_uint(a.cand_val[e]) & 0x7fffffffu;
             const int sg = seg_of(a.cand_idx[e]);
-            if (level == 1) atomicAdd(&a.hist[(size_t)sg * kBins + ((key >> 7) & 0xfffu)], 1u);
-            else if ((key >> 7) == a.state[sg].prefix) atomicAdd(&a.hist[(size_t)sg * kBins + (key & 0x7fu)], 1u);
+            if (level == 1) {
+              if (!a.state[sg].fine) atomicAdd(&a.hist[(size_t)sg * kBins + ((key >> 7) & 0xfffu)], 1u);
+            } else if ((key >> 7) == a.state[sg].prefix) {
+              atomicAdd(&a.hist[(size_t)sg * kBins + (key & 0x7fu)], 1u);
+            }
           }
         }
         ok = bar.sync();
         if (ok) {
-          for (int sg = blockIdx.x; sg < a.nseg; sg += gridDim.x)
+          for (int sg = blockIdx.x; sg < a.nseg; sg += gridDim.x) {
+            if (level == 1 && a.state[sg].fine) continue;
             pivot_segment(sm, a.hist + (size_t)sg * kBins, &a.state[sg], a.state[sg].need, level == 2 ? 7 : 12);
+          }
         }
         ok = bar.sync();
       }

@@ -145,7 +145,11 @@ class ExchangeChannel:
         self.status = torch.zeros(32, dtype=torch.int32, device=dev)   # [0..3] error block, [8..] optional phase counters
         self.status_host = torch.zeros(32, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
         self.status_event: Optional[torch.cuda.Event] = None
-        self.hist = torch.zeros(max(1, nseg) * 4096, dtype=torch.int32, device=dev)
+        # radix-select histograms: first level, hinted second level (zero between launches), then one hint word per
+        # segment (the first-level pivot bin of the previous launch, -1 = none; a speed hint only)
+        self._hist_segs = max(1, nseg)
+        self.hist = torch.zeros(self._hist_segs * (2 * 4096 + 1), dtype=torch.int32, device=dev)
+        self.hist[2 * 4096 * self._hist_segs:] = -1
         self.sparse_state = torch.zeros((max(1, nseg) + 1) * (C.SPARSE_STATE_BYTES // 4), dtype=torch.int32, device=dev)
         self.cand = None  # candidate list of the fast top-k path, allocated by run_sparse on first use
         self._tile = None  # scratch of the tile-bucketed decode: (key, buffers) or (key, None) when not worthwhile
@@ -238,6 +242,7 @@ class ExchangeChannel:
             self.clip_sq.zero_()
         self.status.zero_()
         self.hist.zero_()
+        self.hist[2 * 4096 * self._hist_segs:] = -1
         self.sparse_state.zero_()
         self.quant_stats.zero_()
         self.seq = 0
@@ -335,7 +340,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         channel.clip_off if clip else 0, channel.clip_ready_off if clip else 0,
         channel.clip_sq.data_ptr() if clip else 0, int(strict), GRAD_DTYPE[g.dtype],
         td[0].data_ptr() if td else 0, td[1].data_ptr() if td else 0, td[2].data_ptr() if td else 0,
-        channel.slot_bytes,
+        channel.slot_bytes, 1 if len(layout.names) == channel._hist_segs else 0,   # hinted histograms: the layout the areas were sized for
     )
     channel.post_status()
     return seq

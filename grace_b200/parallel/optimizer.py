@@ -204,9 +204,10 @@ class _DistributedMixin:
             self._side_stream = torch.cuda.Stream(priority=-1)
         return self._side_stream
 
-    def _launch_bucket(self, bucket, overlapped: bool):
+    def _launch_bucket(self, bucket, overlapped: bool, from_hook: bool = True):
         """One fused exchange for the whole bucket, on the side stream.  ``overlapped``: backward is still
-        running, so the kernel takes a capped share of the SMs (``grace.overlap_sms``)."""
+        running, so the kernel takes a capped share of the SMs (``grace.overlap_sms``).  ``overlap_log`` entries:
+        ``(bucket, start event, end event, launched from a gradient hook, capped)``."""
         side = self._comm_stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -224,7 +225,7 @@ class _DistributedMixin:
             ev = torch.cuda.Event(enable_timing=self.trace_overlap)
             ev.record(side)
             if self.trace_overlap:
-                self.overlap_log.append((bucket.index, start, ev, overlapped))
+                self.overlap_log.append((bucket.index, start, ev, from_hook, overlapped))
         self._bucket_events[bucket.index] = ev
 
     def _plain_allreduce(self, tensor):
@@ -270,7 +271,9 @@ class _DistributedMixin:
             bucket.pending -= 1
             e.ticket = ("bucket", bucket.index)
             if bucket.pending == 0:
-                self._launch_bucket(bucket, overlapped=True)
+                # the last bucket of a step has (almost) nothing of backward left to share the SMs with: full width
+                last = len(self._bucket_events) == len(self._flat.buckets) - 1
+                self._launch_bucket(bucket, overlapped=not last)
         else:
             self._launch_entry(e)
 
@@ -280,7 +283,7 @@ class _DistributedMixin:
         if self._bucketed():
             for b in self._flat.buckets:
                 if b.index not in self._bucket_events:
-                    self._launch_bucket(b, overlapped=False)   # backward is over: nothing left to share the SMs with
+                    self._launch_bucket(b, overlapped=False, from_hook=False)   # backward is over: nothing left to share the SMs with
             cur = torch.cuda.current_stream()
             for ev in self._bucket_events.values():
                 cur.wait_event(ev)

@@ -128,6 +128,7 @@ def test_bucket_exchanges_start_before_backward_ends():
     assert len(log) == depth // 2
     from_hooks = [e for e in log if e[3]]
     assert len(from_hooks) == depth // 2                        # every bucket was launched by a hook
+    assert [e[4] for e in log] == [True] * (depth // 2 - 1) + [False]   # capped next to backward; the last one is not
     early = [e for e in from_hooks if e[1].elapsed_time(bwd_end) > 0]      # started before backward ended
     done_early = [e for e in from_hooks if e[2].elapsed_time(bwd_end) > 0]  # ... and finished before it ended
     assert len(early) >= depth // 2 - 1, [e[1].elapsed_time(bwd_end) for e in log]

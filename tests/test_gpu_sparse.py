@@ -374,3 +374,58 @@ def test_tile_bucketed_decode_threshold_and_segments(monkeypatch):
         expect += torch.where(flats[r].abs() >= 2e-3, flats[r], torch.zeros_like(flats[r])) * (1.0 / W)
     for r in range(W):
         assert torch.equal(outs[r], expect)
+
+
+@pytest.mark.parametrize("W", [1, 2])
+@pytest.mark.parametrize("memory", ["none", "residual"])
+def test_topk_over_many_steps_hint_hits_and_misses(W, memory):
+    """From its second launch on the kernel counts the previous launch's pivot bin by 24 key bits in its first pass
+    (a speed hint for the steady state under error feedback).  Without memory the same gradients are sent three
+    times (the hint must hit), then scaled by 64 (it must miss), then sent again; with residual memory sixteen steps
+    of similar gradients let the threshold settle.  Every step must select exactly what a dense top-k of the
+    accumulator selects, whichever path ran."""
+    from grace_b200.ops.exchange import FlatLayout
+
+    ratio = 0.25 if memory == "residual" else 0.01
+    numels = [200_000, 4096, 300_003, 130]
+    nseg = len(numels)
+    layout = FlatLayout.from_named([("p%d" % i, n) for i, n in enumerate(numels)])
+    vw = _world(W, {"compressor": "topk", "memory": memory, "communicator": "allgather", "compress_ratio": ratio})
+    residual = [torch.zeros(layout.total, device=_dev()) for _ in range(W)]
+    steps = 16 if memory == "residual" else 6
+    hits = []
+    for step in range(steps):
+        scale = 64.0 if step == 3 else 1.0
+        noise = 0.05 if memory == "residual" else 0.0
+        flats = []
+        for r in range(W):
+            f = torch.zeros(layout.total, device=_dev())
+            for i, (o, n) in enumerate(zip(layout.offsets, layout.numels)):
+                f[o:o + n] = (_rand(n, seed=10 * r + i) + noise * _rand(n, seed=1000 + 100 * step + 10 * r + i)) * scale
+            flats.append(f)
+        grads = [f.clone() for f in flats]
+        outs = vw.step_flat(flats, layout)
+        vw.check()
+        expect = torch.zeros(layout.total, device=_dev())
+        step_hits = 0
+        for r in range(W):
+            acc = grads[r] + (residual[r] if memory == "residual" else 0)
+            sel = torch.zeros_like(acc)
+            for o, n in zip(layout.offsets, layout.numels):
+                sel[o:o + n] = _dense_topk(acc[o:o + n], max(1, int(n * ratio)))
+            residual[r] = acc - sel
+            expect += sel
+            plan = next(iter(vw.comms[r]._plans.values()))
+            if memory == "residual":
+                torch.testing.assert_close(plan.acc[:layout.total], residual[r], rtol=0, atol=0)
+            state = plan.channel.sparse_state.view(nseg + 1, -1)
+            step_hits += int(state[:nseg, 5].sum())          # SparseState.fine of the launch that just ran
+        hits.append(step_hits)
+        torch.testing.assert_close(outs[0], expect / W, rtol=1e-6, atol=1e-9)
+        for r in range(1, W):
+            assert torch.equal(outs[0], outs[r])
+    if memory == "none":
+        # launch 0 has no hint; 1 and 2 repeat launch 0; 3 is scaled (64 = 6 octaves: another bin); 4 returns (miss), 5 hits
+        assert hits == [0, nseg * W, nseg * W, 0, 0, nseg * W], hits
+    else:
+        assert hits[0] == 0 and sum(hits) > 0, hits
