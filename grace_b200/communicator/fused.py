@@ -160,6 +160,10 @@ class _Plan:
                 if buf is not None:
                     self.recv = (buf, stride)
         self.clip = kind == "sparse" and bool(getattr(owner.memory, "gradient_clipping", False))
+        # pipelined all-gather mode (encode of chunk c + 1 next to the pull of chunk c): same decision on every rank
+        self.pipeline = None
+        if (kind == "quant" and owner.pipeline and not self.alltoall and self.recv is None and owner._virtual is None):
+            self.pipeline = X.pipeline_plan(layout.total, owner.world_size, self.codec, force=owner.pipeline == "force")
         heap_bytes = 2 * ((slot_bytes + 255) // 256 * 256) + 8192 + (16 * nseg + 1024 if self.clip else 0)
         self.heap = owner._make_heap(layout.key(), heap_bytes)
         self.channel = X.ExchangeChannel(self.heap, slot_bytes, nseg, owner.timeout_ms, owner.comm_sms, clip=self.clip)
@@ -176,7 +180,7 @@ class _Plan:
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
                  group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None, nvls=False,
-                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None, split_overlap=True):
+                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None, split_overlap=True, pipeline=True):
         """``comm_sms``: SMs an exchange may use when nothing else runs (None: all of them).  ``overlap_sms``: SMs
         of an exchange that runs next to the backward pass (launched from a gradient hook: ``send_step``, the
         bucketed ``DistributedOptimizer``, the DDP hook); the rest stays with backward.  With ``split_overlap`` such an
@@ -188,6 +192,9 @@ class FusedExchange(Communicator):
         self.mode = mode
         self.overlap_sms = overlap_sms
         self.split_overlap = bool(split_overlap)
+        # quantised all-gather exchanges of 32 Mi elements and more: encode chunk c + 1 while chunk c is pulled
+        # (False: phase by phase; "force": also for small buffers and a single rank, for tests)
+        self.pipeline = pipeline
         self.arena_bytes = int(arena_mb * (1 << 20))
         self._arena = None
         self._side_stream = None
@@ -373,7 +380,8 @@ class FusedExchange(Communicator):
                 lr=float(getattr(comp, "learning_rate", 1.0)), scale=scale, seed=plan.seed, step=plan.steps,
                 phases=phases | (X.PHASE_REDUCE if (plan.alltoall and phases == X.PHASE_ALL) else 0), seq=seq,
                 recv=plan.recv, alltoall=plan.alltoall, grid=grid, qsgd_bucket=plan.qsgd_bucket,
-                qsgd_nbuckets=plan.qsgd_nbuckets)
+                qsgd_nbuckets=plan.qsgd_nbuckets,
+                pipeline=plan.pipeline if (phases == X.PHASE_ALL and plan.channel.chunk_ready_off) else None)
         return seq
 
     # ------------------------------------------------------------------

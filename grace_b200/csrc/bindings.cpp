@@ -85,6 +85,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
   m.attr("QUANT_STATS_BYTES") = sizeof(QuantSegStats);
   m.attr("SGD_TENSOR_BYTES") = sizeof(SgdTensor);
   m.attr("MAX_WORLD") = (int)kMaxWorldH;
+  m.attr("PIPE_MAX_CHUNKS") = (int)kPipeMaxChunks;
 
   // ---- fused sparse exchange ----
   m.def("sparse_exchange",
@@ -126,8 +127,11 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
            const std::vector<uintptr_t>& heaps, unsigned long long ready_off, unsigned long long ack_off,
            unsigned long long slot_off, int grid, uintptr_t stream, int alltoall, unsigned long long ready2_off,
            uintptr_t recv_local, uintptr_t recv_mc, unsigned long long recv_stride, int g_dtype, int qsgd_bucket,
-           long long qsgd_nbuckets, unsigned long long slot_bytes) {
+           long long qsgd_nbuckets, unsigned long long slot_bytes, uintptr_t pipe, unsigned long long chunk_ready_off,
+           int pipe_chunks, int pipe_chunk_items, int pipe_item_elems) {
           QuantArgs a{};
+          a.pipe = ptr<unsigned>(pipe); a.chunk_ready_off = chunk_ready_off; a.pipe_chunks = pipe_chunks;
+          a.pipe_chunk_items = pipe_chunk_items; a.pipe_item_elems = pipe_item_elems;
           a.qsgd_bucket = qsgd_bucket; a.qsgd_nbuckets = qsgd_nbuckets;
           if (g_dtype < 0 || g_dtype > 2) throw std::invalid_argument("g_dtype: 0 fp32, 1 bf16, 2 fp16");
           a.g_dtype = g_dtype;
@@ -143,7 +147,10 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
           a.phases = phases;
           a.peers = make_peers(rank, world, seq, timeout_ns, heaps, ready_off, ack_off, slot_off, slot_bytes);
           if (total % 128 != 0) throw std::invalid_argument("total must be a multiple of 128");
-          check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
+          if (pipe_chunks > 0)
+            check(launch_quant_pipeline(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange (pipelined)");
+          else
+            check(launch_quant_exchange(a, grid, reinterpret_cast<cudaStream_t>(stream)), "quant_exchange");
         });
 
   // ---- dense all-reduce over the NVSwitch multicast mapping ----

@@ -160,13 +160,24 @@ struct QuantArgs {
   char* recv_local;               // this GPU's receive area of the current parity: world regions of recv_stride bytes
   char* recv_mc;                  // multicast address of the same area
   unsigned long long recv_stride;
+  // Pipelined all-gather mode (quant_pipeline_kernel; QSGD with 128-element buckets and natural compression, pull
+  // transport, 2..8 ranks): the buffer is cut into chunks of tiles; CTAs take tiles from one queue in which the
+  // encode tiles of chunk c + 1 come before the decode tiles of chunk c, and a chunk is published to the peers as
+  // soon as its last tile is encoded, so that pulling chunk c over NVLink runs next to encoding chunk c + 1.
+  unsigned* pipe;                 // [0] queue head, [1 + c] encoded tiles of chunk c; zeroed by the launcher
+  unsigned long long chunk_ready_off;   // kMaxWorldH x kPipeMaxChunks uint64 flags in every heap (value = seq)
+  int pipe_chunks;                // 0: not pipelined
+  int pipe_chunk_items;           // tiles per chunk (the last chunk may have fewer)
+  int pipe_item_elems;            // elements per tile, a multiple of 8192
   PeerTable peers;
 };
+constexpr int kPipeMaxChunks = 16;
 
 // alltoall_world > 0 adds the second region (one re-encoded chunk per rank) used by the two-phase mode.
 size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world = 0, long long nbuckets = 0);
 int quant_max_grid(int device, int sm_limit);
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream);
+cudaError_t launch_quant_pipeline(const QuantArgs& a, int grid, cudaStream_t stream);   // pipelined all-gather mode
 
 // ------------------------------------------------------------ dense NVLS ----
 // Uncompressed all-reduce over the NVSwitch multicast mapping of a symmetric buffer

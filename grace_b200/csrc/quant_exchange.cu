@@ -1106,6 +1106,255 @@ __global__ void __launch_bounds__(kBlock, 2) quant_exchange_kernel(const QuantAr
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Pipelined all-gather mode: encode and pull overlap tile by tile inside one launch.
+//
+// The flat buffer is cut into tiles of `pipe_item_elems` elements and chunks of `pipe_chunk_items` tiles.  All
+// CTAs draw work from one queue whose order is  E(0) | E(1) D(0) | E(2) D(1) | ... | E(C-1) D(C-2) | D(C-1)
+// (E(c) = the encode tiles of chunk c, D(c) = its decode tiles).  The CTA that encodes the last tile of chunk c
+// publishes the chunk to every peer (one flag per rank and chunk, value = sequence number); a CTA that draws a
+// decode tile of chunk c waits (bounded) until all ranks have published chunks 0..c and then pulls that tile's
+// codes from every rank with the staged decode.  While some CTAs pull chunk c over NVLink, the others encode chunk
+// c + 1 out of HBM: the two halves of the exchange, one link bound and one memory bound, run side by side.
+// Encode tiles never wait, and the encode tiles of chunks <= c + 1 are all handed out before the first decode tile
+// of chunk c, so no wait can depend on work that is still in the queue.  Results are bit-identical to the
+// phase-by-phase kernel above (same random streams by element index, same rank order of the sums).
+template <int C>
+__global__ void __launch_bounds__(kBlock, 2) quant_pipeline_kernel(const QuantArgs a) {
+  static_assert(C == kCodecQSGD || C == kCodecNatural, "pipelined mode: 8-bit codecs without a statistics pass");
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  struct Work { int kind, chunk, chunk_tiles; long long lo; };
+  __shared__ Work s_work[2];
+  __shared__ int s_flag;
+
+  const Status status{a.status};
+  GridBarrier bar{a.barrier, 0u, a.peers.timeout_ns, status};
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = a.peers.rank, world = a.peers.world;
+  char* const my_heap = a.peers.heap[rank];
+  char* const my_slot = my_heap + a.peers.slot_off;
+  const size_t off_codes = kHeaderBytes + scalars_bytes(a.nseg);
+  const size_t off_norms = off_codes + codes_bytes(8, a.total);
+
+  // the slot of this parity was last used by sequence seq-2: wait until every peer has acknowledged reading it
+  if (tid < world && tid != rank && a.peers.seq > 2) {
+    const uint64_t* ack = reinterpret_cast<const uint64_t*>(my_heap + a.peers.ack_off) + tid;
+    wait_flag_ge(ack, a.peers.seq - 2, a.peers.timeout_ns, status, kTimeoutPeerAck, tid);
+  }
+  __syncthreads();
+
+  auto encode_range = [&](long long r_lo, long long r_hi) {
+    for_each_segment_range(a.segs, a.nseg, r_lo, r_hi, [&](int, long long b0, long long e0) {
+      // a tile is at most 2^20 elements: 32-bit offsets from b0 keep the loop's live state small
+      const int len = (int)(e0 - b0);
+      for (int o0 = 128 * warp; o0 < len; o0 += 128 * kWarps * kU) {
+        float pav[kU][4];
+#pragma unroll
+        for (int q = 0; q < kU; ++q) {
+          const int po = o0 + 128 * kWarps * q + 4 * lane;
+          const int pv = po < len ? ((len - po) >= 4 ? 4 : len - po) : 0;
+          float gv[4] = {0.f, 0.f, 0.f, 0.f}, rv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (pv) {
+            load4g(a.g, a.g_dtype, b0 + po, pv, gv);
+            if (a.acc && a.beta != 0.f) load4(a.acc, b0 + po, pv, rv);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) pav[q][j] = a.beta * rv[j] + a.gamma * gv[j];
+        }
+#pragma unroll
+        for (int q = 0; q < kU; ++q) {
+          const int go = o0 + 128 * kWarps * q;
+          if (go >= len) break;  // warp-uniform
+          const long long gb = b0 + go;
+          const long long i = gb + 4 * lane;
+          const int valid = (go + 4 * lane) < len ? ((len - go - 4 * lane) >= 4 ? 4 : len - go - 4 * lane) : 0;
+          float xv[4], dv[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { xv[j] = pav[q][j]; dv[j] = 0.f; }
+          Philox4 rnd{0u, 0u, 0u, 0u};
+          if (C == kCodecQSGD || !a.deterministic) rnd = philox_group((uint64_t)(i >> 2), a.step, 0u, a.seed);
+          const unsigned rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+          unsigned word = 0;
+          if (C == kCodecQSGD) {
+            float sq = xv[0] * xv[0] + xv[1] * xv[1] + xv[2] * xv[2] + xv[3] * xv[3];
+            sq = warp_sum(sq);
+            const float norm = sqrtf(sq);
+            const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f;
+            const float dq = norm / (float)a.quantum;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lf = qn * fabsf(xv[j]);
+              const float fl = floorf(lf);
+              float level = fl + ((u01(rw[j]) < lf - fl) ? 1.f : 0.f);
+              level = fminf(level, 127.f);
+              const int code = xv[j] < 0.f ? -(int)level : (int)level;
+              word |= ((unsigned)code & 0xffu) << (8 * j);
+              dv[j] = dq * (float)code;
+            }
+            if (lane == 0) *reinterpret_cast<float*>(my_slot + off_norms + (size_t)(gb >> 7) * 4) = norm;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const unsigned bits = __float_as_uint(xv[j]);
+              const unsigned biased = (bits >> 23) & 0xffu;
+              const unsigned mant = bits & 0x7fffffu;
+              bool up;
+              if (a.deterministic) up = mant > 0x400000u;
+              else up = u01(rw[j]) < (float)mant * 1.1920928955078125e-07f;
+              int c7 = (int)biased + (up ? 1 : 0) - 17;
+              c7 = c7 < 0 ? 0 : (c7 > 127 ? 127 : c7);
+              if (biased == 0) c7 = 0;
+              const unsigned code = (unsigned)c7 | ((bits >> 24) & 0x80u);
+              word |= code << (8 * j);
+              dv[j] = natural_decode(code);
+            }
+          }
+          if (GRACE_IN_RANGE(status, kKernelQuant, off_codes + (size_t)i + 3, a.peers.slot_bytes))
+            *reinterpret_cast<unsigned*>(my_slot + off_codes + (size_t)i) = word;
+          if (a.acc && valid) {
+            float res[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) res[j] = xv[j] - dv[j];
+            store4(a.acc, i, valid, res);
+          }
+        }
+      }
+    });
+  };
+
+  auto decode_range = [&](long long r_lo, long long r_hi) {
+    uint4* const st_codes = reinterpret_cast<uint4*>(s_dyn + warp * kStageWarpBytes);                      // [rank][32]
+    float* const st_norms = reinterpret_cast<float*>(s_dyn + warp * kStageWarpBytes + kStagePeers * 512);  // [rank][4]
+    for_each_segment_range(a.segs, a.nseg, r_lo, r_hi, [&](int, long long b0, long long e0) {
+      for (long long w0 = b0 + 512ll * warp; w0 < e0; w0 += 512ll * kWarps) {
+        {
+          const long long le = w0 + 16ll * lane;
+          const bool have = le < e0;
+          uint4 v[kStagePeers];
+          // the four norms of the block from each of up to eight ranks: one load per lane (rank = lane / 4)
+          float nv = 0.f;
+          if (C == kCodecQSGD && (lane >> 2) < world && w0 + 128ll * (lane & 3) < e0)
+            nv = ld_cg_f32(a.peers.heap[lane >> 2] + a.peers.slot_off + off_norms + (size_t)((w0 >> 7) + (lane & 3)) * 4);
+#pragma unroll
+          for (int p = 0; p < kStagePeers; ++p) {
+            v[p] = make_uint4(0u, 0u, 0u, 0u);
+            if (p < world) {
+              const char* slot = a.peers.heap[p] + a.peers.slot_off;
+              if (have && GRACE_IN_RANGE(status, kKernelQuant, off_codes + (size_t)le + 15, a.peers.slot_bytes))
+                v[p] = ld_cg_u4(slot + off_codes + (size_t)le);
+            }
+          }
+          __syncwarp();   // the previous trip's readers are done with the staging area
+          if (C == kCodecQSGD) st_norms[lane] = nv;   // [rank][4]
+#pragma unroll
+          for (int p = 0; p < kStagePeers; ++p)
+            if (p < world) st_codes[p * 32 + lane] = v[p];
+          __syncwarp();
+        }
+        float acc16[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
+        for (int p = 0; p < world; ++p) {
+          const uint4 cw = st_codes[p * 32 + lane];
+          const unsigned words[4] = {cw.x, cw.y, cw.z, cw.w};
+          float d = 0.f;
+          if (C == kCodecQSGD) d = st_norms[p * 4 + (lane >> 3)] / (float)a.quantum;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const unsigned byte = (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+            if (C == kCodecQSGD) acc16[j] += d * (float)(int)(signed char)byte;
+            else acc16[j] += natural_decode(byte);
+          }
+        }
+        const long long i = w0 + 16ll * lane;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const long long iv = i + 4 * v4;
+          if (iv >= e0) continue;
+          const int valid = (e0 - iv) >= 4 ? 4 : (int)(e0 - iv);
+          const float ov[4] = {acc16[4 * v4] * a.scale, acc16[4 * v4 + 1] * a.scale, acc16[4 * v4 + 2] * a.scale,
+                               acc16[4 * v4 + 3] * a.scale};
+          store4g(a.out, a.g_dtype, iv, valid, ov);
+        }
+      }
+    });
+  };
+
+  // ---- the queue: thread 0 draws a position and turns it into (encode or decode, chunk, element range) ----
+  auto draw = [&](int slot) {
+    const unsigned n_items = (unsigned)((a.total + a.pipe_item_elems - 1) / a.pipe_item_elems);   // tiles of one pass
+    const unsigned T = (unsigned)a.pipe_chunk_items, NC = (unsigned)a.pipe_chunks;
+    const unsigned n_last = n_items - (NC - 1) * T;                                                // tiles of the last chunk
+    const unsigned q = atomicAdd(&a.pipe[0], 1u);
+    int kind = 0;   // 0: the queue is empty, 1: encode, 2: decode
+    unsigned c = 0, t = 0;
+    if (q < 2u * n_items) {
+      if (q < (NC > 1 ? T : n_last)) {
+        kind = 1; c = 0; t = q;
+      } else if (NC == 1) {
+        kind = 2; c = 0; t = q - n_last;
+      } else {
+        const unsigned q1 = q - T;
+        if (q1 < (NC - 2) * 2u * T) {                  // full blocks: E(k) then D(k - 1), k = 1 .. NC - 2
+          const unsigned k = 1 + q1 / (2u * T), r = q1 % (2u * T);
+          kind = r < T ? 1 : 2; c = r < T ? k : k - 1; t = r < T ? r : r - T;
+        } else {                                        // the last block: E(NC - 1), D(NC - 2), D(NC - 1)
+          const unsigned r = q1 - (NC - 2) * 2u * T;
+          if (r < n_last) { kind = 1; c = NC - 1; t = r; }
+          else if (r < n_last + T) { kind = 2; c = NC - 2; t = r - n_last; }
+          else { kind = 2; c = NC - 1; t = r - n_last - T; }
+        }
+      }
+    }
+    s_work[slot].kind = kind;
+    s_work[slot].chunk = (int)c;
+    s_work[slot].chunk_tiles = (int)(c + 1 < NC ? T : n_last);
+    s_work[slot].lo = ((long long)c * T + t) * a.pipe_item_elems;
+  };
+  if (tid == 0) draw(0);
+  __syncthreads();
+  for (unsigned n = 0;; ++n) {
+    const int kind = s_work[n & 1].kind;
+    if (kind == 0) break;
+    if (tid == 0) draw((n + 1) & 1);   // the next draw travels while this tile is worked on
+    const long long r_lo = s_work[n & 1].lo;
+    const long long r_hi = r_lo + a.pipe_item_elems < a.total ? r_lo + a.pipe_item_elems : a.total;
+    if (kind == 1) {
+      if (!status.failed()) encode_range(r_lo, r_hi);
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();
+        const unsigned done = atomicAdd(&a.pipe[1 + s_work[n & 1].chunk], 1u) + 1u;
+        s_flag = done == (unsigned)s_work[n & 1].chunk_tiles;
+        if (s_flag) __threadfence();
+      }
+      __syncthreads();
+      if (s_flag && tid < world && !status.failed()) {   // this CTA encoded the chunk's last tile: publish it
+        __threadfence_system();
+        uint64_t* flag = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.chunk_ready_off) +
+                         (size_t)rank * kPipeMaxChunks + s_work[n & 1].chunk;
+        st_release_sys(flag, a.peers.seq);
+      }
+    } else {
+      if (tid == 0) s_flag = 1;
+      __syncthreads();
+      if (tid < world * (s_work[n & 1].chunk + 1)) {      // chunks 0..c of every rank (own rank included)
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(my_heap + a.chunk_ready_off) +
+                               (size_t)(tid % world) * kPipeMaxChunks + tid / world;
+        if (!wait_flag_ge(flag, a.peers.seq, a.peers.timeout_ns, status, kTimeoutPeerReady, tid % world)) s_flag = 0;
+      }
+      __syncthreads();
+      if (s_flag) decode_range(r_lo, r_hi);
+    }
+    __syncthreads();
+  }
+  bar.sync();
+  if (blockIdx.x == 0 && tid < world && tid != rank && !status.failed()) {
+    uint64_t* ack = reinterpret_cast<uint64_t*>(a.peers.heap[tid] + a.peers.ack_off) + rank;
+    st_release_sys(ack, a.peers.seq);
+  }
+}
+
 // Dynamic shared memory of a launch: the staging areas, when the staged decode can run.
 template <int C>
 constexpr bool staged_codec() { return CodecTraits<C>::bits == 1 || CodecTraits<C>::bits == 2 || CodecTraits<C>::bits == 8; }
@@ -1183,6 +1432,42 @@ size_t quant_slot_bytes(int codec, long long total, int nseg, int alltoall_world
 }
 
 int quant_max_grid(int device, int sm_limit) { return occupancy<kCodecQSGD>(device, sm_limit); }
+
+template <int C>
+static cudaError_t launch_pipeline(const QuantArgs& a, int grid, cudaStream_t stream) {
+  const void* fn = (const void*)quant_pipeline_kernel<C>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+    if (err != cudaSuccess) return err;
+    attr_set[dev] = true;
+  }
+  int per_sm = 0;
+  cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kBlock, kStageBytes);
+  if (err != cudaSuccess) return err;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  QuantArgs copy = a;
+  void* params[] = {&copy};
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kBlock), params, kStageBytes, stream);
+}
+
+cudaError_t launch_quant_pipeline(const QuantArgs& a, int grid, cudaStream_t stream) {
+  const long long items = a.pipe_item_elems > 0 ? (a.total + a.pipe_item_elems - 1) / a.pipe_item_elems : 0;
+  if (!a.pipe || !a.chunk_ready_off || a.pipe_chunks < 1 || a.pipe_chunks > kPipeMaxChunks || a.pipe_item_elems < 8192 ||
+      a.pipe_item_elems % 8192 || a.pipe_chunk_items < 1 || a.peers.world < 1 || a.peers.world > kStagePeers ||
+      a.alltoall || a.recv_mc || a.phases != kPhaseAll || !a.out ||
+      (long long)(a.pipe_chunks - 1) * a.pipe_chunk_items >= items || (long long)a.pipe_chunks * a.pipe_chunk_items < items)
+    return cudaErrorInvalidValue;
+  cudaError_t err = cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream);
+  if (err != cudaSuccess) return err;
+  err = cudaMemsetAsync(a.pipe, 0, sizeof(unsigned) * (1 + kPipeMaxChunks), stream);
+  if (err != cudaSuccess) return err;
+  if (a.codec == kCodecQSGD) return launch_pipeline<kCodecQSGD>(a, grid, stream);
+  if (a.codec == kCodecNatural) return launch_pipeline<kCodecNatural>(a, grid, stream);
+  return cudaErrorInvalidValue;
+}
 
 cudaError_t launch_quant_exchange(const QuantArgs& a, int grid, cudaStream_t stream) {
   static bool edges_loaded[64] = {};

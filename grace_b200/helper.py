@@ -116,6 +116,7 @@ def grace_from_params(params: Dict[str, Any]):
             nvls=_nvls(params), nvls_min_world=params.get("nvls_min_world", 4),
             overlap_sms=params.get("overlap_sms", 32), arena_mb=params.get("arena_mb", 64),
             split_overlap=params.get("split_overlap", True), store=params.get("store"),
+            pipeline=params.get("pipeline", True),
         )
         if _nvls(params) and comp_name == "none" and mem_name == "none":
             from .communicator.nvls import NvlsAllreduce

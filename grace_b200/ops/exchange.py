@@ -128,6 +128,10 @@ class ExchangeChannel:
             for off in self.guard_off:
                 heap.view(off, GUARD_BYTES, torch.uint8).fill_(GUARD_PATTERN)
         self.ready2_off = heap.alloc(C.MAX_WORLD * 8) if heap.free_bytes >= C.MAX_WORLD * 8 + 256 else 0
+        # pipelined quantised exchange: one "published" flag per rank and chunk, and the queue / chunk counters
+        chunk_flags = C.MAX_WORLD * C.PIPE_MAX_CHUNKS * 8
+        self.chunk_ready_off = heap.alloc(chunk_flags) if heap.free_bytes >= chunk_flags + 256 else 0
+        self.pipe = torch.zeros(1 + C.PIPE_MAX_CHUNKS, dtype=torch.int32, device=heap.device)
         # DGC gradient clipping: every rank publishes its per-tensor sums of squares (two parities) + a flag pad
         self.clip_off = self.clip_ready_off = 0
         self.clip_sq = None
@@ -237,6 +241,8 @@ class ExchangeChannel:
         self.heap.view(self.flags_off, 2 * C.MAX_WORLD, torch.int64).zero_()
         if self.ready2_off:
             self.heap.view(self.ready2_off, C.MAX_WORLD, torch.int64).zero_()
+        if self.chunk_ready_off:
+            self.heap.view(self.chunk_ready_off, C.MAX_WORLD * C.PIPE_MAX_CHUNKS, torch.int64).zero_()
         if self.clip_ready_off:
             self.heap.view(self.clip_ready_off, C.MAX_WORLD, torch.int64).zero_()
             self.clip_sq.zero_()
@@ -352,9 +358,10 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
               gamma: float = 1.0, mom_beta: float = 0.0, lr: float = 1.0, scale: float = 1.0, seed: int = 0,
               step: int = 0, phases: int = PHASE_ALL, seq: Optional[int] = None, grid: Optional[int] = None,
               alltoall: bool = False, recv=None, qsgd_bucket: int = 0, qsgd_nbuckets: int = 0,
-              slot_bytes: Optional[int] = None) -> int:
+              slot_bytes: Optional[int] = None, pipeline: Optional[Tuple[int, int, int]] = None) -> int:
     """``recv``: ``(NvlsBuffer, stride)`` of the push transport (two parities of ``world`` regions of ``stride``
-    bytes each), or None for the pull transport."""
+    bytes each), or None for the pull transport.  ``pipeline``: ``(chunks, tiles per chunk, elements per tile)`` from
+    ``pipeline_plan`` runs the pipelined kernel (whole exchange in one launch, pull transport only)."""
     C = native()
     heap = channel.heap
     if seq is None:
@@ -382,9 +389,28 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
         grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
         int(qsgd_bucket), int(qsgd_nbuckets), channel.slot_bytes if slot_bytes is None else int(slot_bytes),
+        channel.pipe.data_ptr() if pipeline else 0, channel.chunk_ready_off if pipeline else 0,
+        *(pipeline if pipeline else (0, 0, 0)),
     )
     channel.post_status()
     return seq
+
+
+def pipeline_plan(total: int, world: int, codec: int, force: bool = False) -> Optional[Tuple[int, int, int]]:
+    """(chunks, tiles per chunk, elements per tile) of the pipelined quantised exchange, or None where it does not
+    apply: QSGD with 128-element buckets and natural compression, 2..8 ranks, at least two chunks of 16 Mi elements
+    (smaller exchanges are dominated by the fixed cost of a launch, not by the order of their phases).  ``force``
+    drops the size and rank-count limits (tests)."""
+    if codec not in (CODEC["qsgd"], CODEC["natural"]) or world > 8:
+        return None
+    if not force and (world < 2 or total < (32 << 20)):
+        return None
+    item = 65536 if total >= (128 << 20) else (32768 if total >= (64 << 20) else (16384 if total >= (1 << 20) else 8192))
+    items = -(-total // item)
+    chunks = max(1, min(native().PIPE_MAX_CHUNKS, total // (16 << 20) if not force else 4, items))
+    per_chunk = -(-items // chunks)
+    chunks = -(-items // per_chunk)
+    return chunks, per_chunk, item
 
 
 def segments_to_device(layout: FlatLayout, ks: Optional[Sequence[int]], device) -> torch.Tensor:

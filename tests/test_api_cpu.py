@@ -346,15 +346,30 @@ def test_bindings_reject_inconsistent_arguments_before_any_launch():
     heaps = [4096]
     with pytest.raises(ValueError):     # push transport needs both addresses of the receive area
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 16, 0, 256, 0, 0, 0, 4096)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 16, 0, 256, 0, 0, 0, 4096, 0, 0, 0, 0, 0)
     with pytest.raises(ValueError):     # total must be a multiple of 128
         C.quant_exchange(16, 0, 0, 16, 16, 1, 100, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096, 0, 0, 0, 0, 0)
     with pytest.raises(ValueError):     # rank outside the world
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 3, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 4096, 0, 0, 0, 0, 0)
     with pytest.raises(ValueError):     # gradient element type: 0 fp32, 1 bf16, 2 fp16
         C.quant_exchange(16, 0, 0, 16, 16, 1, 128, 0, 64, 0, 0, 1.0, 1.0, 0.0, 1.0, 1.0, 0, 0, 16, 16, 16, 7, 0, 1, 1,
-                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 5, 0, 0, 4096)
+                         10 ** 9, heaps, 0, 128, 256, 1, 0, 0, 0, 0, 0, 0, 5, 0, 0, 4096, 0, 0, 0, 0, 0)
     with pytest.raises(ValueError):     # dense all-reduce: 16-byte aligned pointers only
         C.dense_allreduce(8, 16, 16, 16, 128, 1.0, 16, 16, 0, 0, 1, 1, 10 ** 9, heaps, 0, 128, 1, 0)
+
+
+def test_pipeline_plan_covers_the_buffer_with_whole_chunks():
+    from grace_b200.ops.exchange import CODEC, pipeline_plan
+
+    assert pipeline_plan(1 << 20, 4, CODEC["qsgd"]) is None            # too small to pay
+    assert pipeline_plan(256 << 20, 1, CODEC["qsgd"]) is None          # nobody to overlap with
+    assert pipeline_plan(256 << 20, 4, CODEC["efsign"]) is None
+    for total in (32 << 20, (336 << 20) + 128 * 77, 256 << 20, 1 << 30):
+        chunks, per_chunk, item = pipeline_plan(total, 8, CODEC["natural"])
+        items = -(-total // item)
+        assert item % 8192 == 0 and 2 <= chunks <= 16
+        assert (chunks - 1) * per_chunk < items <= chunks * per_chunk
+    chunks, per_chunk, item = pipeline_plan(300_032, 1, CODEC["qsgd"], force=True)
+    assert (chunks - 1) * per_chunk < -(-300_032 // item) <= chunks * per_chunk

@@ -82,6 +82,29 @@ def _body(rank, world, dev):
         dist.all_gather(gathered, got)
         same = all(torch.equal(gathered[0], t) for t in gathered)
         out[comp] = (worst, same)
+    # pipelined all-gather mode (encode of chunk c + 1 next to the pull of chunk c) against the phase-by-phase
+    # kernel: same random streams, same order of the sums, so the same bits, step after step
+    layout = FlatLayout.from_named([("a", 250_000), ("b", 64), ("c", 1_234_567)])
+    for comp, extra in (("qsgd", {"quantum_num": 64}), ("natural_cuda", {})):
+        pair = [grace_from_params({"compressor": comp, "memory": "residual", "communicator": "allgather",
+                                   "world_size": world, "fused": True, "timeout_ms": 5000, "pipeline": mode, **extra})
+                for mode in ("force", False)]
+        same = True
+        for step in range(4):
+            g = torch.Generator().manual_seed(31 * step + rank)
+            flat = torch.zeros(layout.total, device=dev)
+            for o, c in zip(layout.offsets, layout.numels):
+                flat[o:o + c] = (torch.randn(c, generator=g) * 1e-3).to(dev)
+            a, b = flat.clone(), flat.clone()
+            pair[0].step_flat(a, layout)
+            pair[1].step_flat(b, layout)
+            pair[0].check()
+            pair[1].check()
+            same = same and torch.equal(a, b)
+        plans = [next(iter(c._plans.values())) for c in pair]
+        assert plans[0].pipeline is not None and plans[1].pipeline is None
+        same = same and torch.equal(plans[0].acc, plans[1].acc)
+        out["pipelined_" + comp] = (0.0, same)
     # flat multi-tensor bucket, several steps on one channel (slot reuse, acknowledgements)
     layout = FlatLayout.from_named([("a", 5000), ("b", 64), ("c", 123_457)])
     fused = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
