@@ -92,7 +92,7 @@ def roofline_ms(case, n, world, bw):
         link = (world - 1) * n / 8
     else:  # powersgd on sqrt(n) x sqrt(n)
         hbm = 28 * n
-        side = int(n ** 0.5)
+        side = int(n ** 0.5)                                 # P and Q of rank 4, padded to 16 columns
         link = (world - 1) * 2 * side * 16 * 4
     return max(hbm / (bw * 1e9), link / (NVLINK_GBS * 1e9)) * 1e3, hbm, link
 
@@ -190,9 +190,11 @@ def main():
         for size_m in [int(s) for s in args.sizes.split(",")]:
             n = size_m << 20
             if case == "powersgd4":
-                if size_m != 16:
+                # matrices: 16 -> 4096 x 4096, 64 -> 8192 x 8192, 98 -> 4096 x 25088 (the first FC layer of VGG-16)
+                shape = {16: (4096, 4096), 64: (8192, 8192), 98: (4096, 25088)}.get(size_m)
+                if shape is None:
                     continue
-                shape = (4096, 4096)
+                n = shape[0] * shape[1]
             else:
                 shape = (n,)
             try:
