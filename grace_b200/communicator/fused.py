@@ -180,12 +180,13 @@ class _Plan:
 class FusedExchange(Communicator):
     def __init__(self, compressor, memory, world_size, mode="allgather", seed=0, timeout_ms=10000.0, comm_sms=None,
                  group=None, inplace=True, max_ratio=0.25, exact=True, rank=None, monitor=None, nvls=False,
-                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None, split_overlap=True, pipeline=True):
+                 nvls_min_world=4, overlap_sms=32, arena_mb=64, store=None, split_overlap=False, pipeline=True):
         """``comm_sms``: SMs an exchange may use when nothing else runs (None: all of them).  ``overlap_sms``: SMs
         of an exchange that runs next to the backward pass (launched from a gradient hook: ``send_step``, the
         bucketed ``DistributedOptimizer``, the DDP hook); the rest stays with backward.  With ``split_overlap`` such an
         exchange is two launches: compress + publish at full width (short, HBM bound), then pull + decode on
-        ``overlap_sms`` SMs (long at 8 GPUs, NVLink bound).  ``arena_mb``: size of
+        ``overlap_sms`` SMs; measured on BERT-large it loses to the single capped launch (a full-width cooperative
+        launch has to wait until backward's kernels have drained), so it is off by default.  ``arena_mb``: size of
         the symmetric heaps the plans are carved from.  ``store``: a ``torch.distributed`` store through which the
         ranks tell each other about a failed exchange (``agree`` / ``recover``)."""
         super().__init__(compressor, memory, world_size)

@@ -15,6 +15,10 @@
 //       order 0..W-1 so that every rank computes bit-identical sums),
 //       dequantises, accumulates in fp32 or counts votes, and stores the
 //       aggregate.
+// For QSGD (128-element buckets) and natural compression the default at 2..8 ranks and 32 Mi elements or more is
+// the pipelined form of this pull (quant_pipeline_kernel below): tiles of the buffer are drawn from one queue in
+// which the encode tiles of chunk c + 1 come before the decode tiles of chunk c, every chunk is published as soon
+// as its last tile is encoded, and the pull of chunk c over NVLink runs next to the encode of chunk c + 1.
 // Two more transports exist besides this pull: the two-phase mode (compressed
 // reduce-scatter, re-encode, compressed all-gather; `alltoall`), and the push
 // mode (kPush instantiation): every store of pass E is a multimem.st through the

@@ -115,7 +115,7 @@ def grace_from_params(params: Dict[str, Any]):
             comm_sms=params.get("comm_sms"), group=params.get("group"),
             nvls=_nvls(params), nvls_min_world=params.get("nvls_min_world", 4),
             overlap_sms=params.get("overlap_sms", 32), arena_mb=params.get("arena_mb", 64),
-            split_overlap=params.get("split_overlap", True), store=params.get("store"),
+            split_overlap=params.get("split_overlap", False), store=params.get("store"),
             pipeline=params.get("pipeline", True),
         )
         if _nvls(params) and comp_name == "none" and mem_name == "none":
