@@ -51,6 +51,9 @@ CASES = {
     # *_phased: the phase-by-phase kernel instead of the pipelined one (encode of chunk c + 1 next to the pull of chunk c)
     "qsgd8_phased": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127, pipeline=False),
     "natural_phased": dict(compressor="natural", memory="residual", communicator="allgather", pipeline=False),
+    # the pipelined kernel on a single rank (queue, chunk counters and flags to itself): for profiling on one GPU
+    "qsgd8_forced": dict(compressor="qsgd", memory="residual", communicator="allgather", quantum_num=127,
+                         pipeline="force"),
     # uncompressed mean: "dense" = one-shot peer loads + two-phase option, "dense_nvls" = NVSwitch multicast kernel
     "dense": dict(compressor="none", memory="none", communicator="alltoall"),
     "dense_nvls": dict(compressor="none", memory="none", communicator="allreduce", nvls=True, nvls_min_world=2),
@@ -76,7 +79,7 @@ def roofline_ms(case, n, world, bw):
         per_elem = 20 if case == "topk1" else 28          # g,r read; r,out write; one re-read (+u read/write for DGC)
         hbm = per_elem * n
         link = (world - 1) * ratio * n * 8
-    elif case in ("qsgd8", "natural", "qsgd8_push", "natural_push", "qsgd8_phased", "natural_phased"):
+    elif case in ("qsgd8", "natural", "qsgd8_push", "natural_push", "qsgd8_phased", "natural_phased", "qsgd8_forced"):
         hbm = (12 + 1 + world + 4) * n                       # g,r read, r write, code write, W code reads, out write
         link = (world - 1) * n * (1 + 4.0 / 128)
     elif case == "qsgd8_a2a":
