@@ -149,7 +149,7 @@ def test_fused_exchange_matches_library_over_real_gpus():
                 assert worst < 1e-5, (comp, worst)
 
 
-def _timeout_entry(rank, world, port, ret):
+def _timeout_entry(rank, world, port, ret, pipelined=False):
     sys.path.insert(0, ROOT)
     os.environ.update(NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -163,8 +163,13 @@ def _timeout_entry(rank, world, port, ret):
         from grace_b200.ops.exchange import GraceCommError
 
         store = dist.distributed_c10d._get_default_store()
-        grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
-                                 "world_size": world, "fused": True, "compress_ratio": 0.01, "timeout_ms": 500})
+        if pipelined:   # the pipelined quantised exchange: its decode tiles wait for the peer's chunk flags
+            grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather",
+                                     "world_size": world, "fused": True, "quantum_num": 64, "timeout_ms": 500,
+                                     "pipeline": "force"})
+        else:
+            grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                                     "world_size": world, "fused": True, "compress_ratio": 0.01, "timeout_ms": 500})
         x = torch.randn(100_000, device=dev) * 1e-3
         for _ in range(2):                       # two healthy steps
             grc.step(x.clone(), "w")
@@ -190,12 +195,13 @@ def _timeout_entry(rank, world, port, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-def test_peer_that_stops_launching_is_reported_as_timeout():
+@pytest.mark.parametrize("pipelined", [False, True])
+def test_peer_that_stops_launching_is_reported_as_timeout(pipelined):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
         port = _token()
-        procs = [ctx.Process(target=_timeout_entry, args=(r, 2, port, ret)) for r in range(2)]
+        procs = [ctx.Process(target=_timeout_entry, args=(r, 2, port, ret, pipelined)) for r in range(2)]
         for p in procs:
             p.start()
         for p in procs:
