@@ -165,17 +165,19 @@ def _timeout_entry(rank, world, port, ret, pipelined=False):
         store = dist.distributed_c10d._get_default_store()
         if pipelined:   # the pipelined quantised exchange: its decode tiles wait for the peer's chunk flags
             grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather",
-                                     "world_size": world, "fused": True, "quantum_num": 64, "timeout_ms": 500,
+                                     "world_size": world, "fused": True, "quantum_num": 64, "timeout_ms": 10000,
                                      "pipeline": "force"})
         else:
             grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
-                                     "world_size": world, "fused": True, "compress_ratio": 0.01, "timeout_ms": 500})
+                                     "world_size": world, "fused": True, "compress_ratio": 0.01, "timeout_ms": 10000})
         x = torch.randn(100_000, device=dev) * 1e-3
-        for _ in range(2):                       # two healthy steps
+        for _ in range(2):                       # two healthy steps (generous limit: the first launch loads the kernels)
             grc.step(x.clone(), "w")
         grc.check()
         torch.cuda.synchronize()
         dist.barrier()
+        for plan in grc._plans.values():         # from here on a wait gives up after half a second
+            plan.channel.timeout_ns = int(500e6)
         if rank == 1:
             # leaves between steps: nothing of its own in flight, it just never launches step 3
             store.wait(["rank0_done"])
@@ -290,13 +292,16 @@ def _recover_entry(rank, world, port, ret):
 
         store = dist.distributed_c10d._get_default_store()
         grc = grace_from_params({"compressor": "qsgd", "memory": "residual", "communicator": "allgather",
-                                 "quantum_num": 64, "world_size": world, "fused": True, "timeout_ms": 300,
+                                 "quantum_num": 64, "world_size": world, "fused": True, "timeout_ms": 10000,
                                  "store": store})
         gen = torch.Generator().manual_seed(rank)
         x = (torch.randn(200_000, generator=gen) * 1e-3).to(dev)
-        grc.step(x.clone(), "w")
+        grc.step(x.clone(), "w")                            # generous limit: the first launch loads the kernels
         grc.check()
         assert grc.agree(timeout_s=60) == []               # a healthy step: nobody votes "failed"
+        dist.barrier()
+        for plan in grc._plans.values():                    # from here on a wait gives up after 300 ms
+            plan.channel.timeout_ns = int(300e6)
         residual_before = next(iter(grc._plans.values())).acc.clone()
         # rank 1 sits this step out (between steps, with nothing of its own in flight): rank 0's wait for its
         # payload expires after 300 ms and is reported; rank 1 itself saw nothing wrong
@@ -304,6 +309,8 @@ def _recover_entry(rank, world, port, ret):
             grc.step(x.clone(), "w")
         failed = grc.agree(timeout_s=60)                    # every rank learns that rank 0 failed
         grc.recover(timeout_s=60)
+        for plan in grc._plans.values():
+            plan.channel.timeout_ns = int(10e9)
         if rank == 1:                                       # rank 1's error feedback did not move while it sat out
             assert torch.equal(next(iter(grc._plans.values())).acc, residual_before)
         # after the recovery: a healthy exchange again, identical on both ranks
