@@ -1132,7 +1132,10 @@ __global__ void __launch_bounds__(kBlock, 2) quant_pipeline_kernel(const QuantAr
   __shared__ int s_flag;
 
   const Status status{a.status};
-  GridBarrier bar{a.barrier, 0u, a.peers.timeout_ns, status};
+  // CTAs that draw no tile reach the final grid barrier at once and wait there for those that are still waiting for
+  // a peer's chunk: the barrier's limit is twice the limit of a flag wait, so that a missing peer is reported as
+  // such (by the flag wait that expires first) and not as a barrier that gave up.
+  GridBarrier bar{a.barrier, 0u, 2 * a.peers.timeout_ns, status};
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rank = a.peers.rank, world = a.peers.world;
   char* const my_heap = a.peers.heap[rank];
