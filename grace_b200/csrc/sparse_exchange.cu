@@ -373,6 +373,7 @@ __global__ void __launch_bounds__(kBlock, 2) sparse_exchange_kernel(const Sparse
                 } else if (hint != 0xffffffffu) {
                   for (int b = tid; b < kBins; b += kBlock) g_hist2(s)[b] = 0;   // leave it zero
                 }
+                __syncthreads();   // every thread has read the hint word before thread 0 replaces it
                 if (tid == 0) {
                   *g_hint(s) = p0;
                   a.state[s].fine = hint == p0 ? 1u : 0u;
