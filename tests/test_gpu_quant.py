@@ -325,6 +325,21 @@ def test_pipelined_exchange_gives_the_bits_of_the_phase_by_phase_kernel(comp, ex
     plans = [next(iter(c._plans.values())) for c in pair]
     assert plans[0].pipeline is not None and plans[1].pipeline is None
     assert torch.equal(plans[0].acc, plans[1].acc)
+    # one tile in one chunk, and two chunks of one tile: the ends of the queue arithmetic
+    for small in ([("s", 5000)], [("s", 12_000), ("t", 3)]):
+        small_layout = FlatLayout.from_named(small)
+        pair = [grace_from_params({"compressor": comp, "memory": "residual", "communicator": "allgather",
+                                   "world_size": 1, "fused": True, "timeout_ms": 3000, "pipeline": mode, **extra})
+                for mode in ("force", False)]
+        for step in range(2):
+            flat = torch.zeros(small_layout.total, device=dev)
+            for o, c in zip(small_layout.offsets, small_layout.numels):
+                flat[o:o + c] = torch.randn(c, device=dev) * 1e-3
+            a, b = flat.clone(), flat.clone()
+            pair[0].step_flat(a, small_layout)
+            pair[1].step_flat(b, small_layout)
+            pair[0].check()
+            assert torch.equal(a, b), (small, step)
     # a bf16 gradient buffer goes through the same typed loads and stores
     pair = [grace_from_params({"compressor": comp, "memory": "residual", "communicator": "allgather", "world_size": 1,
                                "fused": True, "timeout_ms": 3000, "pipeline": mode, **extra}) for mode in ("force", False)]
