@@ -4,12 +4,14 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <cerrno>
 #include <cstring>
 #include <stdexcept>
 #include <string>
 #include <vector>
 
 #include "exchange.h"
+#include "host_exchange.h"
 #include "runtime.h"
 
 namespace py = pybind11;
@@ -250,4 +252,46 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
                            reinterpret_cast<cudaStream_t>(stream)),
           "multi_sgd");
   });
+
+  // ---- host engine of the exchange protocol (CPU ranks over POSIX shared memory) ----
+  m.attr("HOST_MAX_WORLD") = host::kMaxWorld;
+  m.def("host_heap_create", [](const std::string& name, size_t bytes) {
+    void* p = host::heap_create(name.c_str(), bytes);
+    if (!p) throw std::runtime_error("host_heap_create(" + name + "): " + std::strerror(errno));
+    return reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("host_heap_open", [](const std::string& name, size_t bytes) {
+    void* p = host::heap_open(name.c_str(), bytes);
+    if (!p) throw std::runtime_error("host_heap_open(" + name + "): " + std::strerror(errno));
+    return reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("host_heap_close", [](uintptr_t base, size_t bytes) { return host::heap_close(ptr<void>(base), bytes); });
+  m.def("host_heap_unlink", [](const std::string& name) { return host::heap_unlink(name.c_str()); });
+  m.def("host_slot_bytes", &host::slot_bytes);
+  m.def("host_exchange",
+        [](int rank, int world, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
+           unsigned long long ack_off, unsigned long long status_off, unsigned long long slot0_off,
+           unsigned long long slot1_off, unsigned long long slot_bytes, unsigned long long timeout_ns, int codec,
+           int phases, unsigned long long seq, uintptr_t g, uintptr_t acc, uintptr_t mom, uintptr_t out, long long n,
+           long long k, float beta, float gamma, float scale, float threshold, int strict, float lr, float mom_beta,
+           int first_step, int quantum, unsigned long long seed, unsigned step) {
+          if (world < 1 || world > host::kMaxWorld || (int)heaps.size() != world || rank < 0 || rank >= world)
+            throw std::invalid_argument("bad rank/world/heap table");
+          host::Channel ch{};
+          ch.rank = rank; ch.world = world;
+          for (int i = 0; i < world; ++i) ch.heap[i] = reinterpret_cast<char*>(heaps[i]);
+          ch.ready_off = ready_off; ch.ack_off = ack_off; ch.status_off = status_off;
+          ch.slot_off[0] = slot0_off; ch.slot_off[1] = slot1_off; ch.slot_bytes = slot_bytes; ch.timeout_ns = timeout_ns;
+          host::Args a{};
+          a.codec = codec; a.phases = phases; a.seq = seq;
+          a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
+          a.n = n; a.k = k; a.beta = beta; a.gamma = gamma; a.scale = scale; a.threshold = threshold; a.strict = strict;
+          a.lr = lr; a.mom_beta = mom_beta; a.first_step = first_step; a.quantum = quantum; a.seed = seed; a.step = step;
+          unsigned rc;
+          {
+            py::gil_scoped_release release;   // ranks of a test may be threads of one process
+            rc = host::exchange(ch, a);
+          }
+          return rc;
+        });
 }

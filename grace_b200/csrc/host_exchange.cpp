@@ -1,0 +1,349 @@
+// Host engine of the exchange protocol (see host_exchange.h): CPU ranks over
+// POSIX shared memory, the same flags / slots / bounded waits as the kernels.
+#include "host_exchange.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <numeric>
+#include <vector>
+
+#include <cuda_runtime.h>   // __host__ / __device__ markers of philox.cuh for the host compiler
+
+#include "philox.cuh"
+
+namespace grace {
+namespace host {
+
+namespace {
+
+inline uint64_t now_ns() {
+  timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+}
+
+inline uint64_t load_acquire(const uint64_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+inline void store_release(uint64_t* p, uint64_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+
+struct StatusBlock {
+  unsigned* words;
+  bool failed() const { return __atomic_load_n(words, __ATOMIC_ACQUIRE) != kOk; }
+  unsigned code() const { return __atomic_load_n(words, __ATOMIC_ACQUIRE); }
+  void fail(unsigned code, unsigned detail, unsigned seq) const {
+    unsigned expected = kOk;
+    if (__atomic_compare_exchange_n(words, &expected, code, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) {
+      words[1] = detail;
+      words[2] = seq;
+    }
+  }
+};
+
+// Bounded wait on a flag that a peer stores with release order.  Spins briefly, then yields the core: the ranks of
+// a test usually outnumber the cores.
+bool wait_flag_ge(const uint64_t* flag, uint64_t want, uint64_t timeout_ns, const StatusBlock& st, unsigned code,
+                  unsigned detail) {
+  if (load_acquire(flag) >= want) return true;
+  const uint64_t t0 = now_ns();
+  unsigned spins = 0;
+  while (load_acquire(flag) < want) {
+    if (++spins > 64) {
+      if (now_ns() - t0 > timeout_ns) {
+        st.fail(code, detail, (unsigned)want);
+        return false;
+      }
+      timespec nap{0, spins > 4096 ? 200000 : 2000};
+      nanosleep(&nap, nullptr);
+    }
+  }
+  return true;
+}
+
+struct SlotView {
+  char* base;
+  uint64_t* count() const { return reinterpret_cast<uint64_t*>(base); }
+  float* scalar(int i) const { return reinterpret_cast<float*>(base + 8) + i; }
+  char* payload() const { return base + kSlotHeaderBytes; }
+};
+
+inline long long groups128(long long n) { return (n + 127) / 128; }
+inline long long words32(long long n) { return (n + 31) / 32; }
+
+// ---- compress: x = beta * acc + gamma * g, encode x into the slot, acc = x - decode(code) ----
+unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail) {
+  const long long n = a.n;
+  if (slot_bytes(a.codec, n, a.k) > slot_bytes_avail) return kSlotOverflow;
+  std::vector<float> xbuf;
+  const float* x = a.g;
+  if (a.acc) {   // error feedback: the accumulator holds x while it is encoded
+    for (long long i = 0; i < n; ++i) a.acc[i] = a.beta * a.acc[i] + a.gamma * a.g[i];
+    x = a.acc;
+  } else if (a.gamma != 1.f) {
+    xbuf.resize(n);
+    for (long long i = 0; i < n; ++i) xbuf[i] = a.gamma * a.g[i];
+    x = xbuf.data();
+  }
+  char* pay = slot.payload();
+  switch (a.codec) {
+    case kTopK: {
+      const long long k = std::min(a.k, n);
+      if (k < 1) return kBadArgument;
+      std::vector<int> order(n);
+      std::iota(order.begin(), order.end(), 0);
+      auto larger = [x](int p, int q) {
+        const float ap = std::fabs(x[p]), aq = std::fabs(x[q]);
+        return ap > aq || (ap == aq && p < q);
+      };
+      if (k < n) std::nth_element(order.begin(), order.begin() + k, order.end(), larger);
+      std::sort(order.begin(), order.begin() + k);   // ascending indices: the same list whatever the partition did
+      float* val = reinterpret_cast<float*>(pay);
+      int* idx = reinterpret_cast<int*>(pay + (size_t)a.k * 4);
+      for (long long j = 0; j < k; ++j) {
+        idx[j] = order[j];
+        val[j] = x[order[j]];
+        if (a.acc) a.acc[order[j]] = 0.f;
+      }
+      *slot.count() = (uint64_t)k;
+      break;
+    }
+    case kThreshold: {
+      float* val = reinterpret_cast<float*>(pay);
+      int* idx = reinterpret_cast<int*>(pay + (size_t)a.k * 4);
+      long long m = 0;
+      for (long long i = 0; i < n && m < a.k; ++i) {
+        const float ax = std::fabs(x[i]);
+        if (a.strict ? ax > a.threshold : ax >= a.threshold) {
+          idx[m] = (int)i;
+          val[m] = x[i];
+          if (a.acc) a.acc[i] = 0.f;
+          ++m;
+        }
+      }
+      *slot.count() = (uint64_t)m;   // what did not fit stays in the accumulator
+      break;
+    }
+    case kQSGD: {
+      if (a.quantum < 1 || a.quantum > 127) return kBadArgument;
+      float* norms = reinterpret_cast<float*>(pay);
+      signed char* codes = reinterpret_cast<signed char*>(pay + (size_t)groups128(n) * 4);
+      for (long long b = 0; b < groups128(n); ++b) {
+        const long long lo = b * 128, hi = std::min(n, lo + 128);
+        float sq = 0.f;
+        for (long long i = lo; i < hi; ++i) sq += x[i] * x[i];
+        const float norm = std::sqrt(sq);
+        norms[b] = norm;
+        const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f, dq = norm / (float)a.quantum;
+        for (long long g4 = lo; g4 < hi; g4 += 4) {
+          const Philox4 r = philox_group((uint64_t)(g4 >> 2), a.step, 0u, a.seed);
+          const unsigned rw[4] = {r.x, r.y, r.z, r.w};
+          for (int j = 0; j < 4 && g4 + j < hi; ++j) {
+            const long long i = g4 + j;
+            const float lf = qn * std::fabs(x[i]), fl = std::floor(lf);
+            float level = fl + ((u01(rw[j]) < lf - fl) ? 1.f : 0.f);
+            level = std::min(level, 127.f);
+            const int code = x[i] < 0.f ? -(int)level : (int)level;
+            codes[i] = (signed char)code;
+            if (a.acc) a.acc[i] = x[i] - dq * (float)code;
+          }
+        }
+      }
+      break;
+    }
+    case kSign:
+    case kEFSign: {
+      unsigned* bits = reinterpret_cast<unsigned*>(pay);
+      float mean = 0.f;
+      if (a.codec == kEFSign) {
+        double s = 0.0;
+        for (long long i = 0; i < n; ++i) s += std::fabs(x[i]);
+        mean = n ? (float)(s / (double)n) : 0.f;
+        *slot.scalar(0) = mean;
+      }
+      std::vector<float> mbuf;
+      const float* enc = x;
+      if (a.codec == kSign && a.mom) {   // signum: the sign of the momentum
+        for (long long i = 0; i < n; ++i)
+          a.mom[i] = a.first_step ? x[i] : (1.f - a.mom_beta) * x[i] + a.mom_beta * a.mom[i];
+        enc = a.mom;
+      }
+      for (long long w = 0; w < words32(n); ++w) {
+        unsigned word = 0;
+        for (int j = 0; j < 32 && w * 32 + j < n; ++j)
+          if (enc[w * 32 + j] >= 0.f) word |= 1u << j;
+        bits[w] = word;
+      }
+      if (a.acc) {
+        const float mag = a.codec == kEFSign ? mean : 1.f;
+        for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - (enc[i] >= 0.f ? mag : -mag);
+      }
+      break;
+    }
+    case kDense: {
+      std::memcpy(pay, x, (size_t)n * 4);
+      if (a.acc) std::memset(a.acc, 0, (size_t)n * 4);
+      break;
+    }
+    default:
+      return kBadArgument;
+  }
+  return kOk;
+}
+
+// ---- decode one rank's slot into the running sum (called in rank order: the sum has one fixed order) ----
+unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes) {
+  const long long n = a.n;
+  const char* pay = slot.payload();
+  switch (a.codec) {
+    case kTopK:
+    case kThreshold: {
+      const uint64_t m = *slot.count();
+      if (m > (uint64_t)a.k) return kBadArgument;
+      const float* val = reinterpret_cast<const float*>(pay);
+      const int* idx = reinterpret_cast<const int*>(pay + (size_t)a.k * 4);
+      for (uint64_t j = 0; j < m; ++j) {
+        if (idx[j] < 0 || idx[j] >= n) return kBadArgument;   // a corrupt index is reported, never followed
+        sum[idx[j]] += val[j];
+      }
+      break;
+    }
+    case kQSGD: {
+      const float* norms = reinterpret_cast<const float*>(pay);
+      const signed char* codes = reinterpret_cast<const signed char*>(pay + (size_t)groups128(n) * 4);
+      for (long long i = 0; i < n; ++i) sum[i] += norms[i >> 7] / (float)a.quantum * (float)codes[i];
+      break;
+    }
+    case kSign:
+    case kEFSign: {
+      const unsigned* bits = reinterpret_cast<const unsigned*>(pay);
+      const float mean = *slot.scalar(0);
+      for (long long i = 0; i < n; ++i) {
+        const bool bit = (bits[i >> 5] >> (i & 31)) & 1u;
+        if (a.codec == kSign) votes[i] += bit ? 1 : -1;
+        else sum[i] += bit ? mean : -mean;
+      }
+      break;
+    }
+    case kDense: {
+      const float* v = reinterpret_cast<const float*>(pay);
+      for (long long i = 0; i < n; ++i) sum[i] += v[i];
+      break;
+    }
+    default:
+      return kBadArgument;
+  }
+  return kOk;
+}
+
+}  // namespace
+
+size_t slot_bytes(int codec, long long n, long long k) {
+  size_t b = kSlotHeaderBytes;
+  switch (codec) {
+    case kTopK:
+    case kThreshold: b += (size_t)k * 8; break;
+    case kQSGD: b += (size_t)groups128(n) * 4 + (size_t)n; break;
+    case kSign:
+    case kEFSign: b += (size_t)words32(n) * 4; break;
+    default: b += (size_t)n * 4; break;
+  }
+  return (b + 63) / 64 * 64;
+}
+
+unsigned exchange(const Channel& ch, const Args& a) {
+  if (ch.world < 1 || ch.world > kMaxWorld || ch.rank < 0 || ch.rank >= ch.world || a.n < 0 || a.seq < 1 || !a.g ||
+      !a.out)
+    return kBadArgument;
+  char* mine = ch.heap[ch.rank];
+  const StatusBlock st{reinterpret_cast<unsigned*>(mine + ch.status_off)};
+  if (st.failed()) return st.code();   // a failed channel stays failed until it is reset
+  const unsigned parity = (unsigned)(a.seq & 1);
+  const SlotView my_slot{mine + ch.slot_off[parity]};
+
+  if (a.phases & kCompress) {
+    // the slot of this parity was last used by sequence seq - 2: every peer must have read it
+    if (a.seq > 2) {
+      const uint64_t* ack = reinterpret_cast<const uint64_t*>(mine + ch.ack_off);
+      for (int p = 0; p < ch.world; ++p)
+        if (p != ch.rank && !wait_flag_ge(ack + p, a.seq - 2, ch.timeout_ns, st, kTimeoutPeerAck, (unsigned)p))
+          return st.code();
+    }
+    const unsigned rc = compress(a, my_slot, ch.slot_bytes);
+    if (rc != kOk) {
+      st.fail(rc, 0, (unsigned)a.seq);
+      return st.code();
+    }
+  }
+
+  if (a.phases & kPublish) {
+    for (int p = 0; p < ch.world; ++p)
+      store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ready_off) + ch.rank, a.seq);
+  }
+
+  if (a.phases & kExchange) {
+    std::vector<float> sum((size_t)a.n, 0.f);
+    std::vector<int> votes(a.codec == kSign ? (size_t)a.n : 0, 0);
+    const uint64_t* ready = reinterpret_cast<const uint64_t*>(mine + ch.ready_off);
+    for (int p = 0; p < ch.world; ++p) {
+      if (!wait_flag_ge(ready + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+      const SlotView peer{ch.heap[p] + ch.slot_off[parity]};
+      const unsigned rc = accumulate(a, peer, sum.data(), votes.data());
+      if (rc != kOk) {
+        st.fail(rc, (unsigned)p, (unsigned)a.seq);
+        return st.code();
+      }
+    }
+    // every slot of this sequence has been read: the peers may reuse theirs
+    for (int p = 0; p < ch.world; ++p)
+      if (p != ch.rank) store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ack_off) + ch.rank, a.seq);
+    if (a.codec == kSign) {
+      for (long long i = 0; i < a.n; ++i) a.out[i] = votes[i] >= 0 ? 1.f : -1.f;
+    } else if (a.codec == kEFSign) {
+      for (long long i = 0; i < a.n; ++i) a.out[i] = sum[i] / a.lr;
+    } else {
+      for (long long i = 0; i < a.n; ++i) a.out[i] = sum[i] * a.scale;
+    }
+  }
+  return kOk;
+}
+
+void* heap_create(const char* name, size_t bytes) {
+  const int fd = shm_open(name, O_CREAT | O_RDWR | O_TRUNC, 0600);
+  if (fd < 0) return nullptr;
+  if (ftruncate(fd, (off_t)bytes) != 0) {
+    close(fd);
+    shm_unlink(name);
+    return nullptr;
+  }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) {
+    shm_unlink(name);
+    return nullptr;
+  }
+  return p;   // a fresh shared-memory object reads as zeros
+}
+
+void* heap_open(const char* name, size_t bytes) {
+  const int fd = shm_open(name, O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  struct stat sb;
+  if (fstat(fd, &sb) != 0 || (size_t)sb.st_size < bytes) {
+    close(fd);
+    return nullptr;
+  }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  return p == MAP_FAILED ? nullptr : p;
+}
+
+int heap_close(void* base, size_t bytes) { return munmap(base, bytes); }
+int heap_unlink(const char* name) { return shm_unlink(name); }
+
+}  // namespace host
+}  // namespace grace

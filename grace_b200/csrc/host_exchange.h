@@ -1,0 +1,84 @@
+// Host engine of the exchange protocol: the state machine of the fused GPU
+// kernels (sequence-numbered ready / ack flags, two send slots keyed by
+// sequence parity, bounded waits that end in a status block) run by CPU ranks
+// over POSIX shared memory.  Every rank owns one shared-memory segment that all
+// other ranks of the host map, so "heap[r] + offset" addresses any rank's flags
+// and slots exactly as the kernels address the peers' device heaps.
+//
+// It serves CPU tensors behind the same communicator API, and it lets the
+// protocol (slot reuse, late or missing peers, recovery) be exercised among
+// real concurrent ranks - processes or threads - without a GPU.
+// The reference has no counterpart: its CPU ranks only meet inside Gloo calls
+// (grace_dl/dist/communicator/allgather.py:8-45).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace grace {
+namespace host {
+
+constexpr int kMaxWorld = 16;
+constexpr size_t kSlotHeaderBytes = 64;   // [0] u64 entry count, [8] f32 scalar, [12] f32 scalar
+
+enum Codec : int {
+  kTopK = 0,        // k largest magnitudes (ties: lowest index), values + int32 indices
+  kThreshold = 1,   // |x| >= threshold (strict: >), at most `cap` entries, the rest stays in the residual
+  kQSGD = 2,        // int8 levels + one fp32 norm per 128 elements, Philox stochastic rounding
+  kSign = 3,        // 1 bit per element, majority vote (ties -> +1)
+  kEFSign = 4,      // 1 bit per element + mean |x|, sum of mean * sign divided by lr
+  kDense = 5,       // no compression: sum of the ranks' tensors
+};
+
+enum Phase : int { kCompress = 1, kPublish = 2, kExchange = 4, kAll = 7 };
+
+// Same codes as the device status block (common.cuh).
+enum Code : unsigned { kOk = 0, kTimeoutPeerReady = 2, kTimeoutPeerAck = 3, kSlotOverflow = 4, kBadArgument = 5 };
+
+// Where a channel lives inside every rank's heap (identical offsets on all ranks).
+struct Channel {
+  int rank, world;
+  char* heap[kMaxWorld];
+  uint64_t ready_off;    // u64[kMaxWorld]: ready[p] = last sequence rank p published to me
+  uint64_t ack_off;      // u64[kMaxWorld]: ack[p]   = last sequence rank p finished reading from me
+  uint64_t status_off;   // unsigned[8]: code, detail, seq (first error wins)
+  uint64_t slot_off[2];  // send slots, used alternately (sequence parity)
+  uint64_t slot_bytes;
+  uint64_t timeout_ns;
+};
+
+struct Args {
+  int codec, phases;
+  uint64_t seq;          // 1, 2, 3, ... identical on all ranks
+  const float* g;        // gradient [n]
+  float* acc;            // error-feedback accumulator [n] or null
+  float* mom;            // signum momentum [n] or null
+  float* out;            // aggregate [n] (may alias g)
+  long long n;
+  long long k;           // kTopK: entries; kThreshold: slot capacity
+  float beta, gamma;     // acc = beta * acc + gamma * g
+  float scale;           // multiplies the sum (1 / W for averaging codecs)
+  float threshold;
+  int strict;            // kThreshold: > instead of >=
+  float lr;              // kEFSign
+  float mom_beta;        // kSign with momentum
+  int first_step;
+  int quantum;           // kQSGD levels (< 128)
+  uint64_t seed;
+  unsigned step;
+};
+
+size_t slot_bytes(int codec, long long n, long long k);
+
+// Runs the phases named by args.phases; returns the status code (0 = ok).  On a timeout the code, the peer and
+// the sequence number are also left in the status words of this rank's heap.
+unsigned exchange(const Channel& ch, const Args& args);
+
+// Shared-memory segments.  create() makes (or truncates) and maps the segment `name`, zero filled; open() maps an
+// existing one of at least `bytes`; both return nullptr on failure with errno set.
+void* heap_create(const char* name, size_t bytes);
+void* heap_open(const char* name, size_t bytes);
+int heap_close(void* base, size_t bytes);
+int heap_unlink(const char* name);
+
+}  // namespace host
+}  // namespace grace

@@ -105,6 +105,13 @@ def grace_from_params(params: Dict[str, Any]):
         raise NotImplementedError(comm_name)
     comp = _COMPRESSORS[comp_name](params)
     mem = _MEMORIES[mem_name](params, comp)
+    if params.get("host_protocol", False):
+        # CPU ranks: the fused exchange protocol over POSIX shared memory (csrc/host_exchange.cpp)
+        from .communicator.host import HostExchange
+
+        return HostExchange(comp, mem, _world(params), world=params.get("host_world"), group=params.get("group"),
+                            seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
+                            arena_mb=params.get("arena_mb", 16), store=params.get("store"))
     if params.get("fused", False) or comm_name == "fused":
         from .communicator.fused import FusedExchange
 

@@ -1,0 +1,368 @@
+"""The host engine of the exchange protocol (``csrc/host_exchange.cpp``): CPU ranks over POSIX shared memory.
+
+Ranks are threads of this process (``ThreadWorld``: the native call releases the interpreter lock, so they run
+and wait concurrently) or gloo processes.  Checked: every codec against a PyTorch restatement, the error-feedback
+identity, slot reuse under a slow peer, both time-outs (a peer that never publishes, a peer that never reads),
+recovery with the error-feedback state kept, checkpoint round trip.
+"""
+import os
+import sys
+import time
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from grace_b200 import compressor as C_  # noqa: E402
+from grace_b200 import memory as M_  # noqa: E402
+from grace_b200.communicator.host import HostExchange, ThreadWorld  # noqa: E402
+from grace_b200.ops.exchange import GraceCommError  # noqa: E402
+
+
+def _grads(world, n, steps, scale=1e-3):
+    return [[torch.randn(n, generator=torch.Generator().manual_seed(100 * s + r)) * scale for r in range(world)]
+            for s in range(steps)]
+
+
+def _run_ranks(world, make, grads, name="w", timeout_ms=5000.0, hook=None):
+    """Every rank steps through ``grads[s][rank]``; returns per-rank lists of outputs and the communicators."""
+    tw = ThreadWorld(world)
+
+    def body(view):
+        comp, mem = make()
+        grc = HostExchange(comp, mem, world, world=view, timeout_ms=timeout_ms)
+        outs = []
+        for s, per_rank in enumerate(grads):
+            if hook is not None:
+                hook(view.rank, s)
+            outs.append(grc.step(per_rank[view.rank].clone(), name))
+        return outs, grc
+
+    res = tw.run(body)
+    return [r[0] for r in res], [r[1] for r in res]
+
+
+def _topk_dense(x, k):
+    idx = torch.topk(x.abs(), k, sorted=False).indices
+    out = torch.zeros_like(x)
+    out[idx] = x[idx]
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_topk_residual_matches_restatement(world):
+    n, ratio, steps = 10000, 0.01, 4
+    grads = _grads(world, n, steps)
+    outs, grcs = _run_ranks(world, lambda: (C_.TopKCompressor(ratio), M_.ResidualMemory()), grads)
+    k = max(1, int(n * ratio))
+    res = [torch.zeros(n) for _ in range(world)]
+    for s in range(steps):
+        want = torch.zeros(n)
+        for r in range(world):
+            acc = res[r] + grads[s][r]
+            sent = _topk_dense(acc, k)
+            res[r] = acc - sent
+            want += sent
+        want /= world
+        for r in range(world):
+            torch.testing.assert_close(outs[r][s], want, rtol=1e-6, atol=1e-9)
+    for r in range(world):   # error-feedback state equals the restatement's residual
+        torch.testing.assert_close(grcs[r].state_dict()["memory"]["residuals"]["w"], res[r], rtol=1e-6, atol=1e-9)
+        assert grcs[r].stats()["compression_ratio"] > 40
+
+
+def test_topk_ties_pick_lowest_indices():
+    x = torch.ones(1000)
+    outs, _ = _run_ranks(1, lambda: (C_.TopKCompressor(0.01), M_.NoneMemory()), [[x]])
+    assert outs[0][0].nonzero().flatten().tolist() == list(range(10))
+
+
+def test_threshold_overflow_stays_in_residual():
+    n = 4096
+    x = torch.full((n,), 0.5)
+    tw = ThreadWorld(1)
+
+    def body(view):
+        grc = HostExchange(C_.ThresholdCompressor(0.1), M_.ResidualMemory(), 1, world=view, max_ratio=0.25)
+        out = grc.step(x.clone(), "t")
+        return out, grc.state_dict()["memory"]["residuals"]["t"]
+
+    out, res = tw.run(body)[0]
+    assert int((out != 0).sum()) == n // 4            # the slot holds a quarter of the elements
+    torch.testing.assert_close(out + res, x)          # what did not fit is kept for the next step
+
+
+@pytest.mark.parametrize("world", [1, 3])
+def test_qsgd_bound_identity_and_unbiasedness(world):
+    n, q = 5000, 64
+    grads = _grads(world, n, 2)
+    outs, grcs = _run_ranks(world, lambda: (C_.QSGDCompressor(q, 128), M_.ResidualMemory()), grads)
+    for s in range(2):
+        for r in range(1, world):
+            assert torch.equal(outs[r][s], outs[0][s])                   # identical on every rank
+    # first step: the decode error of an element is below one level of its bucket (norm / q), summed over ranks
+    pad = (-n) % 128
+    stacked = torch.nn.functional.pad(torch.stack(grads[0]), (0, pad)).view(world, -1, 128)
+    level = (stacked.norm(dim=2) / q).sum(0).repeat_interleave(128)[:n]
+    err = (outs[0][0] * world - sum(grads[0])).abs()
+    assert bool((err <= level * 1.001 + 1e-9).all()), float((err - level).max())
+    # error feedback: after two steps, sent_0 + sent_1 + residual = g_0 + g_1 on every rank; summed over the
+    # ranks the left side is W * (out_0 + out_1) + sum of the residuals
+    res = sum(g.state_dict()["memory"]["residuals"]["w"] for g in grcs)
+    torch.testing.assert_close((outs[0][0] + outs[0][1]) * world + res, sum(grads[0]) + sum(grads[1]),
+                               rtol=1e-4, atol=1e-7)
+    # unbiased over many draws (different tensor names give different Philox keys)
+    x = torch.randn(2048, generator=torch.Generator().manual_seed(7)) * 1e-3
+    tw = ThreadWorld(1)
+
+    def body(view):
+        grc = HostExchange(C_.QSGDCompressor(q, 128), M_.NoneMemory(), 1, world=view)
+        return torch.stack([grc.step(x.clone(), "n%d" % i) for i in range(300)]).mean(0)
+
+    mean = tw.run(body)[0]
+    one_level = float(x.view(-1, 128).norm(dim=1).max()) / q
+    assert float((mean - x).abs().max()) < 4 * 0.5 * one_level / 300 ** 0.5
+
+
+def test_qsgd_matches_numpy_philox_restatement():
+    from grace_b200.communicator.host import _name_seed
+    from grace_b200.utils import philox
+
+    n, q = 1024, 64
+    x = torch.randn(n, generator=torch.Generator().manual_seed(3)) * 1e-2
+    outs, _ = _run_ranks(1, lambda: (C_.QSGDCompressor(q, 128), M_.NoneMemory()), [[x]], name="layer.weight")
+    xb = x.view(-1, 128)
+    norms = torch.stack([b.pow(2).sum(dtype=torch.float32).sqrt() for b in xb])   # fp32, as the engine sums
+    u = torch.from_numpy(philox.uniform(n, _name_seed(0, "layer.weight"), 0, 0)).view(-1, 128)
+    lf = (q / norms)[:, None] * xb.abs()
+    level = torch.floor(lf) + (u < lf - torch.floor(lf)).float()
+    want = (norms / q)[:, None] * level * torch.sign(xb)
+    diff = (outs[0][0].view(-1, 128) - want).abs()
+    # the engine adds squares one after the other, torch in a tree: a norm may differ in its last bit, which moves
+    # a decoded value by an ulp and, once in a while, a rounding decision by one level
+    one_level = (norms / q)[:, None].expand_as(diff)
+    assert float((diff > 1e-7).float().mean()) < 0.01
+    assert bool((diff <= one_level * 1.001).all())
+
+
+@pytest.mark.parametrize("world", [1, 3, 4])
+def test_sign_majority_vote(world):
+    n = 3000
+    grads = _grads(world, n, 2)
+    outs, _ = _run_ranks(world, lambda: (C_.SignSGDCompressor(), M_.NoneMemory()), grads)
+    for s in range(2):
+        votes = sum(torch.where(grads[s][r] >= 0, 1, -1) for r in range(world))
+        want = torch.where(votes >= 0, 1.0, -1.0)     # ties go to +1
+        for r in range(world):
+            assert torch.equal(outs[r][s], want)
+
+
+def test_signum_momentum_state():
+    n, beta = 2000, 0.9
+    grads = _grads(2, n, 3)
+    outs, grcs = _run_ranks(2, lambda: (C_.SignumCompressor(beta), M_.NoneMemory()), grads)
+    m = [None, None]
+    for s in range(3):
+        for r in range(2):
+            m[r] = grads[s][r].clone() if s == 0 else (1 - beta) * grads[s][r] + beta * m[r]
+        votes = sum(torch.where(m[r] >= 0, 1, -1) for r in range(2))
+        assert torch.equal(outs[0][s], torch.where(votes >= 0, 1.0, -1.0))
+    torch.testing.assert_close(grcs[1].state_dict()["compressor"]["momentums"]["w"], m[1])
+
+
+def test_efsign_scaled_sum_and_memory():
+    n, lr, world = 4000, 0.1, 2
+    grads = _grads(world, n, 3)
+    outs, grcs = _run_ranks(world, lambda: (C_.EFSignSGDCompressor(lr), M_.EFSignSGDMemory(lr)), grads)
+    res = [torch.zeros(n) for _ in range(world)]
+    for s in range(3):
+        want = torch.zeros(n)
+        for r in range(world):
+            acc = grads[s][r].clone() if s == 0 else res[r] + lr * grads[s][r]
+            dec = acc.abs().mean() * torch.where(acc >= 0, 1.0, -1.0)
+            res[r] = acc - dec
+            want += dec
+        torch.testing.assert_close(outs[0][s], want / lr, rtol=1e-5, atol=1e-8)
+        assert torch.equal(outs[0][s], outs[1][s])
+    torch.testing.assert_close(grcs[0].state_dict()["memory"]["residuals"]["w"], res[0], rtol=1e-5, atol=1e-8)
+
+
+def test_dense_mean():
+    grads = _grads(4, 777, 2)
+    outs, _ = _run_ranks(4, lambda: (C_.NoneCompressor(), M_.NoneMemory()), grads)
+    for s in range(2):
+        torch.testing.assert_close(outs[2][s], sum(grads[s]) / 4, rtol=1e-6, atol=1e-9)
+
+
+def test_slot_reuse_with_a_slow_peer():
+    """Rank 1 lags behind in every step: rank 0 must wait for its acknowledgement before it overwrites a slot,
+    and for its data before it decodes; eight steps use each slot four times."""
+    n, world, steps = 2048, 2, 8
+    grads = _grads(world, n, steps)
+
+    def hook(rank, s):
+        if rank == 1:
+            time.sleep(0.03)
+
+    outs, _ = _run_ranks(world, lambda: (C_.NoneCompressor(), M_.NoneMemory()), grads, hook=hook)
+    for s in range(steps):
+        torch.testing.assert_close(outs[0][s], (grads[s][0] + grads[s][1]) / 2, rtol=1e-6, atol=1e-9)
+        assert torch.equal(outs[0][s], outs[1][s])
+
+
+def test_peer_that_never_publishes_times_out_then_recovery():
+    """Rank 1 skips the publish of step 1 (host-side injection).  Rank 0's bounded wait gives up and reports the
+    peer; after recover() on both ranks the next exchange is healthy and the error feedback went on untouched."""
+    from grace_b200.utils.faults import FaultPlan
+
+    n, world = 4096, 2
+    grads = _grads(world, n, 3)
+    tw = ThreadWorld(world)
+
+    def body(view):
+        grc = HostExchange(C_.TopKCompressor(0.05), M_.ResidualMemory(), world, world=view, timeout_ms=300.0)
+        grc._faults = FaultPlan("skip_publish", rank=1, step=1)
+        out0 = grc.step(grads[0][view.rank].clone(), "w")
+        err = None
+        t0 = time.time()
+        try:
+            grc.step(grads[1][view.rank].clone(), "w")
+        except GraceCommError as e:
+            err = e
+        waited = time.time() - t0
+        with pytest.raises(GraceCommError):
+            grc.check()                        # the channel stays failed until it is reset
+        view.barrier()                         # what agree() does through a store among processes
+        grc.recover()
+        grc._faults = FaultPlan()
+        res_before = grc.state_dict()["memory"]["residuals"]["w"].clone()
+        out2 = grc.step(grads[2][view.rank].clone(), "w")
+        grc.check()
+        return out0, err, waited, res_before, out2
+
+    r0, r1 = tw.run(body)
+    assert isinstance(r0[1], GraceCommError) and r0[1].code == 2 and r0[1].detail == 1 and r0[1].seq == 2
+    assert 0.25 < r0[2] < 5.0
+    # rank 1 saw its own flag missing as well (it reads its own slot through the same flags)
+    assert isinstance(r1[1], GraceCommError) and r1[1].code == 2
+    assert torch.equal(r0[4], r1[4])           # the exchange after the recovery agrees on both ranks
+    k = int(n * 0.05)
+    want = sum(_topk_dense(rb + g, k) for rb, g in ((r0[3], grads[2][0]), (r1[3], grads[2][1]))) / 2
+    torch.testing.assert_close(r0[4], want, rtol=1e-6, atol=1e-9)
+
+
+def test_peer_that_never_reads_blocks_slot_reuse():
+    """send_step twice is fine (two slots); the third needs the peer's acknowledgement of the first."""
+    n, world = 512, 2
+    tw = ThreadWorld(world)
+
+    def body(view):
+        grc = HostExchange(C_.NoneCompressor(), M_.NoneMemory(), world, world=view, timeout_ms=200.0)
+        x = torch.ones(n)
+        grc.prepare([("w", x)])                # heaps are created by all ranks together
+        err = None
+        if view.rank == 0:
+            grc.send_step(x, "w")
+            grc.send_step(x, "w")
+            try:
+                grc.send_step(x, "w")
+            except GraceCommError as e:
+                err = e
+        view.barrier()
+        return err
+
+    e0, _ = tw.run(body)
+    assert isinstance(e0, GraceCommError) and e0.code == 3 and e0.detail == 1
+
+
+def test_split_phase_equals_step_and_checkpoint_round_trip():
+    n = 3000
+    grads = _grads(1, n, 4)
+    tw = ThreadWorld(1)
+
+    def body(view):
+        make = lambda: HostExchange(C_.TopKCompressor(0.02), M_.ResidualMemory(0.9, 1.0), 1, world=view)  # noqa: E731
+        a, b = make(), make()
+        for s in range(2):
+            h, ctx = a.send_step(grads[s][0].clone(), "p")
+            out_a = a.receive_step(h, ctx)
+            out_b = b.step(grads[s][0].clone(), "p")
+            assert torch.equal(out_a, out_b)
+        c = make()
+        c.load_state_dict(a.state_dict())
+        for s in range(2, 4):
+            assert torch.equal(a.step(grads[s][0].clone(), "p"), c.step(grads[s][0].clone(), "p"))
+        for g in (a, b, c):
+            g.close()
+        return True
+
+    assert tw.run(body) == [True]
+
+
+def test_unsupported_pairs_use_the_library_path():
+    grc = HostExchange(C_.TernGradCompressor(), M_.NoneMemory(), 1)
+    x = torch.randn(100)
+    assert not grc.supported(x)
+    assert grc.step(x, "t").shape == x.shape
+
+
+def _gloo_ranks(rank, world):
+    from grace_b200 import grace_from_params
+
+    grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                             "compress_ratio": 0.02, "world_size": world, "host_protocol": True, "timeout_ms": 20000})
+    lib = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                             "compress_ratio": 0.02, "world_size": world})
+    worst = 0.0
+    for s in range(3):
+        g = torch.randn(5000, generator=torch.Generator().manual_seed(10 * s + rank))
+        worst = max(worst, float((grc.step(g.clone(), "w") - lib.step(g.clone(), "w")).abs().max()))
+    grc.close()
+    return worst
+
+
+def _gloo_failure(rank, world):
+    import torch.distributed as dist
+
+    from grace_b200 import grace_from_params
+    from grace_b200.utils.faults import FaultPlan
+
+    store = dist.distributed_c10d._get_default_store()
+    grc = grace_from_params({"compressor": "efsignsgd", "memory": "efsignsgd", "communicator": "allgather", "lr": 0.1,
+                             "world_size": world, "host_protocol": True, "timeout_ms": 400, "store": store})
+    grc._faults = FaultPlan("skip_publish", rank=1, step=1)
+    g = [torch.randn(3000, generator=torch.Generator().manual_seed(10 * s + rank)) for s in range(3)]
+    grc.step(g[0].clone(), "w")
+    failed = None
+    try:
+        grc.step(g[1].clone(), "w")
+    except GraceCommError as e:
+        failed = e
+    bad = grc.agree(failed)                    # every rank learns who failed, through the store
+    if bad:
+        grc.recover()
+    grc._faults = FaultPlan()
+    out = grc.step(g[2].clone(), "w")
+    grc.check()
+    grc.close()
+    return (failed.code if failed else 0, bad, float(out.sum()))
+
+
+def test_gloo_processes_agree_and_recover():
+    from test_dist_cpu import _free_port, _run
+
+    _free_port.port = _free_port()
+    res = _run(_gloo_failure, world=2)
+    assert res[0][0] == 2 and res[0][1] == [0, 1] and res[1][1] == [0, 1], res
+    assert res[0][2] == res[1][2]
+
+
+def test_gloo_processes_match_library_allgather():
+    from test_dist_cpu import _free_port, _run
+
+    _free_port.port = _free_port()
+    res = _run(_gloo_ranks, world=2)
+    assert max(res.values()) < 1e-6, res
