@@ -188,6 +188,8 @@ class _HostPlan:
         self.ack_off = self.ready_off + C.HOST_MAX_WORLD * 8
         self.status_off = heap.alloc(64)
         self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+        # the key of the random stream: as the GPU path derives it for a single tensor (name and padded length)
+        self.seed = _name_seed(owner.seed, name + str((numel + 127) // 128 * 128))
         self.seq = 0          # sequence number of the last exchange started
         self.steps = 0
         self.acc = torch.zeros(numel, dtype=torch.float32) if owner._needs_acc else None
@@ -312,7 +314,7 @@ class HostExchange(Communicator):
             (1.0 / self.world_size) if comp.average else 1.0, float(getattr(comp, "threshold", 0.0)),
             int(bool(getattr(comp, "strict", False))), float(getattr(comp, "learning_rate", 1.0)),
             float(getattr(comp, "momentum", 0.0)), int(plan.steps == 0), int(getattr(comp, "quantum_num", 0)),
-            _name_seed(self.seed, plan.name), plan.steps)
+            plan.seed, plan.steps)
         if rc != 0:
             st = plan.status()
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)

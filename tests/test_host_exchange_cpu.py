@@ -136,7 +136,7 @@ def test_qsgd_matches_numpy_philox_restatement():
     outs, _ = _run_ranks(1, lambda: (C_.QSGDCompressor(q, 128), M_.NoneMemory()), [[x]], name="layer.weight")
     xb = x.view(-1, 128)
     norms = torch.stack([b.pow(2).sum(dtype=torch.float32).sqrt() for b in xb])   # fp32, as the engine sums
-    u = torch.from_numpy(philox.uniform(n, _name_seed(0, "layer.weight"), 0, 0)).view(-1, 128)
+    u = torch.from_numpy(philox.uniform(n, _name_seed(0, "layer.weight" + str(n)), 0, 0)).view(-1, 128)
     lf = (q / norms)[:, None] * xb.abs()
     level = torch.floor(lf) + (u < lf - torch.floor(lf)).float()
     want = (norms / q)[:, None] * level * torch.sign(xb)
