@@ -105,6 +105,11 @@ size_t sparse_slot_bytes(unsigned cap, long long tiled_total = 0);
 size_t sparse_smem_bytes();
 int sparse_max_grid(int device, int sm_limit);
 cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t stream);
+// Single-CTA variant for one tensor of at most 8192 elements (sparse_small.cu): same arguments, phases, flags and
+// slot header; needs none of the scratch areas.  launch_sparse_exchange() uses it whenever it applies, unless the
+// environment variable GRACE_SMALL_KERNEL is "0".
+bool sparse_small_applies(const SparseArgs& a);
+cudaError_t launch_sparse_small(const SparseArgs& a, cudaStream_t stream);
 
 // ----------------------------------------------------------------- quant ----
 enum Codec : int {

@@ -38,6 +38,8 @@
 // (radixtopk_cuda/rdxtopk_cuda.cu:459-529), the W dense decompressions of
 // communicator/allgather.py:40-45, memory/residual.py:18-20 and
 // memory/dgc.py:21-39.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "exchange.h"
 #include "philox.cuh"
@@ -1016,13 +1018,18 @@ int sparse_max_grid(int device, int sm_limit) {
 }
 
 cudaError_t launch_sparse_exchange(const SparseArgs& a, int grid, cudaStream_t stream) {
+  if ((a.phases & kPhaseClip) && (!a.clip_off || !a.clip_sq)) return cudaErrorInvalidValue;
+  static const bool small_enabled = [] {
+    const char* e = getenv("GRACE_SMALL_KERNEL");
+    return !(e && e[0] == '0');
+  }();
+  if (small_enabled && sparse_small_applies(a)) return launch_sparse_small(a, stream);
   cudaError_t err = cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream);
   if (err != cudaSuccess) return err;
   if (a.phases & kPhaseCompress) {
     err = cudaMemsetAsync(a.state, 0, sizeof(SparseState) * (size_t)(a.nseg + 1), stream);
     if (err != cudaSuccess) return err;
   }
-  if ((a.phases & kPhaseClip) && (!a.clip_off || !a.clip_sq)) return cudaErrorInvalidValue;
   SparseArgs copy = a;
   void* params[] = {&copy};
   const void* fn = a.tile_start ? (const void*)sparse_exchange_kernel<true> : (const void*)sparse_exchange_kernel<false>;
