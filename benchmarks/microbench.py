@@ -103,6 +103,7 @@ def roofline_ms(case, n, world, bw):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="1,4,16,64", help="millions of elements (2^20)")
+    ap.add_argument("--elems", default="", help="further sizes as plain element counts (small tensors), e.g. 256,4096,8192")
     ap.add_argument("--cases", default=",".join(CASES))
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -190,8 +191,9 @@ def main():
 
     rows = []
     for case in args.cases.split(","):
-        for size_m in [int(s) for s in args.sizes.split(",")]:
-            n = size_m << 20
+        sizes = [(int(s), int(s) << 20) for s in args.sizes.split(",") if s]
+        sizes += [(int(e) / float(1 << 20), int(e)) for e in args.elems.split(",") if e]
+        for size_m, n in sizes:
             if case == "powersgd4":
                 # matrices: 16 -> 4096 x 4096, 64 -> 8192 x 8192, 98 -> 4096 x 25088 (the first FC layer of VGG-16)
                 shape = {16: (4096, 4096), 64: (8192, 8192), 98: (4096, 25088)}.get(size_m)
@@ -267,7 +269,7 @@ def main():
             if vranks:                       # emulated ranks share one GPU: nothing crosses a link, HBM is the bound
                 link = 0
                 roof = hbm / (bw * 1e9) * 1e3
-            row = {"case": case, "impl": args.impl, "size_m": size_m, "n_gpus": world, "ms": round(ms, 4),
+            row = {"case": case, "impl": args.impl, "size_m": size_m, "elems": n, "n_gpus": world, "ms": round(ms, 4),
                    "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / ms, 3) if args.impl == "ours" else None,
                    "hbm_bytes": int(hbm), "link_bytes": int(link), "hbm_gbs": bw, "hbm_source": bw_src,
                    "timing": "cuda events, median of %d, max over ranks, L2 flushed" % len(times),

@@ -37,6 +37,7 @@ used by the DDP hook and ``DistributedOptimizer``).
 """
 from __future__ import annotations
 
+import os
 import zlib
 from typing import Dict, List, Optional, Sequence
 
@@ -213,7 +214,7 @@ class FusedExchange(Communicator):
         self.max_ratio = max_ratio
         self.exact = exact
         self.monitor = monitor   # optional utils.faults.HeartbeatMonitor: checked before every launch
-        self.nvtx = True
+        self.nvtx = os.environ.get("GRACE_NVTX", "0") not in ("", "0")   # NVTX range around every exchange
         self.device = None
         self._rank = rank
         self._plans: Dict[tuple, _Plan] = {}

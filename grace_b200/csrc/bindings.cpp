@@ -75,6 +75,30 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
     check(cudaMemsetAsync(ptr<void>(p), value, bytes, reinterpret_cast<cudaStream_t>(stream)), "memset_async");
   });
 
+  // ---- events (plain CUDA events: recording one costs a microsecond; the framework's event objects cost ten) ----
+  m.def("event_create", []() {
+    cudaEvent_t e = nullptr;
+    check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event_create");
+    return reinterpret_cast<uintptr_t>(e);
+  });
+  m.def("event_record", [](uintptr_t e, uintptr_t stream) {
+    check(cudaEventRecord(reinterpret_cast<cudaEvent_t>(e), reinterpret_cast<cudaStream_t>(stream)), "event_record");
+  });
+  m.def("event_query", [](uintptr_t e) {
+    const cudaError_t r = cudaEventQuery(reinterpret_cast<cudaEvent_t>(e));
+    if (r == cudaErrorNotReady) {
+      cudaGetLastError();   // "not ready" is an answer, not an error: it must not linger as the thread's last error
+      return false;
+    }
+    check(r, "event_query");
+    return true;
+  });
+  m.def("event_synchronize", [](uintptr_t e) {
+    py::gil_scoped_release release;
+    check(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(e)), "event_synchronize");
+  });
+  m.def("event_destroy", [](uintptr_t e) { cudaEventDestroy(reinterpret_cast<cudaEvent_t>(e)); });
+
   // ---- sizes / occupancy ----
   m.def("sparse_slot_bytes", &sparse_slot_bytes, pybind11::arg("cap"), pybind11::arg("tiled_total") = 0);
   m.def("sparse_max_grid", &sparse_max_grid);

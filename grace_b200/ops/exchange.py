@@ -141,14 +141,18 @@ class ExchangeChannel:
             self.clip_sq = torch.zeros(max(1, nseg), dtype=torch.float64, device=heap.device)
         self.seq = 0
         self._grids = {}
-        self._events = [None, None]
         self.timeout_ns = int(timeout_ms * 1e6)
         self.sm_limit = sm_limit or 0
         dev = self.device
         self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(32, dtype=torch.int32, device=dev)   # [0..3] error block, [8..] optional phase counters
         self.status_host = torch.zeros(32, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
-        self.status_event: Optional[torch.cuda.Event] = None
+        self.status_event: Optional[int] = None    # event of the last launch (None: nothing launched since a reset)
+        self.status_every = max(1, int(os.environ.get("GRACE_STATUS_EVERY", "8")))   # launches per status copy for poll()
+        self._since_copy = 0
+        self._copy_event: Optional[int] = None     # plain CUDA events (handles), created on first use
+        self._last_event: Optional[int] = None
+        self._copy_pending = False
         # radix-select histograms: first level, hinted second level (zero between launches), then one hint word per
         # segment (the first-level pivot bin of the previous launch, -1 = none; a speed hint only)
         self._hist_segs = max(1, nseg)
@@ -190,27 +194,52 @@ class ExchangeChannel:
 
     # -- error surface ----------------------------------------------------
     def post_status(self):
-        """Queue a copy of the status block to pinned memory (no sync)."""
-        self.status_host.copy_(self.status, non_blocking=True)
-        slot = self.seq & 1                      # two events, reused alternately
-        ev = self._events[slot]
-        if ev is None:
-            ev = self._events[slot] = torch.cuda.Event()
-        ev.record()
-        self.status_event = ev
+        """Mark the launch just queued on the current stream (a plain CUDA event, no sync).  Every
+        ``status_every``-th launch also queues a copy of the status block to pinned memory, which is what ``poll()``
+        looks at; ``check()`` fetches the block itself, so it never depends on those copies.  (A copy and a
+        framework event per launch cost more host time than the launch of a small exchange.)"""
+        C = native()
+        if self._last_event is None:
+            self._last_event = C.event_create()
+        C.event_record(self._last_event, _stream_ptr(self.device.index))
+        self.status_event = self._last_event
+        self._since_copy += 1
+        if self._since_copy >= self.status_every:
+            self._since_copy = 0
+            self.status_host.copy_(self.status, non_blocking=True)
+            if self._copy_event is None:
+                self._copy_event = C.event_create()
+            C.event_record(self._copy_event, _stream_ptr(self.device.index))
+            self._copy_pending = True
 
     def poll(self):
-        """Raise if the last finished launch reported a failure; never blocks."""
-        if self.status_event is not None and self.status_event.query():
+        """Raise if a launch whose status has already reached the host reported a failure; never blocks."""
+        if self._copy_pending and native().event_query(self._copy_event):
+            self._copy_pending = False
             self._raise_if_failed()
 
     def check(self):
-        """Synchronise with the last launch and raise if it failed."""
+        """Synchronise with the last launch, fetch its status block and raise if it failed."""
         if self.status_event is not None:
-            self.status_event.synchronize()
+            C = native()
+            C.event_synchronize(self.status_event)
+            if self._copy_pending:
+                C.event_synchronize(self._copy_event)   # an older copy must not land after the one below
+                self._copy_pending = False
+            self.status_host.copy_(self.status)
+            self._since_copy = 0
             self._raise_if_failed()
         if self.guard:
             self.verify_guards()
+
+    def __del__(self):
+        try:
+            C = native()
+            for ev in (self._last_event, self._copy_event):
+                if ev is not None:
+                    C.event_destroy(ev)
+        except Exception:
+            pass
 
     def verify_guards(self):
         for off in self.guard_off:
@@ -253,13 +282,19 @@ class ExchangeChannel:
         self.quant_stats.zero_()
         self.seq = 0
         self.status_event = None
+        self._since_copy = 0
+        self._copy_pending = False
         if self.status_host is not None:
             self.status_host.zero_()
         torch.cuda.synchronize(self.device)
 
 
-def _stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+def _stream_ptr(device_index: Optional[int] = None) -> int:
+    """Handle of the current stream of a device (the short way: ``torch.cuda.current_stream()`` builds a stream
+    object and resolves the device on every call, ten times the cost)."""
+    if device_index is None:
+        device_index = torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(device_index)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> int:
@@ -340,7 +375,7 @@ def run_sparse(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Ten
         beta, gamma, momentum, threshold, scale, channel.hist.data_ptr(), channel.sparse_state.data_ptr(),
         channel.barrier.data_ptr(), channel.status.data_ptr(), cap, phases, heap.rank, heap.world, seq,
         channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1], grid,
-        _stream_ptr(), channel.cand.data_ptr() if cand_cap else 0,
+        _stream_ptr(channel.device.index), channel.cand.data_ptr() if cand_cap else 0,
         (channel.cand.data_ptr() + 4 * cand_cap) if cand_cap else 0, cand_cap,
         _ptr(kprefix), _ptr(seg_seed), rk_step & 0xFFFFFFFF,
         channel.clip_off if clip else 0, channel.clip_ready_off if clip else 0,
@@ -387,7 +422,7 @@ def run_quant(channel: ExchangeChannel, layout: FlatLayout, segs_dev: torch.Tens
         int(deterministic), int(first_step), beta, gamma, mom_beta, lr, scale, seed & (2 ** 64 - 1), step & 0xFFFFFFFF,
         channel.quant_stats.data_ptr(), channel.barrier.data_ptr(), channel.status.data_ptr(), phases, heap.rank,
         heap.world, seq, channel.timeout_ns, heap.bases, channel.ready_off, channel.ack_off, channel.slot_off[seq & 1],
-        grid, _stream_ptr(), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
+        grid, _stream_ptr(channel.device.index), int(alltoall), channel.ready2_off, recv_local, recv_mc, recv_stride, GRAD_DTYPE[g.dtype],
         int(qsgd_bucket), int(qsgd_nbuckets), channel.slot_bytes if slot_bytes is None else int(slot_bytes),
         channel.pipe.data_ptr() if pipeline else 0, channel.chunk_ready_off if pipeline else 0,
         *(pipeline if pipeline else (0, 0, 0)),
