@@ -9,7 +9,8 @@
 //   * a thread holds 16 consecutive elements in registers (compensated value,
 //     DGC momentum), nothing is re-read from global memory;
 //   * the k-th largest magnitude comes from four radix passes (8 + 8 + 8 + 7
-//     key bits) over a 256-bin shared-memory histogram; among equal keys the
+//     key bits) over 256-bin shared-memory histograms (one per warp, summed
+//     and suffix-scanned by 256 threads); among equal keys the
 //     lowest indices win, so exactly k entries travel and the list is in
 //     index order whatever the timing;
 //   * compaction by a block-wide prefix sum straight into the send slot, the
@@ -39,8 +40,7 @@ constexpr int kSmallMax = kSmallBlock * kSmallPer;     // 8192
 constexpr unsigned kSmallHeaderBytes = 128;            // slot header of sparse_exchange.cu: [0] entries, [1] overflow
 
 struct SmallSmem {
-  float out[kSmallMax];        // the dense output while the ranks' lists are added
-  unsigned hist[256];
+  float out[kSmallMax];        // the dense output while the ranks' lists are added; per-warp histograms before
   unsigned warp_tot[kSmallBlock / 32];
   float warp_max[kSmallBlock / 32];
   unsigned prefix, need, total;
@@ -125,30 +125,47 @@ __global__ void __launch_bounds__(kSmallBlock, 1) sparse_small_kernel(const Spar
       unsigned sel_mask = 0;
       if (a.mode == kSparseTopK) {
         unsigned prefix = 0, need = (unsigned)(seg.k < 1 ? 1 : (seg.k > n ? n : seg.k));
+        // one 256-bin histogram per warp (in the area of the output copy, idle until the exchange): keys of one
+        // tensor share a few exponents, and a single histogram would serialise the whole CTA on those bins
+        unsigned* const whist = reinterpret_cast<unsigned*>(sm.out);
+        static_assert(sizeof(float) * kSmallMax >= sizeof(unsigned) * 256 * (kSmallBlock / 32), "warp histograms do not fit");
 #pragma unroll 1
         for (int pass = 0; pass < 4; ++pass) {
           const int bits = pass == 3 ? 7 : 8;
           const int shift = pass == 3 ? 0 : 23 - 8 * pass;        // position of this pass's digit in the 31-bit key
-          if (tid < 256) sm.hist[tid] = 0;
+          for (int b = tid; b < 256 * (kSmallBlock / 32); b += kSmallBlock) whist[b] = 0;
           __syncthreads();
 #pragma unroll
           for (int e = 0; e < kSmallPer; ++e) {
             if (e < mine) {
               const unsigned key = __float_as_uint(av[e]) & 0x7fffffffu;
-              if (pass == 0 || (key >> (shift + bits)) == prefix) atomicAdd(&sm.hist[(key >> shift) & ((1u << bits) - 1u)], 1u);
+              if (pass == 0 || (key >> (shift + bits)) == prefix)
+                atomicAdd(&whist[warp * 256 + ((key >> shift) & ((1u << bits) - 1u))], 1u);
             }
           }
           __syncthreads();
-          if (tid == 0) {
-            unsigned above = 0;
-            int d = (1 << bits) - 1;
-            for (; d > 0; --d) {                                   // the digit holding the need-th largest key
-              const unsigned c = sm.hist[d];
-              if (above + c >= need) break;
-              above += c;
+          // the digit holding the need-th largest key: thread d < 256 owns bin d and learns how many keys lie in
+          // the bins above it (suffix sums over the lanes, then over the eight warps of bins)
+          unsigned c = 0, incl = 0;
+          if (tid < 256) {
+#pragma unroll
+            for (int w = 0; w < kSmallBlock / 32; ++w) c += whist[w * 256 + tid];
+            incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const unsigned t = __shfl_down_sync(0xffffffffu, incl, o);
+              if (lane + o < 32) incl += t;
             }
-            sm.prefix = (prefix << bits) | (unsigned)d;
-            sm.need = need - above;
+            if (lane == 0) sm.warp_tot[warp] = incl;
+          }
+          __syncthreads();
+          if (tid < 256) {
+            unsigned above = incl - c;
+            for (int w = warp + 1; w < 8; ++w) above += sm.warp_tot[w];
+            if (c && above < need && need <= above + c) {          // true for exactly one bin
+              sm.prefix = (prefix << bits) | (unsigned)tid;
+              sm.need = need - above;
+            }
           }
           __syncthreads();
           prefix = sm.prefix;
