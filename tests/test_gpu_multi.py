@@ -82,6 +82,29 @@ def _body(rank, world, dev):
         dist.all_gather(gathered, got)
         same = all(torch.equal(gathered[0], t) for t in gathered)
         out[comp] = (worst, same)
+    # small tensors one by one (the single-CTA sparse kernel: one plain launch per tensor and rank, real peers):
+    # six steps so that both send slots are reused and the acknowledgements are needed
+    for comp, mem, extra in (("topk", "residual", {"compress_ratio": 0.05}),
+                             ("dgc", "dgc", {"compress_ratio": 0.01, "momentum": 0.9})):
+        fused = grace_from_params({"compressor": comp, "memory": mem, "communicator": "allgather", "world_size": world,
+                                   "fused": True, "timeout_ms": 5000, **extra})
+        lib = grace_from_params({"compressor": comp, "memory": mem, "communicator": "allgather", "world_size": world,
+                                 **extra})
+        if comp == "dgc":
+            lib.compressor.mode = "exact"
+        worst, same = 0.0, True
+        for step in range(6):
+            for numel in (1, 100, 2048, 8192):
+                g = torch.Generator().manual_seed(1000 * step + 10 * rank + numel)
+                x = (torch.randn(numel, generator=g) * 1e-3).to(dev)
+                got = fused.step(x.clone(), "s%d" % numel)
+                ref = lib.step(x.clone(), "s%d" % numel)
+                worst = max(worst, (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-12))
+                gathered = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(gathered, got)
+                same = same and all(torch.equal(gathered[0], t) for t in gathered)
+        fused.check()
+        out["small_" + comp] = (worst, same)
     # pipelined all-gather mode (encode of chunk c + 1 next to the pull of chunk c) against the phase-by-phase
     # kernel: same random streams, same order of the sums, so the same bits, step after step
     layout = FlatLayout.from_named([("a", 250_000), ("b", 64), ("c", 1_234_567)])
