@@ -94,14 +94,37 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
     case kTopK: {
       const long long k = std::min(a.k, n);
       if (k < 1) return kBadArgument;
-      std::vector<int> order(n);
-      std::iota(order.begin(), order.end(), 0);
-      auto larger = [x](int p, int q) {
-        const float ap = std::fabs(x[p]), aq = std::fabs(x[q]);
-        return ap > aq || (ap == aq && p < q);
+      // Radix select as on the GPU: a 4096-bin histogram of the top 12 key bits finds the bin of the k-th largest
+      // magnitude; everything above that bin travels, the bin itself is partitioned (ties: lowest index first).
+      auto key_of = [x](long long i) {
+        uint32_t b;
+        std::memcpy(&b, x + i, 4);
+        return b & 0x7fffffffu;
       };
-      if (k < n) std::nth_element(order.begin(), order.begin() + k, order.end(), larger);
-      std::sort(order.begin(), order.begin() + k);   // ascending indices: the same list whatever the partition did
+      std::vector<uint32_t> hist(4096, 0);
+      for (long long i = 0; i < n; ++i) ++hist[key_of(i) >> 19];
+      long long above = 0;
+      int bin = 4095;
+      for (; bin > 0; --bin) {
+        if (above + hist[bin] >= k) break;
+        above += hist[bin];
+      }
+      std::vector<int> order, cand;
+      order.reserve((size_t)k);
+      cand.reserve(hist[bin]);
+      for (long long i = 0; i < n; ++i) {
+        const uint32_t top = key_of(i) >> 19;
+        if (top > (uint32_t)bin) order.push_back((int)i);
+        else if (top == (uint32_t)bin) cand.push_back((int)i);
+      }
+      const long long need = k - above;
+      auto larger = [&](int p, int q) {
+        const uint32_t kp = key_of(p), kq = key_of(q);
+        return kp > kq || (kp == kq && p < q);
+      };
+      if (need < (long long)cand.size()) std::nth_element(cand.begin(), cand.begin() + need, cand.end(), larger);
+      order.insert(order.end(), cand.begin(), cand.begin() + need);
+      std::sort(order.begin(), order.end());   // ascending indices: the same list whatever the partition did
       float* val = reinterpret_cast<float*>(pay);
       int* idx = reinterpret_cast<int*>(pay + (size_t)a.k * 4);
       for (long long j = 0; j < k; ++j) {
@@ -174,13 +197,13 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
       }
       for (long long w = 0; w < words32(n); ++w) {
         unsigned word = 0;
-        for (int j = 0; j < 32 && w * 32 + j < n; ++j)
-          if (enc[w * 32 + j] >= 0.f) word |= 1u << j;
+        const long long lim = std::min<long long>(32, n - w * 32);
+        for (long long j = 0; j < lim; ++j) word |= (unsigned)(enc[w * 32 + j] >= 0.f) << j;   // no branch: signs are coin flips
         bits[w] = word;
       }
       if (a.acc) {
         const float mag = a.codec == kEFSign ? mean : 1.f;
-        for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - (enc[i] >= 0.f ? mag : -mag);
+        for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - mag * (float)(2 * (int)(enc[i] >= 0.f) - 1);
       }
       break;
     }
@@ -222,10 +245,10 @@ unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes)
     case kEFSign: {
       const unsigned* bits = reinterpret_cast<const unsigned*>(pay);
       const float mean = *slot.scalar(0);
-      for (long long i = 0; i < n; ++i) {
-        const bool bit = (bits[i >> 5] >> (i & 31)) & 1u;
-        if (a.codec == kSign) votes[i] += bit ? 1 : -1;
-        else sum[i] += bit ? mean : -mean;
+      if (a.codec == kSign) {
+        for (long long i = 0; i < n; ++i) votes[i] += 2 * (int)((bits[i >> 5] >> (i & 31)) & 1u) - 1;
+      } else {
+        for (long long i = 0; i < n; ++i) sum[i] += mean * (float)(2 * (int)((bits[i >> 5] >> (i & 31)) & 1u) - 1);
       }
       break;
     }

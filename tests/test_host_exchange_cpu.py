@@ -366,3 +366,93 @@ def test_gloo_processes_match_library_allgather():
     _free_port.port = _free_port()
     res = _run(_gloo_ranks, world=2)
     assert max(res.values()) < 1e-6, res
+
+
+def _train_resnet20(rank, world):
+    """The plumbing configuration (ResNet-20, TopK 1 %, residual memory, all-gather, two gloo ranks, 20 steps)
+    through the host engine and through the library communicator: the same entries travel and the sums are formed
+    in the same order, so the two loss curves coincide."""
+    from grace_b200 import grace_from_params
+    from grace_b200.models import resnet20
+
+    def run(extra):
+        torch.manual_seed(0)
+        model = resnet20()
+        opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+        grc = grace_from_params({"compressor": "topk", "memory": "residual", "communicator": "allgather",
+                                 "compress_ratio": 0.01, "world_size": world, **extra})
+        if hasattr(grc, "prepare"):
+            grc.prepare(list(model.named_parameters()))
+        g = torch.Generator().manual_seed(100 + rank)
+        losses = []
+        for _ in range(20):
+            x = torch.randn(32, 3, 32, 32, generator=g)
+            y = torch.randint(0, 10, (32,), generator=g)
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            for name, p in model.named_parameters():
+                p.grad.copy_(grc.step(p.grad, name))
+            opt.step()
+            losses.append(loss.item())
+        if hasattr(grc, "close"):
+            grc.close()
+        return losses
+
+    return run({}), run({"host_protocol": True, "timeout_ms": 30000})
+
+
+def test_resnet20_topk_host_engine_tracks_the_library_path():
+    from test_dist_cpu import _free_port, _run
+
+    _free_port.port = _free_port()
+    res = _run(_train_resnet20, world=2)
+    lib, host = res[0]
+    assert all(l == l for l in host)
+    assert abs(lib[0] - host[0]) < 1e-5
+    # identical selections and summation order: the curves agree until rounding differences get amplified
+    assert max(abs(a - b) for a, b in zip(lib[:5], host[:5])) < 1e-3
+    assert abs(sum(lib[-5:]) / 5 - sum(host[-5:]) / 5) < 1.0
+
+
+def _optimizer_ranks(rank, world):
+    """Horovod-style wrapper over the host engine: hooks call send_step during backward, step() receives."""
+    from grace_b200 import grace_from_params
+    from grace_b200.parallel import DistributedOptimizer
+
+    def make_model():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(40, 64), torch.nn.ReLU(), torch.nn.Linear(64, 10))
+
+    params = {"compressor": "topk", "memory": "residual", "communicator": "allgather", "compress_ratio": 0.05,
+              "world_size": world, "host_protocol": True, "timeout_ms": 30000}
+    g = torch.Generator().manual_seed(7 + rank)
+    data = [(torch.randn(16, 40, generator=g), torch.randint(0, 10, (16,), generator=g)) for _ in range(5)]
+
+    model = make_model()
+    opt = DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.05), grace=grace_from_params(dict(params)),
+                               named_parameters=model.named_parameters(), always_hook=True)
+    for x, y in data:
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x), y).backward()
+        opt.step()
+
+    ref = make_model()
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.05)
+    grc = grace_from_params(dict(params))
+    grc.prepare(list(ref.named_parameters()))
+    for x, y in data:
+        ropt.zero_grad()
+        torch.nn.functional.cross_entropy(ref(x), y).backward()
+        for name, p in ref.named_parameters():
+            p.grad.copy_(grc.step(p.grad, name))
+        ropt.step()
+    return max(float((a - b).abs().max()) for a, b in zip(model.parameters(), ref.parameters()))
+
+
+def test_distributed_optimizer_over_the_host_engine():
+    from test_dist_cpu import _free_port, _run
+
+    _free_port.port = _free_port()
+    res = _run(_optimizer_ranks, world=2)
+    assert max(res.values()) < 1e-6, res
