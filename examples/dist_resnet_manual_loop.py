@@ -6,6 +6,7 @@ step (cf. ``examples/dist/CIFAR10-dawndist/core.py:195-209`` and
 
     python examples/dist_resnet_manual_loop.py --compressor topk --memory residual --communicator allgather
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/dist_resnet_manual_loop.py --fused
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/dist_resnet_manual_loop.py --host-protocol
 """
 import argparse
 import os
@@ -30,6 +31,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--fused", action="store_true", help="single-kernel exchange on CUDA")
+    ap.add_argument("--host-protocol", action="store_true",
+                    help="CPU ranks: the exchange protocol in native code over shared memory instead of gloo collectives")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -47,7 +50,10 @@ def main():
     model = (resnet20() if args.model == "resnet20" else resnet9()).to(device)
     optimizer = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, nesterov=True, weight_decay=5e-4)
     grc = grace_from_params({"compressor": args.compressor, "memory": args.memory, "communicator": args.communicator,
-                             "compress_ratio": args.compress_ratio, "world_size": world, "fused": args.fused})
+                             "compress_ratio": args.compress_ratio, "world_size": world, "fused": args.fused,
+                             "host_protocol": args.host_protocol and not cuda})
+    if hasattr(grc, "prepare"):   # shared heaps are created by all ranks together, before the first backward pass
+        grc.prepare(list(model.named_parameters()))
     gen = torch.Generator().manual_seed(100 + rank)
     for step in range(args.steps):
         x = torch.randn(args.batch, 3, 32, 32, generator=gen).to(device)
@@ -60,6 +66,8 @@ def main():
         optimizer.step()
         if rank == 0 and step % 5 == 0:
             print("step %3d  loss %.4f  %s" % (step, loss.item(), grc.stats()))
+    if hasattr(grc, "close"):
+        grc.close()
     if dist.is_initialized():
         dist.destroy_process_group()
 

@@ -36,6 +36,11 @@ def test_manual_loop_example_single_process():
     assert "loss" in out.lower()
 
 
+def test_manual_loop_example_host_protocol_two_gloo_ranks():
+    out = _run(_torchrun("examples/dist_resnet_manual_loop.py", ["--steps", "6", "--batch", "8", "--host-protocol"]))
+    assert "loss" in out.lower() and "compression_ratio" in out
+
+
 def test_cifar10_fast_example_two_gloo_ranks():
     out = _run(_torchrun("examples/cifar10_fast_dawn.py", ["--epochs", "1", "--train-size", "256", "--test-size", "64",
                                                             "--batch", "64", "--peak-epoch", "0.5", "--compressor", "topk",
