@@ -16,10 +16,13 @@ publishes, agreement and recovery - runs among really concurrent ranks
 (processes of a ``torch.distributed`` group, or threads of one process through
 ``ThreadWorld``) on a machine without a GPU.
 
-Pairs covered: TopK / Threshold with none or residual memory, QSGD (buckets
-of 128, fewer than 128 levels) with none or residual memory, signSGD / signum,
-EF-signSGD with its memory, and no compression.  Anything else uses the
-library ``Allgather`` path.
+Pairs covered: TopK / Threshold with none or residual memory, TopK / DGC with
+the momentum-corrected DGC memory (exact k-th magnitude, no clipping), QSGD
+(buckets of 128, fewer than 128 levels), TernGrad, natural compression (the
+CUDA extension's code table; stochastic or deterministic), 8-bit, 1-bit and
+fp16 with none or residual memory, signSGD / signum, EF-signSGD with its
+memory, and no compression.  Stochastic codecs draw the Philox stream of the
+GPU path.  Anything else uses the library ``Allgather`` path.
 
 The reference's CPU ranks meet only inside Gloo collectives
 (``grace_dl/dist/communicator/allgather.py:8-45``).
@@ -42,7 +45,7 @@ from ..core import Communicator
 from .allgather import Allgather
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
-TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE = range(6)
+TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16 = range(11)
 _ALIGN = 64
 
 
@@ -194,6 +197,7 @@ class _HostPlan:
         self.steps = 0
         self.acc = torch.zeros(numel, dtype=torch.float32) if owner._needs_acc else None
         self.mom = torch.zeros(numel, dtype=torch.float32) if owner._needs_mom else None
+        self.u = torch.zeros(numel, dtype=torch.float32) if owner._needs_u else None
 
     def status(self) -> np.ndarray:
         return self.heap.view(self.status_off, 8, np.uint32)
@@ -235,10 +239,14 @@ class HostExchange(Communicator):
     def _resolve(self):
         comp, mem = self.compressor, self.memory
         self._codec = None
-        self._needs_acc = isinstance(mem, (M_.ResidualMemory, M_.EFSignSGDMemory))
+        self._needs_acc = isinstance(mem, (M_.ResidualMemory, M_.EFSignSGDMemory, M_.DgcMemory))
+        self._needs_u = isinstance(mem, M_.DgcMemory)
         self._needs_mom = isinstance(comp, C_.SignumCompressor)
         plain = isinstance(mem, (M_.NoneMemory, M_.ResidualMemory))
-        if isinstance(comp, C_.TopKCompressor) and plain:
+        if isinstance(mem, M_.DgcMemory):
+            if isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and not getattr(mem, "gradient_clipping", False):
+                self._codec = TOPK
+        elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and plain:
             self._codec = TOPK
         elif isinstance(comp, C_.ThresholdCompressor) and plain:
             self._codec = THRESHOLD
@@ -250,6 +258,12 @@ class HostExchange(Communicator):
             self._codec = EFSIGN
         elif isinstance(comp, C_.NoneCompressor) and isinstance(mem, M_.NoneMemory):
             self._codec = DENSE
+        elif plain:
+            for cls, codec in ((C_.TernGradCompressor, TERNGRAD), (C_.NaturalCompressor, NATURAL),
+                               (C_.U8bitCompressor, U8BIT), (C_.OneBitCompressor, ONEBIT), (C_.FP16Compressor, FP16)):
+                if isinstance(comp, cls):
+                    self._codec = codec
+                    break
 
     def supported(self, tensor: torch.Tensor) -> bool:
         return (self._codec is not None and not tensor.is_cuda and tensor.is_floating_point()
@@ -314,7 +328,8 @@ class HostExchange(Communicator):
             (1.0 / self.world_size) if comp.average else 1.0, float(getattr(comp, "threshold", 0.0)),
             int(bool(getattr(comp, "strict", False))), float(getattr(comp, "learning_rate", 1.0)),
             float(getattr(comp, "momentum", 0.0)), int(plan.steps == 0), int(getattr(comp, "quantum_num", 0)),
-            plan.seed, plan.steps)
+            plan.seed, plan.steps, plan.u.data_ptr() if plan.u is not None else 0,
+            float(getattr(self.memory, "momentum", 0.0)), int(bool(getattr(comp, "deterministic", False))))
         if rc != 0:
             st = plan.status()
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)
@@ -415,12 +430,17 @@ class HostExchange(Communicator):
     def state_dict(self):
         if not self._plans:
             return self._fallback.state_dict()
-        residuals = {p.name: p.acc.clone() for p in self._plans.values() if p.acc is not None}
+        residuals = {p.name: p.acc.clone() for p in self._plans.values() if p.acc is not None and p.u is None}
+        gradients = {p.name: p.acc.clone() for p in self._plans.values() if p.u is not None}   # DGC: v
+        residuals.update({p.name: p.u.clone() for p in self._plans.values() if p.u is not None})   # DGC: u
         comp = self.compressor.state_dict()
         momentums = {p.name: p.mom.clone() for p in self._plans.values() if p.mom is not None}
         if momentums:
             comp["momentums"] = momentums
-        return {"compressor": comp, "memory": {"residuals": residuals}, "world_size": self.world_size,
+        mem = {"residuals": residuals}
+        if gradients:
+            mem["gradients"] = gradients
+        return {"compressor": comp, "memory": mem, "world_size": self.world_size,
                 "host_steps": {p.name: p.steps for p in self._plans.values()}}
 
     def load_state_dict(self, state):
@@ -430,10 +450,13 @@ class HostExchange(Communicator):
             self._restore_plan(plan, state)
 
     def _restore_plan(self, plan: _HostPlan, state):
-        res = state.get("memory", {}).get("residuals", {})
+        mem = state.get("memory", {})
+        res = mem.get("gradients" if plan.u is not None else "residuals", {})
         if plan.acc is not None and plan.name in res:
             plan.acc.copy_(res[plan.name].reshape(-1).to(torch.float32))
             plan.steps = max(plan.steps, 1)
+        if plan.u is not None and plan.name in mem.get("residuals", {}):
+            plan.u.copy_(mem["residuals"][plan.name].reshape(-1).to(torch.float32))
         moms = state.get("compressor", {}).get("momentums", {})
         if plan.mom is not None and plan.name in moms:
             plan.mom.copy_(moms[plan.name].reshape(-1).to(torch.float32))

@@ -73,6 +73,85 @@ struct SlotView {
 };
 
 inline long long groups128(long long n) { return (n + 127) / 128; }
+
+inline uint32_t float_bits(float f) {
+  uint32_t b;
+  std::memcpy(&b, &f, 4);
+  return b;
+}
+inline float bits_float(uint32_t b) {
+  float f;
+  std::memcpy(&f, &b, 4);
+  return f;
+}
+
+// Natural compression, the code of the CUDA extension (cnat_cuda.cu:8-66): 7 bits of biased exponent minus 17
+// (0 = zero, saturating at 127) and the sign in bit 7.
+inline float natural_decode(unsigned code) {
+  const unsigned c7 = code & 0x7fu;
+  return bits_float((c7 ? ((c7 + 17u) << 23) : 0u) | ((code & 0x80u) << 24));
+}
+
+// fp32 -> fp16 -> fp32 with round-to-nearest-even (what __float2half_rn does), without relying on a half type.
+inline uint16_t float_to_half(float f) {
+  const uint32_t b = float_bits(f), sign = (b >> 16) & 0x8000u;
+  const uint32_t e = (b >> 23) & 0xffu, m = b & 0x7fffffu;
+  if (e == 0xffu) return (uint16_t)(sign | 0x7c00u | (m ? 0x200u : 0u));
+  const int he = (int)e - 127 + 15;
+  if (he >= 31) return (uint16_t)(sign | 0x7c00u);
+  if (he <= 0) {
+    if (he < -10) return (uint16_t)sign;
+    const uint32_t mant = m | 0x800000u;
+    const int shift = 14 - he;
+    uint32_t h = mant >> shift;
+    const uint32_t rem = mant & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (h & 1u))) ++h;
+    return (uint16_t)(sign | h);
+  }
+  uint32_t h = ((uint32_t)he << 10) | (m >> 13);
+  const uint32_t rem = m & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) ++h;   // a carry into the exponent is the right answer
+  return (uint16_t)(sign | h);
+}
+inline float half_to_float(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 0x1fu, m = h & 0x3ffu;
+  if (e == 0) {
+    if (!m) return bits_float(sign);
+    const float v = std::ldexp((float)m, -24);
+    return sign ? -v : v;
+  }
+  if (e == 31) return bits_float(sign | 0x7f800000u | (m << 13));
+  return bits_float(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+// The 128 bin edges of the 8-bit dynamic-tree data type (grace_dl/tensorflow/compressor/u8bit.py:12-47): seven
+// hand-placed small values, eight linear runs whose step grows from run to run, the top edge.
+const float* u8_edges() {
+  static float e[128];
+  static const bool built = [] {
+    const float head[7] = {1.5000001e-06f, 2.7500000e-06f, 7.2499997e-06f, 1.8750001e-05f,
+                           3.6250000e-05f, 5.8749996e-05f, 8.6249995e-05f};
+    int n = 0;
+    for (int i = 0; i < 7; ++i) e[n++] = head[i];
+    const double start[8] = {1.4375e-04, 5.1875e-04, 1.21875e-03, 4.84375e-03, 1.109375e-02, 4.671875e-02, 1.0546875e-01, 4.5859375e-01};
+    const double step[8] = {8.75e-05, 1.375e-04, 4.375e-04, 6.875e-04, 2.1875e-03, 3.4375e-03, 1.09375e-02, 1.71875e-02};
+    const int count[8] = {4, 4, 8, 8, 16, 16, 32, 32};
+    for (int r = 0; r < 8; ++r)
+      for (int i = 0; i < count[r]; ++i) e[n++] = (float)(start[r] + i * step[r]);
+    e[n++] = 9.9570298e-01f;
+    return n == 128;
+  }();
+  (void)built;
+  return e;
+}
+inline int u8_bin(float y, const float* edges) {   // largest i in [0, 126] with edges[i] <= y (0 below the first edge)
+  int lo = 0, hi = 127;
+  for (int it = 0; it < 7; ++it) {
+    const int mid = (lo + hi) >> 1;
+    if (edges[mid] <= y) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 inline long long words32(long long n) { return (n + 31) / 32; }
 
 // ---- compress: x = beta * acc + gamma * g, encode x into the slot, acc = x - decode(code) ----
@@ -81,7 +160,13 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
   if (slot_bytes(a.codec, n, a.k) > slot_bytes_avail) return kSlotOverflow;
   std::vector<float> xbuf;
   const float* x = a.g;
-  if (a.acc) {   // error feedback: the accumulator holds x while it is encoded
+  if (a.u && a.acc) {   // DGC momentum correction (memory/dgc.py:21-30): u = m u + g, v += u, v is what is encoded
+    for (long long i = 0; i < n; ++i) {
+      a.u[i] = a.momentum * a.u[i] + a.g[i];
+      a.acc[i] += a.u[i];
+    }
+    x = a.acc;
+  } else if (a.acc) {   // error feedback: the accumulator holds x while it is encoded
     for (long long i = 0; i < n; ++i) a.acc[i] = a.beta * a.acc[i] + a.gamma * a.g[i];
     x = a.acc;
   } else if (a.gamma != 1.f) {
@@ -131,6 +216,7 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
         idx[j] = order[j];
         val[j] = x[order[j]];
         if (a.acc) a.acc[order[j]] = 0.f;
+        if (a.u) a.u[order[j]] = 0.f;
       }
       *slot.count() = (uint64_t)k;
       break;
@@ -212,6 +298,97 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
       if (a.acc) std::memset(a.acc, 0, (size_t)n * 4);
       break;
     }
+    case kTernGrad: {
+      double sum = 0.0, sumsq = 0.0;
+      float maxabs = 0.f;
+      for (long long i = 0; i < n; ++i) {
+        sum += x[i];
+        sumsq += (double)x[i] * x[i];
+        maxabs = std::max(maxabs, std::fabs(x[i]));
+      }
+      const double mean = n ? sum / (double)n : 0.0;
+      const double var = n ? std::max(0.0, sumsq / (double)n - mean * mean) : 0.0;
+      const float c = 2.5f * (float)std::sqrt(var), s0 = std::min(maxabs, c);   // max |clamp(x, -c, c)|
+      *slot.scalar(0) = s0;
+      signed char* codes = reinterpret_cast<signed char*>(pay);
+      for (long long g4 = 0; g4 < n; g4 += 4) {
+        const Philox4 r = philox_group((uint64_t)(g4 >> 2), a.step, 0u, a.seed);
+        const unsigned rw[4] = {r.x, r.y, r.z, r.w};
+        for (int j = 0; j < 4 && g4 + j < n; ++j) {
+          const long long i = g4 + j;
+          const bool keep = u01(rw[j]) * s0 < std::min(std::fabs(x[i]), c);
+          const int code = keep ? (x[i] < 0.f ? -1 : 1) : 0;
+          codes[i] = (signed char)code;
+          if (a.acc) a.acc[i] = x[i] - s0 * (float)code;
+        }
+      }
+      break;
+    }
+    case kNatural: {
+      unsigned char* codes = reinterpret_cast<unsigned char*>(pay);
+      for (long long g4 = 0; g4 < n; g4 += 4) {
+        Philox4 r{0u, 0u, 0u, 0u};
+        if (!a.deterministic) r = philox_group((uint64_t)(g4 >> 2), a.step, 0u, a.seed);
+        const unsigned rw[4] = {r.x, r.y, r.z, r.w};
+        for (int j = 0; j < 4 && g4 + j < n; ++j) {
+          const long long i = g4 + j;
+          const uint32_t bits = float_bits(x[i]), biased = (bits >> 23) & 0xffu, mant = bits & 0x7fffffu;
+          const bool up = a.deterministic ? mant > 0x400000u : u01(rw[j]) < (float)mant * 1.1920928955078125e-07f;
+          int c7 = (int)biased + (up ? 1 : 0) - 17;
+          c7 = c7 < 0 ? 0 : (c7 > 127 ? 127 : c7);
+          if (biased == 0) c7 = 0;
+          const unsigned code = (unsigned)c7 | ((bits >> 24) & 0x80u);
+          codes[i] = (unsigned char)code;
+          if (a.acc) a.acc[i] = x[i] - natural_decode(code);
+        }
+      }
+      break;
+    }
+    case kU8bit: {
+      const float* edges = u8_edges();
+      float s0 = 0.f;
+      for (long long i = 0; i < n; ++i) s0 = std::max(s0, std::fabs(x[i]));
+      *slot.scalar(0) = s0;
+      const float safe = s0 > 0.f ? s0 : 1.f;
+      signed char* codes = reinterpret_cast<signed char*>(pay);
+      for (long long i = 0; i < n; ++i) {
+        const int bin = u8_bin(std::fabs(x[i]) / safe, edges);
+        const int sg = x[i] > 0.f ? 1 : (x[i] < 0.f ? -1 : 0);
+        const int code = bin * sg;
+        codes[i] = (signed char)code;
+        if (a.acc) a.acc[i] = x[i] - (code ? edges[bin] * s0 * (float)sg : 0.f);   // bin 0 decodes to exactly 0
+      }
+      break;
+    }
+    case kOneBit: {
+      double sneg = 0.0, spos = 0.0;
+      long long nneg = 0;
+      for (long long i = 0; i < n; ++i) {
+        if (x[i] < 0.f) { sneg += x[i]; ++nneg; } else spos += x[i];
+      }
+      const float m0 = nneg ? (float)(sneg / (double)nneg) : 0.f;
+      const float m1 = n - nneg ? (float)(spos / (double)(n - nneg)) : 0.f;
+      *slot.scalar(0) = m0;
+      *slot.scalar(1) = m1;
+      unsigned* bits = reinterpret_cast<unsigned*>(pay);
+      for (long long w = 0; w < words32(n); ++w) {
+        unsigned word = 0;
+        const long long lim = std::min<long long>(32, n - w * 32);
+        for (long long j = 0; j < lim; ++j) word |= (unsigned)(x[w * 32 + j] < 0.f) << j;
+        bits[w] = word;
+      }
+      if (a.acc)
+        for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - (x[i] < 0.f ? m0 : m1);
+      break;
+    }
+    case kFP16: {
+      uint16_t* h = reinterpret_cast<uint16_t*>(pay);
+      for (long long i = 0; i < n; ++i) {
+        h[i] = float_to_half(x[i]);
+        if (a.acc) a.acc[i] = x[i] - half_to_float(h[i]);
+      }
+      break;
+    }
     default:
       return kBadArgument;
   }
@@ -257,6 +434,39 @@ unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes)
       for (long long i = 0; i < n; ++i) sum[i] += v[i];
       break;
     }
+    case kTernGrad: {
+      const signed char* codes = reinterpret_cast<const signed char*>(pay);
+      const float s0 = *slot.scalar(0);
+      for (long long i = 0; i < n; ++i) sum[i] += s0 * (float)codes[i];
+      break;
+    }
+    case kNatural: {
+      const unsigned char* codes = reinterpret_cast<const unsigned char*>(pay);
+      for (long long i = 0; i < n; ++i) sum[i] += natural_decode(codes[i]);
+      break;
+    }
+    case kU8bit: {
+      const float* edges = u8_edges();
+      const signed char* codes = reinterpret_cast<const signed char*>(pay);
+      const float s0 = *slot.scalar(0);
+      for (long long i = 0; i < n; ++i) {
+        const int code = codes[i], bin = code < 0 ? -code : code;
+        if (bin > 126) return kBadArgument;
+        sum[i] += code ? edges[bin] * s0 * (code < 0 ? -1.f : 1.f) : 0.f;
+      }
+      break;
+    }
+    case kOneBit: {
+      const unsigned* bits = reinterpret_cast<const unsigned*>(pay);
+      const float m0 = *slot.scalar(0), m1 = *slot.scalar(1);
+      for (long long i = 0; i < n; ++i) sum[i] += ((bits[i >> 5] >> (i & 31)) & 1u) ? m0 : m1;
+      break;
+    }
+    case kFP16: {
+      const uint16_t* h = reinterpret_cast<const uint16_t*>(pay);
+      for (long long i = 0; i < n; ++i) sum[i] += half_to_float(h[i]);
+      break;
+    }
     default:
       return kBadArgument;
   }
@@ -272,7 +482,12 @@ size_t slot_bytes(int codec, long long n, long long k) {
     case kThreshold: b += (size_t)k * 8; break;
     case kQSGD: b += (size_t)groups128(n) * 4 + (size_t)n; break;
     case kSign:
-    case kEFSign: b += (size_t)words32(n) * 4; break;
+    case kEFSign:
+    case kOneBit: b += (size_t)words32(n) * 4; break;
+    case kTernGrad:
+    case kNatural:
+    case kU8bit: b += (size_t)n; break;
+    case kFP16: b += (size_t)n * 2; break;
     default: b += (size_t)n * 4; break;
   }
   return (b + 63) / 64 * 64;

@@ -27,6 +27,11 @@ enum Codec : int {
   kSign = 3,        // 1 bit per element, majority vote (ties -> +1)
   kEFSign = 4,      // 1 bit per element + mean |x|, sum of mean * sign divided by lr
   kDense = 5,       // no compression: sum of the ranks' tensors
+  kTernGrad = 6,    // {-1, 0, +1} codes (one byte each) + scale min(max|x|, 2.5 sigma), Philox keep probability |x| / scale
+  kNatural = 7,     // 8-bit sign / exponent code, exponent rounded up with probability mantissa / 2^23 (or at 1/2)
+  kU8bit = 8,       // 8-bit table code (128 non-uniform bin edges) + scale max|x|
+  kOneBit = 9,      // 1 bit per element (x < 0) + the means of the negative and of the other elements
+  kFP16 = 10,       // half-precision values, summed in fp32
 };
 
 enum Phase : int { kCompress = 1, kPublish = 2, kExchange = 4, kAll = 7 };
@@ -52,6 +57,9 @@ struct Args {
   const float* g;        // gradient [n]
   float* acc;            // error-feedback accumulator [n] or null
   float* mom;            // signum momentum [n] or null
+  float* u;              // DGC momentum correction [n] or null: u = momentum * u + g, acc += u, both zeroed at the picks
+  float momentum;        // DGC
+  int deterministic;     // kNatural: round the exponent at mantissa 1/2 instead of drawing
   float* out;            // aggregate [n] (may alias g)
   long long n;
   long long k;           // kTopK: entries; kThreshold: slot capacity

@@ -303,7 +303,7 @@ def test_split_phase_equals_step_and_checkpoint_round_trip():
 
 
 def test_unsupported_pairs_use_the_library_path():
-    grc = HostExchange(C_.TernGradCompressor(), M_.NoneMemory(), 1)
+    grc = HostExchange(C_.RandomKCompressor(0.1), M_.ResidualMemory(), 1)   # random-k has no host codec
     x = torch.randn(100)
     assert not grc.supported(x)
     assert grc.step(x, "t").shape == x.shape
@@ -456,3 +456,91 @@ def test_distributed_optimizer_over_the_host_engine():
     _free_port.port = _free_port()
     res = _run(_optimizer_ranks, world=2)
     assert max(res.values()) < 1e-6, res
+
+
+# ---- the codecs added after the first set: against the Python compressor classes (library path, one rank) ----
+def _lib_and_host(params, n, steps=3, scale=1e-3):
+    from grace_b200 import grace_from_params
+
+    grads = [torch.randn(n, generator=torch.Generator().manual_seed(11 * s + 1)) * scale for s in range(steps)]
+    lib = grace_from_params(dict(params, world_size=1))
+    if params["compressor"] == "dgc":
+        lib.compressor.mode = "exact"
+    want = [lib.step(g.clone(), "w") for g in grads]
+
+    def body(view):
+        host = grace_from_params(dict(params, world_size=1, host_protocol=True, host_world=view))
+        assert host.supported(grads[0])
+        outs = [host.step(g.clone(), "w") for g in grads]
+        return outs, host.state_dict()
+
+    got, state = ThreadWorld(1).run(body)[0]
+    return want, got, state, lib
+
+
+@pytest.mark.parametrize("params", [
+    {"compressor": "onebit", "memory": "residual", "communicator": "allgather"},
+    {"compressor": "fp16", "memory": "residual", "communicator": "allgather"},
+    {"compressor": "u8bit", "memory": "residual", "communicator": "allgather"},
+    {"compressor": "natural", "memory": "residual", "communicator": "allgather", "deterministic": True},
+    {"compressor": "dgc", "memory": "dgc", "communicator": "allgather", "compress_ratio": 0.01, "momentum": 0.9},
+], ids=lambda p: p["compressor"] + "+" + p["memory"])
+def test_more_codecs_match_the_python_classes(params):
+    want, got, state, lib = _lib_and_host(params, 5000)
+    for a, b in zip(want, got):
+        torch.testing.assert_close(b, a, rtol=1e-6, atol=1e-10)
+    if params["memory"] == "dgc":      # checkpoint names of the reference: residuals = u, gradients = v
+        torch.testing.assert_close(state["memory"]["residuals"]["w"], lib.memory.residuals["w"].reshape(-1))
+        torch.testing.assert_close(state["memory"]["gradients"]["w"], lib.memory.gradients["w"].reshape(-1))
+    else:
+        # (1-bit: the means are formed in fp64 here and in fp32 there; the residual is a difference of nearly equal
+        # numbers, so the comparison is absolute, at rounding level of the 1e-3 sized inputs)
+        torch.testing.assert_close(state["memory"]["residuals"]["w"], lib.memory.residuals["w"].reshape(-1),
+                                   rtol=1e-6, atol=2e-9)
+
+
+def test_fp16_conversion_edge_cases():
+    x = torch.tensor([0.0, -0.0, 1.0, -2.5, 65504.0, 65520.0, 1e5, -1e5, 6.0e-8, 3.0e-8, 2.0e-8, 1e-4, 0.1,
+                      1.0 + 2 ** -11, 1.0 + 3 * 2 ** -11, float("inf"), float("-inf")])
+    outs, _ = _run_ranks(1, lambda: (C_.FP16Compressor(), M_.NoneMemory()), [[x]])
+    assert torch.equal(outs[0][0], x.half().float())
+
+
+def test_terngrad_and_natural_draw_the_philox_stream():
+    from grace_b200.communicator.host import _name_seed
+    from grace_b200.utils import philox
+
+    n = 4096
+    x = torch.randn(n, generator=torch.Generator().manual_seed(5)) * 1e-2
+    u = torch.from_numpy(philox.uniform(n, _name_seed(0, "w" + str(n)), 0, 0))
+    # TernGrad: keep with probability |clamp(x)| / s, s = min(max|x|, 2.5 sigma)
+    outs, _ = _run_ranks(1, lambda: (C_.TernGradCompressor(), M_.NoneMemory()), [[x]])
+    c = 2.5 * x.double().var(unbiased=False).sqrt().float()
+    s0 = torch.minimum(x.abs().max(), c)
+    want = torch.where(u * s0 < torch.minimum(x.abs(), c), torch.sign(x) * s0, torch.zeros(n))
+    mism = (outs[0][0] != want)
+    assert float(mism.float().mean()) < 0.002       # sigma in fp64 here and there, but summed in another order
+    assert set(torch.unique(outs[0][0] / s0).round().tolist()) <= {-1.0, 0.0, 1.0}
+    # natural compression: exponent + 1 with probability mantissa / 2^23
+    outs, _ = _run_ranks(1, lambda: (C_.NaturalCompressor(), M_.NoneMemory()), [[x]])
+    bits = x.view(torch.int32)
+    mant = (bits & 0x7FFFFF).float() * 2.0 ** -23
+    low = torch.sign(x) * torch.exp2(torch.floor(torch.log2(x.abs())))
+    want = torch.where(u < mant, 2 * low, low)
+    assert torch.equal(outs[0][0], want)
+
+
+@pytest.mark.parametrize("world", [3])
+def test_onebit_and_u8bit_average_over_ranks(world):
+    n = 3001
+    grads = _grads(world, n, 1)
+    outs, _ = _run_ranks(world, lambda: (C_.OneBitCompressor(), M_.NoneMemory()), grads)
+    want = torch.zeros(n)
+    for g in grads[0]:
+        neg = g < 0
+        want += torch.where(neg, g[neg].mean(), g[~neg].mean())
+    torch.testing.assert_close(outs[0][0], want / world, rtol=1e-5, atol=1e-9)
+    outs, _ = _run_ranks(world, lambda: (C_.U8bitCompressor(), M_.NoneMemory()), grads)
+    comp = C_.U8bitCompressor()
+    want = sum(comp.decompress(*comp.compress(g, "w")) for g in grads[0]) / world
+    torch.testing.assert_close(outs[1][0], want, rtol=1e-6, atol=1e-10)
