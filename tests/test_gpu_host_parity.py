@@ -58,3 +58,37 @@ def test_qsgd_same_random_stream():
     g = torch.randn(n, generator=torch.Generator().manual_seed(0)) * 1e-3
     one_level = (g.view(-1, 128).norm(dim=1) / q)[:, None]
     assert bool((diff <= one_level * 1.01).all())                    # and no code is off by more than one level
+
+
+def test_natural_compression_same_codes():
+    for det in (True, False):
+        dev, host = _pair({"compressor": "natural", "memory": "residual", "communicator": "allgather",
+                           "deterministic": det}, 100_003, steps=3)
+        for a, b in zip(dev, host):
+            assert torch.equal(a, b)           # same Philox words, integer decisions: the same powers of two
+
+
+def test_eight_bit_and_fp16_are_identical():
+    dev, host = _pair({"compressor": "u8bit", "memory": "residual", "communicator": "allgather"}, 50_001, steps=2)
+    assert all(torch.equal(a, b) for a, b in zip(dev, host))
+    dev, host = _pair({"compressor": "fp16", "memory": "residual", "communicator": "allgather"}, 50_001, steps=2)
+    assert all(torch.equal(a, b) for a, b in zip(dev, host))
+
+
+def test_one_bit_and_terngrad_agree_to_rounding():
+    dev, host = _pair({"compressor": "onebit", "memory": "none", "communicator": "allgather"}, 60_000, steps=1)
+    torch.testing.assert_close(dev[0], host[0], rtol=1e-5, atol=1e-10)   # the two means: summed in another order
+    dev, host = _pair({"compressor": "terngrad", "memory": "none", "communicator": "allgather"}, 60_000, steps=1)
+    s = dev[0].abs().max()
+    assert abs(float(s) - float(host[0].abs().max())) < 1e-6 * float(s)
+    differ = ((dev[0] / s).round() != (host[0] / host[0].abs().max()).round()).float().mean()
+    assert float(differ) < 0.005               # the scale differs in its last bits: a few keep decisions flip
+
+
+def test_dgc_momentum_memory_small_and_large():
+    for n in (5000, 150_000):                  # the single-CTA kernel and the large one
+        dev, host = _pair({"compressor": "dgc", "memory": "dgc", "communicator": "allgather", "compress_ratio": 0.01,
+                           "momentum": 0.9}, n, steps=3)
+        for a, b in zip(dev, host):
+            assert int((a != 0).sum()) == int((b != 0).sum()) == max(1, int(n * 0.01))
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-9)   # u = m u + g is one fused multiply-add on the GPU
