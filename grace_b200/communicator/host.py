@@ -121,8 +121,6 @@ class HostHeap:
     ranks drive with the same requests.  The names are unlinked as soon as everybody has mapped them, so nothing
     stays behind in ``/dev/shm`` when a rank dies."""
 
-    _serial_lock = threading.Lock()
-
     def __init__(self, nbytes: int, world, serial: int):
         from ..ops import native
 
@@ -365,6 +363,25 @@ class HostExchange(Communicator):
 
     def send_receive(self, tensors, name, ctx):
         return self._fallback.send_receive(tensors, name, ctx)
+
+    def step_flat(self, flat: torch.Tensor, layout, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """A whole flat buffer of named gradients (``FlatLayout``: names, offsets, numels), tensor by tensor: every
+        tensor is published before the first one is pulled, so the ranks' encode passes overlap.  In place unless
+        ``out`` is given.  (The call shape of ``FusedExchange.step_flat``; used by ``DistributedOptimizer`` with
+        ``FlatParams`` on CPU.)"""
+        out = flat if out is None else out
+        pending = []
+        for name, off, numel in zip(layout.names, layout.offsets, layout.numels):
+            pending.append((off, numel, self.send_step(flat[off:off + numel], name)))
+        for off, numel, (handles, ctx) in pending:
+            out[off:off + numel] = self.receive_step(handles, ctx)
+        return out
+
+    def prepare_layouts(self, layouts, device=None):
+        """Create the plans of whole buckets up front, in the order given (same on every rank)."""
+        for layout in layouts:
+            for name, numel in zip(layout.names, layout.numels):
+                self._plan(name, numel)
 
     # ------------------------------------------------------------------ failures
     def check(self):

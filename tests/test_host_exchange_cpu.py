@@ -544,3 +544,30 @@ def test_onebit_and_u8bit_average_over_ranks(world):
     comp = C_.U8bitCompressor()
     want = sum(comp.decompress(*comp.compress(g, "w")) for g in grads[0]) / world
     torch.testing.assert_close(outs[1][0], want, rtol=1e-6, atol=1e-10)
+
+
+def test_step_flat_equals_tensor_by_tensor():
+    from grace_b200.ops.exchange import FlatLayout
+
+    world = 2
+    layout = FlatLayout.from_named([("a", 700), ("b", 64), ("c", 5001)])
+    tw = ThreadWorld(world)
+
+    def body(view):
+        make = lambda: HostExchange(C_.TopKCompressor(0.05), M_.ResidualMemory(), world, world=view)  # noqa: E731
+        flat_grc, single = make(), make()
+        flat_grc.prepare_layouts([layout])
+        single.prepare([(n, torch.empty(c)) for n, c in zip(layout.names, layout.numels)])
+        worst = 0.0
+        for step in range(3):
+            flat = torch.zeros(layout.total)
+            for i, (o, c) in enumerate(zip(layout.offsets, layout.numels)):
+                flat[o:o + c] = torch.randn(c, generator=torch.Generator().manual_seed(100 * step + 10 * view.rank + i))
+            want = flat.clone()
+            for n, o, c in zip(layout.names, layout.offsets, layout.numels):
+                want[o:o + c] = single.step(flat[o:o + c].clone(), n)
+            got = flat_grc.step_flat(flat.clone(), layout)
+            worst = max(worst, float((got - want).abs().max()))
+        return worst
+
+    assert max(tw.run(body)) == 0.0
