@@ -16,7 +16,7 @@ publishes, agreement and recovery - runs among really concurrent ranks
 (processes of a ``torch.distributed`` group, or threads of one process through
 ``ThreadWorld``) on a machine without a GPU.
 
-Pairs covered: TopK / Threshold with none or residual memory, TopK / DGC with
+Pairs covered: TopK / Threshold / RandomK with none or residual memory, TopK / DGC with
 the momentum-corrected DGC memory (exact k-th magnitude, no clipping), QSGD
 (buckets of 128, fewer than 128 levels), TernGrad, natural compression (the
 CUDA extension's code table; stochastic or deterministic), 8-bit, 1-bit and
@@ -45,7 +45,7 @@ from ..core import Communicator
 from .allgather import Allgather
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
-TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16 = range(11)
+TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16, RANDOMK = range(12)
 _ALIGN = 64
 
 
@@ -177,7 +177,7 @@ class _HostPlan:
         self.name, self.numel = name, numel
         comp = owner.compressor
         self.k = 0
-        if owner._codec == TOPK:
+        if owner._codec in (TOPK, RANDOMK):
             self.k = topk_count(numel, comp.compress_ratio)
         elif owner._codec == THRESHOLD:
             self.k = max(1, int(numel * owner.max_ratio))
@@ -191,6 +191,8 @@ class _HostPlan:
         self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
         # the key of the random stream: as the GPU path derives it for a single tensor (name and padded length)
         self.seed = _name_seed(owner.seed, name + str((numel + 127) // 128 * 128))
+        if owner._codec == RANDOMK:   # the positions are keyed by the tensor's name alone, as on the GPU
+            self.seed = _name_seed(owner.seed, name)
         self.seq = 0          # sequence number of the last exchange started
         self.steps = 0
         self.acc = torch.zeros(numel, dtype=torch.float32) if owner._needs_acc else None
@@ -248,6 +250,8 @@ class HostExchange(Communicator):
             self._codec = TOPK
         elif isinstance(comp, C_.ThresholdCompressor) and plain:
             self._codec = THRESHOLD
+        elif isinstance(comp, C_.RandomKCompressor) and plain:
+            self._codec = RANDOMK
         elif isinstance(comp, C_.QSGDCompressor) and plain and comp.bucket_size == 128 and comp.quantum_num < 128:
             self._codec = QSGD
         elif isinstance(comp, (C_.SignSGDCompressor, C_.SignumCompressor)) and plain:
@@ -333,6 +337,8 @@ class HostExchange(Communicator):
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)
 
     def _payload_bytes(self, plan: _HostPlan) -> int:
+        if self._codec == RANDOMK:
+            return 4 * plan.k
         return 8 * plan.k if self._codec in (TOPK, THRESHOLD) else int(plan.slot_bytes)
 
     def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:

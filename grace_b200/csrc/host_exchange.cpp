@@ -74,6 +74,13 @@ struct SlotView {
 
 inline long long groups128(long long n) { return (n + 127) / 128; }
 
+// Position e of a random-k exchange: word e of Philox stream 7 (the stream the GPU kernel uses), modulo the length.
+inline long long randomk_position(const Args& a, long long e) {
+  const Philox4 r = philox_group((uint64_t)(e >> 2), a.step, 7u, a.seed);
+  const unsigned w = (e & 3) == 0 ? r.x : ((e & 3) == 1 ? r.y : ((e & 3) == 2 ? r.z : r.w));
+  return (long long)(w % (unsigned)a.n);
+}
+
 inline uint32_t float_bits(float f) {
   uint32_t b;
   std::memcpy(&b, &f, 4);
@@ -381,6 +388,16 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
         for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - (x[i] < 0.f ? m0 : m1);
       break;
     }
+    case kRandomK: {
+      if (a.k < 1 || n < 1) return kBadArgument;
+      float* val = reinterpret_cast<float*>(pay);
+      for (long long e = 0; e < a.k; ++e) val[e] = x[randomk_position(a, e)];
+      // the residual is zeroed only after every value was read: a position drawn twice sends the same value twice
+      if (a.acc)
+        for (long long e = 0; e < a.k; ++e) a.acc[randomk_position(a, e)] = 0.f;
+      *slot.count() = (uint64_t)a.k;
+      break;
+    }
     case kFP16: {
       uint16_t* h = reinterpret_cast<uint16_t*>(pay);
       for (long long i = 0; i < n; ++i) {
@@ -467,6 +484,12 @@ unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes)
       for (long long i = 0; i < n; ++i) sum[i] += half_to_float(h[i]);
       break;
     }
+    case kRandomK: {   // entry e of every rank belongs to the same position: the first k sums are per entry
+      if (*slot.count() != (uint64_t)a.k || a.k > n) return kBadArgument;
+      const float* val = reinterpret_cast<const float*>(pay);
+      for (long long e = 0; e < a.k; ++e) sum[e] += val[e];
+      break;
+    }
     default:
       return kBadArgument;
   }
@@ -480,6 +503,7 @@ size_t slot_bytes(int codec, long long n, long long k) {
   switch (codec) {
     case kTopK:
     case kThreshold: b += (size_t)k * 8; break;
+    case kRandomK: b += (size_t)k * 4; break;
     case kQSGD: b += (size_t)groups128(n) * 4 + (size_t)n; break;
     case kSign:
     case kEFSign:
@@ -543,6 +567,10 @@ unsigned exchange(const Channel& ch, const Args& a) {
       for (long long i = 0; i < a.n; ++i) a.out[i] = votes[i] >= 0 ? 1.f : -1.f;
     } else if (a.codec == kEFSign) {
       for (long long i = 0; i < a.n; ++i) a.out[i] = sum[i] / a.lr;
+    } else if (a.codec == kRandomK) {
+      std::vector<float> per_entry(sum.begin(), sum.begin() + a.k);
+      for (long long i = 0; i < a.n; ++i) a.out[i] = 0.f;
+      for (long long e = 0; e < a.k; ++e) a.out[randomk_position(a, e)] = per_entry[(size_t)e] * a.scale;   // a store, as scatter_ does
     } else {
       for (long long i = 0; i < a.n; ++i) a.out[i] = sum[i] * a.scale;
     }

@@ -32,6 +32,7 @@ enum Codec : int {
   kU8bit = 8,       // 8-bit table code (128 non-uniform bin edges) + scale max|x|
   kOneBit = 9,      // 1 bit per element (x < 0) + the means of the negative and of the other elements
   kFP16 = 10,       // half-precision values, summed in fp32
+  kRandomK = 11,    // k positions drawn with replacement from Philox(seed, step), the same on every rank: only values travel
 };
 
 enum Phase : int { kCompress = 1, kPublish = 2, kExchange = 4, kAll = 7 };

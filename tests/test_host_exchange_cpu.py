@@ -303,7 +303,7 @@ def test_split_phase_equals_step_and_checkpoint_round_trip():
 
 
 def test_unsupported_pairs_use_the_library_path():
-    grc = HostExchange(C_.RandomKCompressor(0.1), M_.ResidualMemory(), 1)   # random-k has no host codec
+    grc = HostExchange(C_.PowerSGDCompressor(rank=2), M_.NoneMemory(), 1)   # low-rank has no host codec
     x = torch.randn(100)
     assert not grc.supported(x)
     assert grc.step(x, "t").shape == x.shape
@@ -571,3 +571,31 @@ def test_step_flat_equals_tensor_by_tensor():
         return worst
 
     assert max(tw.run(body)) == 0.0
+
+
+def test_randomk_positions_from_philox_and_values_only():
+    from grace_b200.communicator.host import _name_seed
+    from grace_b200.utils import philox
+
+    n, ratio, world = 5000, 0.05, 2
+    k = int(n * ratio)
+    grads = _grads(world, n, 2)
+    outs, grcs = _run_ranks(world, lambda: (C_.RandomKCompressor(ratio), M_.ResidualMemory()), grads, name="fc.weight")
+    res = [torch.zeros(n) for _ in range(world)]
+    for s in range(2):
+        # stream 7 of the tensor's key, entry e uses word e: the same positions on every rank, with replacement
+        words = philox.random_words(k, _name_seed(0, "fc.weight"), s, 7)
+        pos = torch.from_numpy((words % np.uint32(n)).astype(np.int64))
+        want = torch.zeros(n)
+        total = torch.zeros(k)
+        for r in range(world):
+            acc = res[r] + grads[s][r]
+            total += acc[pos]
+            res[r] = acc.clone()
+            res[r][pos] = 0
+        want[pos] = total / world                 # a store: a position drawn twice is not counted twice
+        for r in range(world):
+            torch.testing.assert_close(outs[r][s], want, rtol=1e-6, atol=1e-10)
+    assert len(set(pos.tolist())) < k             # the case has repeated positions
+    torch.testing.assert_close(grcs[0].state_dict()["memory"]["residuals"]["fc.weight"], res[0], rtol=1e-6, atol=1e-10)
+    assert grcs[0].stats()["compression_ratio"] == pytest.approx(1 / ratio, rel=0.01)
