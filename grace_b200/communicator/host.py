@@ -18,7 +18,7 @@ publishes, agreement and recovery - runs among really concurrent ranks
 
 Pairs covered: TopK / Threshold / RandomK with none or residual memory, TopK / DGC with
 the momentum-corrected DGC memory (exact k-th magnitude, no clipping), QSGD
-(buckets of 128, fewer than 128 levels), TernGrad, natural compression (the
+(any bucket size, up to 32767 levels), TernGrad, natural compression (the
 CUDA extension's code table; stochastic or deterministic), 8-bit, 1-bit and
 fp16 with none or residual memory, signSGD / signum, EF-signSGD with its
 memory, and no compression.  Stochastic codecs draw the Philox stream of the
@@ -45,7 +45,7 @@ from ..core import Communicator
 from .allgather import Allgather
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
-TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16, RANDOMK = range(12)
+TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16, RANDOMK, QSGDX = range(13)
 _ALIGN = 64
 
 
@@ -181,7 +181,8 @@ class _HostPlan:
             self.k = topk_count(numel, comp.compress_ratio)
         elif owner._codec == THRESHOLD:
             self.k = max(1, int(numel * owner.max_ratio))
-        self.slot_bytes = C.host_slot_bytes(owner._codec, numel, self.k)
+        self.bucket = int(getattr(comp, "bucket_size", 0)) if owner._codec == QSGDX else 0
+        self.slot_bytes = C.host_slot_bytes(owner._codec, numel, self.bucket if owner._codec == QSGDX else self.k)
         need = 2 * C.HOST_MAX_WORLD * 8 + 64 + 2 * self.slot_bytes + 6 * _ALIGN
         heap = self.heap = owner._heap_with_room(need)
         self.flag_words = 2 * C.HOST_MAX_WORLD
@@ -254,6 +255,8 @@ class HostExchange(Communicator):
             self._codec = RANDOMK
         elif isinstance(comp, C_.QSGDCompressor) and plain and comp.bucket_size == 128 and comp.quantum_num < 128:
             self._codec = QSGD
+        elif isinstance(comp, C_.QSGDCompressor) and plain and comp.bucket_size >= 1 and comp.quantum_num < 32768:
+            self._codec = QSGDX   # any bucket size, int16 codes
         elif isinstance(comp, (C_.SignSGDCompressor, C_.SignumCompressor)) and plain:
             self._codec = SIGN
         elif isinstance(comp, C_.EFSignSGDCompressor) and isinstance(mem, (M_.EFSignSGDMemory, M_.NoneMemory)):
@@ -331,7 +334,8 @@ class HostExchange(Communicator):
             int(bool(getattr(comp, "strict", False))), float(getattr(comp, "learning_rate", 1.0)),
             float(getattr(comp, "momentum", 0.0)), int(plan.steps == 0), int(getattr(comp, "quantum_num", 0)),
             plan.seed, plan.steps, plan.u.data_ptr() if plan.u is not None else 0,
-            float(getattr(self.memory, "momentum", 0.0)), int(bool(getattr(comp, "deterministic", False))))
+            float(getattr(self.memory, "momentum", 0.0)), int(bool(getattr(comp, "deterministic", False))),
+            plan.bucket)
         if rc != 0:
             st = plan.status()
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)

@@ -164,7 +164,7 @@ inline long long words32(long long n) { return (n + 31) / 32; }
 // ---- compress: x = beta * acc + gamma * g, encode x into the slot, acc = x - decode(code) ----
 unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail) {
   const long long n = a.n;
-  if (slot_bytes(a.codec, n, a.k) > slot_bytes_avail) return kSlotOverflow;
+  if (slot_bytes(a.codec, n, a.codec == kQSGDX ? a.bucket : a.k) > slot_bytes_avail) return kSlotOverflow;
   std::vector<float> xbuf;
   const float* x = a.g;
   if (a.u && a.acc) {   // DGC momentum correction (memory/dgc.py:21-30): u = m u + g, v += u, v is what is encoded
@@ -388,6 +388,31 @@ unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail
         for (long long i = 0; i < n; ++i) a.acc[i] = x[i] - (x[i] < 0.f ? m0 : m1);
       break;
     }
+    case kQSGDX: {
+      if (a.quantum < 1 || a.quantum > 32767 || a.bucket < 1) return kBadArgument;
+      const long long nb = (n + a.bucket - 1) / a.bucket;
+      float* norms = reinterpret_cast<float*>(pay);
+      int16_t* codes = reinterpret_cast<int16_t*>(pay + (size_t)((nb + 3) / 4 * 4) * 4);
+      for (long long b = 0; b < nb; ++b) {
+        const long long lo = b * a.bucket, hi = std::min(n, lo + a.bucket);
+        float sq = 0.f;
+        for (long long i = lo; i < hi; ++i) sq += x[i] * x[i];
+        const float norm = std::sqrt(sq);
+        norms[b] = norm;
+        const float qn = norm > 0.f ? (float)a.quantum / norm : 0.f, dq = norm / (float)a.quantum;
+        for (long long i = lo; i < hi; ++i) {   // element i draws word i % 4 of Philox group i / 4, whatever the bucket size
+          const Philox4 r = philox_group((uint64_t)(i >> 2), a.step, 0u, a.seed);
+          const unsigned w = (i & 3) == 0 ? r.x : ((i & 3) == 1 ? r.y : ((i & 3) == 2 ? r.z : r.w));
+          const float lf = qn * std::fabs(x[i]), fl = std::floor(lf);
+          float level = fl + ((u01(w) < lf - fl) ? 1.f : 0.f);
+          level = std::min(level, 32767.f);
+          const int code = x[i] < 0.f ? -(int)level : (int)level;
+          codes[i] = (int16_t)code;
+          if (a.acc) a.acc[i] = x[i] - dq * (float)code;
+        }
+      }
+      break;
+    }
     case kRandomK: {
       if (a.k < 1 || n < 1) return kBadArgument;
       float* val = reinterpret_cast<float*>(pay);
@@ -484,6 +509,13 @@ unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes)
       for (long long i = 0; i < n; ++i) sum[i] += half_to_float(h[i]);
       break;
     }
+    case kQSGDX: {
+      const long long nb = (n + a.bucket - 1) / a.bucket;
+      const float* norms = reinterpret_cast<const float*>(pay);
+      const int16_t* codes = reinterpret_cast<const int16_t*>(pay + (size_t)((nb + 3) / 4 * 4) * 4);
+      for (long long i = 0; i < n; ++i) sum[i] += norms[i / a.bucket] / (float)a.quantum * (float)codes[i];
+      break;
+    }
     case kRandomK: {   // entry e of every rank belongs to the same position: the first k sums are per entry
       if (*slot.count() != (uint64_t)a.k || a.k > n) return kBadArgument;
       const float* val = reinterpret_cast<const float*>(pay);
@@ -501,6 +533,11 @@ unsigned accumulate(const Args& a, const SlotView& slot, float* sum, int* votes)
 size_t slot_bytes(int codec, long long n, long long k) {
   size_t b = kSlotHeaderBytes;
   switch (codec) {
+    case kQSGDX: {   // k carries the bucket size
+      const long long nb = k > 0 ? (n + k - 1) / k : 0;
+      b += (size_t)((nb + 3) / 4 * 4) * 4 + (size_t)n * 2;
+      break;
+    }
     case kTopK:
     case kThreshold: b += (size_t)k * 8; break;
     case kRandomK: b += (size_t)k * 4; break;

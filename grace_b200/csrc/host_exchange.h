@@ -32,6 +32,7 @@ enum Codec : int {
   kU8bit = 8,       // 8-bit table code (128 non-uniform bin edges) + scale max|x|
   kOneBit = 9,      // 1 bit per element (x < 0) + the means of the negative and of the other elements
   kFP16 = 10,       // half-precision values, summed in fp32
+  kQSGDX = 12,      // QSGD with any bucket size and up to 32767 levels: int16 codes + one fp32 norm per bucket
   kRandomK = 11,    // k positions drawn with replacement from Philox(seed, step), the same on every rank: only values travel
 };
 
@@ -71,7 +72,8 @@ struct Args {
   float lr;              // kEFSign
   float mom_beta;        // kSign with momentum
   int first_step;
-  int quantum;           // kQSGD levels (< 128)
+  int quantum;           // kQSGD levels (< 128); kQSGDX levels (< 32768)
+  int bucket;            // kQSGDX: elements per bucket
   uint64_t seed;
   unsigned step;
 };

@@ -65,7 +65,7 @@ float pseudo(int rank, int step, long long i) {   // deterministic test gradient
 int run_codec(int codec, int world, long long n, int steps) {
   const long long k = codec == kTopK ? std::max<long long>(1, n / 50)
                       : (codec == kThreshold ? std::max<long long>(1, n / 4) : (codec == kRandomK ? std::max<long long>(1, n / 20) : 0));
-  const size_t sb = slot_bytes(codec, n, k);
+  const size_t sb = slot_bytes(codec, n, codec == kQSGDX ? 100 : k);
   World w{world, 2 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
   for (int r = 0; r < world; ++r) {
     void* p = heap_new(w.heap_bytes);
@@ -89,7 +89,7 @@ int run_codec(int codec, int world, long long n, int steps) {
         a.u = nullptr; a.out = outs[r].data(); a.n = n; a.k = k;
         a.beta = s == 0 ? 0.f : 1.f; a.gamma = 1.f; a.scale = 1.f / (float)world; a.threshold = 5e-4f; a.strict = 0;
         a.lr = 0.1f; a.mom_beta = 0.9f; a.first_step = s == 0; a.quantum = 64; a.seed = 77; a.step = (unsigned)s;
-        a.momentum = 0.f; a.deterministic = 0;
+        a.momentum = 0.f; a.deterministic = 0; a.bucket = 100;
         // split phases on odd steps: publish first, pull later (what send_step / receive_step do)
         unsigned code;
         if (s & 1) {
@@ -188,7 +188,7 @@ int main(int argc, char** argv) {
   if (argc > 1 && std::string(argv[1]) == "broken") return run_broken_publish();
   const int world = argc > 1 ? std::atoi(argv[1]) : 4;
   const int steps = argc > 2 ? std::atoi(argv[2]) : 12;
-  const int codecs[] = {kTopK, kThreshold, kQSGD, kSign, kEFSign, kDense, kTernGrad, kNatural, kU8bit, kOneBit, kFP16, kRandomK};
+  const int codecs[] = {kTopK, kThreshold, kQSGD, kSign, kEFSign, kDense, kTernGrad, kNatural, kU8bit, kOneBit, kFP16, kRandomK, kQSGDX};
   for (int codec : codecs) {
     for (long long n : {1ll, 127ll, 4099ll}) {
       const int rc = run_codec(codec, world, n, steps);
@@ -197,6 +197,6 @@ int main(int argc, char** argv) {
   }
   if (const int rc = run_timeout()) { std::fprintf(stderr, "time-out scenario: failure %d\n", rc); return 1; }
   if (const int rc = run_shm()) { std::fprintf(stderr, "shared-memory calls: failure %d\n", rc); return 1; }
-  std::printf("host protocol: %d ranks x %d steps x 12 codecs x 3 sizes ok, time-out reported\n", world, steps);
+  std::printf("host protocol: %d ranks x %d steps x 13 codecs x 3 sizes ok, time-out reported\n", world, steps);
   return 0;
 }

@@ -599,3 +599,22 @@ def test_randomk_positions_from_philox_and_values_only():
     assert len(set(pos.tolist())) < k             # the case has repeated positions
     torch.testing.assert_close(grcs[0].state_dict()["memory"]["residuals"]["fc.weight"], res[0], rtol=1e-6, atol=1e-10)
     assert grcs[0].stats()["compression_ratio"] == pytest.approx(1 / ratio, rel=0.01)
+
+
+def test_general_qsgd_buckets_and_levels():
+    """Bucket sizes other than 128 and 128 levels or more (int16 codes): bound, identity and the Philox stream."""
+    from grace_b200.communicator.host import _name_seed
+    from grace_b200.utils import philox
+
+    n, q, bucket = 1000, 512, 100
+    x = torch.randn(n, generator=torch.Generator().manual_seed(9)) * 1e-2
+    outs, grcs = _run_ranks(1, lambda: (C_.QSGDCompressor(q, bucket), M_.ResidualMemory()), [[x]])
+    xb = x.view(-1, bucket)
+    norms = torch.stack([b.pow(2).sum(dtype=torch.float32).sqrt() for b in xb])
+    u = torch.from_numpy(philox.uniform(n, _name_seed(0, "w" + str((n + 127) // 128 * 128)), 0, 0)).view(-1, bucket)
+    lf = (q / norms)[:, None] * xb.abs()
+    want = (norms / q)[:, None] * (torch.floor(lf) + (u < lf - torch.floor(lf)).float()) * torch.sign(xb)
+    diff = (outs[0][0].view(-1, bucket) - want).abs()
+    assert float((diff > 1e-7).float().mean()) < 0.01
+    assert bool((diff <= (norms / q)[:, None] * 1.001).all())
+    torch.testing.assert_close(outs[0][0] + grcs[0].state_dict()["memory"]["residuals"]["w"], x, rtol=1e-5, atol=1e-9)

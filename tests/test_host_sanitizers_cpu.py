@@ -1,6 +1,6 @@
 """Sanitizer builds of the host engine of the exchange protocol.
 
-``tests/native/host_protocol_sanitize.cpp`` runs W ranks as threads over one copy of every rank's heap, all twelve
+``tests/native/host_protocol_sanitize.cpp`` runs W ranks as threads over one copy of every rank's heap, all thirteen
 codecs, three sizes, twelve steps with ranks de-synchronised on purpose and split phases on odd steps.  Built with
 ThreadSanitizer the run must be free of data races (the flags are atomics, slots and error-feedback arrays are
 plain memory: a slot rewritten while a peer reads it, or read before its flag, would be reported); built with
@@ -54,7 +54,7 @@ def test_thread_sanitizer_finds_no_race_in_the_protocol_but_finds_a_planted_one(
     exe = _build(tmp_path, "thread")
     res = subprocess.run([exe, "4", "12"], capture_output=True, text=True, timeout=600, env=_env())
     assert res.returncode == 0 and "data race" not in res.stderr, res.stdout[-1000:] + res.stderr[-3000:]
-    assert "12 codecs" in res.stdout
+    assert "13 codecs" in res.stdout
     bad = subprocess.run([exe, "broken"], capture_output=True, text=True, timeout=600, env=_env())
     assert bad.returncode != 0 and "data race" in bad.stderr, "the planted race went unreported"
 
