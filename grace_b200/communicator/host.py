@@ -61,6 +61,12 @@ class DistWorld:
         if self.world > 1:
             dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         self.token = box[0]
+        self._serial = 0
+
+    def next_serial(self) -> int:
+        """Number of the next heap these ranks create together (part of its shared-memory name)."""
+        self._serial += 1
+        return self._serial
 
     def barrier(self):
         if self.world > 1:
@@ -75,6 +81,7 @@ class ThreadWorld:
         self.world = int(world)
         self.token = uuid.uuid4().hex[:12]
         self._barrier = threading.Barrier(self.world)
+        self._serials = [0] * self.world   # heaps created so far, per rank (all ranks create them in the same order)
 
     def view(self, rank: int) -> "_ThreadRank":
         return _ThreadRank(self, rank)
@@ -111,6 +118,10 @@ class _ThreadRank:
     def __init__(self, owner: ThreadWorld, rank: int):
         self.owner, self.rank, self.world, self.token = owner, rank, owner.world, owner.token
 
+    def next_serial(self) -> int:
+        self.owner._serials[self.rank] += 1
+        return self.owner._serials[self.rank]
+
     def barrier(self):
         self.owner._barrier.wait(timeout=60.0)
 
@@ -121,12 +132,13 @@ class HostHeap:
     ranks drive with the same requests.  The names are unlinked as soon as everybody has mapped them, so nothing
     stays behind in ``/dev/shm`` when a rank dies."""
 
-    def __init__(self, nbytes: int, world, serial: int):
+    def __init__(self, nbytes: int, world):
         from ..ops import native
 
         self._C = native()
         self.nbytes = (int(nbytes) + 4095) // 4096 * 4096
         self.rank, self.world = world.rank, world.world
+        serial = world.next_serial()   # the same number on every rank: heaps are created in the same order
 
         def name(r):
             return "/grace_%s_%d_%d" % (world.token, serial, r)
@@ -287,7 +299,7 @@ class HostExchange(Communicator):
         world = self._meet()
         if self._heaps and self._heaps[-1].nbytes - self._heaps[-1]._cursor >= nbytes + _ALIGN:
             return self._heaps[-1]
-        heap = HostHeap(max(self.arena_bytes, nbytes + 4096), world, serial=len(self._heaps) + 1000 * self._epoch)
+        heap = HostHeap(max(self.arena_bytes, nbytes + 4096), world)
         self._heaps.append(heap)
         return heap
 
