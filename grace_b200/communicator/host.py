@@ -21,7 +21,8 @@ the momentum-corrected DGC memory (exact k-th magnitude, no clipping), QSGD
 (any bucket size, up to 32767 levels), TernGrad, natural compression (the
 CUDA extension's code table; stochastic or deterministic), 8-bit, 1-bit and
 fp16 with none or residual memory, signSGD / signum, EF-signSGD with its
-memory, and no compression.  Stochastic codecs draw the Philox stream of the
+memory, PowerSGD (ranks up to 16, with or without its error-feedback memory;
+1-D tensors travel uncompressed) and no compression.  Stochastic codecs draw the Philox stream of the
 GPU path.  Anything else uses the library ``Allgather`` path.
 
 The reference's CPU ranks meet only inside Gloo collectives
@@ -45,7 +46,7 @@ from ..core import Communicator
 from .allgather import Allgather
 
 PHASE_COMPRESS, PHASE_PUBLISH, PHASE_EXCHANGE, PHASE_ALL = 1, 2, 4, 7
-TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16, RANDOMK, QSGDX = range(13)
+TOPK, THRESHOLD, QSGD, SIGN, EFSIGN, DENSE, TERNGRAD, NATURAL, U8BIT, ONEBIT, FP16, RANDOMK, QSGDX, LOWRANK = range(14)
 _ALIGN = 64
 
 
@@ -184,33 +185,65 @@ class HostHeap:
 class _HostPlan:
     """Flags, status block and two send slots of one tensor, plus its error-feedback state."""
 
-    def __init__(self, owner: "HostExchange", name: str, numel: int):
+    def __init__(self, owner: "HostExchange", name: str, numel: int, codec: Optional[int] = None, shape=None):
         C = owner._C
         self.name, self.numel = name, numel
         comp = owner.compressor
+        self.codec = codec = owner._codec if codec is None else codec
         self.k = 0
-        if owner._codec in (TOPK, RANDOMK):
+        if codec == LOWRANK:
+            self._init_lowrank(owner, shape)
+            return
+        if codec in (TOPK, RANDOMK):
             self.k = topk_count(numel, comp.compress_ratio)
-        elif owner._codec == THRESHOLD:
+        elif codec == THRESHOLD:
             self.k = max(1, int(numel * owner.max_ratio))
-        self.bucket = int(getattr(comp, "bucket_size", 0)) if owner._codec == QSGDX else 0
-        self.slot_bytes = C.host_slot_bytes(owner._codec, numel, self.bucket if owner._codec == QSGDX else self.k)
-        need = 2 * C.HOST_MAX_WORLD * 8 + 64 + 2 * self.slot_bytes + 6 * _ALIGN
-        heap = self.heap = owner._heap_with_room(need)
-        self.flag_words = 2 * C.HOST_MAX_WORLD
-        self.ready_off = heap.alloc(self.flag_words * 8)   # ready[MAX_WORLD] followed by ack[MAX_WORLD]
-        self.ack_off = self.ready_off + C.HOST_MAX_WORLD * 8
-        self.status_off = heap.alloc(64)
-        self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+        self.bucket = int(getattr(comp, "bucket_size", 0)) if codec == QSGDX else 0
+        self.slot_bytes = C.host_slot_bytes(codec, numel, self.bucket if codec == QSGDX else self.k)
+        self._carve(owner, flag_pads=2)
         # the key of the random stream: as the GPU path derives it for a single tensor (name and padded length)
         self.seed = _name_seed(owner.seed, name + str((numel + 127) // 128 * 128))
-        if owner._codec == RANDOMK:   # the positions are keyed by the tensor's name alone, as on the GPU
+        if codec == RANDOMK:   # the positions are keyed by the tensor's name alone, as on the GPU
             self.seed = _name_seed(owner.seed, name)
         self.seq = 0          # sequence number of the last exchange started
         self.steps = 0
-        self.acc = torch.zeros(numel, dtype=torch.float32) if owner._needs_acc else None
+        plain_dense = codec == DENSE and owner._codec == LOWRANK   # a 1-D tensor next to PowerSGD matrices
+        self.acc = torch.zeros(numel, dtype=torch.float32) if (owner._needs_acc and not plain_dense) else None
         self.mom = torch.zeros(numel, dtype=torch.float32) if owner._needs_mom else None
         self.u = torch.zeros(numel, dtype=torch.float32) if owner._needs_u else None
+
+    def _carve(self, owner, flag_pads: int):
+        """Flag pads (ready, ack and, for the low-rank exchange, the second rendezvous), status block, two slots."""
+        C = owner._C
+        need = flag_pads * C.HOST_MAX_WORLD * 8 + 64 + 2 * self.slot_bytes + 8 * _ALIGN
+        heap = self.heap = owner._heap_with_room(need)
+        self.flag_words = flag_pads * C.HOST_MAX_WORLD
+        self.ready_off = heap.alloc(self.flag_words * 8)   # ready[MAX_WORLD], ack[MAX_WORLD] (, ready2[MAX_WORLD])
+        self.ack_off = self.ready_off + C.HOST_MAX_WORLD * 8
+        self.ready2_off = self.ready_off + 2 * C.HOST_MAX_WORLD * 8 if flag_pads > 2 else 0
+        self.status_off = heap.alloc(64)
+        self.slot_off = [heap.alloc(self.slot_bytes), heap.alloc(self.slot_bytes)]
+
+    def _init_lowrank(self, owner, shape):
+        """PowerSGD on one matrix: rows = shape[0], columns = the rest; Q starts from the orthogonalised N(0, 1)
+        draw the GPU path uses (same seed: identical on every rank)."""
+        import zlib
+
+        from ..ops.lowrank import orthogonal_init
+
+        self.rows = int(shape[0])
+        self.cols = self.numel // self.rows
+        self.rank = min(self.rows, self.cols, int(owner.compressor.rank))
+        self.slot_bytes = owner._C.host_lowrank_slot_bytes(self.rows, self.cols, self.rank)
+        self._carve(owner, flag_pads=3)
+        self.seed = 0
+        self.seq = self.steps = 0
+        self.bucket = 0
+        self.acc = torch.zeros(self.numel, dtype=torch.float32) if isinstance(owner.memory, M_.PowerSGDMemory) else None
+        self.mom = self.u = None
+        self.q = orthogonal_init(self.cols, self.rank, owner.seed ^ zlib.crc32(self.name.encode("utf8")),
+                                 "cpu").contiguous()
+        self.p_work = torch.zeros(self.rows * self.rank, dtype=torch.float32)
 
     def status(self) -> np.ndarray:
         return self.heap.view(self.status_off, 8, np.uint32)
@@ -256,7 +289,11 @@ class HostExchange(Communicator):
         self._needs_u = isinstance(mem, M_.DgcMemory)
         self._needs_mom = isinstance(comp, C_.SignumCompressor)
         plain = isinstance(mem, (M_.NoneMemory, M_.ResidualMemory))
-        if isinstance(mem, M_.DgcMemory):
+        if isinstance(comp, C_.PowerSGDCompressor):
+            if isinstance(mem, (M_.PowerSGDMemory, M_.NoneMemory)) and 1 <= int(comp.rank) <= 16:
+                self._codec = LOWRANK
+                self._needs_acc = False   # the low-rank plans own their residual; 1-D tensors travel uncompressed
+        elif isinstance(mem, M_.DgcMemory):
             if isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and not getattr(mem, "gradient_clipping", False):
                 self._codec = TOPK
         elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and plain:
@@ -307,13 +344,17 @@ class HostExchange(Communicator):
         """Create the plans now, in name order (heap creation is collective; gradient hooks may fire in any order)."""
         for name, t in sorted(((n, t) for n, t in named_tensors), key=lambda kv: kv[0]):
             if self.supported(t):
-                self._plan(name, t.numel())
+                self._plan(name, t.numel(), tuple(t.shape))
 
-    def _plan(self, name: str, numel: int) -> _HostPlan:
+    def _plan(self, name: str, numel: int, shape=None) -> _HostPlan:
         key = (name, numel)
         plan = self._plans.get(key)
         if plan is None:
-            plan = self._plans[key] = _HostPlan(self, name, numel)
+            codec = None
+            if self._codec == LOWRANK:   # matrices are compressed, 1-D tensors are exchanged as they are
+                matrix = shape is not None and len(shape) >= 2 and int(shape[0]) >= 1 and numel // int(shape[0]) >= 1
+                codec = LOWRANK if matrix else DENSE
+            plan = self._plans[key] = _HostPlan(self, name, numel, codec, shape)
             if self._pending_state:
                 self._restore_plan(plan, self._pending_state)
         return plan
@@ -337,9 +378,19 @@ class HostExchange(Communicator):
             phases &= ~PHASE_PUBLISH   # host-side fault injection: this rank "forgets" to publish
         beta, gamma = self._coeffs(plan)
         heap = plan.heap
+        if plan.codec == LOWRANK:
+            rc = self._C.host_lowrank_exchange(
+                world.rank, world.world, heap.bases, plan.ready_off, plan.ack_off, plan.status_off, plan.slot_off[0],
+                plan.slot_off[1], plan.slot_bytes, int(self.timeout_ms * 1e6), plan.ready2_off, phases, plan.seq,
+                g.data_ptr(), plan.acc.data_ptr() if plan.acc is not None else 0, out.data_ptr(), plan.q.data_ptr(),
+                plan.p_work.data_ptr(), plan.rows, plan.cols, plan.rank)
+            if rc != 0:
+                st = plan.status()
+                raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)
+            return
         rc = self._C.host_exchange(
             world.rank, world.world, heap.bases, plan.ready_off, plan.ack_off, plan.status_off, plan.slot_off[0],
-            plan.slot_off[1], plan.slot_bytes, int(self.timeout_ms * 1e6), self._codec, phases, plan.seq,
+            plan.slot_off[1], plan.slot_bytes, int(self.timeout_ms * 1e6), plan.codec, phases, plan.seq,
             g.data_ptr(), plan.acc.data_ptr() if plan.acc is not None else 0,
             plan.mom.data_ptr() if plan.mom is not None else 0, out.data_ptr(), plan.numel, plan.k, beta, gamma,
             (1.0 / self.world_size) if comp.average else 1.0, float(getattr(comp, "threshold", 0.0)),
@@ -353,9 +404,11 @@ class HostExchange(Communicator):
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)
 
     def _payload_bytes(self, plan: _HostPlan) -> int:
-        if self._codec == RANDOMK:
+        if plan.codec == LOWRANK:
+            return 4 * (plan.rows + plan.cols) * plan.rank
+        if plan.codec == RANDOMK:
             return 4 * plan.k
-        return 8 * plan.k if self._codec in (TOPK, THRESHOLD) else int(plan.slot_bytes)
+        return 8 * plan.k if plan.codec in (TOPK, THRESHOLD) else int(plan.slot_bytes)
 
     def step(self, tensor: torch.Tensor, name: str) -> torch.Tensor:
         handles, ctx = self.send_step(tensor, name)
@@ -366,7 +419,7 @@ class HostExchange(Communicator):
         if not self.supported(tensor):
             return self._fallback.send_step(tensor, name)
         g = tensor.detach().reshape(-1).to(torch.float32).contiguous()
-        plan = self._plan(name, g.numel())
+        plan = self._plan(name, g.numel(), tuple(tensor.shape))
         plan.seq += 1
         self._stats["steps"] += 1
         self._stats["dense_bytes"] += 4 * plan.numel
@@ -476,6 +529,9 @@ class HostExchange(Communicator):
         momentums = {p.name: p.mom.clone() for p in self._plans.values() if p.mom is not None}
         if momentums:
             comp["momentums"] = momentums
+        q_memory = {p.name: p.q.clone() for p in self._plans.values() if p.codec == LOWRANK}
+        if q_memory:
+            comp["q_memory"] = q_memory   # [columns x rank], the reference's shape
         mem = {"residuals": residuals}
         if gradients:
             mem["gradients"] = gradients
@@ -500,6 +556,9 @@ class HostExchange(Communicator):
         if plan.mom is not None and plan.name in moms:
             plan.mom.copy_(moms[plan.name].reshape(-1).to(torch.float32))
             plan.steps = max(plan.steps, 1)
+        qs = state.get("compressor", {}).get("q_memory", {})
+        if plan.codec == LOWRANK and plan.name in qs and tuple(qs[plan.name].shape) == (plan.cols, plan.rank):
+            plan.q.copy_(qs[plan.name].to(torch.float32))
         plan.steps = max(plan.steps, int(state.get("host_steps", {}).get(plan.name, 0)))
 
 

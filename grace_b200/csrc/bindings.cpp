@@ -292,6 +292,31 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
   m.def("host_heap_close", [](uintptr_t base, size_t bytes) { return host::heap_close(ptr<void>(base), bytes); });
   m.def("host_heap_unlink", [](const std::string& name) { return host::heap_unlink(name.c_str()); });
   m.def("host_slot_bytes", &host::slot_bytes);
+  m.def("host_lowrank_slot_bytes", &host::lowrank_slot_bytes);
+  m.def("host_lowrank_exchange",
+        [](int rank, int world, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
+           unsigned long long ack_off, unsigned long long status_off, unsigned long long slot0_off,
+           unsigned long long slot1_off, unsigned long long slot_bytes, unsigned long long timeout_ns,
+           unsigned long long ready2_off, int phases, unsigned long long seq, uintptr_t g, uintptr_t acc, uintptr_t out,
+           uintptr_t q, uintptr_t p_work, int rows, int cols, int lr_rank) {
+          if (world < 1 || world > host::kMaxWorld || (int)heaps.size() != world || rank < 0 || rank >= world)
+            throw std::invalid_argument("bad rank/world/heap table");
+          host::Channel ch{};
+          ch.rank = rank; ch.world = world;
+          for (int i = 0; i < world; ++i) ch.heap[i] = reinterpret_cast<char*>(heaps[i]);
+          ch.ready_off = ready_off; ch.ack_off = ack_off; ch.status_off = status_off;
+          ch.slot_off[0] = slot0_off; ch.slot_off[1] = slot1_off; ch.slot_bytes = slot_bytes; ch.timeout_ns = timeout_ns;
+          host::LowRankArgs a{};
+          a.phases = phases; a.seq = seq; a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.out = ptr<float>(out);
+          a.q = ptr<float>(q); a.p_work = ptr<float>(p_work); a.rows = rows; a.cols = cols; a.rank = lr_rank;
+          a.ready2_off = ready2_off;
+          unsigned rc;
+          {
+            py::gil_scoped_release release;
+            rc = host::lowrank_exchange(ch, a);
+          }
+          return rc;
+        });
   m.def("host_exchange",
         [](int rank, int world, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
            unsigned long long ack_off, unsigned long long status_off, unsigned long long slot0_off,

@@ -615,6 +615,135 @@ unsigned exchange(const Channel& ch, const Args& a) {
   return kOk;
 }
 
+size_t lowrank_slot_bytes(int rows, int cols, int rank) {
+  return (kSlotHeaderBytes + ((size_t)rows + (size_t)cols) * (size_t)rank * 4 + 63) / 64 * 64;
+}
+
+unsigned lowrank_exchange(const Channel& ch, const LowRankArgs& a) {
+  if (ch.world < 1 || ch.world > kMaxWorld || ch.rank < 0 || ch.rank >= ch.world || a.seq < 1 || !a.g || !a.out || !a.q ||
+      !a.p_work || a.rows < 1 || a.cols < 1 || a.rank < 1 || a.rank > 16 || a.rank > a.rows || a.rank > a.cols)
+    return kBadArgument;
+  char* mine = ch.heap[ch.rank];
+  const StatusBlock st{reinterpret_cast<unsigned*>(mine + ch.status_off)};
+  if (st.failed()) return st.code();
+  if (lowrank_slot_bytes(a.rows, a.cols, a.rank) > ch.slot_bytes) {
+    st.fail(kSlotOverflow, 0, (unsigned)a.seq);
+    return st.code();
+  }
+  const int n = a.rows, m = a.cols, r = a.rank;
+  const unsigned parity = (unsigned)(a.seq & 1);
+  auto slot_p = [&](int p) { return reinterpret_cast<float*>(ch.heap[p] + ch.slot_off[parity] + kSlotHeaderBytes); };
+  auto slot_q = [&](int p) { return slot_p(p) + (size_t)n * r; };
+  const float inv_world = 1.f / (float)ch.world;
+  // without error feedback M' is the gradient itself
+  const float* mprime = a.acc ? a.acc : a.g;
+
+  if (a.phases & kCompress) {
+    if (a.seq > 2) {
+      const uint64_t* ack = reinterpret_cast<const uint64_t*>(mine + ch.ack_off);
+      for (int p = 0; p < ch.world; ++p)
+        if (p != ch.rank && !wait_flag_ge(ack + p, a.seq - 2, ch.timeout_ns, st, kTimeoutPeerAck, (unsigned)p))
+          return st.code();
+    }
+    if (a.acc)
+      for (size_t i = 0; i < (size_t)n * m; ++i) a.acc[i] += a.g[i];   // M' = g + residual
+    float* P = slot_p(ch.rank);
+    for (int i = 0; i < n; ++i) {                                      // P = M' Q
+      float accum[16] = {};
+      const float* row = mprime + (size_t)i * m;
+      for (int j = 0; j < m; ++j) {
+        const float v = row[j];
+        const float* qj = a.q + (size_t)j * r;
+        for (int c = 0; c < r; ++c) accum[c] += v * qj[c];
+      }
+      for (int c = 0; c < r; ++c) P[(size_t)i * r + c] = accum[c];
+    }
+  }
+  if (a.phases & kPublish) {
+    for (int p = 0; p < ch.world; ++p)
+      store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ready_off) + ch.rank, a.seq);
+  }
+  if (!(a.phases & kExchange)) return kOk;
+
+  // ---- mean of P over the ranks (rank order), orthogonalisation ----
+  const uint64_t* ready = reinterpret_cast<const uint64_t*>(mine + ch.ready_off);
+  for (int p = 0; p < ch.world; ++p)
+    if (!wait_flag_ge(ready + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+  float* P = a.p_work;
+  for (size_t i = 0; i < (size_t)n * r; ++i) {
+    float s = 0.f;
+    for (int p = 0; p < ch.world; ++p) s += slot_p(p)[i];
+    P[i] = s * inv_world;
+  }
+  double gram[16][16] = {}, R[16][16] = {}, inv[16][16] = {};
+  for (int i = 0; i < n; ++i)
+    for (int c = 0; c < r; ++c)
+      for (int d = c; d < r; ++d) gram[c][d] += (double)P[(size_t)i * r + c] * (double)P[(size_t)i * r + d];
+  for (int j = 0; j < r; ++j)                       // upper Cholesky factor: R^T R = Gram
+    for (int i = 0; i <= j; ++i) {
+      double s = gram[i][j];
+      for (int k = 0; k < i; ++k) s -= R[k][i] * R[k][j];
+      if (i == j) R[i][j] = s > 0.0 ? std::sqrt(s) : 0.0;
+      else R[i][j] = R[i][i] > 0.0 ? s / R[i][i] : 0.0;
+    }
+  for (int j = 0; j < r; ++j) {                     // its inverse by back substitution
+    if (R[j][j] > 0.0) inv[j][j] = 1.0 / R[j][j];
+    for (int i = j - 1; i >= 0; --i) {
+      double s = 0.0;
+      for (int k = i + 1; k <= j; ++k) s += R[i][k] * inv[k][j];
+      inv[i][j] = R[i][i] > 0.0 ? -s / R[i][i] : 0.0;
+    }
+  }
+  for (int i = 0; i < n; ++i) {                     // P <- P R^-1
+    float v[16];
+    for (int c = 0; c < r; ++c) v[c] = P[(size_t)i * r + c];
+    for (int c = 0; c < r; ++c) {
+      double s = 0.0;
+      for (int k = 0; k <= c; ++k) s += (double)v[k] * inv[k][c];
+      P[(size_t)i * r + c] = (float)s;
+    }
+  }
+
+  // ---- Q = M'^T P, published through the second flag pad ----
+  float* Q = slot_q(ch.rank);
+  std::memset(Q, 0, (size_t)m * r * 4);
+  for (int i = 0; i < n; ++i) {
+    const float* row = mprime + (size_t)i * m;
+    const float* pi = P + (size_t)i * r;
+    for (int j = 0; j < m; ++j) {
+      const float v = row[j];
+      float* qj = Q + (size_t)j * r;
+      for (int c = 0; c < r; ++c) qj[c] += v * pi[c];
+    }
+  }
+  for (int p = 0; p < ch.world; ++p)
+    store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + a.ready2_off) + ch.rank, a.seq);
+  const uint64_t* ready2 = reinterpret_cast<const uint64_t*>(mine + a.ready2_off);
+  for (int p = 0; p < ch.world; ++p)
+    if (!wait_flag_ge(ready2 + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+  for (size_t i = 0; i < (size_t)m * r; ++i) {
+    float s = 0.f;
+    for (int p = 0; p < ch.world; ++p) s += slot_q(p)[i];
+    a.q[i] = s * inv_world;                          // also the start of the next step
+  }
+  for (int p = 0; p < ch.world; ++p)                 // both regions of every slot of this sequence have been read
+    if (p != ch.rank) store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ack_off) + ch.rank, a.seq);
+
+  // ---- out = P Q^T, residual = M' - out ----
+  for (int i = 0; i < n; ++i) {
+    const float* pi = P + (size_t)i * r;
+    for (int j = 0; j < m; ++j) {
+      const float* qj = a.q + (size_t)j * r;
+      float o = 0.f;
+      for (int c = 0; c < r; ++c) o += pi[c] * qj[c];
+      const size_t at = (size_t)i * m + j;
+      if (a.acc) a.acc[at] = a.acc[at] - o;          // M' lives in acc
+      a.out[at] = o;
+    }
+  }
+  return kOk;
+}
+
 void* heap_create(const char* name, size_t bytes) {
   const int fd = shm_open(name, O_CREAT | O_RDWR | O_TRUNC, 0600);
   if (fd < 0) return nullptr;

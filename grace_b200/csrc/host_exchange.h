@@ -78,6 +78,25 @@ struct Args {
   unsigned step;
 };
 
+// PowerSGD (compressor/powersgd.py:21-65 and memory/powersgd.py:12-37 of the reference) for one matrix: P = M' Q with
+// M' = g + residual, mean of P over the ranks, orthogonalisation (Cholesky factor of P^T P in fp64: what modified
+// Gram-Schmidt computes in exact arithmetic; a dependent direction is dropped), Q = M'^T P, mean of Q over the ranks
+// (kept as the next step's start), out = P Q^T, residual = M' - out.  Two rendezvous per exchange: the slot holds
+// P [rows x rank] followed by Q [cols x rank]; the second one uses the flag pad at ready2_off.
+struct LowRankArgs {
+  int phases;            // kCompress | kPublish: up to the publication of P; kExchange: everything after it
+  uint64_t seq;
+  const float* g;        // [rows x cols], row-major
+  float* acc;            // residual [rows x cols] or null (no error feedback); holds M' between the two phases
+  float* out;            // [rows x cols] (may alias g)
+  float* q;              // [cols x rank]: start of this step in, mean Q out
+  float* p_work;         // [rows x rank] scratch that survives between the phases (the orthogonalised P)
+  int rows, cols, rank;
+  uint64_t ready2_off;   // u64[kMaxWorld] in every heap
+};
+size_t lowrank_slot_bytes(int rows, int cols, int rank);
+unsigned lowrank_exchange(const Channel& ch, const LowRankArgs& args);
+
 size_t slot_bytes(int codec, long long n, long long k);
 
 // Runs the phases named by args.phases; returns the status code (0 = ok).  On a timeout the code, the peer and

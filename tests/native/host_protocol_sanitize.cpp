@@ -133,6 +133,57 @@ int run_timeout() {
   return bad;
 }
 
+// PowerSGD: two rendezvous per exchange (P, then Q through the second flag pad), warm-started Q, error feedback.
+int run_lowrank(int world, int steps) {
+  const int rows = 24, cols = 20, rank = 3;
+  const size_t sb = lowrank_slot_bytes(rows, cols, rank);
+  World w{world, 3 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
+  for (int r = 0; r < world; ++r) {
+    w.base.push_back(heap_new(w.heap_bytes));
+    if (!w.base.back()) return 2;
+  }
+  std::vector<std::vector<float>> outs(world, std::vector<float>((size_t)rows * cols));
+  std::vector<int> rc(world, 0);
+  std::vector<std::thread> threads;
+  for (int r = 0; r < world; ++r) {
+    threads.emplace_back([&, r] {
+      Channel ch{};
+      ch.rank = r; ch.world = world;
+      for (int p = 0; p < world; ++p) ch.heap[p] = static_cast<char*>(w.base[p]);
+      ch.ready_off = 0; ch.ack_off = kMaxWorld * 8; ch.status_off = 3 * kMaxWorld * 8;
+      ch.slot_off[0] = 3 * kMaxWorld * 8 + 64; ch.slot_off[1] = ch.slot_off[0] + sb; ch.slot_bytes = sb;
+      ch.timeout_ns = 20ull * 1000000000ull;
+      std::vector<float> g((size_t)rows * cols), acc((size_t)rows * cols, 0.f), q((size_t)cols * rank), pw((size_t)rows * rank);
+      for (size_t i = 0; i < q.size(); ++i) q[i] = pseudo(99, 0, (long long)i) * 500.f;   // the same start on every rank
+      for (int s = 0; s < steps; ++s) {
+        for (size_t i = 0; i < g.size(); ++i) g[i] = pseudo(r, s, (long long)i);
+        if ((r + s) % 2 == 0) std::this_thread::sleep_for(std::chrono::microseconds(200 * (r + 1)));
+        LowRankArgs a{};
+        a.seq = (uint64_t)s + 1; a.g = g.data(); a.acc = acc.data(); a.out = outs[r].data(); a.q = q.data();
+        a.p_work = pw.data(); a.rows = rows; a.cols = cols; a.rank = rank; a.ready2_off = 2 * kMaxWorld * 8;
+        unsigned code;
+        if (s & 1) {
+          a.phases = kCompress | kPublish;
+          code = lowrank_exchange(ch, a);
+          if (code == kOk) { a.phases = kExchange; code = lowrank_exchange(ch, a); }
+        } else {
+          a.phases = kAll;
+          code = lowrank_exchange(ch, a);
+        }
+        if (code != kOk) { rc[r] = 10 + (int)code; return; }
+        for (float v : outs[r]) if (!std::isfinite(v)) { rc[r] = 3; return; }
+      }
+    });
+  }
+  for (auto& t : threads) t.join();
+  int bad = 0;
+  for (int r = 0; r < world; ++r) bad |= rc[r];
+  for (int r = 1; r < world && !bad; ++r)
+    if (std::memcmp(outs[0].data(), outs[r].data(), outs[0].size() * 4) != 0) bad = 4;
+  for (int r = 0; r < world; ++r) heap_delete(w.base[r]);
+  return bad;
+}
+
 // Negative control (argument "broken"): rank 1 raises its ready flag BEFORE it writes its slot, which is exactly
 // the error the protocol exists to prevent.  A ThreadSanitizer build must report the race between rank 1's slot
 // writes and rank 0's reads; this shows that the clean runs above are clean because of the protocol, not because
@@ -195,8 +246,9 @@ int main(int argc, char** argv) {
       if (rc) { std::fprintf(stderr, "codec %d, %lld elements: failure %d\n", codec, n, rc); return 1; }
     }
   }
+  if (const int rc = run_lowrank(world, steps)) { std::fprintf(stderr, "low-rank exchange: failure %d\n", rc); return 1; }
   if (const int rc = run_timeout()) { std::fprintf(stderr, "time-out scenario: failure %d\n", rc); return 1; }
   if (const int rc = run_shm()) { std::fprintf(stderr, "shared-memory calls: failure %d\n", rc); return 1; }
-  std::printf("host protocol: %d ranks x %d steps x 13 codecs x 3 sizes ok, time-out reported\n", world, steps);
+  std::printf("host protocol: %d ranks x %d steps x 13 codecs x 3 sizes and the low-rank exchange ok, time-out reported\n", world, steps);
   return 0;
 }

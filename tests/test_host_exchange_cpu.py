@@ -303,7 +303,7 @@ def test_split_phase_equals_step_and_checkpoint_round_trip():
 
 
 def test_unsupported_pairs_use_the_library_path():
-    grc = HostExchange(C_.PowerSGDCompressor(rank=2), M_.NoneMemory(), 1)   # low-rank has no host codec
+    grc = HostExchange(C_.SketchCompressor(64), M_.NoneMemory(), 1)   # quantile sketches have no host codec
     x = torch.randn(100)
     assert not grc.supported(x)
     assert grc.step(x, "t").shape == x.shape
@@ -618,3 +618,73 @@ def test_general_qsgd_buckets_and_levels():
     assert float((diff > 1e-7).float().mean()) < 0.01
     assert bool((diff <= (norms / q)[:, None] * 1.001).all())
     torch.testing.assert_close(outs[0][0] + grcs[0].state_dict()["memory"]["residuals"]["w"], x, rtol=1e-5, atol=1e-9)
+
+
+# ---- PowerSGD on the host engine ----
+def test_powersgd_matches_the_python_classes_from_the_same_start():
+    from grace_b200 import grace_from_params
+
+    shape, name, rank = (48, 5, 8), "conv.weight", 4
+    grads = [torch.randn(shape, generator=torch.Generator().manual_seed(3 * s + 1)) for s in range(3)]
+    params = {"compressor": "powersgd", "memory": "powersgd", "communicator": "allreduce", "compress_rank": rank,
+              "use_memory": True, "world_size": 1}
+
+    def body(view):
+        host = grace_from_params(dict(params, host_protocol=True, host_world=view))
+        host.prepare([(name, grads[0])])
+        q0 = next(iter(host._plans.values())).q.clone()
+        outs = [host.step(g.clone(), name) for g in grads]
+        bias = host.step(torch.arange(7.0), "conv.bias")          # 1-D tensors travel uncompressed
+        return q0, outs, bias, host.state_dict()
+
+    q0, got, bias, state = ThreadWorld(1).run(body)[0]
+    lib = grace_from_params(dict(params))
+    lib.compressor.q_memory[name] = q0.clone()                     # the same start as the host plan
+    for g, out in zip(grads, got):
+        want = lib.step(g.clone(), name)
+        torch.testing.assert_close(out, want, rtol=2e-4, atol=2e-5)   # Cholesky in fp64 here, Gram-Schmidt in fp32 there
+    assert torch.equal(bias, torch.arange(7.0))
+    torch.testing.assert_close(state["compressor"]["q_memory"][name], lib.compressor.q_memory[name], rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(state["memory"]["residuals"][name].view(shape), lib.memory.residuals[name].view(shape),
+                               rtol=2e-3, atol=2e-4)
+
+
+def test_powersgd_recovers_a_shared_low_rank_mean_over_ranks():
+    """Every rank's gradient is A_r B^T with the same B (rank 2 < 4): the mean is in the span PowerSGD can
+    represent, so the exchange returns it exactly; the orthogonalisation meets two dependent directions."""
+    world, n, m = 3, 40, 64
+    B = torch.randn(m, 2, generator=torch.Generator().manual_seed(1))
+    A = [torch.randn(n, 2, generator=torch.Generator().manual_seed(10 + r)) for r in range(world)]
+    grads = [[A[r] @ B.t() for r in range(world)]]
+
+    def make():
+        comp = C_.PowerSGDCompressor(rank=4, use_memory=True, world_size=world)
+        return comp, M_.PowerSGDMemory(comp.q_memory, 4)
+
+    outs, grcs = _run_ranks(world, make, grads, name="fc.weight")
+    mean = sum(grads[0]) / world
+    for r in range(world):
+        torch.testing.assert_close(outs[r][0], mean, rtol=1e-3, atol=1e-4)
+        assert torch.equal(outs[r][0], outs[0][0])                 # replicas agree bit for bit
+    # what a rank could not send stays in its residual: g_r - mean here
+    torch.testing.assert_close(grcs[1].state_dict()["memory"]["residuals"]["fc.weight"].view(n, m),
+                               grads[0][1] - outs[1][0], rtol=1e-4, atol=1e-5)
+
+
+def test_powersgd_checkpoint_continues_identically():
+    shape = (32, 24)
+    grads = [torch.randn(shape, generator=torch.Generator().manual_seed(s)) for s in range(4)]
+
+    def body(view):
+        def make():
+            comp = C_.PowerSGDCompressor(rank=2, use_memory=True, world_size=1)
+            return HostExchange(comp, M_.PowerSGDMemory(comp.q_memory, 2), 1, world=view)
+
+        a = make()
+        for g in grads[:2]:
+            a.step(g.clone(), "w")
+        b = make()
+        b.load_state_dict(a.state_dict())
+        return all(torch.equal(a.step(g.clone(), "w"), b.step(g.clone(), "w")) for g in grads[2:])
+
+    assert ThreadWorld(1).run(body) == [True]
