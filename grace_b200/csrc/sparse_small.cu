@@ -263,7 +263,11 @@ __global__ void __launch_bounds__(kSmallBlock, 1) sparse_small_kernel(const Spar
     }
     for (int i = tid; i < kSmallMax; i += kSmallBlock) sm.out[i] = 0.f;
     __syncthreads();
-    if (sm.ok && !status.failed()) {
+    // one decision for the whole CTA (the loop below has CTA barriers): a status word that another launch of the
+    // channel changes at this moment must not split the threads
+    if (tid == 0 && status.failed()) sm.ok = 0;
+    __syncthreads();
+    if (sm.ok) {
       for (int p = 0; p < world; ++p) {   // rank order: the same sums, bit for bit, on every GPU
         const char* slot = a.peers.heap[p] + a.peers.slot_off;
         unsigned count = ld_cg_u32(slot);
