@@ -221,6 +221,8 @@ class FusedExchange(Communicator):
         self._single_layouts = {}
         self._virtual = None
         self._fallback = Allgather(compressor, memory, world_size)
+        # what CPU tensors (and pairs without a kernel) go through: the library communicator, or - attach_host() -
+        # the host engine of the same protocol, which itself falls back to the library path
         from ..utils.faults import FaultPlan
 
         self._faults = FaultPlan.from_env()
@@ -261,6 +263,12 @@ class FusedExchange(Communicator):
                     self._codec = CODEC["qsgdx"]
                 else:
                     self._kind = None
+
+    def attach_host(self, host) -> "FusedExchange":
+        """Route what the kernels do not take (CPU tensors above all) through ``host`` (a ``HostExchange`` built
+        for the same compressor and memory objects) instead of the library communicator."""
+        self._fallback = host
+        return self
 
     def supported(self, tensor: torch.Tensor) -> bool:
         if self._kind == "powersgd":
@@ -321,6 +329,8 @@ class FusedExchange(Communicator):
         if self._arena is not None:
             self._arena.close()
             self._arena = None
+        if hasattr(self._fallback, "close"):   # an attached host engine
+            self._fallback.close()
 
     def _plan(self, layout) -> _Plan:
         key = getattr(layout, "_key", None)
@@ -579,6 +589,8 @@ class FusedExchange(Communicator):
                 plan.check()
             else:
                 plan.channel.check()
+        if hasattr(self._fallback, "check"):   # an attached host engine
+            self._fallback.check()
 
     # ------------------------------------------------------------------
     def state_dict(self):

@@ -105,13 +105,16 @@ def grace_from_params(params: Dict[str, Any]):
         raise NotImplementedError(comm_name)
     comp = _COMPRESSORS[comp_name](params)
     mem = _MEMORIES[mem_name](params, comp)
+    host = None
     if params.get("host_protocol", False):
         # CPU ranks: the fused exchange protocol over POSIX shared memory (csrc/host_exchange.cpp)
         from .communicator.host import HostExchange
 
-        return HostExchange(comp, mem, _world(params), world=params.get("host_world"), group=params.get("group"),
+        host = HostExchange(comp, mem, _world(params), world=params.get("host_world"), group=params.get("group"),
                             seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
                             arena_mb=params.get("arena_mb", 16), store=params.get("store"))
+        if not (params.get("fused", False) or comm_name == "fused"):
+            return host
     if params.get("fused", False) or comm_name == "fused":
         from .communicator.fused import FusedExchange
 
@@ -131,5 +134,7 @@ def grace_from_params(params: Dict[str, Any]):
             return NvlsAllreduce(comp, mem, _world(params), fallback=fused, group=params.get("group"),
                                  timeout_ms=params.get("timeout_ms", 10000), comm_sms=params.get("comm_sms"),
                                  min_world=params.get("nvls_min_world", 4))
+        if host is not None:   # both: kernels for CUDA tensors, the host engine for CPU tensors
+            fused.attach_host(host)
         return fused
     return _COMMUNICATORS[comm_name](comp, mem, params)

@@ -688,3 +688,25 @@ def test_powersgd_checkpoint_continues_identically():
         return all(torch.equal(a.step(g.clone(), "w"), b.step(g.clone(), "w")) for g in grads[2:])
 
     assert ThreadWorld(1).run(body) == [True]
+
+
+def test_fused_communicator_with_attached_host_engine_serves_cpu_tensors():
+    """``fused`` and ``host_protocol`` together: kernels for CUDA tensors, the host engine for CPU tensors."""
+    from grace_b200 import grace_from_params
+    from grace_b200.communicator.fused import FusedExchange
+
+    params = {"compressor": "topk", "memory": "residual", "communicator": "allgather", "compress_ratio": 0.05,
+              "world_size": 1}
+    grads = [torch.randn(2000, generator=torch.Generator().manual_seed(s)) for s in range(3)]
+
+    def body(view):
+        both = grace_from_params(dict(params, fused=True, host_protocol=True, host_world=view))
+        alone = grace_from_params(dict(params, host_protocol=True, host_world=view))
+        assert isinstance(both, FusedExchange) and isinstance(both._fallback, HostExchange)
+        same = all(torch.equal(both.step(g.clone(), "w"), alone.step(g.clone(), "w")) for g in grads)
+        both.check()
+        state = both.state_dict()
+        both.close()
+        return same, sorted(state["memory"]["residuals"])
+
+    assert ThreadWorld(1).run(body) == [(True, ["w"])]
