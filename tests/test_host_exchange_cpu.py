@@ -27,7 +27,7 @@ def _grads(world, n, steps, scale=1e-3):
             for s in range(steps)]
 
 
-def _run_ranks(world, make, grads, name="w", timeout_ms=5000.0, hook=None):
+def _run_ranks(world, make, grads, name="w", timeout_ms=30000.0, hook=None):
     """Every rank steps through ``grads[s][rank]``; returns per-rank lists of outputs and the communicators."""
     tw = ThreadWorld(world)
 
@@ -245,7 +245,7 @@ def test_peer_that_never_publishes_times_out_then_recovery():
 
     r0, r1 = tw.run(body)
     assert isinstance(r0[1], GraceCommError) and r0[1].code == 2 and r0[1].detail == 1 and r0[1].seq == 2
-    assert 0.25 < r0[2] < 5.0
+    assert 0.25 < r0[2] < 20.0
     # rank 1 saw its own flag missing as well (it reads its own slot through the same flags)
     assert isinstance(r1[1], GraceCommError) and r1[1].code == 2
     assert torch.equal(r0[4], r1[4])           # the exchange after the recovery agrees on both ranks
