@@ -199,8 +199,12 @@ class _HostPlan:
         elif codec == THRESHOLD:
             self.k = max(1, int(numel * owner.max_ratio))
         self.bucket = int(getattr(comp, "bucket_size", 0)) if codec == QSGDX else 0
-        self.slot_bytes = C.host_slot_bytes(codec, numel, self.bucket if codec == QSGDX else self.k)
-        self._carve(owner, flag_pads=2)
+        self.two_phase = owner.mode == "alltoall" and codec in (QSGD, NATURAL, FP16, DENSE)
+        if self.two_phase:
+            self.slot_bytes = C.host_two_phase_slot_bytes(codec, numel, owner.world_size)
+        else:
+            self.slot_bytes = C.host_slot_bytes(codec, numel, self.bucket if codec == QSGDX else self.k)
+        self._carve(owner, flag_pads=3 if self.two_phase else 2)
         # the key of the random stream: as the GPU path derives it for a single tensor (name and padded length)
         self.seed = _name_seed(owner.seed, name + str((numel + 127) // 128 * 128))
         if codec == RANDOMK:   # the positions are keyed by the tensor's name alone, as on the GPU
@@ -239,6 +243,7 @@ class _HostPlan:
         self.seed = 0
         self.seq = self.steps = 0
         self.bucket = 0
+        self.two_phase = False
         self.acc = torch.zeros(self.numel, dtype=torch.float32) if isinstance(owner.memory, M_.PowerSGDMemory) else None
         self.mom = self.u = None
         self.q = orthogonal_init(self.cols, self.rank, owner.seed ^ zlib.crc32(self.name.encode("utf8")),
@@ -256,11 +261,15 @@ class _HostPlan:
 
 class HostExchange(Communicator):
     def __init__(self, compressor, memory, world_size, world=None, group=None, seed=0, timeout_ms=10000.0,
-                 arena_mb=16, max_ratio=0.25, store=None, rank=None):
+                 arena_mb=16, max_ratio=0.25, store=None, rank=None, mode="allgather"):
         """``world``: how the ranks meet (``DistWorld`` by default: the processes of ``group``; a
         ``ThreadWorld.view(r)`` for ranks that are threads).  ``timeout_ms``: limit of every wait for a peer.
-        ``store``: a ``torch.distributed`` store for ``agree`` / ``recover`` (process ranks only)."""
+        ``store``: a ``torch.distributed`` store for ``agree`` / ``recover`` (process ranks only).  ``mode``:
+        ``"alltoall"`` selects the two-phase exchange (compressed reduce-scatter, re-encode, compressed all-gather:
+        the reference's ``AllToAll`` communicator) for QSGD with 128-element buckets, natural compression, fp16 and
+        no compression; every other codec keeps the all-gather form."""
         super().__init__(compressor, memory, world_size)
+        self.mode = mode
         from ..ops import native
         from ..utils.faults import FaultPlan
 
@@ -398,7 +407,7 @@ class HostExchange(Communicator):
             float(getattr(comp, "momentum", 0.0)), int(plan.steps == 0), int(getattr(comp, "quantum_num", 0)),
             plan.seed, plan.steps, plan.u.data_ptr() if plan.u is not None else 0,
             float(getattr(self.memory, "momentum", 0.0)), int(bool(getattr(comp, "deterministic", False))),
-            plan.bucket)
+            plan.bucket, plan.ready2_off if plan.two_phase else 0)
         if rc != 0:
             st = plan.status()
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)

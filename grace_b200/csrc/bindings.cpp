@@ -292,6 +292,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
   m.def("host_heap_close", [](uintptr_t base, size_t bytes) { return host::heap_close(ptr<void>(base), bytes); });
   m.def("host_heap_unlink", [](const std::string& name) { return host::heap_unlink(name.c_str()); });
   m.def("host_slot_bytes", &host::slot_bytes);
+  m.def("host_two_phase_slot_bytes", &host::two_phase_slot_bytes);
   m.def("host_lowrank_slot_bytes", &host::lowrank_slot_bytes);
   m.def("host_lowrank_exchange",
         [](int rank, int world, const std::vector<uintptr_t>& heaps, unsigned long long ready_off,
@@ -324,7 +325,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
            int phases, unsigned long long seq, uintptr_t g, uintptr_t acc, uintptr_t mom, uintptr_t out, long long n,
            long long k, float beta, float gamma, float scale, float threshold, int strict, float lr, float mom_beta,
            int first_step, int quantum, unsigned long long seed, unsigned step, uintptr_t u, float momentum,
-           int deterministic, int bucket) {
+           int deterministic, int bucket, unsigned long long ready2_off) {
           if (world < 1 || world > host::kMaxWorld || (int)heaps.size() != world || rank < 0 || rank >= world)
             throw std::invalid_argument("bad rank/world/heap table");
           host::Channel ch{};
@@ -337,7 +338,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
           a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
           a.n = n; a.k = k; a.beta = beta; a.gamma = gamma; a.scale = scale; a.threshold = threshold; a.strict = strict;
           a.lr = lr; a.mom_beta = mom_beta; a.first_step = first_step; a.quantum = quantum; a.seed = seed; a.step = step;
-          a.u = ptr<float>(u); a.momentum = momentum; a.deterministic = deterministic; a.bucket = bucket;
+          a.u = ptr<float>(u); a.momentum = momentum; a.deterministic = deterministic; a.bucket = bucket; a.ready2_off = ready2_off;
           unsigned rc;
           {
             py::gil_scoped_release release;   // ranks of a test may be threads of one process

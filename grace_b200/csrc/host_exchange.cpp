@@ -554,6 +554,137 @@ size_t slot_bytes(int codec, long long n, long long k) {
   return (b + 63) / 64 * 64;
 }
 
+namespace {
+
+struct Chunking {
+  long long chunk;                       // elements per chunk (a multiple of 128)
+  long long begin(int r, long long n) const { return std::min(n, chunk * r); }
+  long long end(int r, long long n) const { return std::min(n, chunk * (r + 1)); }
+};
+inline Chunking chunking(long long n, int world) {
+  const long long groups = groups128(n), per = (groups + world - 1) / world;
+  return Chunking{per * 128};
+}
+inline size_t region2_bytes(int codec, long long chunk) {
+  switch (codec) {
+    case kQSGD: return (size_t)(chunk / 128) * 4 + (size_t)chunk;
+    case kNatural: return (size_t)chunk;
+    case kFP16: return (size_t)chunk * 2;
+    default: return (size_t)chunk * 4;
+  }
+}
+inline bool two_phase_codec(int codec) { return codec == kQSGD || codec == kNatural || codec == kFP16 || codec == kDense; }
+
+// Encode the reduced chunk xs[0 .. len) (elements e0 .. e0 + len of the tensor) into region 2.
+void encode_chunk(const Args& a, char* r2, const float* xs, long long e0, long long len, long long chunk) {
+  switch (a.codec) {
+    case kQSGD: {
+      float* norms = reinterpret_cast<float*>(r2);
+      signed char* codes = reinterpret_cast<signed char*>(r2 + (size_t)(chunk / 128) * 4);
+      for (long long b = 0; b * 128 < len; ++b) {
+        const long long lo = b * 128, hi = std::min(len, lo + 128);
+        float sq = 0.f;
+        for (long long i = lo; i < hi; ++i) sq += xs[i] * xs[i];
+        const float norm = std::sqrt(sq), qn = norm > 0.f ? (float)a.quantum / norm : 0.f;
+        norms[b] = norm;
+        for (long long i = lo; i < hi; ++i) {
+          const long long gi = e0 + i;   // the random stream is indexed by the element's place in the tensor
+          const Philox4 r = philox_group((uint64_t)(gi >> 2), a.step, 1u, a.seed);
+          const unsigned w = (gi & 3) == 0 ? r.x : ((gi & 3) == 1 ? r.y : ((gi & 3) == 2 ? r.z : r.w));
+          const float lf = qn * std::fabs(xs[i]), fl = std::floor(lf);
+          const float level = std::min(fl + ((u01(w) < lf - fl) ? 1.f : 0.f), 127.f);
+          codes[i] = (signed char)(xs[i] < 0.f ? -(int)level : (int)level);
+        }
+      }
+      break;
+    }
+    case kNatural: {
+      unsigned char* codes = reinterpret_cast<unsigned char*>(r2);
+      for (long long i = 0; i < len; ++i) {
+        const long long gi = e0 + i;
+        unsigned w = 0;
+        if (!a.deterministic) {
+          const Philox4 r = philox_group((uint64_t)(gi >> 2), a.step, 1u, a.seed);
+          w = (gi & 3) == 0 ? r.x : ((gi & 3) == 1 ? r.y : ((gi & 3) == 2 ? r.z : r.w));
+        }
+        const uint32_t bits = float_bits(xs[i]), biased = (bits >> 23) & 0xffu, mant = bits & 0x7fffffu;
+        const bool up = a.deterministic ? mant > 0x400000u : u01(w) < (float)mant * 1.1920928955078125e-07f;
+        int c7 = (int)biased + (up ? 1 : 0) - 17;
+        c7 = c7 < 0 ? 0 : (c7 > 127 ? 127 : c7);
+        if (biased == 0) c7 = 0;
+        codes[i] = (unsigned char)((unsigned)c7 | ((bits >> 24) & 0x80u));
+      }
+      break;
+    }
+    case kFP16: {
+      uint16_t* h = reinterpret_cast<uint16_t*>(r2);
+      for (long long i = 0; i < len; ++i) h[i] = float_to_half(xs[i]);
+      break;
+    }
+    default:
+      if (len > 0) std::memcpy(r2, xs, (size_t)len * 4);   // a rank past the end of a short tensor owns an empty chunk
+  }
+}
+
+void decode_chunk(const Args& a, const char* r2, float* out, long long len, long long chunk) {
+  switch (a.codec) {
+    case kQSGD: {
+      const float* norms = reinterpret_cast<const float*>(r2);
+      const signed char* codes = reinterpret_cast<const signed char*>(r2 + (size_t)(chunk / 128) * 4);
+      for (long long i = 0; i < len; ++i) out[i] = norms[i >> 7] / (float)a.quantum * (float)codes[i] * a.scale;
+      break;
+    }
+    case kNatural: {
+      const unsigned char* codes = reinterpret_cast<const unsigned char*>(r2);
+      for (long long i = 0; i < len; ++i) out[i] = natural_decode(codes[i]) * a.scale;
+      break;
+    }
+    case kFP16: {
+      const uint16_t* h = reinterpret_cast<const uint16_t*>(r2);
+      for (long long i = 0; i < len; ++i) out[i] = half_to_float(h[i]) * a.scale;
+      break;
+    }
+    default: {
+      const float* v = reinterpret_cast<const float*>(r2);
+      for (long long i = 0; i < len; ++i) out[i] = v[i] * a.scale;
+    }
+  }
+}
+
+// Sum of all ranks' decoded payloads over [e0, e1) (rank order), for the codecs of the two-phase mode.
+void reduce_range(const Args& a, const SlotView& slot, float* sum, long long e0, long long e1) {
+  const char* pay = slot.payload();
+  switch (a.codec) {
+    case kQSGD: {
+      const float* norms = reinterpret_cast<const float*>(pay);
+      const signed char* codes = reinterpret_cast<const signed char*>(pay + (size_t)groups128(a.n) * 4);
+      for (long long i = e0; i < e1; ++i) sum[i - e0] += norms[i >> 7] / (float)a.quantum * (float)codes[i];
+      break;
+    }
+    case kNatural: {
+      const unsigned char* codes = reinterpret_cast<const unsigned char*>(pay);
+      for (long long i = e0; i < e1; ++i) sum[i - e0] += natural_decode(codes[i]);
+      break;
+    }
+    case kFP16: {
+      const uint16_t* h = reinterpret_cast<const uint16_t*>(pay);
+      for (long long i = e0; i < e1; ++i) sum[i - e0] += half_to_float(h[i]);
+      break;
+    }
+    default: {
+      const float* v = reinterpret_cast<const float*>(pay);
+      for (long long i = e0; i < e1; ++i) sum[i - e0] += v[i];
+    }
+  }
+}
+
+}  // namespace
+
+size_t two_phase_slot_bytes(int codec, long long n, int world) {
+  if (world < 1) world = 1;
+  return slot_bytes(codec, n, 0) + (region2_bytes(codec, chunking(n, world).chunk) + 63) / 64 * 64;
+}
+
 unsigned exchange(const Channel& ch, const Args& a) {
   if (ch.world < 1 || ch.world > kMaxWorld || ch.rank < 0 || ch.rank >= ch.world || a.n < 0 || a.seq < 1 || !a.g ||
       !a.out)
@@ -582,6 +713,34 @@ unsigned exchange(const Channel& ch, const Args& a) {
   if (a.phases & kPublish) {
     for (int p = 0; p < ch.world; ++p)
       store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ready_off) + ch.rank, a.seq);
+  }
+
+  if ((a.phases & kExchange) && a.ready2_off) {
+    // ---- two-phase mode: reduce my chunk, encode it again, publish; then decode everybody's chunk ----
+    if (!two_phase_codec(a.codec) || two_phase_slot_bytes(a.codec, a.n, ch.world) > ch.slot_bytes) {
+      st.fail(kBadArgument, 0, (unsigned)a.seq);
+      return st.code();
+    }
+    const Chunking ck = chunking(a.n, ch.world);
+    const size_t r2_off = slot_bytes(a.codec, a.n, 0);          // region 2 follows the one-phase payload
+    const uint64_t* ready = reinterpret_cast<const uint64_t*>(mine + ch.ready_off);
+    for (int p = 0; p < ch.world; ++p)
+      if (!wait_flag_ge(ready + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+    const long long e0 = ck.begin(ch.rank, a.n), e1 = ck.end(ch.rank, a.n);
+    std::vector<float> xs((size_t)std::max<long long>(e1 - e0, 0), 0.f);
+    for (int p = 0; p < ch.world; ++p) reduce_range(a, SlotView{ch.heap[p] + ch.slot_off[parity]}, xs.data(), e0, e1);
+    encode_chunk(a, mine + ch.slot_off[parity] + r2_off, xs.data(), e0, e1 - e0, ck.chunk);
+    for (int p = 0; p < ch.world; ++p)
+      store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + a.ready2_off) + ch.rank, a.seq);
+    const uint64_t* ready2 = reinterpret_cast<const uint64_t*>(mine + a.ready2_off);
+    for (int p = 0; p < ch.world; ++p) {
+      if (!wait_flag_ge(ready2 + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+      const long long b0 = ck.begin(p, a.n), b1 = ck.end(p, a.n);
+      decode_chunk(a, ch.heap[p] + ch.slot_off[parity] + r2_off, a.out + b0, b1 - b0, ck.chunk);
+    }
+    for (int p = 0; p < ch.world; ++p)
+      if (p != ch.rank) store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + ch.ack_off) + ch.rank, a.seq);
+    return kOk;
   }
 
   if (a.phases & kExchange) {

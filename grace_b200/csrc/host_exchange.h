@@ -74,6 +74,11 @@ struct Args {
   int first_step;
   int quantum;           // kQSGD levels (< 128); kQSGDX levels (< 32768)
   int bucket;            // kQSGDX: elements per bucket
+  // Two-phase mode (the reference's AllToAll communicator, communicator/all_to_all.py:29-124: compressed
+  // reduce-scatter, re-encode, compressed all-gather; kQSGD, kNatural, kFP16, kDense): rank j sums chunk j of all
+  // ranks' payloads, encodes the sum again (Philox stream 1) into the second region of its slot and publishes it
+  // through the flag pad at ready2_off; every rank then decodes the W chunks.  0 = one-phase (all-gather) mode.
+  uint64_t ready2_off;
   uint64_t seed;
   unsigned step;
 };
@@ -98,6 +103,7 @@ size_t lowrank_slot_bytes(int rows, int cols, int rank);
 unsigned lowrank_exchange(const Channel& ch, const LowRankArgs& args);
 
 size_t slot_bytes(int codec, long long n, long long k);
+size_t two_phase_slot_bytes(int codec, long long n, int world);   // both regions
 
 // Runs the phases named by args.phases; returns the status code (0 = ok).  On a timeout the code, the peer and
 // the sequence number are also left in the status words of this rank's heap.

@@ -112,7 +112,8 @@ def grace_from_params(params: Dict[str, Any]):
 
         host = HostExchange(comp, mem, _world(params), world=params.get("host_world"), group=params.get("group"),
                             seed=params.get("seed", 0), timeout_ms=params.get("timeout_ms", 10000),
-                            arena_mb=params.get("arena_mb", 16), store=params.get("store"))
+                            arena_mb=params.get("arena_mb", 16), store=params.get("store"),
+                            mode="alltoall" if comm_name == "alltoall" else "allgather")
         if not (params.get("fused", False) or comm_name == "fused"):
             return host
     if params.get("fused", False) or comm_name == "fused":

@@ -47,9 +47,9 @@ Channel channel_for(const World& w, int rank, size_t slot_bytes_, uint64_t timeo
   ch.world = w.world;
   for (int r = 0; r < w.world; ++r) ch.heap[r] = static_cast<char*>(w.base[r]);
   ch.ready_off = 0;
-  ch.ack_off = kMaxWorld * 8;
-  ch.status_off = 2 * kMaxWorld * 8;
-  ch.slot_off[0] = 2 * kMaxWorld * 8 + 64;
+  ch.ack_off = kMaxWorld * 8;                 // the third pad (second rendezvous of the two-phase mode) follows
+  ch.status_off = 3 * kMaxWorld * 8;
+  ch.slot_off[0] = 3 * kMaxWorld * 8 + 64;
   ch.slot_off[1] = ch.slot_off[0] + slot_bytes_;
   ch.slot_bytes = slot_bytes_;
   ch.timeout_ns = timeout_ns;
@@ -62,11 +62,11 @@ float pseudo(int rank, int step, long long i) {   // deterministic test gradient
   return ((float)(h & 0xffffu) / 65536.f - 0.5f) * 2e-3f;
 }
 
-int run_codec(int codec, int world, long long n, int steps) {
+int run_codec(int codec, int world, long long n, int steps, bool two_phase = false) {
   const long long k = codec == kTopK ? std::max<long long>(1, n / 50)
                       : (codec == kThreshold ? std::max<long long>(1, n / 4) : (codec == kRandomK ? std::max<long long>(1, n / 20) : 0));
-  const size_t sb = slot_bytes(codec, n, codec == kQSGDX ? 100 : k);
-  World w{world, 2 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
+  const size_t sb = two_phase ? two_phase_slot_bytes(codec, n, world) : slot_bytes(codec, n, codec == kQSGDX ? 100 : k);
+  World w{world, 3 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
   for (int r = 0; r < world; ++r) {
     void* p = heap_new(w.heap_bytes);
     if (!p) return 2;
@@ -89,7 +89,7 @@ int run_codec(int codec, int world, long long n, int steps) {
         a.u = nullptr; a.out = outs[r].data(); a.n = n; a.k = k;
         a.beta = s == 0 ? 0.f : 1.f; a.gamma = 1.f; a.scale = 1.f / (float)world; a.threshold = 5e-4f; a.strict = 0;
         a.lr = 0.1f; a.mom_beta = 0.9f; a.first_step = s == 0; a.quantum = 64; a.seed = 77; a.step = (unsigned)s;
-        a.momentum = 0.f; a.deterministic = 0; a.bucket = 100;
+        a.momentum = 0.f; a.deterministic = 0; a.bucket = 100; a.ready2_off = two_phase ? 2 * kMaxWorld * 8 : 0;
         // split phases on odd steps: publish first, pull later (what send_step / receive_step do)
         unsigned code;
         if (s & 1) {
@@ -117,7 +117,7 @@ int run_codec(int codec, int world, long long n, int steps) {
 int run_timeout() {
   const long long n = 1000;
   const size_t sb = slot_bytes(kDense, n, 0);
-  World w{2, 2 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
+  World w{2, 3 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
   for (int r = 0; r < 2; ++r) {
     w.base.push_back(heap_new(w.heap_bytes));
     if (!w.base.back()) return 2;
@@ -191,7 +191,7 @@ int run_lowrank(int world, int steps) {
 int run_broken_publish() {
   const long long n = 2000;
   const size_t sb = slot_bytes(kDense, n, 0);
-  World w{2, 2 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
+  World w{2, 3 * kMaxWorld * 8 + 64 + 2 * sb + 256, {}};
   for (int r = 0; r < 2; ++r) {
     w.base.push_back(heap_new(w.heap_bytes));
     if (!w.base.back()) return 2;
@@ -246,9 +246,14 @@ int main(int argc, char** argv) {
       if (rc) { std::fprintf(stderr, "codec %d, %lld elements: failure %d\n", codec, n, rc); return 1; }
     }
   }
+  for (int codec : {kQSGD, kNatural, kFP16, kDense})   // two-phase mode: reduce my chunk, encode again, gather
+    for (long long n : {1ll, 127ll, 4099ll}) {
+      const int rc = run_codec(codec, world, n, steps, true);
+      if (rc) { std::fprintf(stderr, "two-phase codec %d, %lld elements: failure %d\n", codec, n, rc); return 1; }
+    }
   if (const int rc = run_lowrank(world, steps)) { std::fprintf(stderr, "low-rank exchange: failure %d\n", rc); return 1; }
   if (const int rc = run_timeout()) { std::fprintf(stderr, "time-out scenario: failure %d\n", rc); return 1; }
   if (const int rc = run_shm()) { std::fprintf(stderr, "shared-memory calls: failure %d\n", rc); return 1; }
-  std::printf("host protocol: %d ranks x %d steps x 13 codecs x 3 sizes and the low-rank exchange ok, time-out reported\n", world, steps);
+  std::printf("host protocol: %d ranks x %d steps x 13 codecs x 3 sizes, the two-phase mode and the low-rank exchange ok, time-out reported\n", world, steps);
   return 0;
 }

@@ -710,3 +710,73 @@ def test_fused_communicator_with_attached_host_engine_serves_cpu_tensors():
         return same, sorted(state["memory"]["residuals"])
 
     assert ThreadWorld(1).run(body) == [(True, ["w"])]
+
+
+# ---- two-phase ("alltoall") mode: compressed reduce-scatter, re-encode, compressed all-gather ----
+def _two_phase(world, comp_factory, grads, **kw):
+    tw = ThreadWorld(world)
+
+    def body(view):
+        grc = HostExchange(comp_factory(), M_.NoneMemory(), world, world=view, mode="alltoall", **kw)
+        outs = [grc.step(per_rank[view.rank].clone(), "w") for per_rank in grads]
+        assert all(p.two_phase for p in grc._plans.values())
+        return outs
+
+    return tw.run(body)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [1, 127, 129, 1000, 5000])
+def test_two_phase_dense_is_the_mean_and_fp16_rounds_twice(world, n):
+    grads = _grads(world, n, 3, scale=1.0)
+    outs = _two_phase(world, C_.NoneCompressor, grads)
+    for s in range(3):
+        want = sum(grads[s])                          # ranks are added in order 0..W-1, then scaled
+        for r in range(world):
+            assert torch.equal(outs[r][s], want * (1.0 / world))
+    outs = _two_phase(world, C_.FP16Compressor, grads)
+    want = sum(g.half().float() for g in grads[0]).half().float() * (1.0 / world)
+    for r in range(world):
+        assert torch.equal(outs[r][0], want)
+
+
+def test_two_phase_natural_deterministic_matches_the_restatement():
+    from grace_b200.compressor.natural import natural_decode, natural_encode
+
+    world, n = 3, 4000
+    grads = _grads(world, n, 2)
+
+    def det(x):   # deterministic natural compression: the larger power of two when the mantissa is above 1/2
+        prob = (x.contiguous().view(torch.int32) & 0x7FFFFF).float() * 2.0 ** -23
+        u = torch.where(prob > 0.5, torch.zeros_like(x), torch.ones_like(x))
+        return natural_decode(natural_encode(x, u)).view(-1)
+
+    outs = _two_phase(world, lambda: C_.NaturalCompressor(deterministic=True), grads)
+    for s in range(2):
+        want = det(sum(det(g) for g in grads[s])) / world
+        for r in range(world):
+            torch.testing.assert_close(outs[r][s], want, rtol=0, atol=0)
+
+
+def test_two_phase_qsgd_close_to_the_mean_and_identical_on_all_ranks():
+    world, n, q = 4, 128 * 40 + 17, 127
+    grads = _grads(world, n, 2)
+    outs = _two_phase(world, lambda: C_.QSGDCompressor(q, 128), grads)
+    for s in range(2):
+        mean = sum(grads[s]) / world
+        for r in range(1, world):
+            assert torch.equal(outs[r][s], outs[0][s])
+        err = (outs[0][s] - mean).norm() / mean.norm()
+        assert float(err) < 0.25, float(err)          # two lossy steps of 127 levels per 128-element bucket
+
+
+def test_alltoall_communicator_name_selects_the_two_phase_mode():
+    from grace_b200 import grace_from_params
+
+    def body(view):
+        grc = grace_from_params({"compressor": "qsgd", "memory": "none", "communicator": "alltoall", "quantum_num": 64,
+                                 "world_size": 1, "host_protocol": True, "host_world": view})
+        out = grc.step(torch.randn(1000), "w")
+        return grc.mode, bool(torch.isfinite(out).all())
+
+    assert ThreadWorld(1).run(body) == [("alltoall", True)]
