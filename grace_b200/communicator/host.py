@@ -17,7 +17,8 @@ publishes, agreement and recovery - runs among really concurrent ranks
 ``ThreadWorld``) on a machine without a GPU.
 
 Pairs covered: TopK / Threshold / RandomK with none or residual memory, TopK / DGC with
-the momentum-corrected DGC memory (exact k-th magnitude, no clipping), QSGD
+the momentum-corrected DGC memory (exact k-th magnitude, optional gradient
+clipping by the ranks' sums of squares), QSGD
 (any bucket size, up to 32767 levels), TernGrad, natural compression (the
 CUDA extension's code table; stochastic or deterministic), 8-bit, 1-bit and
 fp16 with none or residual memory, signSGD / signum, EF-signSGD with its
@@ -204,7 +205,8 @@ class _HostPlan:
             self.slot_bytes = C.host_two_phase_slot_bytes(codec, numel, owner.world_size)
         else:
             self.slot_bytes = C.host_slot_bytes(codec, numel, self.bucket if codec == QSGDX else self.k)
-        self._carve(owner, flag_pads=3 if self.two_phase else 2)
+        self.clip = codec == TOPK and owner._needs_u and bool(getattr(owner.memory, "gradient_clipping", False))
+        self._carve(owner, flag_pads=3 if (self.two_phase or self.clip) else 2)   # the third pad serves either use
         # the key of the random stream: as the GPU path derives it for a single tensor (name and padded length)
         self.seed = _name_seed(owner.seed, name + str((numel + 127) // 128 * 128))
         if codec == RANDOMK:   # the positions are keyed by the tensor's name alone, as on the GPU
@@ -243,7 +245,7 @@ class _HostPlan:
         self.seed = 0
         self.seq = self.steps = 0
         self.bucket = 0
-        self.two_phase = False
+        self.two_phase = self.clip = False
         self.acc = torch.zeros(self.numel, dtype=torch.float32) if isinstance(owner.memory, M_.PowerSGDMemory) else None
         self.mom = self.u = None
         self.q = orthogonal_init(self.cols, self.rank, owner.seed ^ zlib.crc32(self.name.encode("utf8")),
@@ -303,8 +305,8 @@ class HostExchange(Communicator):
                 self._codec = LOWRANK
                 self._needs_acc = False   # the low-rank plans own their residual; 1-D tensors travel uncompressed
         elif isinstance(mem, M_.DgcMemory):
-            if isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and not getattr(mem, "gradient_clipping", False):
-                self._codec = TOPK
+            if isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)):
+                self._codec = TOPK   # with gradient_clipping: sums of squares are exchanged before the encode
         elif isinstance(comp, (C_.TopKCompressor, C_.DgcCompressor)) and plain:
             self._codec = TOPK
         elif isinstance(comp, C_.ThresholdCompressor) and plain:
@@ -407,7 +409,7 @@ class HostExchange(Communicator):
             float(getattr(comp, "momentum", 0.0)), int(plan.steps == 0), int(getattr(comp, "quantum_num", 0)),
             plan.seed, plan.steps, plan.u.data_ptr() if plan.u is not None else 0,
             float(getattr(self.memory, "momentum", 0.0)), int(bool(getattr(comp, "deterministic", False))),
-            plan.bucket, plan.ready2_off if plan.two_phase else 0)
+            plan.bucket, plan.ready2_off if plan.two_phase else 0, plan.ready2_off if plan.clip else 0)
         if rc != 0:
             st = plan.status()
             raise GraceCommError(int(rc), int(st[1]), int(st[2]), world.rank)

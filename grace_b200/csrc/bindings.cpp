@@ -325,7 +325,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
            int phases, unsigned long long seq, uintptr_t g, uintptr_t acc, uintptr_t mom, uintptr_t out, long long n,
            long long k, float beta, float gamma, float scale, float threshold, int strict, float lr, float mom_beta,
            int first_step, int quantum, unsigned long long seed, unsigned step, uintptr_t u, float momentum,
-           int deterministic, int bucket, unsigned long long ready2_off) {
+           int deterministic, int bucket, unsigned long long ready2_off, unsigned long long clip_ready_off) {
           if (world < 1 || world > host::kMaxWorld || (int)heaps.size() != world || rank < 0 || rank >= world)
             throw std::invalid_argument("bad rank/world/heap table");
           host::Channel ch{};
@@ -338,7 +338,7 @@ PYBIND11_MODULE(GRACE_MODULE_NAME, m) {
           a.g = ptr<const float>(g); a.acc = ptr<float>(acc); a.mom = ptr<float>(mom); a.out = ptr<float>(out);
           a.n = n; a.k = k; a.beta = beta; a.gamma = gamma; a.scale = scale; a.threshold = threshold; a.strict = strict;
           a.lr = lr; a.mom_beta = mom_beta; a.first_step = first_step; a.quantum = quantum; a.seed = seed; a.step = step;
-          a.u = ptr<float>(u); a.momentum = momentum; a.deterministic = deterministic; a.bucket = bucket; a.ready2_off = ready2_off;
+          a.u = ptr<float>(u); a.momentum = momentum; a.deterministic = deterministic; a.bucket = bucket; a.ready2_off = ready2_off; a.clip_ready_off = clip_ready_off;
           unsigned rc;
           {
             py::gil_scoped_release release;   // ranks of a test may be threads of one process

@@ -162,14 +162,15 @@ inline int u8_bin(float y, const float* edges) {   // largest i in [0, 126] with
 inline long long words32(long long n) { return (n + 31) / 32; }
 
 // ---- compress: x = beta * acc + gamma * g, encode x into the slot, acc = x - decode(code) ----
-unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail) {
+unsigned compress(const Args& a, const SlotView& slot, uint64_t slot_bytes_avail, float clip_bound) {
   const long long n = a.n;
   if (slot_bytes(a.codec, n, a.codec == kQSGDX ? a.bucket : a.k) > slot_bytes_avail) return kSlotOverflow;
   std::vector<float> xbuf;
   const float* x = a.g;
   if (a.u && a.acc) {   // DGC momentum correction (memory/dgc.py:21-30): u = m u + g, v += u, v is what is encoded
     for (long long i = 0; i < n; ++i) {
-      a.u[i] = a.momentum * a.u[i] + a.g[i];
+      const float g = std::max(std::min(a.g[i], clip_bound), -clip_bound);   // the bound is +inf without clipping
+      a.u[i] = a.momentum * a.u[i] + g;
       a.acc[i] += a.u[i];
     }
     x = a.acc;
@@ -703,7 +704,23 @@ unsigned exchange(const Channel& ch, const Args& a) {
         if (p != ch.rank && !wait_flag_ge(ack + p, a.seq - 2, ch.timeout_ns, st, kTimeoutPeerAck, (unsigned)p))
           return st.code();
     }
-    const unsigned rc = compress(a, my_slot, ch.slot_bytes);
+    float clip_bound = INFINITY;
+    if (a.clip_ready_off) {
+      // every rank's sum of squares first: the bound must be known before the first element is encoded
+      double sq = 0.0;
+      for (long long i = 0; i < a.n; ++i) sq += (double)a.g[i] * (double)a.g[i];
+      *reinterpret_cast<double*>(my_slot.base + 16) = sq;
+      for (int p = 0; p < ch.world; ++p)
+        store_release(reinterpret_cast<uint64_t*>(ch.heap[p] + a.clip_ready_off) + ch.rank, a.seq);
+      const uint64_t* clip_ready = reinterpret_cast<const uint64_t*>(mine + a.clip_ready_off);
+      double total = 0.0;
+      for (int p = 0; p < ch.world; ++p) {   // rank order: the same bound, bit for bit, on every rank
+        if (!wait_flag_ge(clip_ready + p, a.seq, ch.timeout_ns, st, kTimeoutPeerReady, (unsigned)p)) return st.code();
+        total += *reinterpret_cast<const double*>(ch.heap[p] + ch.slot_off[parity] + 16);
+      }
+      clip_bound = (float)std::sqrt(total / (double)ch.world);
+    }
+    const unsigned rc = compress(a, my_slot, ch.slot_bytes, clip_bound);
     if (rc != kOk) {
       st.fail(rc, 0, (unsigned)a.seq);
       return st.code();

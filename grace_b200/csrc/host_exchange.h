@@ -18,7 +18,7 @@ namespace grace {
 namespace host {
 
 constexpr int kMaxWorld = 16;
-constexpr size_t kSlotHeaderBytes = 64;   // [0] u64 entry count, [8] f32 scalar, [12] f32 scalar
+constexpr size_t kSlotHeaderBytes = 64;   // [0] u64 entry count, [8] f32 scalar, [12] f32 scalar, [16] f64 sum of squares (clipping)
 
 enum Codec : int {
   kTopK = 0,        // k largest magnitudes (ties: lowest index), values + int32 indices
@@ -79,6 +79,10 @@ struct Args {
   // ranks' payloads, encodes the sum again (Philox stream 1) into the second region of its slot and publishes it
   // through the flag pad at ready2_off; every rank then decodes the W chunks.  0 = one-phase (all-gather) mode.
   uint64_t ready2_off;
+  // DGC gradient clipping (memory/dgc.py:16-19 of the Horovod flavour): every rank publishes the sum of squares of
+  // its gradient (in its slot header, through the flag pad at clip_ready_off) BEFORE anything is encoded; the
+  // gradient is then clamped element-wise to +-sqrt(mean over ranks of the sums).  0 = no clipping.
+  uint64_t clip_ready_off;
   uint64_t seed;
   unsigned step;
 };
@@ -97,7 +101,11 @@ struct LowRankArgs {
   float* q;              // [cols x rank]: start of this step in, mean Q out
   float* p_work;         // [rows x rank] scratch that survives between the phases (the orthogonalised P)
   int rows, cols, rank;
-  uint64_t ready2_off;   // u64[kMaxWorld] in every heap
+  uint64_t ready2_off;
+  // DGC gradient clipping (memory/dgc.py:16-19 of the Horovod flavour): every rank publishes the sum of squares of
+  // its gradient (in its slot header, through the flag pad at clip_ready_off) BEFORE anything is encoded; the
+  // gradient is then clamped element-wise to +-sqrt(mean over ranks of the sums).  0 = no clipping.
+  uint64_t clip_ready_off;   // u64[kMaxWorld] in every heap
 };
 size_t lowrank_slot_bytes(int rows, int cols, int rank);
 unsigned lowrank_exchange(const Channel& ch, const LowRankArgs& args);

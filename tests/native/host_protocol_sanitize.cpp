@@ -86,10 +86,12 @@ int run_codec(int codec, int world, long long n, int steps, bool two_phase = fal
         Args a{};
         a.codec = codec; a.phases = kAll; a.seq = (uint64_t)s + 1;
         a.g = g.data(); a.acc = ef ? acc.data() : nullptr; a.mom = codec == kSign ? mom.data() : nullptr;
-        a.u = nullptr; a.out = outs[r].data(); a.n = n; a.k = k;
+        a.u = codec == kTopK ? u.data() : nullptr; a.out = outs[r].data(); a.n = n; a.k = k;
         a.beta = s == 0 ? 0.f : 1.f; a.gamma = 1.f; a.scale = 1.f / (float)world; a.threshold = 5e-4f; a.strict = 0;
         a.lr = 0.1f; a.mom_beta = 0.9f; a.first_step = s == 0; a.quantum = 64; a.seed = 77; a.step = (unsigned)s;
         a.momentum = 0.f; a.deterministic = 0; a.bucket = 100; a.ready2_off = two_phase ? 2 * kMaxWorld * 8 : 0;
+        a.clip_ready_off = codec == kTopK ? 2 * kMaxWorld * 8 : 0;   // DGC memory with gradient clipping
+        a.momentum = 0.9f;
         // split phases on odd steps: publish first, pull later (what send_step / receive_step do)
         unsigned code;
         if (s & 1) {

@@ -780,3 +780,31 @@ def test_alltoall_communicator_name_selects_the_two_phase_mode():
         return grc.mode, bool(torch.isfinite(out).all())
 
     assert ThreadWorld(1).run(body) == [("alltoall", True)]
+
+
+def test_dgc_gradient_clipping_bound_from_all_ranks():
+    """DgcMemory(gradient_clipping=True): clamp to +-sqrt(mean over ranks of sum g^2) before the momentum correction."""
+    world, n, ratio, m = 3, 3000, 0.02, 0.9
+    k = int(n * ratio)
+    grads = _grads(world, n, 3, scale=1.0)
+    for s in range(3):                                  # one rank has an outlier above the RMS of the ranks' norms
+        grads[s][0][7 + s] = 1000.0
+    outs, grcs = _run_ranks(world, lambda: (C_.DgcCompressor(ratio), M_.DgcMemory(m, True, world)), grads)
+    u = [torch.zeros(n) for _ in range(world)]
+    v = [torch.zeros(n) for _ in range(world)]
+    for s in range(3):
+        bound = torch.sqrt(sum(g.double().pow(2).sum() for g in grads[s]) / world).float()
+        assert any(bool((g.abs() > bound).any()) for g in grads[s])
+        want = torch.zeros(n)
+        for r in range(world):
+            g = torch.maximum(torch.minimum(grads[s][r], bound), -bound)
+            u[r] = m * u[r] + g
+            v[r] = v[r] + u[r]
+            sel = _topk_dense(v[r], k)
+            keep = sel == 0
+            want += sel
+            u[r] = u[r] * keep
+            v[r] = v[r] * keep
+        for r in range(world):
+            torch.testing.assert_close(outs[r][s], want / world, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(grcs[2].state_dict()["memory"]["gradients"]["w"], v[2], rtol=1e-5, atol=1e-7)
