@@ -146,15 +146,18 @@ class HostHeap:
             return "/grace_%s_%d_%d" % (world.token, serial, r)
 
         self.bases: List[int] = [0] * self.world
-        self.bases[self.rank] = self._C.host_heap_create(name(self.rank), self.nbytes)
-        world.barrier()
-        for r in range(self.world):
-            if r != self.rank:
-                self.bases[r] = self._C.host_heap_open(name(r), self.nbytes)
-        world.barrier()
-        self._C.host_heap_unlink(name(self.rank))
         self._cursor = 0
         self._closed = False
+        self.bases[self.rank] = self._C.host_heap_create(name(self.rank), self.nbytes)
+        try:
+            world.barrier()
+            for r in range(self.world):
+                if r != self.rank:
+                    self.bases[r] = self._C.host_heap_open(name(r), self.nbytes)
+            world.barrier()
+        finally:
+            # also when a peer never showed up: the name must not outlive this call (the mappings keep the memory)
+            self._C.host_heap_unlink(name(self.rank))
 
     def alloc(self, nbytes: int) -> int:
         off = (self._cursor + _ALIGN - 1) // _ALIGN * _ALIGN
